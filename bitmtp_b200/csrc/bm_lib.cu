@@ -1,0 +1,365 @@
+// libbitmtp_b200.so: single translation unit holding every kernel and the C ABI
+// declared in include/bitmtp_b200.h.  Host code here only validates arguments,
+// picks a launch geometry and enqueues; it allocates nothing.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/bitmtp_b200.h"
+#include "bm_common.cuh"
+
+#include "t2_gemv.cuh"
+#include "fused_ops.cuh"
+#include "verify_attn.cuh"
+
+namespace {
+
+constexpr int kMaxSmemPerCta = 227 * 1024;
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+};
+
+DeviceInfo current_device() {
+    static thread_local DeviceInfo cached;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cached.device != dev) {
+        cached.device = dev;
+        cudaDeviceGetAttribute(&cached.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (cached.sm_count <= 0) cached.sm_count = 148;
+    }
+    return cached;
+}
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? BM_OK : BM_ECUDA_BASE + (int)e; }
+
+// Generic launch with the optional programmatic-serialisation attribute.
+template <typename Kernel, typename... Args>
+int launch_ex(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int pdl,
+              Args... args) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_status(e);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
+template <typename Kernel>
+int launch(Kernel kernel, int grid, int block, int smem, cudaStream_t stream, int pdl,
+           const bm::GemvParams &p) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, p));
+}
+
+// Rows per tile: the largest of 32/16/8 that still leaves two tiles per SM, so
+// that the tail of the last wave stays short.
+int pick_rb(int N, int sms) {
+    for (int rb = 4; rb > 1; rb >>= 1)
+        if (N / (8 * rb) >= 2 * sms) return rb;
+    return 1;
+}
+
+struct Plan {
+    int rb, stages, grid, smem;
+};
+
+bool make_plan(int W, int N, int K, bool mma, int sms, Plan *out) {
+    int rb = pick_rb(N, sms);
+    for (; rb >= 1; rb >>= 1) {
+        const int tiles = (N + 8 * rb - 1) / (8 * rb);
+        // Two CTAs per SM when both fit; otherwise one.
+        for (int per_sm = 2; per_sm >= 1; --per_sm) {
+            const int grid = tiles < sms * per_sm ? tiles : sms * per_sm;
+            const int tiles_per_cta = (tiles + grid - 1) / grid;
+            const int budget = per_sm == 2 ? (kMaxSmemPerCta - 2048) / 2 : kMaxSmemPerCta;
+            int stages = tiles_per_cta + 1 < bm::kMaxStages ? tiles_per_cta + 1 : bm::kMaxStages;
+            if (stages < 2) stages = 2;
+            for (; stages >= 2; --stages) {
+                const bm::GemvSmem L = bm::gemv_smem_layout(W, K, rb, stages, mma);
+                if (L.total <= budget) {
+                    out->rb = rb;
+                    out->stages = stages;
+                    out->grid = grid;
+                    out->smem = L.total;
+                    return true;
+                }
+            }
+        }
+    }
+    return false;
+}
+
+int gemv_launch_dp4a(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
+    Plan pl;
+    if (!make_plan(p0.W, p0.N, p0.K, false, sms, &pl)) return BM_EINVAL;
+    bm::GemvParams p = p0;
+    p.stages = pl.stages;
+    p.pdl = pdl;
+    const int wb = p.W == 1 ? 1 : (p.W == 2 ? 2 : 4);
+#define BM_DP4A_CASE(WB_, RB_)                                                               \
+    if (wb == WB_ && pl.rb == RB_)                                                           \
+        return launch(bm::t2_gemv_dp4a_kernel<WB_, RB_>, pl.grid, bm::kGemvThreads, pl.smem, \
+                      stream, pdl, p);
+    BM_DP4A_CASE(1, 1) BM_DP4A_CASE(1, 2) BM_DP4A_CASE(1, 4)
+    BM_DP4A_CASE(2, 1) BM_DP4A_CASE(2, 2) BM_DP4A_CASE(2, 4)
+    BM_DP4A_CASE(4, 1) BM_DP4A_CASE(4, 2) BM_DP4A_CASE(4, 4)
+#undef BM_DP4A_CASE
+    return BM_EINVAL;
+}
+
+int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
+    // Tokens beyond 16 go through a second launch over the remaining rows.
+    for (int m0 = 0; m0 < p0.W; m0 += 16) {
+        bm::GemvParams p = p0;
+        p.W = p0.W - m0 < 16 ? p0.W - m0 : 16;
+        p.A = p0.A + (size_t)m0 * p0.K;
+        p.s = p0.s + m0;
+        const size_t esz = p0.out_kind == BM_OUT_BF16 ? 2 : 4;
+        p.C = static_cast<char *>(p0.C) + (size_t)m0 * p0.ldc * esz;
+        if (p0.G) p.G = p0.G + (size_t)m0 * p0.N * (p0.K / BM_GROUP);
+        Plan pl;
+        if (!make_plan(p.W, p.N, p.K, true, sms, &pl)) return BM_EINVAL;
+        p.stages = pl.stages;
+        p.pdl = (m0 == 0) ? pdl : 0;
+        int rc = BM_EINVAL;
+        const int use_pdl = (m0 == 0) ? pdl : 0;
+        if (pl.rb == 1)
+            rc = launch(bm::t2_gemv_mma_kernel<1>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
+        else if (pl.rb == 2)
+            rc = launch(bm::t2_gemv_mma_kernel<2>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
+        else if (pl.rb == 4)
+            rc = launch(bm::t2_gemv_mma_kernel<4>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
+        if (rc != BM_OK) return rc;
+    }
+    return BM_OK;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+const char *bm_version(void) { return "bitmtp_b200 0.1 (sm_100a)"; }
+
+int bm_sm_count(void) { return current_device().sm_count; }
+
+int bm_device_error(void) {
+    int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, bm::g_dev_err, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(bm::g_dev_err, &zero, sizeof(int));
+    }
+    return v;
+}
+
+int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind) {
+    const int64_t esz = out_kind == BM_OUT_BF16 ? 2 : 4;
+    return (int64_t)N * K / 4 + (int64_t)N * (K / 128) * 2 + (int64_t)W * K + 4 * (int64_t)W +
+           esz * W * N;
+}
+
+int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void *ws, int W, int N,
+               int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
+    if (!A || !B || !C || !s || !ws) return BM_EINVAL;
+    if (W < 1 || W > BM_MAX_W || N < 8 || (N % 8) != 0 || K < 128 || (K % 128) != 0) return BM_EINVAL;
+    if (ldc < N || out_kind < 0 || out_kind > 2) return BM_EINVAL;
+    if (!aligned16(A) || !aligned16(B) || !aligned16(ws)) return BM_EINVAL;
+    bm::GemvParams p;
+    p.A = static_cast<const int8_t *>(A);
+    p.B = static_cast<const uint8_t *>(B);
+    p.ws = static_cast<const uint16_t *>(ws);
+    p.s = static_cast<const float *>(s);
+    p.C = C;
+    p.G = static_cast<int32_t *>(G_out);
+    p.W = W;
+    p.N = N;
+    p.K = K;
+    p.ldc = ldc;
+    p.out_kind = out_kind;
+    p.stages = 2;
+    p.pdl = 0;
+    const int sms = current_device().sm_count;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (path == BM_PATH_AUTO) path = W <= 2 ? BM_PATH_DP4A : BM_PATH_MMA;
+    if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
+    if (path == BM_PATH_MMA) return gemv_launch_mma(p, sms, pdl, st);
+    return BM_EINVAL;
+}
+
+void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, int M, int N,
+                             int K, void *stream) {
+    const int rc = bm_t2_gemv(A, B, C, s, ws, M, N, K, N, BM_OUT_BF16, BM_PATH_AUTO, nullptr, 0, stream);
+    if (rc != BM_OK) fprintf(stderr, "[t2g128] unsupported shape M=%d N=%d K=%d (status %d)\n", M, N, K, rc);
+}
+
+// ---------------------------------------------------------------------------- fused operators
+int bm_quant_rows(const void *x, int M, int K, void *q, void *s, int pdl, void *stream) {
+    if (!x || !q || !s || M < 1 || K < 8 || (K % 8) != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7u))
+        return BM_EINVAL;
+    return launch_ex(bm::quant_rows_kernel, dim3(M), dim3(bm::kRowThreads), 0, static_cast<cudaStream_t>(stream), pdl,
+                     static_cast<const uint16_t *>(x), K, static_cast<int8_t *>(q), static_cast<float *>(s), pdl);
+}
+
+int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps, int M,
+                     int dim, int row0, void *h_out, void *q, void *s, void *n_out, int pdl, void *stream) {
+    if (!x || !w || M < 1 || dim < 256 || (dim % 256) != 0 || dim > 8192) return BM_EINVAL;
+    if ((q == nullptr) != (s == nullptr)) return BM_EINVAL;
+    if (!aligned16(x) || !aligned16(w) || (res && !aligned16(res))) return BM_EINVAL;
+    bm::NormParams p;
+    p.x = static_cast<const uint16_t *>(x);
+    p.gather = static_cast<const int64_t *>(gather);
+    p.res = static_cast<const uint16_t *>(res);
+    p.w = static_cast<const uint16_t *>(w);
+    p.h_out = static_cast<uint16_t *>(h_out);
+    p.q = static_cast<int8_t *>(q);
+    p.s = static_cast<float *>(s);
+    p.n_out = static_cast<uint16_t *>(n_out);
+    p.eps = eps;
+    p.dim = dim;
+    p.row0 = row0;
+    p.pdl = pdl;
+    return launch_ex(bm::rmsnorm_kernel, dim3(M), dim3(dim / 8), 0, static_cast<cudaStream_t>(stream), pdl, p);
+}
+
+int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *s, void *inner_out, int pdl, void *stream) {
+    if (!gu || !q || !s || M < 1 || F < 8 || (F % 8) != 0 || !aligned16(gu)) return BM_EINVAL;
+    const size_t smem = (size_t)F * 2;
+    if (smem > 200 * 1024) return BM_EINVAL;
+    return launch_ex(bm::silu_mul_quant_kernel, dim3(M), dim3(bm::kRowThreads), smem, static_cast<cudaStream_t>(stream),
+                     pdl, static_cast<const uint16_t *>(gu), F, static_cast<int8_t *>(q), static_cast<float *>(s),
+                     static_cast<uint16_t *>(inner_out), pdl);
+}
+
+int bm_qknorm_rope_kvappend(const void *xqkv, const void *q_w, const void *k_w, float eps, const void *cos_t,
+                            const void *sin_t, const void *positions, int M, int H, int Hkv, void *k_base,
+                            void *v_base, int kv_rows, int sigma, void *q_out, int pdl, void *stream) {
+    if (!xqkv || !q_w || !k_w || !cos_t || !sin_t || !positions || !k_base || !v_base || !q_out) return BM_EINVAL;
+    if (M < 1 || M > BM_MAX_W || H < 1 || Hkv < 1 || (H % Hkv) != 0 || sigma < 0 || sigma + M > kv_rows) return BM_EINVAL;
+    bm::RopeParams p;
+    p.xqkv = static_cast<const uint16_t *>(xqkv);
+    p.q_w = static_cast<const uint16_t *>(q_w);
+    p.k_w = static_cast<const uint16_t *>(k_w);
+    p.cos_t = static_cast<const uint16_t *>(cos_t);
+    p.sin_t = static_cast<const uint16_t *>(sin_t);
+    p.positions = static_cast<const int64_t *>(positions);
+    p.k_base = static_cast<uint16_t *>(k_base);
+    p.v_base = static_cast<uint16_t *>(v_base);
+    p.q_out = static_cast<uint16_t *>(q_out);
+    p.eps = eps;
+    p.M = M; p.H = H; p.Hkv = Hkv; p.kv_rows = kv_rows; p.sigma = sigma; p.pdl = pdl;
+    const int heads = H + 2 * Hkv;
+    return launch_ex(bm::qknorm_rope_kvappend_kernel, dim3((heads + 3) / 4, M), dim3(128), 0,
+                     static_cast<cudaStream_t>(stream), pdl, p);
+}
+
+int bm_set_step_state(void *state, int cache_len, int n_pend, int role, int P, void *stream) {
+    if (!state || cache_len < 0 || role < 0 || role > 2) return BM_EINVAL;
+    bm::set_step_state_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<bm::StepState *>(state), cache_len, n_pend, role, P);
+    return cuda_status(cudaGetLastError());
+}
+
+int bm_kv_copy_rows(void *kv, int planes, int kv_rows, int src_row, int dst_row, int n, void *stream) {
+    if (!kv || planes < 1 || n < 0 || src_row < 0 || dst_row < 0 || src_row + n > kv_rows || dst_row + n > kv_rows)
+        return BM_EINVAL;
+    if (n == 0) return BM_OK;
+    if (!(src_row >= dst_row + n || dst_row >= src_row + n)) return BM_EINVAL;   // ranges must not overlap
+    bm::kv_copy_rows_kernel<<<planes, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t *>(kv), planes, kv_rows, src_row, dst_row, n);
+    return cuda_status(cudaGetLastError());
+}
+
+int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma) {
+    return (int64_t)bm::attn_scratch_bytes(M, H, sigma);
+}
+
+int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv, int kv_rows,
+                        int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *s_out,
+                        int pdl, void *stream) {
+    if (!q || !k_base || !v_base || !state || !scratch || !att_out || !q_out || !s_out) return BM_EINVAL;
+    if (M < 1 || M > BM_MAX_W || H < 2 || (H % 2) != 0 || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
+    if (sigma < 0 || sigma + M > kv_rows || !aligned16(q) || !aligned16(k_base) || !aligned16(v_base) ||
+        !aligned16(scratch) || !aligned16(att_out))
+        return BM_EINVAL;
+    const int NC = (sigma + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK + 1;
+    if (NC > 160) return BM_EINVAL;
+    const int G = H / Hkv, QV = G * M;
+    bm::AttnParams p;
+    p.q = static_cast<const uint16_t *>(q);
+    p.k_base = static_cast<const uint16_t *>(k_base);
+    p.v_base = static_cast<const uint16_t *>(v_base);
+    p.state = static_cast<const bm::StepState *>(state);
+    p.M = M; p.H = H; p.Hkv = Hkv; p.kv_rows = kv_rows; p.sigma = sigma; p.NC = NC;
+    char *sc = static_cast<char *>(scratch);
+    p.ctr = reinterpret_cast<int *>(sc);
+    p.amax = reinterpret_cast<unsigned int *>(sc + 128);
+    p.pm = reinterpret_cast<float *>(sc + 256);
+    p.pl = p.pm + (size_t)M * H * NC;
+    p.po = p.pl + (size_t)M * H * NC;
+    p.att = static_cast<uint16_t *>(att_out);
+    p.q_out = static_cast<int8_t *>(q_out);
+    p.s_out = static_cast<float *>(s_out);
+    p.pdl = pdl;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
+    int rc = launch_ex(bm::attn_chunk_kernel, dim3(NC, Hkv), dim3(bm::kAttnThreads), smem, st, pdl, p);
+    if (rc != BM_OK) return rc;
+    return launch_ex(bm::attn_merge_kernel, dim3(H / 2, M), dim3(bm::kAttnThreads), 0, st, pdl, p);
+}
+
+// ---------------------------------------------------------------------------- logits
+int bm_argmax_rows(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out, void *stream) {
+    if (!logits || !idx || rows < 1 || vocab < 1 || ld < vocab) return BM_EINVAL;
+    bm::argmax_rows_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float *>(logits), vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_out));
+    return cuda_status(cudaGetLastError());
+}
+
+int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf, void *conf,
+                   void *n_out, void *stream) {
+    if (!logits || !idx || !max_buf || !conf || !n_out || D < 1 || D > BM_MAX_W || vocab < 1 || ld < vocab ||
+        vocab > bm::kConfMaxChunks * 256)
+        return BM_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bm::argmax_rows_kernel<<<D, 1024, 0, st>>>(static_cast<const float *>(logits), vocab, ld,
+                                               static_cast<int64_t *>(idx), static_cast<float *>(max_buf));
+    bm::row_confidence_kernel<<<D, 256, 0, st>>>(static_cast<const float *>(logits), vocab, ld,
+                                                 static_cast<const float *>(max_buf), static_cast<float *>(conf));
+    bm::chain_length_kernel<<<1, 32, 0, st>>>(static_cast<const float *>(conf), D, tau, static_cast<int *>(n_out));
+    return cuda_status(cudaGetLastError());
+}
+
+int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, void *stream) {
+    if (!draft || !verify || !n_out || D < 1) return BM_EINVAL;
+    bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
+    return cuda_status(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,406 @@
+// Small fused operators of the decode step: activation absmax/INT8 quantisation,
+// (residual add +) RMSNorm (+ quantisation), SiLU*up + quantisation, q/k head
+// norm + RoPE + KV append, embedding gather, argmax / confidence reductions.
+//
+// Each kernel states the reference expression it replaces.  All of them round
+// where the reference's eager tensor code rounds (bf16 in memory, fp32
+// arithmetic) and reduce in the order fixed by oracle/bm_oracle.c, so results
+// equal the oracle's bit for bit.
+#pragma once
+
+#include "bm_common.cuh"
+
+namespace bm {
+
+// Device-resident description of the replay in flight.  Written by
+// bm_set_step_state (a one-thread kernel, so it can sit in front of a captured
+// graph) and read by the attention kernels, so that a captured graph can be
+// replayed for any cache length and pending count.
+struct StepState {
+    int cache_len;   // history rows [0, cache_len) are valid
+    int n_pend;      // pending rows at the head of a draft replay
+    int role;        // BM_ROLE_*
+    int P;           // M - D
+};
+
+// ---- block-wide helpers -------------------------------------------------------
+// Sum of per-warp values in ascending warp order, same result in every thread.
+__device__ __forceinline__ float block_sum_ordered(float warp_val, float *sh, int lane, int warp,
+                                                   int nwarps) {
+    if (lane == 0) sh[warp] = warp_val;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nwarps; ++w) t += sh[w];
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *sh, int lane, int warp, int nwarps) {
+    v = warp_max(v);
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = sh[0];
+    for (int w = 1; w < nwarps; ++w) t = fmaxf(t, sh[w]);
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = (uint32_t)bm_f32_to_bf16(f[2 * i]) | ((uint32_t)bm_f32_to_bf16(f[2 * i + 1]) << 16);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        lo |= ((uint32_t)(bm_quant_i8(f[i], s) & 0xff)) << (8 * i);
+        hi |= ((uint32_t)(bm_quant_i8(f[4 + i], s) & 0xff)) << (8 * i);
+    }
+    return make_uint2(lo, hi);
+}
+
+// =============================================================================
+// quant_rows: per-row absmax INT8 quantisation of bf16 activations.
+// Replaces T2LinearKernel.quant_input (src/bonsai_sft/gpu/model.py:632-636) and
+// the inline copy in _lm_head (model.py:1247-1249).  One CTA per row.
+// =============================================================================
+constexpr int kRowThreads = 512;
+
+__global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(const uint16_t *__restrict__ x,
+                                                                 int K, int8_t *__restrict__ q,
+                                                                 float *__restrict__ s_out,
+                                                                 int pdl) {
+    __shared__ float sh[kRowThreads / 32];
+    if (pdl) pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)m * K);
+    const int units = K / 8;
+    float amax = 0.0f;
+    for (int u = threadIdx.x; u < units; u += kRowThreads) {
+        float f[8];
+        unpack8(xr[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    }
+    amax = block_max(amax, sh, lane, warp, kRowThreads / 32);
+    const float s = bm_act_scale(amax);
+    uint2 *qr = reinterpret_cast<uint2 *>(q + (size_t)m * K);
+    for (int u = threadIdx.x; u < units; u += kRowThreads) {
+        float f[8];
+        unpack8(xr[u], f);
+        qr[u] = quant8(f, s);
+    }
+    if (threadIdx.x == 0) s_out[m] = s;
+}
+
+// =============================================================================
+// (gather | residual add) + RMSNorm + (INT8 quantisation | bf16 store).
+// Replaces _fused_norm_quant (model.py:307-319), _fused_add_norm_quant
+// (model.py:322-336), RMSNorm.forward on the logit rows (model.py:290-295,
+// 1401-1402) and the embedding gather in front of layer 0 (model.py:1386).
+//   x        bf16 rows; with `gather` row m is x[gather[m]] (embedding table)
+//   res      optional bf16 [M, dim]: h = bf16(x + res)
+//   h_out    optional bf16 [M, dim]: the (gathered / summed) row before the norm
+//   q, s     optional INT8 row + multiplier of the normed row
+//   n_out    optional bf16 normed row
+// One CTA per row, dim/8 threads (dim a multiple of 256): thread t owns
+// elements 8t..8t+7, which is exactly the lane-partial of the oracle's
+// sum-of-squares order; warps are its 256-element chunks.
+// =============================================================================
+struct NormParams {
+    const uint16_t *x;
+    const int64_t *gather;
+    const uint16_t *res;
+    const uint16_t *w;
+    uint16_t *h_out;
+    int8_t *q;
+    float *s;
+    uint16_t *n_out;
+    float eps;
+    int dim;
+    int row0;        // first row of x / res to read (logit rows start at logits_start)
+    int pdl;
+};
+
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
+    __shared__ float sh[32];
+    if (p.pdl) pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const size_t src_row = p.gather ? (size_t)p.gather[m] : (size_t)(p.row0 + m);
+    float h[8];
+    unpack8(reinterpret_cast<const uint4 *>(p.x + src_row * p.dim)[t], h);
+    if (p.res) {
+        float r[8];
+        unpack8(reinterpret_cast<const uint4 *>(p.res + (size_t)(p.row0 + m) * p.dim)[t], r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = bm_bf16_rn(h[i] + r[i]);
+    }
+    if (p.h_out) reinterpret_cast<uint4 *>(p.h_out + (size_t)m * p.dim)[t] = pack8(h);
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(h[i], h[i], acc);
+    const float total = block_sum_ordered(warp_sum_butterfly(acc), sh, lane, warp, nwarps);
+    const float r = bm_rsqrtf(total / (float)p.dim + p.eps);
+    float wv[8], n[8];
+    unpack8(reinterpret_cast<const uint4 *>(p.w)[t], wv);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        n[i] = bm_bf16_rn(wv[i] * bm_bf16_rn(h[i] * r));
+        amax = fmaxf(amax, fabsf(n[i]));
+    }
+    if (p.n_out) reinterpret_cast<uint4 *>(p.n_out + (size_t)m * p.dim)[t] = pack8(n);
+    if (p.q) {
+        amax = block_max(amax, sh, lane, warp, nwarps);
+        const float s = bm_act_scale(amax);
+        reinterpret_cast<uint2 *>(p.q + (size_t)m * p.dim)[t] = quant8(n, s);
+        if (t == 0) p.s[m] = s;
+    }
+}
+
+// =============================================================================
+// SiLU(gate) * up + INT8 quantisation of the down-projection input.
+// Replaces `inner = F.silu(g) * u; quant_input(inner)` (model.py:1059-1061).
+// gu bf16 [M, 2F] holds gate | up.  One CTA per row; the bf16 products wait in
+// shared memory between the absmax pass and the quantisation pass.
+// =============================================================================
+__global__ void __launch_bounds__(kRowThreads) silu_mul_quant_kernel(
+    const uint16_t *__restrict__ gu, int F, int8_t *__restrict__ q, float *__restrict__ s_out,
+    uint16_t *__restrict__ inner_out, int pdl) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ float sh[kRowThreads / 32];
+    if (pdl) pdl_wait();
+    pdl_launch_dependents();
+    uint4 *inner = reinterpret_cast<uint4 *>(dyn);
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4 *g = reinterpret_cast<const uint4 *>(gu + (size_t)m * 2 * F);
+    const uint4 *u = reinterpret_cast<const uint4 *>(gu + (size_t)m * 2 * F + F);
+    const int units = F / 8;
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < units; i += kRowThreads) {
+        float gf[8], uf[8], v[8];
+        unpack8(g[i], gf);
+        unpack8(u[i], uf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            v[e] = bm_bf16_rn(bm_silu_bf16(gf[e]) * uf[e]);
+            amax = fmaxf(amax, fabsf(v[e]));
+        }
+        const uint4 packed = pack8(v);
+        inner[i] = packed;
+        if (inner_out) reinterpret_cast<uint4 *>(inner_out + (size_t)m * F)[i] = packed;
+    }
+    amax = block_max(amax, sh, lane, warp, kRowThreads / 32);
+    const float s = bm_act_scale(amax);
+    uint2 *qr = reinterpret_cast<uint2 *>(q + (size_t)m * F);
+    for (int i = threadIdx.x; i < units; i += kRowThreads) {
+        float v[8];
+        unpack8(inner[i], v);
+        qr[i] = quant8(v, s);
+    }
+    if (threadIdx.x == 0) s_out[m] = s;
+}
+
+// =============================================================================
+// Split qkv, per-head RMSNorm of q and k, RoPE, append K and V rows.
+// Replaces _fused_qkv_qknorm_rope_kv_write (model.py:388-436).
+//   xqkv bf16 [M, (H + 2*Hkv)*128]; cos/sin bf16 [max_pos, 128]; positions int64
+//   k_base/v_base: one layer of the shared KV buffer, bf16 [Hkv, kv_rows, 128];
+//   rows [sigma, sigma+M) are written.  q_out bf16 [M, H, 128].
+// One warp per head vector: lane l owns elements 4l..4l+3 (the oracle's lane
+// partial for a 128-wide row); the RoPE partner i +- 64 lives in lane l ^ 16.
+// =============================================================================
+struct RopeParams {
+    const uint16_t *xqkv;
+    const uint16_t *q_w, *k_w;
+    const uint16_t *cos_t, *sin_t;
+    const int64_t *positions;
+    uint16_t *k_base, *v_base, *q_out;
+    float eps;
+    int M, H, Hkv, kv_rows, sigma, pdl;
+};
+
+__global__ void __launch_bounds__(128) qknorm_rope_kvappend_kernel(const RopeParams p) {
+    if (p.pdl) pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = p.H + 2 * p.Hkv;
+    const int m = blockIdx.y;
+    const int hd = blockIdx.x * 4 + warp;
+    if (hd >= heads) return;
+    const uint16_t *src = p.xqkv + ((size_t)m * heads + hd) * 128 + 4 * lane;
+    const uint2 raw = *reinterpret_cast<const uint2 *>(src);
+    if (hd >= p.H + p.Hkv) {                          // V head: plain copy
+        const int hk = hd - p.H - p.Hkv;
+        *reinterpret_cast<uint2 *>(p.v_base + ((size_t)hk * p.kv_rows + p.sigma + m) * 128 + 4 * lane) = raw;
+        return;
+    }
+    float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                  __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc = fmaf(x[i], x[i], acc);
+    const float total = warp_sum_butterfly(acc);      // one chunk: 0 + chunk sum
+    const float r = bm_rsqrtf((0.0f + total) / 128.0f + p.eps);
+    const uint16_t *wsrc = (hd < p.H ? p.q_w : p.k_w) + 4 * lane;
+    const uint2 wraw = *reinterpret_cast<const uint2 *>(wsrc);
+    const float w[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u),
+                        __uint_as_float(wraw.y << 16), __uint_as_float(wraw.y & 0xffff0000u)};
+    const size_t pos = (size_t)p.positions[m];
+    const uint2 craw = *reinterpret_cast<const uint2 *>(p.cos_t + pos * 128 + 4 * lane);
+    const uint2 sraw = *reinterpret_cast<const uint2 *>(p.sin_t + pos * 128 + 4 * lane);
+    const float c[4] = {__uint_as_float(craw.x << 16), __uint_as_float(craw.x & 0xffff0000u),
+                        __uint_as_float(craw.y << 16), __uint_as_float(craw.y & 0xffff0000u)};
+    const float sn[4] = {__uint_as_float(sraw.x << 16), __uint_as_float(sraw.x & 0xffff0000u),
+                         __uint_as_float(sraw.y << 16), __uint_as_float(sraw.y & 0xffff0000u)};
+    float n[4], o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n[i] = bm_bf16_rn(w[i] * bm_bf16_rn(x[i] * r));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
+        const float rot = lane < 16 ? -partner : partner;
+        o[i] = bm_bf16_rn(n[i] * c[i]) + bm_bf16_rn(rot * sn[i]);
+    }
+    const uint2 packed = make_uint2(
+        (uint32_t)bm_f32_to_bf16(o[0]) | ((uint32_t)bm_f32_to_bf16(o[1]) << 16),
+        (uint32_t)bm_f32_to_bf16(o[2]) | ((uint32_t)bm_f32_to_bf16(o[3]) << 16));
+    uint16_t *dst = hd < p.H
+                        ? p.q_out + ((size_t)m * p.H + hd) * 128
+                        : p.k_base + ((size_t)(hd - p.H) * p.kv_rows + p.sigma + m) * 128;
+    *reinterpret_cast<uint2 *>(dst + 4 * lane) = packed;
+}
+
+// =============================================================================
+// Step state and KV row promotion
+// =============================================================================
+__global__ void set_step_state_kernel(StepState *st, int cache_len, int n_pend, int role, int P) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        st->cache_len = cache_len;
+        st->n_pend = n_pend;
+        st->role = role;
+        st->P = P;
+    }
+}
+
+// Copies rows [src_row, src_row + n) to [dst_row, dst_row + n) in every
+// (k|v, layer, kv head) plane of the shared buffer [planes, kv_rows, 128] bf16.
+// Replaces GraphAtlas.commit_kv / commit_kv_from_verify
+// (src/bonsai_sft/gpu/fast_runtime.py:467-508); the two ranges never overlap
+// because the source rows sit at or beyond sigma and the destination below it.
+__global__ void kv_copy_rows_kernel(uint16_t *kv, int planes, int kv_rows, int src_row, int dst_row,
+                                    int n) {
+    const int plane = blockIdx.x;
+    if (plane >= planes) return;
+    uint4 *base = reinterpret_cast<uint4 *>(kv + (size_t)plane * kv_rows * 128);
+    for (int i = threadIdx.x; i < n * 16; i += blockDim.x)
+        base[(size_t)dst_row * 16 + i] = base[(size_t)src_row * 16 + i];
+}
+
+// =============================================================================
+// Logit reductions
+// =============================================================================
+// Row argmax with the lowest index winning ties.  logits fp32 [rows, ld].
+// Replaces `.argmax(dim=-1)` on logits_out (fast_generate.py:786,809,1079) and
+// the max of _fused_draft_chain (fast_generate.py:125).  One CTA per row.
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *__restrict__ logits,
+                                                           int vocab, int ld,
+                                                           int64_t *__restrict__ idx,
+                                                           float *__restrict__ max_out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *x = logits + (size_t)r * ld;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+        const float f = x[v];
+        if (f > best || (f == best && v < bi)) { best = f; bi = v; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        idx[r] = bi;
+        if (max_out) max_out[r] = best;
+    }
+}
+
+// Sum of exp(x - max) per row in the oracle's chunk order (256-element chunks:
+// 32 lanes x 8 consecutive terms, butterfly, chunks added in ascending order),
+// then conf = exp(max - (max + log(sum))).  One CTA of 8 warps per row: warp w
+// takes chunks w, w+8, ... and keeps their sums in shared memory; thread 0 adds
+// them in order.  Part of _fused_draft_chain (fast_generate.py:126-127).
+constexpr int kConfMaxChunks = 1024;   // vocab <= 262144
+
+__global__ void __launch_bounds__(256) row_confidence_kernel(const float *__restrict__ logits,
+                                                             int vocab, int ld,
+                                                             const float *__restrict__ row_max,
+                                                             float *__restrict__ conf) {
+    __shared__ float chunk_sum[kConfMaxChunks];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *x = logits + (size_t)r * ld;
+    const float mx = row_max[r];
+    const int nchunks = (vocab + 255) / 256;
+    for (int c = warp; c < nchunks; c += 8) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int v = c * 256 + lane * 8 + e;
+            if (v < vocab) acc += bm_expf(x[v] - mx);
+        }
+        acc = warp_sum_butterfly(acc);
+        if (lane == 0) chunk_sum[c] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int c = 0; c < nchunks; ++c) total += chunk_sum[c];
+        const float lse = mx + bm_logf(total);
+        conf[r] = bm_expf(mx - lse);
+    }
+}
+
+// iter_accept = 1 + longest prefix of rows r >= 1 with conf[r] > tau
+// (fast_generate.py:128-129); accept = longest prefix with draft == verify
+// (fast_generate.py:146).  Single-thread kernels over <= 32 values.
+__global__ void chain_length_kernel(const float *conf, int D, float tau, int *out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int n = 1;
+    for (int r = 1; r < D; ++r) {
+        if (conf[r] > tau) ++n; else break;
+    }
+    *out = n;
+}
+
+__global__ void verify_accept_kernel(const int64_t *draft, const int64_t *verify, int D, int *out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int n = 0;
+    while (n < D && draft[n] == verify[n]) ++n;
+    *out = n;
+}
+
+}  // namespace bm

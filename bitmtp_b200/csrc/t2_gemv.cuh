@@ -1,0 +1,491 @@
+// Packed T2-g128 ternary GEMV / skinny GEMM for sm_100a.
+//
+// Replaces the reference kernel t2g128_mfused and its dispatcher
+// (src/bonsai_sft/gpu/t2g128_kernels/t2g128_kernels.cu:29-92, 94-148):
+//   C[m, n] = ( sum_g  ws[n, g] * G[m, n, g] ) / s[m]
+//   G[m, n, g] = sum_{k in group g} A[m, k] * (code[n, k] - 2)      (int32, exact)
+// with A int8 [W, K], codes packed 4 per byte in natural order, ws bf16
+// [N, K/128], s fp32 [W].
+//
+// Structure (one persistent CTA per SM slot, 8 warps):
+//   * the weight matrix is cut into tiles of R = 8*RB consecutive output rows;
+//     a tile is R contiguous rows of K/4 bytes plus R*K/128 bf16 scales, all
+//     contiguous in global memory, so warp 0 fetches it with one bulk async
+//     copy (TMA, untiled form) per row into a padded shared-memory row and one
+//     copy for the scales, completion counted on an mbarrier.  STAGES tiles are
+//     in flight per CTA; for the layer-sized matrices that is the CTA's whole
+//     share, so every byte the kernel will read is requested before the first
+//     one is consumed;
+//   * the W activation rows are staged once per CTA into shared memory with a
+//     4x4 byte transpose per 16 elements, so that the register produced by
+//     `(word >> 2i) & 0x03030303` (codes 4e+i, e=0..3, of a 16-code word) meets
+//     the four activations it multiplies in one 32-bit register.  Per-group
+//     activation sums are kept too: codes are used unsigned (1,2,3) and
+//     2*sum(A) is subtracted once per group, which removes the `code-2` from
+//     the inner loop and keeps the group sum exact;
+//   * two consumers share that frame:
+//       lanes-across-K (dp4a): a warp owns rows, lane l owns the 64 weights of
+//         one 16-byte piece; two lanes make a group.  Best for W <= 2.
+//       tokens-as-MMA-rows (mma.sync m16n8k32 s8 x u8): a warp owns two of the
+//         16 scale slots for all rows of the tile; the 16 tokens are the MMA's
+//         M dimension, 8 output rows its N dimension, four MMAs cover a group
+//         and the int32 fragment IS the group sum.  Cost is flat in W up to 16.
+//
+// fp32 order (shared with oracle/bm_oracle.c: bmo_t2_gemv): group g feeds slot
+// g%16 with fma((float)G, scale, slot) in ascending g; the 16 slots are summed
+// as a butterfly with offsets 1,2,4,8; one IEEE division by s[m].  The order
+// does not depend on W, on the consumer, or on the tile size, so a token's row
+// is bit-identical at every replay width.
+#pragma once
+
+#include "bm_common.cuh"
+
+namespace bm {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = 8;
+constexpr int kRowPad = 32;        // bytes appended to each staged weight row
+constexpr int kActPad = 16;        // bytes appended to each staged activation row
+constexpr int kMaxStages = 8;
+
+struct GemvParams {
+    const int8_t *A;        // [W, K]
+    const uint8_t *B;       // [N, K/4]
+    const uint16_t *ws;     // [N, K/128] bf16 bits
+    const float *s;         // [W]
+    void *C;                // [W, ldc]  bf16 (out_kind 0) or fp32 (1, 2)
+    int32_t *G;             // [W, N, K/128] or nullptr
+    int W, N, K, ldc;
+    int out_kind;           // 0 bf16, 1 fp32, 2 fp32 holding the bf16-rounded value
+    int stages;             // tiles in flight per CTA
+    int pdl;                // 1: wait for the previous grid before reading A / s
+};
+
+struct GemvSmem {
+    // Byte offsets into dynamic shared memory, computed identically on host and device.
+    int act_stride, act_off, asum_off, stage_off, stage_bytes, row_stride, scale_off_in_stage,
+        part_off, total;
+};
+
+__host__ __device__ inline GemvSmem gemv_smem_layout(int W, int K, int RB, int stages,
+                                                     bool mma) {
+    GemvSmem L;
+    const int ng = K / BM_GROUP;
+    const int R = 8 * RB;
+    const int wrows = mma ? 16 : W;
+    int off = 128;                                   // mbarriers live in the first 128 bytes
+    L.act_stride = K + kActPad;
+    L.act_off = off;
+    off += wrows * L.act_stride;
+    off = (off + 15) & ~15;
+    L.asum_off = off;
+    off += wrows * ng * 4;
+    off = (off + 127) & ~127;
+    L.row_stride = K / 4 + kRowPad;
+    L.scale_off_in_stage = R * L.row_stride;
+    L.stage_bytes = (L.scale_off_in_stage + R * ng * 2 + 127) & ~127;
+    L.stage_off = off;
+    off += stages * L.stage_bytes;
+    L.part_off = off;
+    if (mma) off += kGemvWarps * 16 * (R + 8) * 4;   // [warp][token][R+8] fp32 partials
+    L.total = off;
+    return L;
+}
+
+// ---- tile producer -----------------------------------------------------------
+// Called by warp 0.  Rows [n0, n0 + rows) with rows a multiple of 8.
+__device__ __forceinline__ void gemv_issue_tile(const GemvParams &p, unsigned char *stage,
+                                                const GemvSmem &L, uint64_t *bar, int n0,
+                                                int rows, int lane) {
+    const int ng = p.K / BM_GROUP;
+    const uint32_t row_bytes = (uint32_t)(p.K / 4);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes + (uint32_t)(rows * ng * 2));
+    __syncwarp();
+    for (int r = lane; r < rows; r += 32)
+        bulk_g2s(stage + r * L.row_stride, p.B + (size_t)(n0 + r) * row_bytes, row_bytes, bar);
+    if (lane == 0)
+        bulk_g2s(stage + L.scale_off_in_stage, p.ws + (size_t)n0 * ng, (uint32_t)(rows * ng * 2),
+                 bar);
+}
+
+// ---- activation staging --------------------------------------------------------
+// A (natural order, global) -> shared, 4x4 byte transpose per 16 elements, plus
+// per-(token, group) sums.  `wrows` rows are written; rows >= W are zero.
+__device__ __forceinline__ void gemv_stage_activations(const GemvParams &p, unsigned char *smem,
+                                                       const GemvSmem &L, int wrows) {
+    const int ng = p.K / BM_GROUP;
+    int *asum = reinterpret_cast<int *>(smem + L.asum_off);
+    for (int i = threadIdx.x; i < wrows * ng; i += kGemvThreads) asum[i] = 0;
+    __syncthreads();
+    const int units = p.K / 16;
+    for (int i = threadIdx.x; i < wrows * units; i += kGemvThreads) {
+        const int m = i / units, j = i - m * units;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        if (m < p.W) x = *reinterpret_cast<const uint4 *>(p.A + (size_t)m * p.K + 16 * j);
+        const uint32_t lo01 = __byte_perm(x.x, x.y, 0x5140), lo23 = __byte_perm(x.z, x.w, 0x5140);
+        const uint32_t hi01 = __byte_perm(x.x, x.y, 0x7362), hi23 = __byte_perm(x.z, x.w, 0x7362);
+        uint4 y;
+        y.x = __byte_perm(lo01, lo23, 0x5410);
+        y.y = __byte_perm(lo01, lo23, 0x7632);
+        y.z = __byte_perm(hi01, hi23, 0x5410);
+        y.w = __byte_perm(hi01, hi23, 0x7632);
+        *reinterpret_cast<uint4 *>(smem + L.act_off + m * L.act_stride + 16 * j) = y;
+        int sum = __dp4a((int)x.x, 0x01010101, 0);
+        sum = __dp4a((int)x.y, 0x01010101, sum);
+        sum = __dp4a((int)x.z, 0x01010101, sum);
+        sum = __dp4a((int)x.w, 0x01010101, sum);
+        if (m < p.W) atomicAdd(&asum[m * ng + (j >> 3)], sum);
+    }
+}
+
+__device__ __forceinline__ void gemv_store(const GemvParams &p, int m, int n, float y) {
+    if (p.out_kind == 0)
+        reinterpret_cast<uint16_t *>(p.C)[(size_t)m * p.ldc + n] = bm_f32_to_bf16(y);
+    else if (p.out_kind == 1)
+        reinterpret_cast<float *>(p.C)[(size_t)m * p.ldc + n] = y;
+    else
+        reinterpret_cast<float *>(p.C)[(size_t)m * p.ldc + n] = bm_bf16_rn(y);
+}
+
+// =============================================================================
+// Consumer 1: lanes across K, dp4a.  WB tokens per pass (W is covered in
+// ceil(W/WB) passes over the staged tile), RB row-blocks of 8 rows per tile;
+// warp w owns rows rb*8 + w.
+// =============================================================================
+template <int WB, int RB>
+__global__ void __launch_bounds__(kGemvThreads) t2_gemv_dp4a_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const GemvSmem L = gemv_smem_layout(p.W, p.K, RB, p.stages, false);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ng = p.K / BM_GROUP;
+    const int R = 8 * RB;
+    const int n_tiles = (p.N + R - 1) / R;
+    const int units = p.K / 64;                       // 16-byte pieces per row
+    const int nch = (units + 31) / 32;                // 2048-element chunks
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < p.stages; ++i) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // Weights do not depend on the previous kernel: request them first.
+    int my_tiles = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) ++my_tiles;
+    if (warp == 0) {
+        for (int i = 0; i < p.stages - 1 && i < my_tiles; ++i) {
+            const int n0 = (blockIdx.x + i * gridDim.x) * R;
+            gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, L, &bars[i], n0,
+                            min(R, p.N - n0), lane);
+        }
+    }
+    if (p.pdl) pdl_wait();
+    pdl_launch_dependents();
+    gemv_stage_activations(p, smem, L, p.W);
+    __syncthreads();
+
+    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
+    const int slot_lane = lane >> 1;                  // slot this lane accumulates
+
+    for (int i = 0; i < my_tiles; ++i) {
+        const int st = i % p.stages;
+        if (warp == 0) {
+            const int nx = i + p.stages - 1;
+            if (nx < my_tiles) {
+                const int n0 = (blockIdx.x + nx * gridDim.x) * R;
+                gemv_issue_tile(p, smem + L.stage_off + (nx % p.stages) * L.stage_bytes, L,
+                                &bars[nx % p.stages], n0, min(R, p.N - n0), lane);
+            }
+        }
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1));
+        if (__syncthreads_or(!ok)) {
+            // Give up: record it, give copies still in flight a last bounded chance
+            // to land in this CTA's shared memory, and leave.
+            if (threadIdx.x == 0) {
+                report_error(kErrGemvWaitTimeout);
+                for (int j = i; j < my_tiles && j < i + p.stages - 1; ++j)
+                    for (int it = 0; it < (1 << 12); ++it)
+                        if (mbar_try_wait(&bars[j % p.stages], (uint32_t)((j / p.stages) & 1))) break;
+            }
+            break;
+        }
+        const unsigned char *stage = smem + L.stage_off + st * L.stage_bytes;
+        const uint16_t *sc = reinterpret_cast<const uint16_t *>(stage + L.scale_off_in_stage);
+        const int n0 = (blockIdx.x + i * gridDim.x) * R;
+        const int rows = min(R, p.N - n0);
+
+        for (int m0 = 0; m0 < p.W; m0 += WB) {
+            float acc[RB][WB];
+#pragma unroll
+            for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                for (int m = 0; m < WB; ++m) acc[rb][m] = 0.0f;
+
+            for (int c = 0; c < nch; ++c) {
+                const int u = c * 32 + lane;
+                const bool active = u < units;
+                const int g = u >> 1;
+                uint4 a[WB][4];
+#pragma unroll
+                for (int m = 0; m < WB; ++m) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a[m][j] = make_uint4(0u, 0u, 0u, 0u);
+                    if (active && m0 + m < p.W) {
+                        const uint4 *ap = reinterpret_cast<const uint4 *>(
+                            smem + L.act_off + (m0 + m) * L.act_stride + 64 * u);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) a[m][j] = ap[j];
+                    }
+                }
+#pragma unroll
+                for (int rb = 0; rb < RB; ++rb) {
+                    const int r = rb * 8 + warp;
+                    if (r >= rows) continue;          // warp-uniform
+                    uint4 w4 = make_uint4(0u, 0u, 0u, 0u);
+                    if (active)
+                        w4 = *reinterpret_cast<const uint4 *>(stage + r * L.row_stride + 16 * u);
+                    const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                    int dot[WB];
+#pragma unroll
+                    for (int m = 0; m < WB; ++m) dot[m] = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t c0 = wv[j] & 0x03030303u, c1 = (wv[j] >> 2) & 0x03030303u,
+                                       c2 = (wv[j] >> 4) & 0x03030303u,
+                                       c3 = (wv[j] >> 6) & 0x03030303u;
+#pragma unroll
+                        for (int m = 0; m < WB; ++m) {
+                            const uint4 av = a[m][j];
+                            dot[m] = __dp4a((int)av.x, (int)c0, dot[m]);
+                            dot[m] = __dp4a((int)av.y, (int)c1, dot[m]);
+                            dot[m] = __dp4a((int)av.z, (int)c2, dot[m]);
+                            dot[m] = __dp4a((int)av.w, (int)c3, dot[m]);
+                        }
+                    }
+                    const float scale = active ? bf16_bits_to_f32(sc[r * ng + g]) : 0.0f;
+#pragma unroll
+                    for (int m = 0; m < WB; ++m) {
+                        const int both = dot[m] + __shfl_xor_sync(0xffffffffu, dot[m], 1);
+                        if (active && m0 + m < p.W) {
+                            const int G = both - 2 * asum[(m0 + m) * ng + g];
+                            acc[rb][m] = fmaf((float)G, scale, acc[rb][m]);
+                            if (p.G != nullptr && (lane & 1) == 0)
+                                p.G[((size_t)(m0 + m) * p.N + n0 + r) * ng + g] = G;
+                        }
+                    }
+                }
+            }
+            // Slot tree: lane bits 1..4 are slot bits 0..3.
+#pragma unroll
+            for (int rb = 0; rb < RB; ++rb) {
+                const int r = rb * 8 + warp;
+                if (r >= rows) continue;
+#pragma unroll
+                for (int m = 0; m < WB; ++m) {
+                    float v = acc[rb][m];
+                    v = v + __shfl_xor_sync(0xffffffffu, v, 2);
+                    v = v + __shfl_xor_sync(0xffffffffu, v, 4);
+                    v = v + __shfl_xor_sync(0xffffffffu, v, 8);
+                    v = v + __shfl_xor_sync(0xffffffffu, v, 16);
+                    if (lane == m && m0 + m < p.W) gemv_store(p, m0 + m, n0 + r, v / p.s[m0 + m]);
+                }
+            }
+        }
+        (void)slot_lane;
+        __syncthreads();                              // stage st may be refilled next iteration
+    }
+}
+
+// =============================================================================
+// Consumer 2: tokens as the 16 MMA rows, mma.sync.m16n8k32 s8 x u8 -> s32.
+// Warp w owns scale slots 2w and 2w+1 (groups g with g%16 in {2w, 2w+1}) for
+// every row of the tile.  Tokens 0..15 (rows >= W are zero).
+// =============================================================================
+__device__ __forceinline__ void mma_s8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct MmaAFrag {
+    uint4 lo0, hi0;   // token r   : k-slots 4q.., 16+4q.. for the four MMA steps
+    uint4 lo8, hi8;   // token r+8
+};
+
+__device__ __forceinline__ MmaAFrag gemv_load_afrag(const unsigned char *smem, const GemvSmem &L,
+                                                    int W, int g, int r, int q) {
+    MmaAFrag f;
+    f.lo0 = f.hi0 = f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
+    if (r < W) {
+        const uint4 *ap = reinterpret_cast<const uint4 *>(smem + L.act_off + r * L.act_stride +
+                                                          BM_GROUP * g + 32 * q);
+        f.lo0 = ap[0];
+        f.hi0 = ap[1];
+    }
+    if (r + 8 < W) {
+        const uint4 *ap = reinterpret_cast<const uint4 *>(
+            smem + L.act_off + (r + 8) * L.act_stride + BM_GROUP * g + 32 * q);
+        f.lo8 = ap[0];
+        f.hi8 = ap[1];
+    }
+    return f;
+}
+
+template <int RB>
+__global__ void __launch_bounds__(kGemvThreads) t2_gemv_mma_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const GemvSmem L = gemv_smem_layout(p.W, p.K, RB, p.stages, true);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = lane >> 2, q = lane & 3;            // token row / k quarter; also B column
+    const int ng = p.K / BM_GROUP;
+    const int R = 8 * RB;
+    const int n_tiles = (p.N + R - 1) / R;
+    const int nch = (ng + BM_SLOTS - 1) / BM_SLOTS;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < p.stages; ++i) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    int my_tiles = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) ++my_tiles;
+    if (warp == 0) {
+        for (int i = 0; i < p.stages - 1 && i < my_tiles; ++i) {
+            const int n0 = (blockIdx.x + i * gridDim.x) * R;
+            gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, L, &bars[i], n0,
+                            min(R, p.N - n0), lane);
+        }
+    }
+    if (p.pdl) pdl_wait();
+    pdl_launch_dependents();
+    gemv_stage_activations(p, smem, L, 16);
+    __syncthreads();
+
+    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
+    float *part = reinterpret_cast<float *>(smem + L.part_off);   // [warp][token][R+8]
+    constexpr int RP = 8 * RB + 8;
+
+    // With one chunk (K <= 2048) the fragments never change: load them once.
+    MmaAFrag af0, af1;
+    const int gA = 2 * warp, gB = 2 * warp + 1;
+    if (nch == 1) {
+        af0 = gemv_load_afrag(smem, L, p.W, gA < ng ? gA : 0, r, q);
+        af1 = gemv_load_afrag(smem, L, p.W, gB < ng ? gB : 0, r, q);
+    }
+
+    for (int i = 0; i < my_tiles; ++i) {
+        const int st = i % p.stages;
+        if (warp == 0) {
+            const int nx = i + p.stages - 1;
+            if (nx < my_tiles) {
+                const int n0 = (blockIdx.x + nx * gridDim.x) * R;
+                gemv_issue_tile(p, smem + L.stage_off + (nx % p.stages) * L.stage_bytes, L,
+                                &bars[nx % p.stages], n0, min(R, p.N - n0), lane);
+            }
+        }
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1));
+        if (__syncthreads_or(!ok)) {
+            // Give up: record it, give copies still in flight a last bounded chance
+            // to land in this CTA's shared memory, and leave.
+            if (threadIdx.x == 0) {
+                report_error(kErrGemvWaitTimeout);
+                for (int j = i; j < my_tiles && j < i + p.stages - 1; ++j)
+                    for (int it = 0; it < (1 << 12); ++it)
+                        if (mbar_try_wait(&bars[j % p.stages], (uint32_t)((j / p.stages) & 1))) break;
+            }
+            break;
+        }
+        const unsigned char *stage = smem + L.stage_off + st * L.stage_bytes;
+        const uint16_t *sc = reinterpret_cast<const uint16_t *>(stage + L.scale_off_in_stage);
+        const int n0 = (blockIdx.x + i * gridDim.x) * R;
+        const int rows = min(R, p.N - n0);
+
+        // acc[rb][slot][i]: i = {token r, row 2q}, {token r, row 2q+1}, {token r+8, 2q}, {r+8, 2q+1}
+        float acc[RB][2][4];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[rb][sl][e] = 0.0f;
+
+        for (int c = 0; c < nch; ++c) {
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+                const int g = c * BM_SLOTS + 2 * warp + sl;
+                if (g >= ng) continue;                // warp-uniform
+                MmaAFrag af;
+                if (nch == 1) af = sl == 0 ? af0 : af1;
+                else af = gemv_load_afrag(smem, L, p.W, g, r, q);
+                const int as0 = r < p.W ? asum[r * ng + g] : 0;
+                const int as8 = r + 8 < p.W ? asum[(r + 8) * ng + g] : 0;
+#pragma unroll
+                for (int rb = 0; rb < RB; ++rb) {
+                    if (rb * 8 >= rows) continue;     // warp-uniform (rows is a multiple of 8)
+                    const uint2 w2 = *reinterpret_cast<const uint2 *>(
+                        stage + (rb * 8 + r) * L.row_stride + 32 * g + 8 * q);
+                    int cf[4] = {0, 0, 0, 0};
+                    mma_s8u8(cf, af.lo0.x, af.lo8.x, af.hi0.x, af.hi8.x, w2.x & 0x03030303u,
+                             w2.y & 0x03030303u);
+                    mma_s8u8(cf, af.lo0.y, af.lo8.y, af.hi0.y, af.hi8.y,
+                             (w2.x >> 2) & 0x03030303u, (w2.y >> 2) & 0x03030303u);
+                    mma_s8u8(cf, af.lo0.z, af.lo8.z, af.hi0.z, af.hi8.z,
+                             (w2.x >> 4) & 0x03030303u, (w2.y >> 4) & 0x03030303u);
+                    mma_s8u8(cf, af.lo0.w, af.lo8.w, af.hi0.w, af.hi8.w,
+                             (w2.x >> 6) & 0x03030303u, (w2.y >> 6) & 0x03030303u);
+                    const int row0 = rb * 8 + 2 * q;
+                    const float s0 = bf16_bits_to_f32(sc[row0 * ng + g]);
+                    const float s1 = bf16_bits_to_f32(sc[(row0 + 1) * ng + g]);
+                    const int G0 = cf[0] - 2 * as0, G1 = cf[1] - 2 * as0;
+                    const int G2 = cf[2] - 2 * as8, G3 = cf[3] - 2 * as8;
+                    acc[rb][sl][0] = fmaf((float)G0, s0, acc[rb][sl][0]);
+                    acc[rb][sl][1] = fmaf((float)G1, s1, acc[rb][sl][1]);
+                    acc[rb][sl][2] = fmaf((float)G2, s0, acc[rb][sl][2]);
+                    acc[rb][sl][3] = fmaf((float)G3, s1, acc[rb][sl][3]);
+                    if (p.G != nullptr) {
+                        if (r < p.W) {
+                            p.G[((size_t)r * p.N + n0 + row0) * ng + g] = G0;
+                            p.G[((size_t)r * p.N + n0 + row0 + 1) * ng + g] = G1;
+                        }
+                        if (r + 8 < p.W) {
+                            p.G[((size_t)(r + 8) * p.N + n0 + row0) * ng + g] = G2;
+                            p.G[((size_t)(r + 8) * p.N + n0 + row0 + 1) * ng + g] = G3;
+                        }
+                    }
+                }
+            }
+        }
+        // First tree level inside the thread (slots 2w, 2w+1), the rest through
+        // shared memory.
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+            const int row0 = rb * 8 + 2 * q;
+            float *pw = part + (size_t)warp * 16 * RP;
+            *reinterpret_cast<float2 *>(&pw[r * RP + row0]) =
+                make_float2(acc[rb][0][0] + acc[rb][1][0], acc[rb][0][1] + acc[rb][1][1]);
+            *reinterpret_cast<float2 *>(&pw[(r + 8) * RP + row0]) =
+                make_float2(acc[rb][0][2] + acc[rb][1][2], acc[rb][0][3] + acc[rb][1][3]);
+        }
+        __syncthreads();
+        for (int o = threadIdx.x; o < R * 16; o += kGemvThreads) {
+            const int m = o / R, row = o - m * R;     // consecutive threads -> consecutive n
+            if (m < p.W && row < rows) {
+                float v[kGemvWarps];
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) v[w] = part[((size_t)w * 16 + m) * RP + row];
+                const float t0 = v[0] + v[1], t1 = v[2] + v[3], t2 = v[4] + v[5], t3 = v[6] + v[7];
+                const float y = (t0 + t1) + (t2 + t3);
+                gemv_store(p, m, n0 + row, y / p.s[m]);
+            }
+        }
+        __syncthreads();                              // stage and `part` are free again
+    }
+}
+
+}  // namespace bm

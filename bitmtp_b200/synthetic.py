@@ -1,0 +1,115 @@
+"""Seeded synthetic weights, activations and checkpoints.
+
+Stand-ins for the real Bonsai checkpoints and prompts (not available offline):
+ternary codes i.i.d. uniform over {-1,0,+1}, one bf16 scale per 128 K-elements
+drawn U[0.01,0.05], bf16 N(0,1) activations.  Everything is generated with a
+CPU torch.Generator, so the CPU oracle and the GPU path see identical bytes.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, Tuple
+
+import torch
+
+GROUP = 128
+
+
+def pack_t2_g128(w_frozen: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 weights on the {-s,0,+s} grid -> (int8 [N,K/4] codes, bf16 [N,K/128] scales).
+
+    Same layout as the reference converter (element j of a row in bits 2*(j%4)
+    of byte j/4, stored as value+2; scale = per-group absmax):
+    src/bonsai_sft/gpu/convert_bonsai_mtp_to_gpu.py:127-144.
+    """
+    assert w_frozen.dtype == torch.bfloat16
+    n, k = w_frozen.shape
+    assert k % GROUP == 0
+    wg = w_frozen.float().view(n, k // GROUP, GROUP)
+    scale = wg.abs().amax(dim=-1).to(torch.bfloat16)
+    q = torch.round(wg / scale.float().unsqueeze(-1).clamp_min(1e-30)).clamp(-1, 1)
+    code = (q.to(torch.int16).view(n, k // 4, 4) + 2).to(torch.uint8)
+    packed = code[..., 0] | (code[..., 1] << 2) | (code[..., 2] << 4) | (code[..., 3] << 6)
+    return packed.view(torch.int8).contiguous(), scale.contiguous()
+
+
+def ternary_weight(n: int, k: int, gen: torch.Generator):
+    """Returns (packed int8 [n,k/4], scale bf16 [n,k/128], dense bf16 [n,k])."""
+    q = torch.randint(-1, 2, (n, k), generator=gen, dtype=torch.int8)
+    sc = (torch.rand(n, k // GROUP, generator=gen) * 0.04 + 0.01).to(torch.bfloat16)
+    w = (q.float().view(n, k // GROUP, GROUP) * sc.float().unsqueeze(-1)).view(n, k).to(torch.bfloat16)
+    packed, scale = pack_t2_g128(w)
+    return packed, scale, w
+
+
+def gemv_case(w: int, n: int, k: int, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """One GEMV problem: packed weights + INT8-quantised N(0,1) activations (CPU tensors)."""
+    gen = torch.Generator().manual_seed(seed)
+    packed, scale, _ = ternary_weight(n, k, gen)
+    x = torch.randn(w, k, generator=gen).to(torch.bfloat16)
+    xf = x.float()
+    s = 127.0 / xf.abs().amax(dim=-1, keepdim=True).clamp_min(1e-5)
+    a = (xf * s).round().clamp(-128, 127).to(torch.int8)
+    return {"A": a, "B": packed, "ws": scale, "s": s.reshape(-1).contiguous(), "x": x}
+
+
+BONSAI_1P7B = dict(dim=2048, n_layers=28, n_heads=16, n_kv_heads=8, head_dim=128, ffn_dim=6144,
+                   vocab_size=151936)
+BONSAI_4B = dict(dim=2560, n_layers=36, n_heads=32, n_kv_heads=8, head_dim=128, ffn_dim=9728,
+                 vocab_size=151936)
+TINY = dict(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, head_dim=128, ffn_dim=512,
+            vocab_size=1000)
+
+
+def make_config(geometry: Dict[str, int], block_size: int = 8) -> Dict:
+    """`bonsai_gpu_config.json` content (convert_bonsai_mtp_to_gpu.py:257-275)."""
+    cfg = dict(geometry)
+    cfg.update(norm_eps=1e-6, rope_theta=1.0e6, rope_original_max=8192, rope_factor=4.0,
+               tie_word_embeddings=True, block_size=block_size, causal_attn=True,
+               mask_token_id=min(151654, geometry["vocab_size"] - 1), kernel_kind="t2g128",
+               quantize_embedding=True)
+    return cfg
+
+
+def make_state(cfg: Dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init packed state dict with the key names of `model_state_t2g128.pt`
+    (convert_bonsai_mtp_to_gpu.py:37-66, 221-242).  Norm weights are 1; the
+    embedding is bf16 on the ternary grid so that re-packing it as the tied
+    head is lossless."""
+    gen = torch.Generator().manual_seed(seed)
+    dim, ffn = cfg["dim"], cfg["ffn_dim"]
+    qd, kd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+    sd: Dict[str, torch.Tensor] = {}
+    _, _, emb = ternary_weight(cfg["vocab_size"], dim, gen)
+    sd["embed_tokens.weight"] = emb
+    sd["norm.weight"] = torch.ones(dim, dtype=torch.bfloat16)
+    for i in range(cfg["n_layers"]):
+        p = f"layers.{i}."
+        sd[p + "input_layernorm.weight"] = torch.ones(dim, dtype=torch.bfloat16)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(dim, dtype=torch.bfloat16)
+        sd[p + "attention.q_norm.weight"] = torch.ones(cfg["head_dim"], dtype=torch.bfloat16)
+        sd[p + "attention.k_norm.weight"] = torch.ones(cfg["head_dim"], dtype=torch.bfloat16)
+        for name, (n, k) in (("attention.q_proj", (qd, dim)), ("attention.k_proj", (kd, dim)),
+                             ("attention.v_proj", (kd, dim)), ("attention.o_proj", (dim, qd)),
+                             ("feed_forward.gate_proj", (ffn, dim)),
+                             ("feed_forward.up_proj", (ffn, dim)),
+                             ("feed_forward.down_proj", (dim, ffn))):
+            packed, scale, _ = ternary_weight(n, k, gen)
+            sd[p + name + ".weight"] = packed
+            sd[p + name + ".weight_scale"] = scale
+    return sd
+
+
+def write_checkpoint(out_dir: str, cfg: Dict, seed: int = 0) -> str:
+    """Write `bonsai_gpu_config.json` + `model_state_t2g128.pt` in the reference's layout."""
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "bonsai_gpu_config.json"), "w") as f:
+        json.dump(cfg, f, indent=2)
+    torch.save(make_state(cfg, seed), os.path.join(out_dir, "model_state_t2g128.pt"))
+    return out_dir
+
+
+def random_prompt(length: int, vocab: int, seed: int = 0) -> torch.Tensor:
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (1, length), generator=gen, dtype=torch.int64)
