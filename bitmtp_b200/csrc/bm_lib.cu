@@ -130,6 +130,55 @@ int gemv_launch_dp4a(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t st
     return BM_EINVAL;
 }
 
+struct MmaPlan {
+    int rb, stages, grid, smem;
+};
+
+// Launch geometry of the MMA consumer.  Rows per tile grow with N so that large
+// matrices amortise the per-tile barrier and merge; CTAs per SM are bounded by
+// shared memory (activations + partials + at least two weight stages).
+bool make_mma_plan(int N, int K, bool half, int sms, MmaPlan *out) {
+    int rb = 1;
+    if (N / 32 >= 6 * sms) rb = 4;
+    else if (N / 16 >= 4 * sms) rb = 2;
+    while (rb > 1 && (N % (8 * rb)) != 0) rb >>= 1;
+    for (; rb >= 1; rb >>= 1) {
+        const int tiles = N / (8 * rb);
+        for (int per_sm = half ? 3 : 2; per_sm >= 1; --per_sm) {
+            const int grid = tiles < sms * per_sm ? tiles : sms * per_sm;
+            const int tiles_per_cta = (tiles + grid - 1) / grid;
+            const int budget = (kMaxSmemPerCta + 1024) / per_sm - 1024;
+            int want = tiles_per_cta < bm::kMaxStages ? tiles_per_cta : bm::kMaxStages;
+            const int floor_stages = tiles_per_cta >= 2 ? 2 : 1;
+            for (int stages = want; stages >= floor_stages; --stages) {
+                const bm::MmaSmem L = bm::mma_smem_layout(K, rb, stages, half);
+                if (L.total <= budget) {
+                    out->rb = rb;
+                    out->stages = stages;
+                    out->grid = grid;
+                    out->smem = L.total;
+                    return true;
+                }
+            }
+        }
+    }
+    return false;
+}
+
+template <int RB, bool HALF, bool ONECHUNK, bool EMIT_G>
+int launch_mma_inst(const MmaPlan &pl, cudaStream_t stream, int pdl, const bm::GemvParams &p) {
+    return launch(bm::t2_gemv_mma_kernel<RB, HALF, ONECHUNK, EMIT_G>, pl.grid, bm::kGemvThreads, pl.smem, stream,
+                  pdl, p);
+}
+
+template <bool HALF, bool ONECHUNK>
+int launch_mma_rb(const MmaPlan &pl, cudaStream_t stream, int pdl, const bm::GemvParams &p) {
+    if (p.G != nullptr) return launch_mma_inst<1, HALF, ONECHUNK, true>(pl, stream, pdl, p);
+    if (pl.rb == 4) return launch_mma_inst<4, HALF, ONECHUNK, false>(pl, stream, pdl, p);
+    if (pl.rb == 2) return launch_mma_inst<2, HALF, ONECHUNK, false>(pl, stream, pdl, p);
+    return launch_mma_inst<1, HALF, ONECHUNK, false>(pl, stream, pdl, p);
+}
+
 int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
     // Tokens beyond 16 go through a second launch over the remaining rows.
     for (int m0 = 0; m0 < p0.W; m0 += 16) {
@@ -140,18 +189,21 @@ int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t str
         const size_t esz = p0.out_kind == BM_OUT_BF16 ? 2 : 4;
         p.C = static_cast<char *>(p0.C) + (size_t)m0 * p0.ldc * esz;
         if (p0.G) p.G = p0.G + (size_t)m0 * p0.N * (p0.K / BM_GROUP);
-        Plan pl;
-        if (!make_plan(p.W, p.N, p.K, true, sms, &pl)) return BM_EINVAL;
+        const bool half = p.W <= 8, one = p.K == 2048;
+        MmaPlan pl;
+        if (!make_mma_plan(p.N, p.K, half, sms, &pl)) return BM_EINVAL;
+        if (p.G != nullptr) {                         // the group-sum build exists for RB = 1 only
+            pl.rb = 1;
+            pl.grid = p.N / 8 < pl.grid ? p.N / 8 : pl.grid;
+            pl.stages = 2;
+            pl.smem = bm::mma_smem_layout(p.K, 1, 2, half).total;
+        }
         p.stages = pl.stages;
-        p.pdl = (m0 == 0) ? pdl : 0;
-        int rc = BM_EINVAL;
         const int use_pdl = (m0 == 0) ? pdl : 0;
-        if (pl.rb == 1)
-            rc = launch(bm::t2_gemv_mma_kernel<1>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
-        else if (pl.rb == 2)
-            rc = launch(bm::t2_gemv_mma_kernel<2>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
-        else if (pl.rb == 4)
-            rc = launch(bm::t2_gemv_mma_kernel<4>, pl.grid, bm::kGemvThreads, pl.smem, stream, use_pdl, p);
+        p.pdl = use_pdl;
+        int rc;
+        if (half) rc = one ? launch_mma_rb<true, true>(pl, stream, use_pdl, p) : launch_mma_rb<true, false>(pl, stream, use_pdl, p);
+        else rc = one ? launch_mma_rb<false, true>(pl, stream, use_pdl, p) : launch_mma_rb<false, false>(pl, stream, use_pdl, p);
         if (rc != BM_OK) return rc;
     }
     return BM_OK;
@@ -188,8 +240,8 @@ int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void 
                int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
     if (!A || !B || !C || !s || !ws) return BM_EINVAL;
     if (W < 1 || W > BM_MAX_W || N < 8 || (N % 8) != 0 || K < 128 || (K % 128) != 0) return BM_EINVAL;
-    if (ldc < N || out_kind < 0 || out_kind > 2) return BM_EINVAL;
-    if (!aligned16(A) || !aligned16(B) || !aligned16(ws)) return BM_EINVAL;
+    if (ldc < N || (ldc % 4) != 0 || out_kind < 0 || out_kind > 2) return BM_EINVAL;
+    if (!aligned16(A) || !aligned16(B) || !aligned16(ws) || !aligned16(C)) return BM_EINVAL;
     bm::GemvParams p;
     p.A = static_cast<const int8_t *>(A);
     p.B = static_cast<const uint8_t *>(B);
@@ -206,9 +258,11 @@ int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void 
     p.pdl = 0;
     const int sms = current_device().sm_count;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (path == BM_PATH_AUTO) path = W <= 2 ? BM_PATH_DP4A : BM_PATH_MMA;
+    // The MMA consumer needs an even number of groups (K % 256 == 0); every model shape
+    // has it.  Odd group counts go to the lanes-across-K consumer.
+    if (path == BM_PATH_AUTO) path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
-    if (path == BM_PATH_MMA) return gemv_launch_mma(p, sms, pdl, st);
+    if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, st) : BM_EINVAL;
     return BM_EINVAL;
 }
 

@@ -33,7 +33,9 @@
 //
 // fp32 order (shared with oracle/bm_oracle.c: bmo_t2_gemv): group g feeds slot
 // g%16 with fma((float)G, scale, slot) in ascending g; the 16 slots are summed
-// as a butterfly with offsets 1,2,4,8; one IEEE division by s[m].  The order
+// as a butterfly with offsets 1,2,4,8; the result is multiplied by the IEEE
+// reciprocal 1/s[m] (the reference divides under --use_fast_math, i.e. by an
+// approximate reciprocal; the exact one is within its error).  The order
 // does not depend on W, on the consumer, or on the tile size, so a token's row
 // is bit-identical at every replay width.
 #pragma once
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_dp4a_kernel(const GemvPa
                     v = v + __shfl_xor_sync(0xffffffffu, v, 4);
                     v = v + __shfl_xor_sync(0xffffffffu, v, 8);
                     v = v + __shfl_xor_sync(0xffffffffu, v, 16);
-                    if (lane == m && m0 + m < p.W) gemv_store(p, m0 + m, n0 + r, v / p.s[m0 + m]);
+                    if (lane == m && m0 + m < p.W) gemv_store(p, m0 + m, n0 + r, v * (1.0f / p.s[m0 + m]));
                 }
             }
         }
@@ -298,54 +300,126 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_dp4a_kernel(const GemvPa
 }
 
 // =============================================================================
-// Consumer 2: tokens as the 16 MMA rows, mma.sync.m16n8k32 s8 x u8 -> s32.
+// Consumer 2: tokens as the MMA rows, mma.sync.m16n8k32 s8 x u8 -> s32.
+//
 // Warp w owns scale slots 2w and 2w+1 (groups g with g%16 in {2w, 2w+1}) for
-// every row of the tile.  Tokens 0..15 (rows >= W are zero).
+// every row of the tile; lane (r = lane/4, q = lane%4) supplies, per group, the
+// 32 codes at k = 32q..32q+31 of output row n0 + rb*8 + r as the B fragment and
+// the same 32 activations of tokens r and r+8 as the A fragment, and receives
+// the group sums of tokens {r, r+8} x rows {2q, 2q+1}.  The first MMA of a
+// group takes -2*sum(A) as its C operand, so the int32 fragment that comes out
+// of the fourth MMA is the exact group sum of A * (code - 2).
+//
+// Everything that can be decided at compile time is: RB row-blocks per tile
+// (N % (8*RB) == 0 is guaranteed by the host), HALF (W <= 8: tokens r+8 do not
+// exist), ONECHUNK (K == 2048: one group per slot, activation fragments loaded
+// once per CTA), EMIT_G (test build that also stores the group sums).  The
+// profile of the first version showed the kernel bound by instruction issue,
+// two thirds of it addressing and shape checks.
+// Requires K % 256 == 0.
 // =============================================================================
-__device__ __forceinline__ void mma_s8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-struct MmaAFrag {
-    uint4 lo0, hi0;   // token r   : k-slots 4q.., 16+4q.. for the four MMA steps
-    uint4 lo8, hi8;   // token r+8
+struct MmaSmem {
+    int invs_off, act_stride, act_off, asum_off, stage_off, stage_bytes, row_stride,
+        scale_off_in_stage, part_off, part_buf_floats, total;
 };
 
-__device__ __forceinline__ MmaAFrag gemv_load_afrag(const unsigned char *smem, const GemvSmem &L,
-                                                    int W, int g, int r, int q) {
-    MmaAFrag f;
-    f.lo0 = f.hi0 = f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
-    if (r < W) {
-        const uint4 *ap = reinterpret_cast<const uint4 *>(smem + L.act_off + r * L.act_stride +
-                                                          BM_GROUP * g + 32 * q);
-        f.lo0 = ap[0];
-        f.hi0 = ap[1];
-    }
-    if (r + 8 < W) {
-        const uint4 *ap = reinterpret_cast<const uint4 *>(
-            smem + L.act_off + (r + 8) * L.act_stride + BM_GROUP * g + 32 * q);
-        f.lo8 = ap[0];
-        f.hi8 = ap[1];
-    }
-    return f;
+__host__ __device__ inline MmaSmem mma_smem_layout(int K, int RB, int stages, bool half) {
+    MmaSmem L;
+    const int ng = K / BM_GROUP, R = 8 * RB, wrows = half ? 8 : 16;
+    int off = 128;
+    L.invs_off = off;
+    off += 64;
+    L.act_stride = K + kActPad;
+    L.act_off = off;
+    off += wrows * L.act_stride;
+    off = (off + 15) & ~15;
+    L.asum_off = off;
+    off += wrows * ng * 4;
+    off = (off + 127) & ~127;
+    L.row_stride = K / 4 + kRowPad;
+    L.scale_off_in_stage = R * L.row_stride;
+    L.stage_bytes = (L.scale_off_in_stage + R * ng * 2 + 127) & ~127;
+    L.stage_off = off;
+    off += stages * L.stage_bytes;
+    L.part_off = off;
+    L.part_buf_floats = kGemvWarps * wrows * (R + 8);
+    off += 2 * L.part_buf_floats * 4;                 // double-buffered partials
+    L.total = off;
+    return L;
 }
 
-template <int RB>
-__global__ void __launch_bounds__(kGemvThreads) t2_gemv_mma_kernel(const GemvParams p) {
+__device__ __forceinline__ void mma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1, int c0, int c1,
+                                         int c2, int c3) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+
+template <bool HALF>
+struct AFrag {
+    uint4 lo0, hi0;   // token r   : the four MMA steps' k-slots 4q.. and 16+4q..
+    uint4 lo8, hi8;   // token r+8 (unused when HALF)
+    int nb0, nb8;     // -2 * sum(A) over the group, tokens r and r+8
+};
+
+template <bool HALF>
+__device__ __forceinline__ void load_afrag(AFrag<HALF> &f, const unsigned char *smem,
+                                           const MmaSmem &L, int ng, int g, int r, int q) {
+    const uint4 *ap = reinterpret_cast<const uint4 *>(smem + L.act_off + r * L.act_stride +
+                                                      BM_GROUP * g + 32 * q);
+    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
+    f.lo0 = ap[0];
+    f.hi0 = ap[1];
+    f.nb0 = -2 * asum[r * ng + g];
+    if (!HALF) {
+        const uint4 *ap8 = reinterpret_cast<const uint4 *>(
+            smem + L.act_off + (r + 8) * L.act_stride + BM_GROUP * g + 32 * q);
+        f.lo8 = ap8[0];
+        f.hi8 = ap8[1];
+        f.nb8 = -2 * asum[(r + 8) * ng + g];
+    } else {
+        f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
+        f.nb8 = 0;
+    }
+}
+
+// One group of one row-block: 4 MMAs, then acc += float(G) * scale.
+template <bool HALF, bool EMIT_G>
+__device__ __forceinline__ void mma_group_step(const AFrag<HALF> &f, uint2 w2, float s0, float s1,
+                                               float (&acc)[4], int32_t *gdst0, int32_t *gdst8,
+                                               int gstride) {
+    constexpr uint32_t M3 = 0x03030303u;
+    int d[4];
+    mma_s8u8(d, f.lo0.x, f.lo8.x, f.hi0.x, f.hi8.x, w2.x & M3, w2.y & M3, f.nb0, f.nb0, f.nb8, f.nb8);
+    mma_s8u8(d, f.lo0.y, f.lo8.y, f.hi0.y, f.hi8.y, (w2.x >> 2) & M3, (w2.y >> 2) & M3, d[0], d[1], d[2], d[3]);
+    mma_s8u8(d, f.lo0.z, f.lo8.z, f.hi0.z, f.hi8.z, (w2.x >> 4) & M3, (w2.y >> 4) & M3, d[0], d[1], d[2], d[3]);
+    mma_s8u8(d, f.lo0.w, f.lo8.w, f.hi0.w, f.hi8.w, (w2.x >> 6) & M3, (w2.y >> 6) & M3, d[0], d[1], d[2], d[3]);
+    acc[0] = fmaf((float)d[0], s0, acc[0]);
+    acc[1] = fmaf((float)d[1], s1, acc[1]);
+    if (!HALF) {
+        acc[2] = fmaf((float)d[2], s0, acc[2]);
+        acc[3] = fmaf((float)d[3], s1, acc[3]);
+    }
+    if (EMIT_G) {
+        if (gdst0) { gdst0[0] = d[0]; gdst0[gstride] = d[1]; }
+        if (!HALF && gdst8) { gdst8[0] = d[2]; gdst8[gstride] = d[3]; }
+    }
+}
+
+template <int RB, bool HALF, bool ONECHUNK, bool EMIT_G>
+__global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const GemvParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(p.W, p.K, RB, p.stages, true);
+    constexpr int R = 8 * RB, RP = R + 8, WROWS = HALF ? 8 : 16;
+    const int ng = p.K / BM_GROUP;
+    const MmaSmem L = mma_smem_layout(p.K, RB, p.stages, HALF);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r = lane >> 2, q = lane & 3;            // token row / k quarter; also B column
-    const int ng = p.K / BM_GROUP;
-    const int R = 8 * RB;
-    const int n_tiles = (p.N + R - 1) / R;
-    const int nch = (ng + BM_SLOTS - 1) / BM_SLOTS;
+    const int r = lane >> 2, q = lane & 3;
+    const int n_tiles = p.N / R;
+    const int nch = ONECHUNK ? 1 : (ng + BM_SLOTS - 1) / BM_SLOTS;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < p.stages; ++i) mbar_init(&bars[i], 1);
@@ -353,60 +427,48 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_mma_kernel(const GemvPar
     }
     __syncthreads();
 
-    int my_tiles = 0;
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) ++my_tiles;
+    // Weights do not depend on the previous kernel in the stream: request them first.
+    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    GemvSmem LS;                                      // the producer only needs these fields
+    LS.row_stride = L.row_stride;
+    LS.scale_off_in_stage = L.scale_off_in_stage;
     if (warp == 0) {
-        for (int i = 0; i < p.stages - 1 && i < my_tiles; ++i) {
-            const int n0 = (blockIdx.x + i * gridDim.x) * R;
-            gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, L, &bars[i], n0,
-                            min(R, p.N - n0), lane);
-        }
+        for (int i = 0; i < p.stages && i < my_tiles; ++i)
+            gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, LS, &bars[i],
+                            (blockIdx.x + i * gridDim.x) * R, R, lane);
     }
     if (p.pdl) pdl_wait();
     pdl_launch_dependents();
-    gemv_stage_activations(p, smem, L, 16);
+    {
+        GemvSmem LA;
+        LA.act_off = L.act_off;
+        LA.act_stride = L.act_stride;
+        LA.asum_off = L.asum_off;
+        gemv_stage_activations(p, smem, LA, WROWS);
+        float *invs = reinterpret_cast<float *>(smem + L.invs_off);
+        if (threadIdx.x < 16) invs[threadIdx.x] = threadIdx.x < p.W ? 1.0f / p.s[threadIdx.x] : 0.0f;
+    }
     __syncthreads();
 
-    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
-    float *part = reinterpret_cast<float *>(smem + L.part_off);   // [warp][token][R+8]
-    constexpr int RP = 8 * RB + 8;
-
-    // With one chunk (K <= 2048) the fragments never change: load them once.
-    MmaAFrag af0, af1;
-    const int gA = 2 * warp, gB = 2 * warp + 1;
-    if (nch == 1) {
-        af0 = gemv_load_afrag(smem, L, p.W, gA < ng ? gA : 0, r, q);
-        af1 = gemv_load_afrag(smem, L, p.W, gB < ng ? gB : 0, r, q);
+    AFrag<HALF> fA, fB;
+    if (ONECHUNK) {
+        load_afrag<HALF>(fA, smem, L, ng, 2 * warp, r, q);
+        load_afrag<HALF>(fB, smem, L, ng, 2 * warp + 1, r, q);
     }
+    float *part = reinterpret_cast<float *>(smem + L.part_off);
+    const float *invs = reinterpret_cast<const float *>(smem + L.invs_off);
+    // Per-thread offsets inside a stage: weight bytes of row r at k-quarter q, and the
+    // packed scale pair of rows 2q / 2q+1 for this warp's two slots.
+    const int woff = r * L.row_stride + 8 * q + 64 * warp;
+    const int soff = L.scale_off_in_stage + (2 * q * ng + 2 * warp) * 2;
+    bool failed = false;
 
     for (int i = 0; i < my_tiles; ++i) {
         const int st = i % p.stages;
-        if (warp == 0) {
-            const int nx = i + p.stages - 1;
-            if (nx < my_tiles) {
-                const int n0 = (blockIdx.x + nx * gridDim.x) * R;
-                gemv_issue_tile(p, smem + L.stage_off + (nx % p.stages) * L.stage_bytes, L,
-                                &bars[nx % p.stages], n0, min(R, p.N - n0), lane);
-            }
-        }
         const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1));
-        if (__syncthreads_or(!ok)) {
-            // Give up: record it, give copies still in flight a last bounded chance
-            // to land in this CTA's shared memory, and leave.
-            if (threadIdx.x == 0) {
-                report_error(kErrGemvWaitTimeout);
-                for (int j = i; j < my_tiles && j < i + p.stages - 1; ++j)
-                    for (int it = 0; it < (1 << 12); ++it)
-                        if (mbar_try_wait(&bars[j % p.stages], (uint32_t)((j / p.stages) & 1))) break;
-            }
-            break;
-        }
         const unsigned char *stage = smem + L.stage_off + st * L.stage_bytes;
-        const uint16_t *sc = reinterpret_cast<const uint16_t *>(stage + L.scale_off_in_stage);
         const int n0 = (blockIdx.x + i * gridDim.x) * R;
-        const int rows = min(R, p.N - n0);
 
-        // acc[rb][slot][i]: i = {token r, row 2q}, {token r, row 2q+1}, {token r+8, 2q}, {r+8, 2q+1}
         float acc[RB][2][4];
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb)
@@ -415,77 +477,93 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_mma_kernel(const GemvPar
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[rb][sl][e] = 0.0f;
 
-        for (int c = 0; c < nch; ++c) {
-#pragma unroll
-            for (int sl = 0; sl < 2; ++sl) {
-                const int g = c * BM_SLOTS + 2 * warp + sl;
-                if (g >= ng) continue;                // warp-uniform
-                MmaAFrag af;
-                if (nch == 1) af = sl == 0 ? af0 : af1;
-                else af = gemv_load_afrag(smem, L, p.W, g, r, q);
-                const int as0 = r < p.W ? asum[r * ng + g] : 0;
-                const int as8 = r + 8 < p.W ? asum[(r + 8) * ng + g] : 0;
+        if (ok) {
+            for (int c = 0; c < nch; ++c) {
+                const int g0 = c * BM_SLOTS + 2 * warp;
+                if (!ONECHUNK) {
+                    if (g0 >= ng) break;              // warp-uniform
+                    load_afrag<HALF>(fA, smem, L, ng, g0, r, q);
+                    load_afrag<HALF>(fB, smem, L, ng, g0 + 1, r, q);
+                }
+                const unsigned char *wp = stage + woff + c * (32 * BM_SLOTS);
+                const unsigned char *sp = stage + soff + c * (2 * BM_SLOTS);
 #pragma unroll
                 for (int rb = 0; rb < RB; ++rb) {
-                    if (rb * 8 >= rows) continue;     // warp-uniform (rows is a multiple of 8)
-                    const uint2 w2 = *reinterpret_cast<const uint2 *>(
-                        stage + (rb * 8 + r) * L.row_stride + 32 * g + 8 * q);
-                    int cf[4] = {0, 0, 0, 0};
-                    mma_s8u8(cf, af.lo0.x, af.lo8.x, af.hi0.x, af.hi8.x, w2.x & 0x03030303u,
-                             w2.y & 0x03030303u);
-                    mma_s8u8(cf, af.lo0.y, af.lo8.y, af.hi0.y, af.hi8.y,
-                             (w2.x >> 2) & 0x03030303u, (w2.y >> 2) & 0x03030303u);
-                    mma_s8u8(cf, af.lo0.z, af.lo8.z, af.hi0.z, af.hi8.z,
-                             (w2.x >> 4) & 0x03030303u, (w2.y >> 4) & 0x03030303u);
-                    mma_s8u8(cf, af.lo0.w, af.lo8.w, af.hi0.w, af.hi8.w,
-                             (w2.x >> 6) & 0x03030303u, (w2.y >> 6) & 0x03030303u);
-                    const int row0 = rb * 8 + 2 * q;
-                    const float s0 = bf16_bits_to_f32(sc[row0 * ng + g]);
-                    const float s1 = bf16_bits_to_f32(sc[(row0 + 1) * ng + g]);
-                    const int G0 = cf[0] - 2 * as0, G1 = cf[1] - 2 * as0;
-                    const int G2 = cf[2] - 2 * as8, G3 = cf[3] - 2 * as8;
-                    acc[rb][sl][0] = fmaf((float)G0, s0, acc[rb][sl][0]);
-                    acc[rb][sl][1] = fmaf((float)G1, s1, acc[rb][sl][1]);
-                    acc[rb][sl][2] = fmaf((float)G2, s0, acc[rb][sl][2]);
-                    acc[rb][sl][3] = fmaf((float)G3, s1, acc[rb][sl][3]);
-                    if (p.G != nullptr) {
-                        if (r < p.W) {
-                            p.G[((size_t)r * p.N + n0 + row0) * ng + g] = G0;
-                            p.G[((size_t)r * p.N + n0 + row0 + 1) * ng + g] = G1;
-                        }
-                        if (r + 8 < p.W) {
-                            p.G[((size_t)(r + 8) * p.N + n0 + row0) * ng + g] = G2;
-                            p.G[((size_t)(r + 8) * p.N + n0 + row0 + 1) * ng + g] = G3;
-                        }
+                    const uint2 wA = *reinterpret_cast<const uint2 *>(wp + rb * 8 * L.row_stride);
+                    const uint2 wB = *reinterpret_cast<const uint2 *>(wp + rb * 8 * L.row_stride + 32);
+                    const uint32_t x0 = *reinterpret_cast<const uint32_t *>(sp + rb * 8 * ng * 2);
+                    const uint32_t x1 = *reinterpret_cast<const uint32_t *>(sp + rb * 8 * ng * 2 + ng * 2);
+                    int32_t *g0p = nullptr, *g8p = nullptr;
+                    if (EMIT_G) {
+                        const size_t col = (size_t)(n0 + rb * 8 + 2 * q) * ng + g0;
+                        if (r < p.W) g0p = p.G + (size_t)r * p.N * ng + col;
+                        if (r + 8 < p.W) g8p = p.G + (size_t)(r + 8) * p.N * ng + col;
                     }
+                    mma_group_step<HALF, EMIT_G>(fA, wA, __uint_as_float(x0 << 16),
+                                                 __uint_as_float(x1 << 16), acc[rb][0], g0p, g8p, ng);
+                    mma_group_step<HALF, EMIT_G>(fB, wB, __uint_as_float(x0 & 0xffff0000u),
+                                                 __uint_as_float(x1 & 0xffff0000u), acc[rb][1],
+                                                 g0p ? g0p + 1 : nullptr, g8p ? g8p + 1 : nullptr, ng);
                 }
             }
         }
-        // First tree level inside the thread (slots 2w, 2w+1), the rest through
-        // shared memory.
+        // Slots 2w + (2w+1) inside the thread, the other three tree levels through
+        // shared memory: part[buf][warp][token][row].
+        float *pw = part + (i & 1) * L.part_buf_floats + warp * WROWS * RP;
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) {
             const int row0 = rb * 8 + 2 * q;
-            float *pw = part + (size_t)warp * 16 * RP;
             *reinterpret_cast<float2 *>(&pw[r * RP + row0]) =
                 make_float2(acc[rb][0][0] + acc[rb][1][0], acc[rb][0][1] + acc[rb][1][1]);
-            *reinterpret_cast<float2 *>(&pw[(r + 8) * RP + row0]) =
-                make_float2(acc[rb][0][2] + acc[rb][1][2], acc[rb][0][3] + acc[rb][1][3]);
+            if (!HALF)
+                *reinterpret_cast<float2 *>(&pw[(r + 8) * RP + row0]) =
+                    make_float2(acc[rb][0][2] + acc[rb][1][2], acc[rb][0][3] + acc[rb][1][3]);
         }
-        __syncthreads();
-        for (int o = threadIdx.x; o < R * 16; o += kGemvThreads) {
-            const int m = o / R, row = o - m * R;     // consecutive threads -> consecutive n
-            if (m < p.W && row < rows) {
-                float v[kGemvWarps];
+        if (__syncthreads_or(!ok)) {
+            // Give up: record it, give copies still in flight a last bounded chance to land
+            // in this CTA's shared memory, and leave.
+            failed = true;
+            if (threadIdx.x == 0) {
+                report_error(kErrGemvWaitTimeout);
+                for (int j = i; j < my_tiles && j < i + p.stages; ++j)
+                    for (int it = 0; it < (1 << 12); ++it)
+                        if (mbar_try_wait(&bars[j % p.stages], (uint32_t)((j / p.stages) & 1))) break;
+            }
+            break;
+        }
+        // Every warp is done with stage `st`: refill it with the tile `stages` ahead.
+        if (warp == 0 && i + p.stages < my_tiles)
+            gemv_issue_tile(p, smem + L.stage_off + st * L.stage_bytes, LS, &bars[st],
+                            (blockIdx.x + (i + p.stages) * gridDim.x) * R, R, lane);
+        // Remaining tree levels, reciprocal multiply, store.  Thread = (token, 4 rows).
+        const float *pr = part + (i & 1) * L.part_buf_floats;
+        for (int o = threadIdx.x; o < p.W * (R / 4); o += kGemvThreads) {
+            const int m = o / (R / 4), rq = o - m * (R / 4);
+            float4 v[kGemvWarps];
 #pragma unroll
-                for (int w = 0; w < kGemvWarps; ++w) v[w] = part[((size_t)w * 16 + m) * RP + row];
-                const float t0 = v[0] + v[1], t1 = v[2] + v[3], t2 = v[4] + v[5], t3 = v[6] + v[7];
-                const float y = (t0 + t1) + (t2 + t3);
-                gemv_store(p, m, n0 + row, y / p.s[m]);
+            for (int w = 0; w < kGemvWarps; ++w)
+                v[w] = *reinterpret_cast<const float4 *>(&pr[(w * WROWS + m) * RP + 4 * rq]);
+            const float is = invs[m];
+            float y[4];
+#define BM_TREE(F) (((v[0].F + v[1].F) + (v[2].F + v[3].F)) + ((v[4].F + v[5].F) + (v[6].F + v[7].F))) * is
+            y[0] = BM_TREE(x); y[1] = BM_TREE(y); y[2] = BM_TREE(z); y[3] = BM_TREE(w);
+#undef BM_TREE
+            const size_t dst = (size_t)m * p.ldc + n0 + 4 * rq;
+            if (p.out_kind == 0) {
+                const uint32_t lo = (uint32_t)bm_f32_to_bf16(y[0]) | ((uint32_t)bm_f32_to_bf16(y[1]) << 16);
+                const uint32_t hi = (uint32_t)bm_f32_to_bf16(y[2]) | ((uint32_t)bm_f32_to_bf16(y[3]) << 16);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.C) + dst) = make_uint2(lo, hi);
+            } else {
+                if (p.out_kind == 2) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) y[e] = bm_bf16_rn(y[e]);
+                }
+                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + dst) =
+                    make_float4(y[0], y[1], y[2], y[3]);
             }
         }
-        __syncthreads();                              // stage and `part` are free again
     }
+    (void)failed;
 }
 
 }  // namespace bm

@@ -67,3 +67,132 @@ def t2_gemv(a_int8: torch.Tensor, b_packed: torch.Tensor, s: torch.Tensor, ws: t
 
 def gemv_bytes(W: int, N: int, K: int, out_kind: int = native.OUT_BF16) -> int:
     return int(native.lib().bm_t2_gemv_bytes(W, N, K, out_kind))
+
+
+# --------------------------------------------------------------------------- fused operators
+def quant_rows(x: torch.Tensor, *, pdl: bool = False):
+    """bf16 [M, K] -> (int8 [M, K], fp32 [M, 1])."""
+    _require_cuda(x)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    check(native.lib().bm_quant_rows(_ptr(x), M, K, _ptr(q), _ptr(s), int(pdl), _stream(x.device)),
+          "bm_quant_rows")
+    return q, s
+
+
+def rmsnorm_fused(x: torch.Tensor, w: torch.Tensor, eps: float, *, M: Optional[int] = None,
+                  gather: Optional[torch.Tensor] = None, res: Optional[torch.Tensor] = None,
+                  row0: int = 0, want_h: bool = False, want_q: bool = True, want_n: bool = False,
+                  pdl: bool = False, out=None):
+    """(gather | residual add) + RMSNorm + (quantise | store).  Returns a dict with the
+    requested outputs among h (bf16), q (int8), s (fp32 [M,1]), n (bf16)."""
+    dim = x.shape[-1]
+    if M is None:
+        M = gather.shape[0] if gather is not None else x.shape[0] - row0
+    dev = x.device
+    out = dict(out) if out else {}
+    if want_h and "h" not in out:
+        out["h"] = torch.empty((M, dim), dtype=torch.bfloat16, device=dev)
+    if want_q and "q" not in out:
+        out["q"] = torch.empty((M, dim), dtype=torch.int8, device=dev)
+        out["s"] = torch.empty((M, 1), dtype=torch.float32, device=dev)
+    if want_n and "n" not in out:
+        out["n"] = torch.empty((M, dim), dtype=torch.bfloat16, device=dev)
+    rc = native.lib().bm_rmsnorm_fused(_ptr(x), _ptr(gather), _ptr(res), _ptr(w), float(eps), M, dim,
+                                       row0, _ptr(out.get("h")), _ptr(out.get("q")),
+                                       _ptr(out.get("s")), _ptr(out.get("n")), int(pdl), _stream(dev))
+    check(rc, f"bm_rmsnorm_fused(M={M}, dim={dim})")
+    return out
+
+
+def silu_mul_quant(gu: torch.Tensor, *, want_inner: bool = False, pdl: bool = False):
+    _require_cuda(gu)
+    M, F2 = gu.shape
+    F = F2 // 2
+    q = torch.empty((M, F), dtype=torch.int8, device=gu.device)
+    s = torch.empty((M, 1), dtype=torch.float32, device=gu.device)
+    inner = torch.empty((M, F), dtype=torch.bfloat16, device=gu.device) if want_inner else None
+    check(native.lib().bm_silu_mul_quant(_ptr(gu), M, F, _ptr(q), _ptr(s), _ptr(inner), int(pdl),
+                                         _stream(gu.device)), "bm_silu_mul_quant")
+    return (q, s, inner) if want_inner else (q, s)
+
+
+def qknorm_rope_kvappend(xqkv, q_w, k_w, eps, cos_t, sin_t, positions, H, Hkv, k_layer, v_layer,
+                         sigma, *, pdl: bool = False, q_out=None):
+    """k_layer / v_layer: bf16 [Hkv, kv_rows, 128] views of one layer of the shared buffer."""
+    M = xqkv.shape[0]
+    kv_rows = k_layer.shape[-2]
+    if q_out is None:
+        q_out = torch.empty((M, H, 128), dtype=torch.bfloat16, device=xqkv.device)
+    rc = native.lib().bm_qknorm_rope_kvappend(
+        _ptr(xqkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos_t), _ptr(sin_t), _ptr(positions),
+        M, H, Hkv, _ptr(k_layer), _ptr(v_layer), kv_rows, sigma, _ptr(q_out), int(pdl),
+        _stream(xqkv.device))
+    check(rc, "bm_qknorm_rope_kvappend")
+    return q_out
+
+
+def new_step_state(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def set_step_state(state: torch.Tensor, cache_len: int, n_pend: int, role: int, P: int) -> None:
+    check(native.lib().bm_set_step_state(_ptr(state), int(cache_len), int(n_pend), int(role), int(P),
+                                         _stream(state.device)), "bm_set_step_state")
+
+
+def kv_copy_rows(kv: torch.Tensor, kv_rows: int, src_row: int, dst_row: int, n: int) -> None:
+    """kv: contiguous bf16 buffer whose trailing dims are [kv_rows, 128]."""
+    planes = kv.numel() // (kv_rows * 128)
+    check(native.lib().bm_kv_copy_rows(_ptr(kv), planes, kv_rows, int(src_row), int(dst_row), int(n),
+                                       _stream(kv.device)), "bm_kv_copy_rows")
+
+
+def attention_scratch(M: int, H: int, sigma: int, device) -> torch.Tensor:
+    n = int(native.lib().bm_verify_attention_scratch_bytes(M, H, sigma))
+    return torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=device)
+
+
+def verify_attention(q, k_layer, v_layer, sigma, state, scratch, *, pdl: bool = False, out=None):
+    """Returns (att bf16 [M, H*128], q int8 [M, H*128], s fp32 [M, 1])."""
+    M, H, _ = q.shape
+    Hkv, kv_rows = k_layer.shape[-3], k_layer.shape[-2]
+    dev = q.device
+    if out is None:
+        out = (torch.empty((M, H * 128), dtype=torch.bfloat16, device=dev),
+               torch.empty((M, H * 128), dtype=torch.int8, device=dev),
+               torch.empty((M, 1), dtype=torch.float32, device=dev))
+    rc = native.lib().bm_verify_attention(_ptr(q), _ptr(k_layer), _ptr(v_layer), M, H, Hkv, kv_rows,
+                                          sigma, _ptr(state), _ptr(scratch), _ptr(out[0]),
+                                          _ptr(out[1]), _ptr(out[2]), int(pdl), _stream(dev))
+    check(rc, "bm_verify_attention")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, *, out=None) -> torch.Tensor:
+    rows, vocab = logits.shape
+    idx = out if out is not None else torch.empty(rows, dtype=torch.int64, device=logits.device)
+    check(native.lib().bm_argmax_rows(_ptr(logits), rows, vocab, logits.stride(0), _ptr(idx), None,
+                                      _stream(logits.device)), "bm_argmax_rows")
+    return idx
+
+
+def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None):
+    """Returns (idx int64 [D], iter_accept int32 [1] (device), conf fp32 [D])."""
+    D, vocab = logits.shape
+    dev = logits.device
+    if bufs is None:
+        bufs = (torch.empty(D, dtype=torch.int64, device=dev), torch.empty(D, device=dev),
+                torch.empty(D, device=dev), torch.empty(1, dtype=torch.int32, device=dev))
+    idx, mx, conf, n = bufs
+    check(native.lib().bm_draft_chain(_ptr(logits), D, vocab, logits.stride(0), float(tau), _ptr(idx),
+                                      _ptr(mx), _ptr(conf), _ptr(n), _stream(dev)), "bm_draft_chain")
+    return idx, n, conf
+
+
+def verify_accept(draft: torch.Tensor, verify: torch.Tensor, D: int, *, out=None) -> torch.Tensor:
+    n = out if out is not None else torch.empty(1, dtype=torch.int32, device=draft.device)
+    check(native.lib().bm_verify_accept(_ptr(draft), _ptr(verify), D, _ptr(n), _stream(draft.device)),
+          "bm_verify_accept")
+    return n

@@ -59,7 +59,10 @@ void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, 
  * lines), with the extras the tests and the runtime need:
  *   ldc       row stride of C in elements (>= N)
  *   out_kind  BM_OUT_*
- *   path      BM_PATH_*  (AUTO: dp4a for W <= 2, MMA above)
+ *   path      BM_PATH_*  (AUTO: the MMA consumer whenever K % 256 == 0, which
+ *             covers every model shape; the lanes-across-K dp4a consumer otherwise.
+ *             BM_PATH_MMA with K % 256 != 0 is BM_EINVAL)
+ *   C         16-byte aligned, ldc a multiple of 4
  *   G_out     int32 [W, N, K/128] exact group sums, or NULL
  *   pdl       1 = launch with programmatic stream serialisation: the kernel
  *             requests its weight tiles at once and waits for the previous
@@ -70,6 +73,95 @@ int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void 
 /* Algorithmic bytes one bm_t2_gemv call moves (codes + scales + A + s + C), the
  * numerator of the roofline figure. Host-only arithmetic. */
 int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind);
+
+/* ------------------------------------------------------------------ fused operators
+ * `pdl` on every call below has the meaning given at bm_t2_gemv: the kernel is
+ * launched with programmatic stream serialisation and waits for its
+ * predecessor before its first read of a tensor the predecessor writes. */
+
+/* Per-row absmax INT8 quantisation: x bf16 [M, K] -> q int8 [M, K], s fp32 [M]
+ * with s = 127 / max(absmax, 1e-5), q = clamp(rint(x * s), -128, 127).
+ * Replaces T2LinearKernel.quant_input (src/bonsai_sft/gpu/model.py:632-636). */
+int bm_quant_rows(const void *x, int M, int K, void *q, void *s, int pdl, void *stream);
+
+/* (gather | residual add) + RMSNorm + (INT8 quantisation | bf16 store), one row per CTA.
+ *   x       bf16 [*, dim]; row m is x[gather[m]] when gather (int64 [M]) is given,
+ *           else x[row0 + m]
+ *   res     optional bf16 [*, dim], read at row0 + m: h = bf16(x + res)
+ *   w       bf16 [dim] norm weight;  dim a multiple of 256, <= 8192
+ *   h_out   optional bf16 [M, dim]: the row before the norm
+ *   q, s    optional int8 [M, dim] + fp32 [M] (both or neither)
+ *   n_out   optional bf16 [M, dim]: the normed row
+ * Replaces _fused_norm_quant, _fused_add_norm_quant, RMSNorm.forward on the logit
+ * rows and the embedding gather (src/bonsai_sft/gpu/model.py:307-336, 290-295,
+ * 1386, 1401-1402). */
+int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps,
+                     int M, int dim, int row0, void *h_out, void *q, void *s, void *n_out, int pdl,
+                     void *stream);
+
+/* inner = bf16(bf16(silu(gate)) * up), then the quantisation of bm_quant_rows.
+ * gu bf16 [M, 2F] = gate | up; q int8 [M, F]; s fp32 [M]; inner_out optional bf16 [M, F].
+ * Replaces src/bonsai_sft/gpu/model.py:1059-1061. */
+int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *s, void *inner_out, int pdl,
+                      void *stream);
+
+/* Split qkv, per-head RMSNorm of q and k, RoPE from bf16 tables, append K / V rows.
+ *   xqkv bf16 [M, (H + 2*Hkv)*128]; q_w, k_w bf16 [128]; cos_t, sin_t bf16 [max_pos, 128];
+ *   positions int64 [M]; k_base, v_base bf16 [Hkv, kv_rows, 128] (one layer of the shared
+ *   buffer), rows [sigma, sigma + M) are written; q_out bf16 [M, H, 128].
+ * Replaces _fused_qkv_qknorm_rope_kv_write (src/bonsai_sft/gpu/model.py:388-436). */
+int bm_qknorm_rope_kvappend(const void *xqkv, const void *q_w, const void *k_w, float eps,
+                            const void *cos_t, const void *sin_t, const void *positions, int M,
+                            int H, int Hkv, void *k_base, void *v_base, int kv_rows, int sigma,
+                            void *q_out, int pdl, void *stream);
+
+/* Writes {cache_len, n_pend, role, P} into the 16-byte device record the attention
+ * reads.  role: 0 draft, 1 verify, 2 ar.  Takes the place of the host-side mask
+ * rebuild GraphAtlas.prepare_step (src/bonsai_sft/gpu/fast_runtime.py:391-465). */
+int bm_set_step_state(void *state, int cache_len, int n_pend, int role, int P, void *stream);
+
+/* Copies rows [src_row, src_row + n) onto [dst_row, dst_row + n) in each of `planes`
+ * planes of a bf16 [planes, kv_rows, 128] buffer (non-overlapping ranges).
+ * Replaces GraphAtlas.commit_kv / commit_kv_from_verify
+ * (src/bonsai_sft/gpu/fast_runtime.py:467-508). */
+int bm_kv_copy_rows(void *kv, int planes, int kv_rows, int src_row, int dst_row, int n,
+                    void *stream);
+
+/* Scratch bytes bm_verify_attention needs for (M, H, sigma). Host-only arithmetic. */
+int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma);
+
+/* Block-verify attention of one layer + INT8 quantisation of its output rows.
+ *   q bf16 [M, H, 128]; k_base, v_base bf16 [Hkv, kv_rows, 128]; history rows are
+ *   [0, cache_len), the M rows of this replay sit at [sigma, sigma + M);
+ *   state: the record written by bm_set_step_state;
+ *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned; its first 256
+ *   bytes must be zero before the first call and are left zero by every call;
+ *   att_out bf16 [M, H*128]; q_out int8 [M, H*128]; s_out fp32 [M].
+ * Visibility follows the reference's draft / verify / ar masks.  Replaces the
+ * attention and o-projection input quantisation of
+ * Attention.forward_sdlm_graph_kernel (src/bonsai_sft/gpu/model.py:989-1005) and the
+ * mask tensors of src/bonsai_sft/gpu/fast_runtime.py:345-372, 423-465. */
+int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H,
+                        int Hkv, int kv_rows, int sigma, const void *state, void *scratch,
+                        void *att_out, void *q_out, void *s_out, int pdl, void *stream);
+
+/* Row argmax (lowest index on ties): logits fp32 [rows, ld] -> idx int64 [rows],
+ * optional max_out fp32 [rows].  Replaces `.argmax(dim=-1)` on the logit rows
+ * (src/bonsai_sft/gpu/fast_generate.py:786, 809, 1079). */
+int bm_argmax_rows(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out,
+                   void *stream);
+
+/* Draft confidence chain: idx int64 [D] = row argmax, conf fp32 [D] =
+ * exp(max - logsumexp), *n_out (device int32) = 1 + number of leading rows r >= 1
+ * with conf[r] > tau.  max_buf: fp32 [D] work area.  Replaces _fused_draft_chain
+ * (src/bonsai_sft/gpu/fast_generate.py:111-130). */
+int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void *idx,
+                   void *max_buf, void *conf, void *n_out, void *stream);
+
+/* *n_out (device int32) = length of the longest common prefix of draft[0:D] and
+ * verify[0:D] (int64).  Replaces _fused_verify_accept
+ * (src/bonsai_sft/gpu/fast_generate.py:133-146). */
+int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, void *stream);
 
 #ifdef __cplusplus
 }

@@ -111,25 +111,34 @@ static float bmo_slot_tree(float slot[BM_SLOTS]) {
 //                       stored code c means the ternary value c-2
 // ws  bf16  [N, K/128]  group scales
 // s   fp32  [W]         activation multipliers (127/absmax); the output is
-//                       DIVIDED by s
+//                       divided by s (as a multiplication by 1/s)
 // G_out   int32 [W, N, K/128] or NULL   exact group sums
 // out_f32 fp32  [W, N] or NULL
 // out_bf16 bf16 [W, N] or NULL          out_f32 rounded once
 //
 // fp32 order: group g feeds slot g%16; a slot accumulates
 // fma((float)G, scale, slot) over its groups in ascending g; the 16 slots are
-// combined by bmo_slot_tree; one IEEE division by s[m].
+// combined by bmo_slot_tree; the sum is multiplied by the IEEE reciprocal
+// 1/s[m] (the reference divides under --use_fast_math, i.e. multiplies by an
+// approximate reciprocal).
 BMO_API void bmo_t2_gemv(const int8_t *A, const uint8_t *B, const uint16_t *ws, const float *s,
                          int W, int N, int K, float *out_f32, uint16_t *out_bf16,
                          int32_t *G_out) {
     const int ng = K / BM_GROUP;
+    // byte -> its four ternary values, as one 32-bit store per packed byte
+    uint32_t lut[256];
+    for (int b = 0; b < 256; ++b) {
+        uint32_t v = 0;
+        for (int i = 0; i < 4; ++i) v |= ((uint32_t)(uint8_t)(int8_t)(((b >> (2 * i)) & 3) - 2)) << (8 * i);
+        lut[b] = v;
+    }
 #pragma omp parallel
     {
         int8_t *t = (int8_t *)malloc((size_t)K);
 #pragma omp for schedule(static)
         for (int n = 0; n < N; ++n) {
             const uint8_t *brow = B + (size_t)n * (K / 4);
-            for (int j = 0; j < K; ++j) t[j] = (int8_t)(((brow[j >> 2] >> (2 * (j & 3))) & 3) - 2);
+            for (int j = 0; j < K / 4; ++j) memcpy(t + 4 * j, &lut[brow[j]], 4);
             for (int m = 0; m < W; ++m) {
                 const int8_t *a = A + (size_t)m * K;
                 float slot[BM_SLOTS];
@@ -143,7 +152,7 @@ BMO_API void bmo_t2_gemv(const int8_t *A, const uint8_t *B, const uint16_t *ws, 
                     const float sc = bm_bf16_to_f32(ws[(size_t)n * ng + g]);
                     slot[g % BM_SLOTS] = fmaf((float)G, sc, slot[g % BM_SLOTS]);
                 }
-                const float y = bmo_slot_tree(slot) / s[m];
+                const float y = bmo_slot_tree(slot) * (1.0f / s[m]);
                 if (out_f32) out_f32[(size_t)m * N + n] = y;
                 if (out_bf16) out_bf16[(size_t)m * N + n] = bm_f32_to_bf16(y);
             }

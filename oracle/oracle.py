@@ -152,7 +152,8 @@ def gemv_numpy(A: np.ndarray, B: np.ndarray, ws: np.ndarray, s: np.ndarray):
         for i in range(0, 16, 2 * step):
             slot[:, :, i] = slot[:, :, i] + slot[:, :, i + step]
         step *= 2
-    y = (slot[:, :, 0] / s.reshape(W, 1).astype(np.float32)).astype(np.float32)
+    inv = (np.float32(1.0) / s.reshape(W, 1).astype(np.float32)).astype(np.float32)
+    y = (slot[:, :, 0] * inv).astype(np.float32)
     return y, f32_to_bf16(y), G
 
 

@@ -1,0 +1,185 @@
+"""GPU parity of the fused operators and the block-verify attention against the CPU
+oracle, through the C ABI.  Everything here is compared bit for bit: INT8 codes,
+fp32 multipliers, bf16 rows."""
+import numpy as np
+import pytest
+import torch
+
+from bitmtp_b200 import native, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _bf16(gen, *shape, scale=1.0):
+    return (torch.randn(*shape, generator=gen) * scale).to(torch.bfloat16)
+
+
+def _u16(O, t):
+    return O.torch_to_u16(t.cpu())
+
+
+@pytest.mark.parametrize("M,K", [(1, 2048), (9, 6144), (16, 9728), (17, 256), (3, 2560), (5, 64)])
+def test_quant_rows(oracle, M, K):
+    gen = torch.Generator().manual_seed(M * 7 + K)
+    x = _bf16(gen, M, K, scale=3.0)
+    x[0, 0] = 0.0
+    if M > 2:
+        x[2].zero_()                                  # all-zero row: the 1e-5 clamp
+    q, s = ops.quant_rows(x.to(DEV))
+    qo, so = oracle.quant_rows(_u16(oracle, x))
+    assert np.array_equal(q.cpu().numpy(), qo)
+    assert np.array_equal(s.cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+
+
+@pytest.mark.parametrize("M,dim", [(1, 2048), (16, 2048), (9, 2560), (17, 256), (4, 4096)])
+def test_rmsnorm_variants(oracle, M, dim):
+    gen = torch.Generator().manual_seed(M + dim)
+    x, res = _bf16(gen, M, dim, scale=2.0), _bf16(gen, M, dim, scale=0.5)
+    w = (1.0 + 0.1 * torch.randn(dim, generator=gen)).to(torch.bfloat16)
+    eps = 1e-6
+    xd, rd, wd = x.to(DEV), res.to(DEV), w.to(DEV)
+    xu, ru, wu = _u16(oracle, x), _u16(oracle, res), _u16(oracle, w)
+    # norm + quant
+    o = ops.rmsnorm_fused(xd, wd, eps)
+    qo, so = oracle.rmsnorm_quant(xu, wu, eps)
+    assert np.array_equal(o["q"].cpu().numpy(), qo)
+    assert np.array_equal(o["s"].cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+    # add + norm + quant, returning h
+    o = ops.rmsnorm_fused(xd, wd, eps, res=rd, want_h=True)
+    ho, qo, so = oracle.add_rmsnorm_quant(xu, ru, wu, eps)
+    assert np.array_equal(_u16(oracle, o["h"]), ho)
+    assert np.array_equal(o["q"].cpu().numpy(), qo)
+    assert np.array_equal(o["s"].cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+    # plain norm with bf16 output, on a row window
+    row0 = 1 if M > 2 else 0
+    o = ops.rmsnorm_fused(xd, wd, eps, row0=row0, M=M - row0, want_q=False, want_n=True)
+    no = oracle.rmsnorm(np.ascontiguousarray(xu[row0:]), wu, eps)
+    assert np.array_equal(_u16(oracle, o["n"]), no)
+
+
+def test_embedding_gather_norm(oracle):
+    gen = torch.Generator().manual_seed(5)
+    table = _bf16(gen, 1000, 2048, scale=0.03)
+    w = torch.ones(2048, dtype=torch.bfloat16)
+    tok = torch.tensor([5, 999, 0, 17, 5], dtype=torch.int64)
+    o = ops.rmsnorm_fused(table.to(DEV), w.to(DEV), 1e-6, gather=tok.to(DEV), want_h=True)
+    rows = np.ascontiguousarray(_u16(oracle, table)[tok.numpy()])
+    qo, so = oracle.rmsnorm_quant(rows, _u16(oracle, w), 1e-6)
+    assert np.array_equal(_u16(oracle, o["h"]), rows)
+    assert np.array_equal(o["q"].cpu().numpy(), qo)
+    assert np.array_equal(o["s"].cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+
+
+@pytest.mark.parametrize("M,F", [(1, 6144), (16, 6144), (9, 9728), (3, 512)])
+def test_silu_mul_quant(oracle, M, F):
+    gen = torch.Generator().manual_seed(M + F)
+    gu = _bf16(gen, M, 2 * F, scale=4.0)
+    gu[0, :4] = torch.tensor([-100.0, 100.0, 0.0, -20.0], dtype=torch.bfloat16)
+    q, s, inner = ops.silu_mul_quant(gu.to(DEV), want_inner=True)
+    qo, so, io = oracle.silu_mul_quant(_u16(oracle, gu), want_inner=True)
+    assert np.array_equal(_u16(oracle, inner), io)
+    assert np.array_equal(q.cpu().numpy(), qo)
+    assert np.array_equal(s.cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+
+
+def _rope_tables(oracle, max_pos):
+    from bitmtp_b200 import synthetic
+    cfg = synthetic.make_config(synthetic.TINY)
+    return oracle.rope_tables(cfg, max_pos)
+
+
+@pytest.mark.parametrize("M,H,Hkv", [(1, 16, 8), (16, 16, 8), (9, 32, 8), (17, 2, 1)])
+def test_qknorm_rope_kvappend(oracle, M, H, Hkv):
+    gen = torch.Generator().manual_seed(M + H)
+    sigma, kv_rows = 40, 40 + 17
+    xqkv = _bf16(gen, M, (H + 2 * Hkv) * 128, scale=2.0)
+    qw = (1.0 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16)
+    kw = (1.0 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16)
+    cos, sin = _rope_tables(oracle, 600)
+    pos = torch.randint(0, 600, (M,), generator=gen, dtype=torch.int64)
+    k0 = _bf16(gen, Hkv, kv_rows, 128)
+    v0 = _bf16(gen, Hkv, kv_rows, 128)
+    ku, vu = _u16(oracle, k0).copy(), _u16(oracle, v0).copy()
+    qo = oracle.qknorm_rope_kvappend(_u16(oracle, xqkv), _u16(oracle, qw), _u16(oracle, kw), 1e-6,
+                                     cos, sin, pos.numpy(), H, Hkv, ku, vu, sigma)
+    kd, vd = k0.to(DEV), v0.to(DEV)
+    q = ops.qknorm_rope_kvappend(xqkv.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6,
+                                 oracle.u16_to_torch(cos).to(DEV), oracle.u16_to_torch(sin).to(DEV),
+                                 pos.to(DEV), H, Hkv, kd, vd, sigma)
+    assert np.array_equal(_u16(oracle, q), qo)
+    assert np.array_equal(_u16(oracle, kd), ku)
+    assert np.array_equal(_u16(oracle, vd), vu)
+
+
+ATTN_CASES = [
+    # (M, H, Hkv, sigma, cache_len, n_pend, D, role)
+    (1, 16, 8, 256, 77, 0, 8, "ar"),
+    (1, 2, 1, 64, 0, 0, 8, "ar"),
+    (9, 16, 8, 256, 100, 1, 8, "draft"),
+    (10, 16, 8, 256, 129, 2, 8, "draft"),
+    (12, 16, 8, 256, 33, 3, 8, "draft"),
+    (16, 16, 8, 1024, 700, 8, 8, "draft"),
+    (16, 32, 8, 256, 64, 5, 8, "draft"),
+    (8, 2, 1, 64, 31, 0, 8, "draft"),
+    (9, 16, 8, 256, 100, 0, 8, "verify"),
+    (9, 32, 8, 1024, 513, 0, 8, "verify"),
+    (5, 2, 1, 64, 20, 1, 4, "draft"),
+    (16, 16, 8, 256, 0, 0, 8, "ar"),
+    (17, 16, 8, 256, 40, 9, 8, "draft"),
+]
+
+
+@pytest.mark.parametrize("M,H,Hkv,sigma,cache_len,n_pend,D,role", ATTN_CASES)
+def test_verify_attention(oracle, M, H, Hkv, sigma, cache_len, n_pend, D, role):
+    gen = torch.Generator().manual_seed(M * 31 + cache_len)
+    kv_rows = sigma + 17
+    q = _bf16(gen, M, H, 128, scale=1.5)
+    k = _bf16(gen, Hkv, kv_rows, 128, scale=1.5)
+    v = _bf16(gen, Hkv, kv_rows, 128)
+    rid = oracle.ROLE_IDS[role]
+    P = M - D
+    att_o = oracle.attention(_u16(oracle, q), _u16(oracle, k), _u16(oracle, v), sigma, cache_len,
+                             n_pend, P, rid)
+    qo, so = oracle.quant_rows(att_o)
+    state = ops.new_step_state(DEV)
+    ops.set_step_state(state, cache_len, n_pend, rid, P)
+    scratch = ops.attention_scratch(M, H, sigma, DEV)
+    for rep in range(2):                               # second call: scratch counters were left zero
+        att, qq, s = ops.verify_attention(q.to(DEV), k.to(DEV), v.to(DEV), sigma, state, scratch)
+        torch.cuda.synchronize()
+        assert np.array_equal(_u16(oracle, att), att_o), f"attention rows differ (call {rep})"
+        assert np.array_equal(qq.cpu().numpy(), qo)
+        assert np.array_equal(s.cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
+    assert int(scratch[:256].sum().item()) == 0
+
+
+def test_kv_copy_rows():
+    gen = torch.Generator().manual_seed(3)
+    kv = _bf16(gen, 2, 3, 1, 2, 50, 128).to(DEV)
+    ref = kv.clone()
+    ops.kv_copy_rows(kv, 50, 40, 7, 5)
+    ref[..., 7:12, :] = ref[..., 40:45, :]
+    assert torch.equal(kv, ref)
+
+
+def test_logit_reductions(oracle):
+    gen = torch.Generator().manual_seed(9)
+    D, vocab = 8, 151936
+    logits = (torch.randn(D, vocab, generator=gen) * 3).to(torch.bfloat16).float()
+    logits[1, 777] = 60.0
+    logits[2, 5] = 60.0
+    logits[3, 100] = logits[3].max()
+    logits[3, 90000] = logits[3].max()                 # tie: the lower index wins
+    lg = logits.to(DEV)
+    idx = ops.argmax_rows(lg)
+    assert np.array_equal(idx.cpu().numpy(), oracle.argmax_rows(logits.numpy()))
+    for tau in (0.9, 0.5):
+        i2, n, conf = ops.draft_chain(lg, tau)
+        io, no, co = oracle.draft_chain(logits.numpy(), tau)
+        assert np.array_equal(i2.cpu().numpy(), io)
+        assert int(n.item()) == no
+        assert np.array_equal(conf.cpu().numpy().view(np.uint32), co.view(np.uint32))
+    a = torch.tensor([1, 2, 3, 4, 5, 6, 7, 8], dtype=torch.int64)
+    b = torch.tensor([1, 2, 3, 9, 5, 6, 7, 8, 0], dtype=torch.int64)
+    assert int(ops.verify_accept(a.to(DEV), b.to(DEV), 8).item()) == oracle.verify_accept(a.numpy(), b.numpy(), 8) == 3

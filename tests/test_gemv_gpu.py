@@ -50,7 +50,15 @@ SMALL = [(1, 8, 128), (2, 16, 256), (3, 24, 128), (4, 64, 384), (5, 40, 2048), (
 @pytest.mark.parametrize("W,N,K", SMALL)
 @pytest.mark.parametrize("path", [native.PATH_DP4A, native.PATH_MMA])
 def test_small_shapes_both_consumers(oracle, W, N, K, path):
-    _check(oracle, synthetic.gemv_case(W, N, K, seed=W * 1000 + N + K), path)
+    case = synthetic.gemv_case(W, N, K, seed=W * 1000 + N + K)
+    if path == native.PATH_MMA and K % 256 != 0:
+        # the MMA consumer needs an even number of groups; the ABI says so with EINVAL
+        dev = torch.device("cuda:0")
+        A, B, ws, s = (case[k].to(dev) for k in ("A", "B", "ws", "s"))
+        with pytest.raises(native.NativeError):
+            ops.t2_gemv(A, B, s, ws, path=path)
+        return
+    _check(oracle, case, path)
 
 
 LAYER_NK = [(2048, 2048), (1024, 2048), (4096, 2048), (6144, 2048), (2048, 6144), (12288, 2048),
@@ -68,6 +76,23 @@ def test_config0_reference_case(oracle):
     case = synthetic.gemv_case(1, 6144, 2048, seed=0)
     for path in (native.PATH_DP4A, native.PATH_MMA):
         _check(oracle, case, path)
+
+
+@pytest.mark.parametrize("N,K,W", [(12288, 2048, 16), (12288, 2048, 3), (151936, 2048, 16),
+                                   (28672, 8192, 16), (19456, 2560, 9), (2560, 9728, 16)])
+def test_large_tiles_without_group_output(oracle, N, K, W):
+    """The production instantiations (16- and 32-row tiles) are only reached when no group
+    sums are requested; check their scaled outputs bit for bit."""
+    case = synthetic.gemv_case(W, N, K, seed=21)
+    y32, y16, _ = oracle.t2_gemv(case["A"].numpy(), case["B"].numpy().view(np.uint8),
+                                 oracle.torch_to_u16(case["ws"]), case["s"].numpy())
+    dev = torch.device("cuda:0")
+    A, B, ws, s = (case[k].to(dev) for k in ("A", "B", "ws", "s"))
+    out = ops.t2_gemv(A, B, s, ws, out_kind=native.OUT_F32)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), y32.view(np.uint32))
+    outb = ops.t2_gemv(A, B, s, ws)
+    assert np.array_equal(oracle.torch_to_u16(outb.cpu()), y16)
+    assert native.lib().bm_device_error() == 0
 
 
 @pytest.mark.parametrize("W", [1, 10, 12, 17])
