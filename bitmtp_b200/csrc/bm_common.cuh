@@ -78,6 +78,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Same, but gives up at once when another warp of the CTA has already given up
+// (`*abort_flag` != 0), so that one lost copy does not make every warp of the CTA sit
+// out its own full limit in turn.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  volatile int *abort_flag) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 32) {
+            if (*abort_flag) return false;
+            __nanosleep(32);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
 // ---- programmatic dependent launch ------------------------------------------
 // wait: block until every grid this one depends on has finished and its writes
 // are visible.  launch_dependents: allow the next grid in the stream to start

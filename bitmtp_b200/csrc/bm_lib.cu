@@ -137,32 +137,49 @@ struct MmaPlan {
 // Launch geometry of the MMA consumer.  Rows per tile grow with N so that large
 // matrices amortise the per-tile barrier and merge; CTAs per SM are bounded by
 // shared memory (activations + partials + at least two weight stages).
-bool make_mma_plan(int N, int K, bool half, int sms, MmaPlan *out) {
-    int rb = 1;
-    if (N / 32 >= 6 * sms) rb = 4;
-    else if (N / 16 >= 4 * sms) rb = 2;
-    while (rb > 1 && (N % (8 * rb)) != 0) rb >>= 1;
-    for (; rb >= 1; rb >>= 1) {
+bool make_mma_plan(int N, int K, bool half, int sms, int force_rb, MmaPlan *out) {
+    // Two CTAs of 8 warps per SM (128 registers per thread); each gets half the shared
+    // memory.  Among the tile heights that divide N, take the one that keeps the most
+    // weight bytes in flight per CTA, larger tiles winning ties (fewer hand-offs per byte);
+    // small matrices keep 8-row tiles so that every SM gets work.
+    const int per_sm = 2;
+    const int budget = (kMaxSmemPerCta + 1024) / per_sm - 1024;
+    int best_rb = 0, best_stages = 0, best_grid = 0, best_smem = 0;
+    long best_flight = -1;
+    for (int rb = 4; rb >= 1; rb >>= 1) {
+        if (force_rb && rb != force_rb) continue;
+        if ((N % (8 * rb)) != 0) continue;
         const int tiles = N / (8 * rb);
-        for (int per_sm = half ? 3 : 2; per_sm >= 1; --per_sm) {
-            const int grid = tiles < sms * per_sm ? tiles : sms * per_sm;
-            const int tiles_per_cta = (tiles + grid - 1) / grid;
-            const int budget = (kMaxSmemPerCta + 1024) / per_sm - 1024;
-            int want = tiles_per_cta < bm::kMaxStages ? tiles_per_cta : bm::kMaxStages;
-            const int floor_stages = tiles_per_cta >= 2 ? 2 : 1;
-            for (int stages = want; stages >= floor_stages; --stages) {
-                const bm::MmaSmem L = bm::mma_smem_layout(K, rb, stages, half);
-                if (L.total <= budget) {
-                    out->rb = rb;
-                    out->stages = stages;
-                    out->grid = grid;
-                    out->smem = L.total;
-                    return true;
-                }
+        if (!force_rb && rb > 1 && tiles < 2 * per_sm * sms) continue;
+        const int grid = tiles < sms * per_sm ? tiles : sms * per_sm;
+        const int tiles_per_cta = (tiles + grid - 1) / grid;
+        const int want = tiles_per_cta < bm::kMaxStages ? tiles_per_cta : bm::kMaxStages;
+        for (int stages = want; stages >= 1; --stages) {
+            const bm::MmaSmem L = bm::mma_smem_layout(K, rb, stages, half);
+            if (L.total > budget) continue;
+            const long flight = (long)stages * L.stage_bytes;
+            if (flight > best_flight) {
+                best_flight = flight;
+                best_rb = rb; best_stages = stages; best_grid = grid; best_smem = L.total;
             }
+            break;
         }
     }
-    return false;
+    if (best_rb == 0) {
+        // Nothing fits twice per SM (very long K): one CTA per SM with the whole budget.
+        const int tiles = N / 8;
+        const int grid = tiles < sms ? tiles : sms;
+        for (int stages = 2; stages >= 1; --stages) {
+            const bm::MmaSmem L = bm::mma_smem_layout(K, 1, stages, half);
+            if (L.total <= kMaxSmemPerCta) {
+                out->rb = 1; out->stages = stages; out->grid = grid; out->smem = L.total;
+                return true;
+            }
+        }
+        return false;
+    }
+    out->rb = best_rb; out->stages = best_stages; out->grid = best_grid; out->smem = best_smem;
+    return true;
 }
 
 template <int RB, bool HALF, bool ONECHUNK, bool EMIT_G>
@@ -179,7 +196,7 @@ int launch_mma_rb(const MmaPlan &pl, cudaStream_t stream, int pdl, const bm::Gem
     return launch_mma_inst<1, HALF, ONECHUNK, false>(pl, stream, pdl, p);
 }
 
-int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
+int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, int force_rb, cudaStream_t stream) {
     // Tokens beyond 16 go through a second launch over the remaining rows.
     for (int m0 = 0; m0 < p0.W; m0 += 16) {
         bm::GemvParams p = p0;
@@ -191,12 +208,12 @@ int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t str
         if (p0.G) p.G = p0.G + (size_t)m0 * p0.N * (p0.K / BM_GROUP);
         const bool half = p.W <= 8, one = p.K == 2048;
         MmaPlan pl;
-        if (!make_mma_plan(p.N, p.K, half, sms, &pl)) return BM_EINVAL;
+        if (!make_mma_plan(p.N, p.K, half, sms, force_rb, &pl)) return BM_EINVAL;
         if (p.G != nullptr) {                         // the group-sum build exists for RB = 1 only
             pl.rb = 1;
             pl.grid = p.N / 8 < pl.grid ? p.N / 8 : pl.grid;
-            pl.stages = 2;
-            pl.smem = bm::mma_smem_layout(p.K, 1, 2, half).total;
+            pl.stages = 1;
+            pl.smem = bm::mma_smem_layout(p.K, 1, 1, half).total;
         }
         p.stages = pl.stages;
         const int use_pdl = (m0 == 0) ? pdl : 0;
@@ -260,9 +277,11 @@ int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The MMA consumer needs an even number of groups (K % 256 == 0); every model shape
     // has it.  Odd group counts go to the lanes-across-K consumer.
+    const int force_rb = (path >> 8) & 0xff;          // tuning aid: BM_PATH_MMA | (rows_per_tile/8 << 8)
+    path &= 0xff;
     if (path == BM_PATH_AUTO) path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
-    if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, st) : BM_EINVAL;
+    if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, force_rb, st) : BM_EINVAL;
     return BM_EINVAL;
 }
 

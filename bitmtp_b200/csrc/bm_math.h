@@ -128,9 +128,12 @@ BM_HD int bm_quant_i8(float x, float s) {
     return (int)r;
 }
 
-// Activation multiplier s = 127 / max(absmax, 1e-5) (model.py:635).
+// Activation multiplier s = 127 / max(absmax, 1e-5) (model.py:635).  torch evaluates
+// `scalar / tensor` as reciprocal(tensor) * scalar, i.e. with two roundings; the fixture
+// recorded from the reference pins that form (a single correctly rounded division differs
+// in the last bit for some absmax values and moves INT8 codes that sit on a .5 boundary).
 BM_HD float bm_act_scale(float absmax) {
-    return 127.0f / (absmax < 1e-5f ? 1e-5f : absmax);
+    return (1.0f / (absmax < 1e-5f ? 1e-5f : absmax)) * 127.0f;
 }
 
 // SiLU on a bf16 value, result rounded to bf16, as F.silu does for a bf16

@@ -103,8 +103,13 @@ __device__ __forceinline__ void gemv_issue_tile(const GemvParams &p, unsigned ch
     const uint32_t row_bytes = (uint32_t)(p.K / 4);
     if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes + (uint32_t)(rows * ng * 2));
     __syncwarp();
+#ifdef BM_EXP_DENSE_TILE_COPY
+    // Timing experiment only (wrong results): the whole tile as one copy, no row padding.
+    if (lane == 0) bulk_g2s(stage, p.B + (size_t)n0 * row_bytes, (uint32_t)rows * row_bytes, bar);
+#else
     for (int r = lane; r < rows; r += 32)
         bulk_g2s(stage + r * L.row_stride, p.B + (size_t)(n0 + r) * row_bytes, row_bytes, bar);
+#endif
     if (lane == 0)
         bulk_g2s(stage + L.scale_off_in_stage, p.ws + (size_t)n0 * ng, (uint32_t)(rows * ng * 2),
                  bar);
@@ -117,10 +122,10 @@ __device__ __forceinline__ void gemv_stage_activations(const GemvParams &p, unsi
                                                        const GemvSmem &L, int wrows) {
     const int ng = p.K / BM_GROUP;
     int *asum = reinterpret_cast<int *>(smem + L.asum_off);
-    for (int i = threadIdx.x; i < wrows * ng; i += kGemvThreads) asum[i] = 0;
+    for (int i = threadIdx.x; i < wrows * ng; i += blockDim.x) asum[i] = 0;
     __syncthreads();
     const int units = p.K / 16;
-    for (int i = threadIdx.x; i < wrows * units; i += kGemvThreads) {
+    for (int i = threadIdx.x; i < wrows * units; i += blockDim.x) {
         const int m = i / units, j = i - m * units;
         uint4 x = make_uint4(0u, 0u, 0u, 0u);
         if (m < p.W) x = *reinterpret_cast<const uint4 *>(p.A + (size_t)m * p.K + 16 * j);
@@ -351,8 +356,9 @@ __host__ __device__ inline MmaSmem mma_smem_layout(int K, int RB, int stages, bo
 __device__ __forceinline__ void mma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1, int c0, int c1,
                                          int c2, int c3) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    // Not volatile: the four MMAs of a group form a dependent chain, and the compiler must be
+    // free to interleave the chains of different groups and row-blocks.
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%11,%12,%13};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));

@@ -11,6 +11,7 @@ libbitmtp_b200.so; PyTorch only owns the memory and the stream.
 from __future__ import annotations
 
 import ctypes
+import math
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -91,3 +92,437 @@ def packed_int8_linear(a_int8, b_packed, s, ws, *, validate_registry: bool = Fal
     if b_packed.shape[-1] * 4 == K:
         return t2g128_int8xint2_linear(a_int8, b_packed, s, ws, validate_registry=validate_registry)
     raise ValueError(f"unknown packed weight layout A.K={K}, B.shape={tuple(b_packed.shape)}")
+
+
+# ===========================================================================
+# Modules (same tree and state-dict keys as the reference, model.py:274-304, 607-656,
+# 689-760, 1015-1076, 1143-1166)
+# ===========================================================================
+@dataclass
+class ModelArgs:
+    """Bonsai-1.7B (Qwen3) defaults, same fields as the reference (model.py:689-713)."""
+    dim: int = 2048
+    n_layers: int = 28
+    n_heads: int = 16
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn_dim: int = 6144
+    vocab_size: int = 151669
+    norm_eps: float = 1.0e-6
+    rope_theta: float = 1.0e6
+    rope_original_max: int = 8192
+    rope_factor: float = 4.0
+    rope_mscale: float = 1.0
+    rope_mscale_all_dim: float = 0.0
+    rope_beta_fast: float = 32.0
+    rope_beta_slow: float = 1.0
+    tie_word_embeddings: bool = True
+    use_kernel: bool = True
+    kernel_kind: str = "t2g128"
+    block_size: int = 8
+    causal_attn: bool = True
+    mask_token_id: int = 151654
+
+
+class RMSNorm(nn.Module):
+    """RMSNorm weight holder; `forward` runs the native kernel (bf16 rows in, bf16 rows out)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        out = ops.rmsnorm_fused(x2, self.weight.data, self.eps, want_q=False, want_n=True)
+        return out["n"].reshape(x.shape)
+
+    def forward_and_quant(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        out = ops.rmsnorm_fused(x.contiguous(), self.weight.data, self.eps)
+        return out["q"], out["s"]
+
+
+class T2LinearKernel(nn.Module):
+    """Q2_0_g128 W2A8 linear: `weight` int8 [out, in/4] (four natural-order ternary codes
+    per byte, 1/2/3 = -1/0/+1), `weight_scale` bf16 [out, in/128] (model.py:607-630)."""
+
+    MAX_ROWS = 16
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False):
+        super().__init__()
+        assert bias is False
+        assert in_features % 128 == 0
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = nn.Parameter(torch.zeros(out_features, in_features // 4, dtype=torch.int8),
+                                   requires_grad=False)
+        self.register_buffer("weight_scale",
+                             torch.zeros(out_features, in_features // 128, dtype=torch.bfloat16),
+                             persistent=True)
+
+    def quant_input(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Per-token absmax INT8 quantisation (model.py:632-636)."""
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        q, s = ops.quant_rows(x2)
+        return q.reshape(x.shape), s.reshape(*x.shape[:-1], 1)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Any number of rows: the native kernel takes up to 32 at a time, so long inputs
+        (prefill) go through it in slabs.  The reference falls back to a dense bf16 GEMM
+        on unpacked weights for unregistered widths (model.py:650-656); the integer path
+        gives the same quantised product without the bf16 roundings and without the dense
+        copy of the weights."""
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        q, s = ops.quant_rows(x2)
+        out = torch.empty((x2.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        for r0 in range(0, x2.shape[0], self.MAX_ROWS):
+            r1 = min(r0 + self.MAX_ROWS, x2.shape[0])
+            ops.t2_gemv(q[r0:r1], self.weight.data, s[r0:r1], self.weight_scale, out=out[r0:r1],
+                        ldc=self.out_features)
+        return out.reshape(*x.shape[:-1], self.out_features)
+
+
+def _yarn_inv_freq(head_dim: int, base: float, factor: float, original_max: int,
+                   beta_fast: float = 32.0, beta_slow: float = 1.0) -> torch.Tensor:
+    """YaRN inverse frequencies, computed on the CPU in the reference's operation order
+    (model.py:342-368) so that the bf16 tables are the same bits everywhere."""
+    dim = head_dim
+    pos_freqs = base ** (torch.arange(0, dim, 2).float() / dim)
+    extrap = 1.0 / pos_freqs
+    interp = 1.0 / (factor * pos_freqs)
+
+    def correction(num_rotations: float) -> float:
+        return (dim * math.log(original_max / (num_rotations * 2 * math.pi))) / (2 * math.log(base))
+
+    low = max(math.floor(correction(beta_fast)), 0)
+    high = min(math.ceil(correction(beta_slow)), dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = torch.clamp((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low), 0.0, 1.0)
+    keep = 1.0 - ramp
+    return interp * (1.0 - keep) + extrap * keep
+
+
+def _yarn_attention_factor(scale: float, mscale: float = 1.0, mscale_all_dim: float = 0.0) -> float:
+    """cos/sin post-scaling (model.py:371-379)."""
+    if scale <= 1.0:
+        return 1.0
+
+    def g(s, m):
+        return 0.1 * m * math.log(s) + 1.0
+    if mscale and mscale_all_dim:
+        return g(scale, mscale) / g(scale, mscale_all_dim)
+    return g(scale, mscale)
+
+
+class Attention(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.args = args
+        self.head_dim = args.head_dim
+        self.n_local_heads = args.n_heads
+        self.n_local_kv_heads = args.n_kv_heads
+        self.heads_per_group = args.n_heads // args.n_kv_heads
+        self.q_dim = args.n_heads * args.head_dim
+        self.k_dim = args.n_kv_heads * args.head_dim
+        self.v_dim = self.k_dim
+        self.q_proj = T2LinearKernel(args.dim, self.q_dim)
+        self.k_proj = T2LinearKernel(args.dim, self.k_dim)
+        self.v_proj = T2LinearKernel(args.dim, self.v_dim)
+        self.o_proj = T2LinearKernel(self.q_dim, args.dim)
+        self.q_norm = RMSNorm(self.head_dim, eps=args.norm_eps)
+        self.k_norm = RMSNorm(self.head_dim, eps=args.norm_eps)
+        self.register_buffer("inv_freq", _yarn_inv_freq(
+            self.head_dim, args.rope_theta, args.rope_factor, args.rope_original_max,
+            args.rope_beta_fast, args.rope_beta_slow), persistent=False)
+        self.rope_mscale = _yarn_attention_factor(args.rope_factor, args.rope_mscale,
+                                                  args.rope_mscale_all_dim)
+
+    def prepare_merged_weights(self, max_positions: int = 256, tables=None) -> None:
+        """Concatenate q|k|v rows and scales; build the bf16 RoPE tables (model.py:931-956).
+        The tables are computed on the CPU and copied over, and shared between layers."""
+        dev = self.q_proj.weight.device
+        self.wqkv_weight = torch.cat([self.q_proj.weight.data, self.k_proj.weight.data,
+                                      self.v_proj.weight.data], dim=0).contiguous()
+        self.wqkv_scale = torch.cat([self.q_proj.weight_scale.data, self.k_proj.weight_scale.data,
+                                     self.v_proj.weight_scale.data], dim=0).contiguous()
+        self._qkv_split = [self.q_dim, self.k_dim, self.v_dim]
+        if tables is None:
+            tables = rope_tables(self.inv_freq.detach().float().cpu(), self.rope_mscale, max_positions)
+            tables = (tables[0].to(dev), tables[1].to(dev))
+        self.rope_cos, self.rope_sin = tables
+        self._attn_scale = 1.0 / math.sqrt(self.head_dim)
+
+
+def rope_tables(inv_freq_cpu: torch.Tensor, mscale: float, max_positions: int):
+    """bf16 cos/sin tables [max_positions, head_dim] (model.py:950-955), on the CPU.  The
+    inverse frequencies are rounded to bf16 first: the reference casts the whole module,
+    this buffer included, to bf16 when it builds the model (generate.py:50)."""
+    inv_freq_cpu = inv_freq_cpu.to(torch.bfloat16).float()
+    pos = torch.arange(max_positions, dtype=torch.float32)
+    freqs = torch.outer(pos, inv_freq_cpu)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return (emb.cos() * mscale).to(torch.bfloat16), (emb.sin() * mscale).to(torch.bfloat16)
+
+
+class FeedForward(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.gate_proj = T2LinearKernel(args.dim, args.ffn_dim)
+        self.up_proj = T2LinearKernel(args.dim, args.ffn_dim)
+        self.down_proj = T2LinearKernel(args.ffn_dim, args.dim)
+
+    def prepare_merged_weights(self) -> None:
+        """gate|up by output row (model.py:1042-1051)."""
+        self.w_gu = torch.cat([self.gate_proj.weight.data, self.up_proj.weight.data], dim=0).contiguous()
+        self.w_gu_scale = torch.cat([self.gate_proj.weight_scale.data,
+                                     self.up_proj.weight_scale.data], dim=0).contiguous()
+        self._gu_split = [self.gate_proj.out_features, self.up_proj.out_features]
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.attention = Attention(args)
+        self.feed_forward = FeedForward(args)
+        self.input_layernorm = RMSNorm(args.dim, eps=args.norm_eps)
+        self.post_attention_layernorm = RMSNorm(args.dim, eps=args.norm_eps)
+
+
+# ===========================================================================
+# Transformer: the captured forward
+# ===========================================================================
+class StepWorkspace:
+    """Every intermediate of one replay width M, allocated once.  A captured graph bakes
+    these addresses in; graphs of the same width share one workspace because replays on
+    a stream never overlap."""
+
+    def __init__(self, args: ModelArgs, M: int, n_pad: int, device):
+        bf, i8, f32 = torch.bfloat16, torch.int8, torch.float32
+        q_dim = args.n_heads * args.head_dim
+        qkv = q_dim + 2 * args.n_kv_heads * args.head_dim
+
+        def buf(shape, dtype):
+            return torch.empty(shape, dtype=dtype, device=device)
+
+        self.M = M
+        self.h = buf((M, args.dim), bf)
+        self.q = buf((M, args.dim), i8)
+        self.s = buf((M, 1), f32)
+        self.xqkv = buf((M, qkv), bf)
+        self.qrot = buf((M, args.n_heads, args.head_dim), bf)
+        self.att = buf((M, q_dim), bf)
+        self.att_q = buf((M, q_dim), i8)
+        self.att_s = buf((M, 1), f32)
+        self.attn_out = buf((M, args.dim), bf)
+        self.gu = buf((M, 2 * args.ffn_dim), bf)
+        self.iq = buf((M, args.ffn_dim), i8)
+        self.is_ = buf((M, 1), f32)
+        self.ffn_out = buf((M, args.dim), bf)
+        self.hq = buf((M, args.dim), i8)
+        self.hs = buf((M, 1), f32)
+        self.n_pad = n_pad
+
+
+class Transformer(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.args = args
+        self.embed_tokens = nn.Embedding(args.vocab_size, args.dim)
+        self.layers = nn.ModuleList([TransformerBlock(args) for _ in range(args.n_layers)])
+        self.norm = RMSNorm(args.dim, eps=args.norm_eps)
+        if not args.tie_word_embeddings:
+            raise NotImplementedError("only tied-embedding T2 checkpoints are in scope")
+        self._lm_head_weight_ref = None
+        self._lm_head_t2_w = None
+        self._workspaces = {}
+        self.use_pdl = False
+
+    def tie_weights(self) -> None:
+        # plain attribute, not a registered parameter: the state dict keeps the reference's keys
+        object.__setattr__(self, "_lm_head_weight_ref", self.embed_tokens.weight)
+
+    def _lm_head_weight(self) -> torch.Tensor:
+        w = self._lm_head_weight_ref
+        return self.embed_tokens.weight if w is None else w
+
+    @torch.no_grad()
+    def prepare_t2_lm_head(self) -> None:
+        """Pack the tied head on its exact Q2_0_g128 grid (model.py:1223-1243).  The
+        reference pads to its one registered head size (151936 rows); here the row count is
+        padded to a multiple of 32, which is that same number for the real vocabularies."""
+        if self._lm_head_t2_w is not None:
+            return
+        from .synthetic import pack_t2_g128
+        W = self._lm_head_weight().data.to(torch.bfloat16)
+        vocab, dim = W.shape
+        n_pad = (vocab + 31) // 32 * 32
+        dev = W.device
+        # packed in slabs on the CPU: the converter's packer is CPU code and the dense
+        # fp32 view of the whole table would not be worth its 1.2 GB on the device
+        Wc = W.cpu()
+        packed = torch.zeros(n_pad, dim // 4, dtype=torch.int8)
+        scale = torch.zeros(n_pad, dim // 128, dtype=torch.bfloat16)
+        for r0 in range(0, vocab, 16384):
+            r1 = min(r0 + 16384, vocab)
+            p, s = pack_t2_g128(Wc[r0:r1].contiguous())
+            packed[r0:r1], scale[r0:r1] = p, s
+        # pad rows keep code bytes 0 and scale 0: their logits are 0 * anything = 0 and are
+        # sliced off before any argmax
+        self._lm_head_t2_w = packed.to(dev)
+        self._lm_head_t2_scale = scale.to(dev)
+        self._lm_head_t2_vocab = vocab
+        self._lm_head_n_pad = n_pad
+
+    def prepare_merged_weights(self, max_positions: int = 256) -> None:
+        """model.py:1444-1447; the RoPE tables are built once and shared by all layers."""
+        dev = self.embed_tokens.weight.device
+        a0 = self.layers[0].attention
+        cos, sin = rope_tables(a0.inv_freq.detach().float().cpu(), a0.rope_mscale, max_positions)
+        tables = (cos.to(dev), sin.to(dev))
+        for layer in self.layers:
+            layer.attention.prepare_merged_weights(max_positions, tables=tables)
+            layer.feed_forward.prepare_merged_weights()
+        self.max_positions = max_positions
+
+    def workspace(self, M: int) -> StepWorkspace:
+        ws = self._workspaces.get(M)
+        if ws is None:
+            self.prepare_t2_lm_head()
+            ws = StepWorkspace(self.args, M, self._lm_head_n_pad, self.embed_tokens.weight.device)
+            self._workspaces[M] = ws
+        return ws
+
+    @torch.no_grad()
+    def forward_sdlm_decode_graph_kernel(
+        self,
+        token_values: torch.Tensor,      # int64 [M]
+        positions: torch.Tensor,         # int64 [M]
+        kv_full: List[SDLMLayerCache],   # per layer (k, v) views [1, n_kv, sigma+M, head_dim]
+        block_size: int,                 # M (replay width)
+        attn_mask: torch.Tensor,         # int32 [4] step state (see below)
+        logits_start: int = 0,
+        logits_end: int = -1,
+        lm_head_precision: str = "t2",
+        *,
+        attn_scratch: Optional[torch.Tensor] = None,
+        logits_buf: Optional[torch.Tensor] = None,
+    ) -> torch.Tensor:
+        """The replay body (reference: model.py:1363-1404, 1119-1137, 958-1009, 1053-1064).
+
+        Same arguments as the reference with one change of meaning: `attn_mask` is not an
+        additive [1,1,M,sigma+M] tensor but the 16-byte device record
+        {cache_len, n_pend, role, P} written by `ops.set_step_state`; the attention kernel
+        derives the same visibility from it.  K and V rows of this replay are written in
+        place at rows [sigma, sigma+M) of every layer's views.  Returns fp32 logits
+        [logits_end - logits_start, vocab] holding bf16-rounded values, as the reference's
+        `.float()` of a bf16 head output does.
+        """
+        if lm_head_precision not in ("t2",):
+            raise RuntimeError(f"unsupported lm_head precision: {lm_head_precision!r}")
+        a = self.args
+        M = int(block_size)
+        if logits_end == -1:
+            logits_end = M
+        rows = logits_end - logits_start
+        W = self.workspace(M)
+        pdl = self.use_pdl
+        k0 = kv_full[0][0]
+        kv_rows = k0.stride(-3) // a.head_dim
+        sigma = k0.shape[-2] - M
+        dev = token_values.device
+        if attn_scratch is None:
+            attn_scratch = ops.attention_scratch(M, a.n_heads, sigma, dev)
+        if logits_buf is None:
+            logits_buf = torch.empty((rows, W.n_pad), dtype=torch.float32, device=dev)
+        eps = a.norm_eps
+        L0 = self.layers[0]
+        ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
+                          gather=token_values, pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
+        for i, layer in enumerate(self.layers):
+            at, ff = layer.attention, layer.feed_forward
+            if i > 0:
+                ops.rmsnorm_fused(W.ffn_out, layer.input_layernorm.weight.data, eps, M=M, res=W.h,
+                                  pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
+            ops.t2_gemv(W.q, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv, ldc=W.xqkv.shape[1], pdl=pdl)
+            k_l, v_l = kv_full[i]
+            ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
+                                     at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                     _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                     pdl=pdl, q_out=W.qrot)
+            ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                 attn_mask, attn_scratch, pdl=pdl, out=(W.att, W.att_q, W.att_s))
+            ops.t2_gemv(W.att_q, at.o_proj.weight.data, W.att_s, at.o_proj.weight_scale,
+                        out=W.attn_out, ldc=a.dim, pdl=pdl)
+            ops.rmsnorm_fused(W.h, layer.post_attention_layernorm.weight.data, eps, M=M,
+                              res=W.attn_out, pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
+            ops.t2_gemv(W.q, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu, ldc=W.gu.shape[1], pdl=pdl)
+            ops.silu_mul_quant(W.gu, pdl=pdl, out=(W.iq, W.is_))
+            ops.t2_gemv(W.iq, ff.down_proj.weight.data, W.is_, ff.down_proj.weight_scale,
+                        out=W.ffn_out, ldc=a.dim, pdl=pdl)
+        # h + ffn_out, final norm of the logit rows, INT8 quantisation for the packed head
+        ops.rmsnorm_fused(W.h, self.norm.weight.data, eps, M=rows, res=W.ffn_out, row0=logits_start,
+                          pdl=pdl, out={"q": W.hq, "s": W.hs})
+        ops.t2_gemv(W.hq[:rows], self._lm_head_t2_w, W.hs[:rows], self._lm_head_t2_scale,
+                    out_kind=native.OUT_F32_OF_BF16, out=logits_buf, ldc=W.n_pad, pdl=pdl)
+        return logits_buf[:, : self._lm_head_t2_vocab]
+
+    @torch.no_grad()
+    def forward_sdlm_prefill(self, token_values: torch.Tensor, cache: List[SDLMLayerCache],
+                             positions: Optional[torch.Tensor] = None, block_size: int = 1,
+                             fast: bool = False, causal_attn: bool = True) -> torch.Tensor:
+        """Variable-length causal prompt forward (reference: model.py:1306-1340).
+
+        Runs the packed integer path in AR-causal slabs of PREFILL_CHUNK rows: each slab
+        writes its K/V rows in place (sigma == cache_len == slab start) and attends to the
+        rows before it.  The reference unpacks every layer to dense bf16 and calls cuBLAS on
+        fake-quantised activations, the same quantised product with bf16 roundings between
+        the steps.  `cache[i]` is replaced by (k, v) views [1, n_kv, seq, head_dim]; returns
+        fp32 logits [seq, vocab]."""
+        if block_size > 1:
+            raise NotImplementedError("block-diffusion prefill masks are outside the decode path")
+        a = self.args
+        seq = int(token_values.shape[0])
+        dev = token_values.device
+        if positions is None:
+            positions = torch.arange(seq, device=dev, dtype=torch.int64)
+        positions = positions.to(torch.int64).contiguous()
+        kv = torch.zeros(2, a.n_layers, 1, a.n_kv_heads, seq + PREFILL_CHUNK, a.head_dim,
+                         dtype=torch.bfloat16, device=dev)
+        state = ops.new_step_state(dev)
+        scratch = ops.attention_scratch(PREFILL_CHUNK, a.n_heads, seq, dev)
+        self.prepare_t2_lm_head()
+        logits = torch.empty((seq, self._lm_head_n_pad), dtype=torch.float32, device=dev)
+        for c0 in range(0, seq, PREFILL_CHUNK):
+            n = min(PREFILL_CHUNK, seq - c0)
+            ops.set_step_state(state, c0, 0, native.ROLE_AR, n - a.block_size)
+            kv_full = [(kv[0, i][:, :, : c0 + n, :], kv[1, i][:, :, : c0 + n, :])
+                       for i in range(a.n_layers)]
+            self.forward_sdlm_decode_graph_kernel(
+                token_values[c0:c0 + n].contiguous(), positions[c0:c0 + n].contiguous(), kv_full, n,
+                state, 0, n, "t2", attn_scratch=scratch, logits_buf=logits[c0:c0 + n])
+        for i in range(a.n_layers):
+            cache[i] = (kv[0, i][:, :, :seq, :], kv[1, i][:, :, :seq, :])
+        return logits[:, : self._lm_head_t2_vocab]
+
+
+PREFILL_CHUNK = 16
+
+
+class _LayerView:
+    """Adapter handing ops the base pointer of a [1, n_kv, rows, hd] view together with the
+    row count of the buffer it was sliced from."""
+
+    def __init__(self, view: torch.Tensor, kv_rows: int):
+        self._v = view
+        self.shape = (view.shape[-3], kv_rows, view.shape[-1])
+
+    def data_ptr(self):
+        return self._v.data_ptr()
+
+
+def make_sdlm_cache(args: ModelArgs, device, dtype: torch.dtype = torch.bfloat16) -> List[SDLMLayerCache]:
+    """Empty (length-0) per-layer cache list for the prefill path (model.py:1453-1469)."""
+    return [(torch.zeros(1, args.n_kv_heads, 0, args.head_dim, dtype=dtype, device=device),
+             torch.zeros(1, args.n_kv_heads, 0, args.head_dim, dtype=dtype, device=device))
+            for _ in range(args.n_layers)]

@@ -106,12 +106,15 @@ def rmsnorm_fused(x: torch.Tensor, w: torch.Tensor, eps: float, *, M: Optional[i
     return out
 
 
-def silu_mul_quant(gu: torch.Tensor, *, want_inner: bool = False, pdl: bool = False):
+def silu_mul_quant(gu: torch.Tensor, *, want_inner: bool = False, pdl: bool = False, out=None):
     _require_cuda(gu)
     M, F2 = gu.shape
     F = F2 // 2
-    q = torch.empty((M, F), dtype=torch.int8, device=gu.device)
-    s = torch.empty((M, 1), dtype=torch.float32, device=gu.device)
+    if out is not None:
+        q, s = out
+    else:
+        q = torch.empty((M, F), dtype=torch.int8, device=gu.device)
+        s = torch.empty((M, 1), dtype=torch.float32, device=gu.device)
     inner = torch.empty((M, F), dtype=torch.bfloat16, device=gu.device) if want_inner else None
     check(native.lib().bm_silu_mul_quant(_ptr(gu), M, F, _ptr(q), _ptr(s), _ptr(inner), int(pdl),
                                          _stream(gu.device)), "bm_silu_mul_quant")

@@ -113,3 +113,51 @@ def write_checkpoint(out_dir: str, cfg: Dict, seed: int = 0) -> str:
 def random_prompt(length: int, vocab: int, seed: int = 0) -> torch.Tensor:
     gen = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (1, length), generator=gen, dtype=torch.int64)
+
+
+def device_ternary(n: int, k: int, gen: torch.Generator, device):
+    """Random packed ternary weight generated on `device`: (packed int8 [n,k/4], scale bf16
+    [n,k/128]).  Codes are uniform over {1,2,3} (= -1,0,+1), scales U[0.01,0.05].  Used by
+    the benchmarks, where only the distribution matters; parity tests use the CPU-seeded
+    generators above."""
+    codes = torch.randint(1, 4, (n, k // 4, 4), generator=gen, device=device, dtype=torch.uint8)
+    packed = codes[..., 0] | (codes[..., 1] << 2) | (codes[..., 2] << 4) | (codes[..., 3] << 6)
+    scale = (torch.rand(n, k // GROUP, generator=gen, device=device) * 0.04 + 0.01).to(torch.bfloat16)
+    return packed.view(torch.int8).contiguous(), scale.contiguous()
+
+
+def device_state(cfg: Dict, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init packed state dict built directly on `device` (seconds instead of a
+    minute for the 1.7B geometry).  Also returns the packed tied head under the private
+    keys `_head.weight` / `_head.weight_scale`, so that the loader need not re-pack the
+    embedding on the CPU."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    dim, ffn = cfg["dim"], cfg["ffn_dim"]
+    qd, kd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+    sd: Dict[str, torch.Tensor] = {}
+    vocab = cfg["vocab_size"]
+    hp, hs = device_ternary(vocab, dim, gen, device)
+    emb = torch.empty(vocab, dim, dtype=torch.bfloat16, device=device)
+    for r0 in range(0, vocab, 16384):
+        r1 = min(r0 + 16384, vocab)
+        p = hp[r0:r1].view(torch.uint8)
+        q = torch.stack([(p >> (2 * i)) & 3 for i in range(4)], dim=-1).to(torch.int8) - 2
+        w = q.view(r1 - r0, dim // GROUP, GROUP).float() * hs[r0:r1].float().unsqueeze(-1)
+        emb[r0:r1] = w.view(r1 - r0, dim).to(torch.bfloat16)
+    sd["embed_tokens.weight"] = emb
+    sd["_head.weight"], sd["_head.weight_scale"] = hp, hs
+    one = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    sd["norm.weight"] = one(dim)
+    for i in range(cfg["n_layers"]):
+        p = f"layers.{i}."
+        sd[p + "input_layernorm.weight"] = one(dim)
+        sd[p + "post_attention_layernorm.weight"] = one(dim)
+        sd[p + "attention.q_norm.weight"] = one(cfg["head_dim"])
+        sd[p + "attention.k_norm.weight"] = one(cfg["head_dim"])
+        for name, (n, k) in (("attention.q_proj", (qd, dim)), ("attention.k_proj", (kd, dim)),
+                             ("attention.v_proj", (kd, dim)), ("attention.o_proj", (dim, qd)),
+                             ("feed_forward.gate_proj", (ffn, dim)),
+                             ("feed_forward.up_proj", (ffn, dim)),
+                             ("feed_forward.down_proj", (dim, ffn))):
+            sd[p + name + ".weight"], sd[p + name + ".weight_scale"] = device_ternary(n, k, gen, device)
+    return sd

@@ -61,7 +61,8 @@ void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, 
  *   out_kind  BM_OUT_*
  *   path      BM_PATH_*  (AUTO: the MMA consumer whenever K % 256 == 0, which
  *             covers every model shape; the lanes-across-K dp4a consumer otherwise.
- *             BM_PATH_MMA with K % 256 != 0 is BM_EINVAL)
+ *             BM_PATH_MMA with K % 256 != 0 is BM_EINVAL).  Tuning aid: BM_PATH_MMA |
+ *             (rb << 8) with rb in {1, 2, 4} forces tiles of 8*rb output rows)
  *   C         16-byte aligned, ldc a multiple of 4
  *   G_out     int32 [W, N, K/128] exact group sums, or NULL
  *   pdl       1 = launch with programmatic stream serialisation: the kernel

@@ -393,6 +393,10 @@ def rope_tables(cfg: dict, max_positions: int) -> Tuple[np.ndarray, np.ndarray]:
     ramp = torch.clamp((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low), 0.0, 1.0)
     extrap_factor = 1.0 - ramp
     inv_freq = inv_interp * (1.0 - extrap_factor) + inv_extrap * extrap_factor
+    # build_model casts the whole module, buffers included, to bf16
+    # (src/bonsai_sft/gpu/generate.py:50), so the tables are built from bf16-rounded
+    # inverse frequencies
+    inv_freq = inv_freq.to(torch.bfloat16).float()
     mscale = 1.0 if factor <= 1.0 else 0.1 * 1.0 * math.log(factor) + 1.0
     pos = torch.arange(max_positions, dtype=torch.float32)
     freqs = torch.outer(pos, inv_freq.float())

@@ -1,0 +1,103 @@
+"""End-to-end GPU parity: the captured forward against the CPU oracle forward (logits and
+appended KV rows, bit for bit) and the decode loops over real CUDA graphs against the token
+streams recorded from the reference's loops."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from bitmtp_b200 import fast_generate as FG, generate, native, ops, synthetic
+from bitmtp_b200.fast_runtime import GraphAtlas
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "streams.json")
+RECORDS = json.load(open(GOLDEN))
+_MODELS = {}
+
+
+def _model(cfg, seed, max_positions):
+    key = (json.dumps(cfg, sort_keys=True), seed)
+    if key not in _MODELS:
+        state = synthetic.make_state(cfg, seed=seed)
+        m = generate.model_from_state(generate.args_from_config(cfg), state, DEV)
+        m.prepare_merged_weights(max_positions=max_positions)
+        _MODELS[key] = (m, state)
+    return _MODELS[key]
+
+
+FORWARD_CASES = [("ar", 1, 20, 0), ("ar", 16, 0, 0), ("ar", 7, 48, 0), ("verify", 9, 30, 0),
+                 ("draft", 9, 30, 1), ("draft", 12, 25, 3), ("draft", 16, 40, 8), ("draft", 17, 33, 9),
+                 ("draft", 10, 64, 1)]
+
+
+@pytest.mark.parametrize("geom", ["tiny", "g4"])
+@pytest.mark.parametrize("role,M,cache_len,n_pend", FORWARD_CASES)
+def test_forward_matches_oracle(oracle, geom, role, M, cache_len, n_pend):
+    geometry = synthetic.TINY if geom == "tiny" else dict(synthetic.TINY, n_heads=4, n_kv_heads=1,
+                                                          dim=512, ffn_dim=768)
+    cfg = synthetic.make_config(geometry, block_size=8)
+    sigma, m_max = 64, 17
+    model, state = _model(cfg, 3, sigma + m_max)
+    om = oracle.OracleModel(cfg, state, max_positions=sigma + m_max)
+    D, L, Hkv = 8, cfg["n_layers"], cfg["n_kv_heads"]
+    gen = torch.Generator().manual_seed(M * 100 + cache_len)
+    kv = (torch.randn(2, L, 1, Hkv, sigma + m_max, 128, generator=gen) * 0.5).to(torch.bfloat16)
+    tokens = torch.randint(0, cfg["vocab_size"], (M,), generator=gen)
+    positions = torch.arange(max(cache_len - 1, 0), max(cache_len - 1, 0) + M)
+    rid = oracle.ROLE_IDS[role]
+    ls, le = {"ar": (0, M), "verify": (0, min(D + 1, M)), "draft": (M - D, M)}[role]
+    kv_np = oracle.torch_to_u16(kv).copy()
+    want = om.forward(tokens.numpy(), positions.numpy(), kv_np, sigma, rid, cache_len, n_pend, ls, le)
+
+    kvd = kv.to(DEV)
+    state_t = ops.new_step_state(DEV)
+    ops.set_step_state(state_t, cache_len, min(n_pend, max(M - D, 0)), rid, M - D)
+    kv_full = [(kvd[0, i][:, :, : sigma + M, :], kvd[1, i][:, :, : sigma + M, :]) for i in range(L)]
+    logits = model.forward_sdlm_decode_graph_kernel(tokens.to(DEV), positions.to(DEV), kv_full, M,
+                                                    state_t, ls, le, "t2")
+    torch.cuda.synchronize()
+    assert native.lib().bm_device_error() == 0
+    assert np.array_equal(logits.cpu().numpy().view(np.uint32), want.view(np.uint32)), "logits differ"
+    assert np.array_equal(oracle.torch_to_u16(kvd.cpu()), kv_np), "KV buffer differs"
+
+
+def _forced(D):
+    chain, accept = FG._fused_draft_chain, FG._fused_verify_accept
+
+    def forced_chain(logits, threshold):
+        idx, n = chain(logits, threshold)
+        return idx, torch.full_like(n, D)
+
+    def forced_accept(draft, verify, Dd):
+        return torch.full_like(accept(draft, verify, Dd), Dd)
+
+    return forced_chain, forced_accept
+
+
+@pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
+                                                         f"{'forced' if r['forced'] else 'free'}")
+def test_token_streams_match_reference_loops(rec, monkeypatch):
+    cfg = rec["cfg"]
+    model, _ = _model(cfg, rec["state_seed"], max(rec["ladder"]) + max(rec["m_set"]))
+    roles = ("ar",) if rec["mode"] == "ar" else ("ar", "draft", "verify")
+    atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=tuple(rec["ladder"]),
+                       m_set=tuple(rec["m_set"]), roles=roles, capture_verbose=False)
+    if rec["forced"]:
+        fc, fa = _forced(cfg["block_size"])
+        monkeypatch.setattr(FG, "_fused_draft_chain", fc)
+        monkeypatch.setattr(FG, "_fused_verify_accept", fa)
+    prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
+    fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
+          "hybrid": FG.fast_hybrid_generate}[rec["mode"]]
+    out, stats = fn(model, atlas, prompt, max_gen_len=rec["new_tokens"], eos_ids=())
+    assert native.lib().bm_device_error() == 0
+    assert out.cpu().tolist() == rec["tokens"]
+    for key, want in rec["stats"].items():
+        assert stats[key] == pytest.approx(want), key
+    # graphs of one segment share one KV buffer (the observable the reference's adapter checks)
+    sig = atlas.segment_ladder[0]
+    ptrs = {g.kv_full[0][0].data_ptr() for (M, s, r), g in atlas.graphs.items() if s == sig}
+    assert ptrs == {atlas.kv_buffers[sig].data_ptr()}

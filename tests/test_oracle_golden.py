@@ -1,0 +1,164 @@
+"""The CPU oracle against fixtures recorded from the reference's own Python code
+(tests/golden/make_golden.py).  Integer and index results must be equal; floating-point
+results are compared at the tolerance stated beside each check, because the reference
+leaves fp32 summation order to torch's CPU kernels and the oracle fixes its own."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+from bitmtp_b200 import synthetic
+from oracle import oracle as O
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+OPS = np.load(os.path.join(G, "ops.npz"))
+MASKS = np.load(os.path.join(G, "masks.npz"))
+KATS = json.load(open(os.path.join(G, "kats.json")))
+
+
+def f32(u16):
+    return O.bf16_to_f32(u16)
+
+
+def bf16_ulp_diff(a_u16, b_u16):
+    """Distance in bf16 code points between two bf16 arrays (monotonic integer mapping)."""
+    def key(u):
+        u = u.astype(np.int32)
+        return np.where(u & 0x8000, 0x8000 - (u & 0x7FFF), 0x8000 + u)
+    return np.abs(key(a_u16) - key(b_u16))
+
+
+# ------------------------------------------------------------------ GEMV + packing
+@pytest.mark.parametrize("tag", ["cfg0", "w9"])
+def test_gemv_group_sums_and_packing(tag):
+    W, N, K, seed = (int(v) for v in OPS[f"gemv_{tag}_shape"])
+    case = synthetic.gemv_case(W, N, K, seed=seed)
+    B = case["B"].numpy().view(np.uint8)
+    ws = O.torch_to_u16(case["ws"])
+    # the package's packer produces the reference packer's bytes
+    assert hashlib.sha256(np.ascontiguousarray(case["B"].numpy()).tobytes()).hexdigest() == \
+        bytes(OPS[f"gemv_{tag}_sha_packed"]).decode()
+    assert hashlib.sha256(ws.tobytes()).hexdigest() == bytes(OPS[f"gemv_{tag}_sha_scale"]).decode()
+    y32, y16, Gs = O.t2_gemv(case["A"].numpy(), B, ws, case["s"].numpy(), want_groups=True)
+    rows = OPS[f"gemv_{tag}_rows"]
+    assert np.array_equal(Gs[:, rows, :], OPS[f"gemv_{tag}_G"]), "int32 group sums must be exact"
+    y64 = OPS[f"gemv_{tag}_y64"]
+    rel = np.abs(y32[:, rows] - y64).max() / np.abs(y64).max()
+    assert rel <= 1e-6, rel                              # spec bound is 1e-3
+    # the reference's CPU fallback (bf16 activations x bf16 weights, bf16 out) agrees to bf16
+    fb = f32(OPS[f"gemv_{tag}_fallback_bf16"])
+    assert np.abs(fb - y64).max() / np.abs(y64).max() <= 2e-2
+    y2, y216, G2 = O.gemv_numpy(case["A"].numpy(), B, ws, case["s"].numpy())
+    assert np.array_equal(G2, Gs) and np.array_equal(y2.view(np.uint32), y32.view(np.uint32))
+
+
+def test_quant_rows_exact():
+    q, s = O.quant_rows(OPS["quant_x"])
+    assert np.array_equal(q, OPS["quant_q"])
+    assert np.array_equal(s.view(np.uint32), OPS["quant_s"].view(np.uint32))
+
+
+@pytest.mark.parametrize("dim", [2048, 2560])
+def test_fused_norm_helpers(dim):
+    x, res, w = OPS[f"norm{dim}_x"], OPS[f"norm{dim}_res"], OPS[f"norm{dim}_w"]
+    q, s = O.rmsnorm_quant(x, w, 1e-6)
+    # the sum of squares is ordered differently: allow the rare bf16 / INT8 boundary flip
+    assert np.abs(q.astype(int) - OPS[f"norm{dim}_q"].astype(int)).max() <= 1
+    assert (q != OPS[f"norm{dim}_q"]).mean() < 2e-3
+    assert np.allclose(s, OPS[f"norm{dim}_s"], rtol=8e-3)          # one bf16 step of the absmax
+    h2, q2, s2 = O.add_rmsnorm_quant(x, res, w, 1e-6)
+    assert np.array_equal(h2, OPS[f"norm{dim}_h2"]), "bf16 residual add is exact"
+    assert np.abs(q2.astype(int) - OPS[f"norm{dim}_q2"].astype(int)).max() <= 1
+    assert (q2 != OPS[f"norm{dim}_q2"]).mean() < 2e-3
+    n = O.rmsnorm(x, w, 1e-6)
+    d = bf16_ulp_diff(n, OPS[f"norm{dim}_n"])
+    assert d.max() <= 1 and (d != 0).mean() < 2e-3
+
+
+def test_silu_mul_quant():
+    q, s, inner = O.silu_mul_quant(OPS["silu_gu"], want_inner=True)
+    d = bf16_ulp_diff(inner, OPS["silu_inner"])
+    assert d.max() <= 1 and (d != 0).mean() < 5e-3       # own exp vs libm's, before a bf16 rounding
+    assert np.abs(q.astype(int) - OPS["silu_q"].astype(int)).max() <= 1
+    assert np.allclose(s, OPS["silu_s"], rtol=8e-3)
+
+
+def test_rope_tables_and_qknorm_rope_kvappend():
+    cfg = synthetic.make_config(synthetic.TINY)
+    cos, sin = O.rope_tables(cfg, 700)
+    assert np.array_equal(cos, OPS["rope_cos"]) and np.array_equal(sin, OPS["rope_sin"])
+    sigma = int(OPS["rope_sigma"][0])
+    k = np.zeros_like(OPS["rope_k"])
+    v = np.zeros_like(OPS["rope_v"])
+    q = O.qknorm_rope_kvappend(OPS["rope_xqkv"], OPS["rope_qw"], OPS["rope_kw"], 1e-6, cos, sin,
+                               OPS["rope_pos"], 4, 2, k, v, sigma)
+    assert np.array_equal(v, OPS["rope_v"]), "V rows are copied"
+    for got, want in ((q, OPS["rope_q"]), (k, OPS["rope_k"])):
+        d = bf16_ulp_diff(got, want)
+        assert d.max() <= 1 and (d != 0).mean() < 5e-3
+
+
+@pytest.mark.parametrize("ci", [int(c) for c in OPS["attn_cases"]])
+def test_attention_against_reference_paths(ci):
+    role, M, sigma, cache_len, n_pend, D, H, Hkv = (int(v) for v in OPS[f"attn{ci}_meta"])
+    out = O.attention(OPS[f"attn{ci}_q"], OPS[f"attn{ci}_k"], OPS[f"attn{ci}_v"], sigma, cache_len,
+                      n_pend, M - D, role)
+    got = f32(out)
+    want32 = OPS[f"attn{ci}_out32"]
+    scale = np.abs(want32).max()
+    assert np.abs(got - want32).max() <= 2 ** -8 * scale           # one bf16 rounding of the output
+    # and against the reference's bf16 matmul/softmax/matmul path, which rounds four times
+    assert np.abs(got - f32(OPS[f"attn{ci}_out"])).max() <= 3e-2 * scale
+
+
+def test_masks_equal_reference_builders():
+    idx = MASKS["index"]
+    assert len(idx) > 250
+    for i, (role, D, M, sigma, cache_len, n_pend) in enumerate(idx):
+        want = np.unpackbits(MASKS[f"m_{i}"])[: M * (sigma + M)].reshape(M, sigma + M).astype(bool)
+        got = O.mask_matrix(int(role), int(M), int(sigma), int(cache_len), int(n_pend), int(M - D))
+        assert np.array_equal(got, want), (role, D, M, cache_len, n_pend)
+
+
+def test_known_answers():
+    for k in KATS["verify_accept"]:
+        assert O.verify_accept(np.array(k["draft"]), np.array(k["verify"]), k["D"]) == k["accept"]
+    for k in KATS["draft_chain"]:
+        idx, n, _ = O.draft_chain(np.array(k["logits"], dtype=np.float32), k["tau"])
+        assert idx.tolist() == k["tokens"] and n == k["length"]
+    from types import SimpleNamespace
+    from bitmtp_b200.fast_generate import _select_M_for_pending
+    for D, rec in KATS["select_M"].items():
+        atlas = SimpleNamespace(D=int(D), m_set=tuple(rec["m_set"]))
+        assert [_select_M_for_pending(atlas, n) for n in range(1, int(D) + 2)] == rec["widths"]
+    assert KATS["select_M"]["8"]["widths"] == [9, 10, 12, 12, 16, 16, 16, 16, 17]
+    from bitmtp_b200 import contracts as C
+    reg = KATS["registry"]
+    assert sorted(C.Q1_M) == reg["Q1_M"] and sorted(C.T2_4B_M) == reg["T2_4B_M"]
+    assert sorted(map(list, C.BONSAI_17B_NK)) == reg["BONSAI_17B_NK"]
+    assert sorted(map(list, C.T2_4B_NK)) == reg["T2_4B_NK"]
+
+
+def test_whole_forward_against_reference_forward():
+    F = np.load(os.path.join(G, "forward.npz"))
+    cfg = json.loads(bytes(F["cfg"]).decode())
+    state = synthetic.make_state(cfg, seed=int(F["seed"][0]))
+    sigma, m_max = int(F["sigma"][0]), int(F["m_max"][0])
+    om = O.OracleModel(cfg, state, max_positions=sigma + m_max)
+    for ci in range(int(F["n_cases"][0])):
+        role, M, cache_len, n_pend, ls, le = (int(v) for v in F[f"c{ci}_meta"])
+        kv = F[f"c{ci}_kv_in"].copy()
+        lg = om.forward(F[f"c{ci}_tokens"], F[f"c{ci}_positions"], kv, sigma, role, cache_len, n_pend,
+                        ls, le)
+        want = F[f"c{ci}_logits"]
+        scale = np.abs(want).max()
+        # two layers of bf16 intermediates: a few bf16 steps on the logits
+        assert np.abs(lg - want).max() <= 4e-2 * scale, ci
+        assert (lg.argmax(-1) == want.argmax(-1)).mean() >= 0.8
+        got_rows, want_rows = f32(kv[:, :, 0, :, sigma:sigma + M, :]), f32(F[f"c{ci}_kv_rows"])
+        assert np.abs(got_rows - want_rows).max() <= 4e-2 * np.abs(want_rows).max()
+        # layer 0 sees identical inputs on both sides: its appended rows agree to one bf16 step
+        d0 = bf16_ulp_diff(kv[:, 0, 0, :, sigma:sigma + M, :], F[f"c{ci}_kv_rows"][:, 0])
+        assert (d0 > 1).mean() < 1e-3
