@@ -202,6 +202,7 @@ int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, int force_rb, cu
         bm::GemvParams p = p0;
         p.W = p0.W - m0 < 16 ? p0.W - m0 : 16;
         p.A = p0.A + (size_t)m0 * p0.K;
+        if (p0.asum) p.asum = p0.asum + (size_t)m0 * (p0.K / BM_GROUP);
         p.s = p0.s + m0;
         const size_t esz = p0.out_kind == BM_OUT_BF16 ? 2 : 4;
         p.C = static_cast<char *>(p0.C) + (size_t)m0 * p0.ldc * esz;
@@ -253,14 +254,29 @@ int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind) {
            esz * W * N;
 }
 
+static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
+                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream);
+
 int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void *ws, int W, int N,
                int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
+    return gemv_common(A, nullptr, B, C, s, ws, W, N, K, ldc, out_kind, path, G_out, pdl, stream);
+}
+
+int bm_t2_gemv_prepared(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s,
+                        const void *ws, int W, int N, int K, int ldc, int out_kind, int pdl, void *stream) {
+    if (!a_sums || (K % 256) != 0) return BM_EINVAL;
+    return gemv_common(A_prep, a_sums, B, C, s, ws, W, N, K, ldc, out_kind, BM_PATH_MMA, nullptr, pdl, stream);
+}
+
+static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
+                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
     if (!A || !B || !C || !s || !ws) return BM_EINVAL;
     if (W < 1 || W > BM_MAX_W || N < 8 || (N % 8) != 0 || K < 128 || (K % 128) != 0) return BM_EINVAL;
     if (ldc < N || (ldc % 4) != 0 || out_kind < 0 || out_kind > 2) return BM_EINVAL;
     if (!aligned16(A) || !aligned16(B) || !aligned16(ws) || !aligned16(C)) return BM_EINVAL;
     bm::GemvParams p;
     p.A = static_cast<const int8_t *>(A);
+    p.asum = static_cast<const int32_t *>(a_sums);
     p.B = static_cast<const uint8_t *>(B);
     p.ws = static_cast<const uint16_t *>(ws);
     p.s = static_cast<const float *>(s);
@@ -292,17 +308,21 @@ void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, 
 }
 
 // ---------------------------------------------------------------------------- fused operators
-int bm_quant_rows(const void *x, int M, int K, void *q, void *s, int pdl, void *stream) {
-    if (!x || !q || !s || M < 1 || K < 8 || (K % 8) != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7u))
-        return BM_EINVAL;
+int bm_quant_rows(const void *x, int M, int K, void *q, void *q_prep, void *asum, void *s, int pdl, void *stream) {
+    if (!x || !s || (!q && !q_prep) || M < 1 || K < 8 || (K % 8) != 0 || !aligned16(x)) return BM_EINVAL;
+    if ((q_prep == nullptr) != (asum == nullptr) || (q_prep && (K % BM_GROUP) != 0)) return BM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(q) & 7u) || (reinterpret_cast<uintptr_t>(q_prep) & 7u)) return BM_EINVAL;
+    bm::QuantSink sink{static_cast<int8_t *>(q), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
     return launch_ex(bm::quant_rows_kernel, dim3(M), dim3(bm::kRowThreads), 0, static_cast<cudaStream_t>(stream), pdl,
-                     static_cast<const uint16_t *>(x), K, static_cast<int8_t *>(q), static_cast<float *>(s), pdl);
+                     static_cast<const uint16_t *>(x), K, sink, static_cast<float *>(s), pdl);
 }
 
 int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps, int M,
-                     int dim, int row0, void *h_out, void *q, void *s, void *n_out, int pdl, void *stream) {
+                     int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s, void *n_out,
+                     int pdl, void *stream) {
     if (!x || !w || M < 1 || dim < 256 || (dim % 256) != 0 || dim > 8192) return BM_EINVAL;
-    if ((q == nullptr) != (s == nullptr)) return BM_EINVAL;
+    if (((q != nullptr) || (q_prep != nullptr)) != (s != nullptr)) return BM_EINVAL;
+    if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
     if (!aligned16(x) || !aligned16(w) || (res && !aligned16(res))) return BM_EINVAL;
     bm::NormParams p;
     p.x = static_cast<const uint16_t *>(x);
@@ -310,7 +330,7 @@ int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const v
     p.res = static_cast<const uint16_t *>(res);
     p.w = static_cast<const uint16_t *>(w);
     p.h_out = static_cast<uint16_t *>(h_out);
-    p.q = static_cast<int8_t *>(q);
+    p.q = bm::QuantSink{static_cast<int8_t *>(q), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
     p.s = static_cast<float *>(s);
     p.n_out = static_cast<uint16_t *>(n_out);
     p.eps = eps;
@@ -320,12 +340,15 @@ int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const v
     return launch_ex(bm::rmsnorm_kernel, dim3(M), dim3(dim / 8), 0, static_cast<cudaStream_t>(stream), pdl, p);
 }
 
-int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *s, void *inner_out, int pdl, void *stream) {
-    if (!gu || !q || !s || M < 1 || F < 8 || (F % 8) != 0 || !aligned16(gu)) return BM_EINVAL;
+int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *q_prep, void *asum, void *s, void *inner_out,
+                      int pdl, void *stream) {
+    if (!gu || !s || (!q && !q_prep) || M < 1 || F < 8 || (F % 8) != 0 || !aligned16(gu)) return BM_EINVAL;
+    if ((q_prep == nullptr) != (asum == nullptr) || (q_prep && (F % BM_GROUP) != 0)) return BM_EINVAL;
     const size_t smem = (size_t)F * 2;
     if (smem > 200 * 1024) return BM_EINVAL;
+    bm::QuantSink sink{static_cast<int8_t *>(q), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
     return launch_ex(bm::silu_mul_quant_kernel, dim3(M), dim3(bm::kRowThreads), smem, static_cast<cudaStream_t>(stream),
-                     pdl, static_cast<const uint16_t *>(gu), F, static_cast<int8_t *>(q), static_cast<float *>(s),
+                     pdl, static_cast<const uint16_t *>(gu), F, sink, static_cast<float *>(s),
                      static_cast<uint16_t *>(inner_out), pdl);
 }
 
@@ -373,9 +396,10 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma) {
 }
 
 int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv, int kv_rows,
-                        int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *s_out,
-                        int pdl, void *stream) {
-    if (!q || !k_base || !v_base || !state || !scratch || !att_out || !q_out || !s_out) return BM_EINVAL;
+                        int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *q_prep,
+                        void *asum, void *s_out, int pdl, void *stream) {
+    if (!q || !k_base || !v_base || !state || !scratch || !att_out || (!q_out && !q_prep) || !s_out) return BM_EINVAL;
+    if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
     if (M < 1 || M > BM_MAX_W || H < 2 || (H % 2) != 0 || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
     if (sigma < 0 || sigma + M > kv_rows || !aligned16(q) || !aligned16(k_base) || !aligned16(v_base) ||
         !aligned16(scratch) || !aligned16(att_out))
@@ -396,7 +420,7 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
     p.pl = p.pm + (size_t)M * H * NC;
     p.po = p.pl + (size_t)M * H * NC;
     p.att = static_cast<uint16_t *>(att_out);
-    p.q_out = static_cast<int8_t *>(q_out);
+    p.q_out = bm::QuantSink{static_cast<int8_t *>(q_out), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
     p.s_out = static_cast<float *>(s_out);
     p.pdl = pdl;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

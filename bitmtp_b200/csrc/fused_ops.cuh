@@ -72,6 +72,41 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
     return make_uint2(lo, hi);
 }
 
+// Where the INT8 codes of a row go.  `nat` is the natural-order row the reference's
+// operator API exposes; `prep` + `asum` are the GEMV-ready form: within every run of 16
+// elements the bytes are transposed 4x4 (prep[4t+e] = nat[4e+t]), which is the order the
+// GEMV kernels' fragments want, and asum[g] is the sum of the 128 codes of group g.  Any
+// of the three may be null.
+struct QuantSink {
+    int8_t *nat;
+    int8_t *prep;
+    int32_t *asum;
+};
+
+// Stores the 8 codes of 8-element unit `unit` of a row.  Whole warps call this together
+// (lanes whose unit lies past the row pass active = false): lane pairs (l, l^1) hold the
+// two halves of a 16-element run and exchange them, 16 consecutive lanes hold one group.
+__device__ __forceinline__ void emit_codes(const QuantSink &sink, size_t row_off, int K, int unit,
+                                           uint2 codes, bool active, int lane) {
+    if (sink.nat && active) reinterpret_cast<uint2 *>(sink.nat + row_off)[unit] = codes;
+    if (sink.prep == nullptr) return;
+    if (!active) codes = make_uint2(0u, 0u);
+    const uint2 other = make_uint2(__shfl_xor_sync(0xffffffffu, codes.x, 1),
+                                   __shfl_xor_sync(0xffffffffu, codes.y, 1));
+    const bool odd = unit & 1;
+    const uint2 lo = odd ? other : codes, hi = odd ? codes : other;
+    const uint32_t sel = odd ? 0x7362u : 0x5140u;
+    const uint32_t t = __byte_perm(lo.x, lo.y, sel), u = __byte_perm(hi.x, hi.y, sel);
+    if (active)
+        reinterpret_cast<uint2 *>(sink.prep + row_off)[unit] =
+            make_uint2(__byte_perm(t, u, 0x5410), __byte_perm(t, u, 0x7632));
+    int sum = __dp4a((int)codes.x, 0x01010101, 0);
+    sum = __dp4a((int)codes.y, 0x01010101, sum);
+#pragma unroll
+    for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (active && (lane & 15) == 0) sink.asum[(row_off / K) * (K / BM_GROUP) + (unit >> 4)] = sum;
+}
+
 // =============================================================================
 // quant_rows: per-row absmax INT8 quantisation of bf16 activations.
 // Replaces T2LinearKernel.quant_input (src/bonsai_sft/gpu/model.py:632-636) and
@@ -80,7 +115,7 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
 constexpr int kRowThreads = 512;
 
 __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(const uint16_t *__restrict__ x,
-                                                                 int K, int8_t *__restrict__ q,
+                                                                 int K, QuantSink sink,
                                                                  float *__restrict__ s_out,
                                                                  int pdl) {
     __shared__ float sh[kRowThreads / 32];
@@ -98,11 +133,12 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(const uint16_t 
     }
     amax = block_max(amax, sh, lane, warp, kRowThreads / 32);
     const float s = bm_act_scale(amax);
-    uint2 *qr = reinterpret_cast<uint2 *>(q + (size_t)m * K);
-    for (int u = threadIdx.x; u < units; u += kRowThreads) {
-        float f[8];
-        unpack8(xr[u], f);
-        qr[u] = quant8(f, s);
+    for (int u0 = 0; u0 < units; u0 += kRowThreads) {
+        const int u = u0 + threadIdx.x;
+        const bool active = u < units;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (active) unpack8(xr[u], f);
+        emit_codes(sink, (size_t)m * K, K, u, quant8(f, s), active, lane);
     }
     if (threadIdx.x == 0) s_out[m] = s;
 }
@@ -127,7 +163,7 @@ struct NormParams {
     const uint16_t *res;
     const uint16_t *w;
     uint16_t *h_out;
-    int8_t *q;
+    QuantSink q;
     float *s;
     uint16_t *n_out;
     float eps;
@@ -166,10 +202,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
         amax = fmaxf(amax, fabsf(n[i]));
     }
     if (p.n_out) reinterpret_cast<uint4 *>(p.n_out + (size_t)m * p.dim)[t] = pack8(n);
-    if (p.q) {
+    if (p.s) {
         amax = block_max(amax, sh, lane, warp, nwarps);
         const float s = bm_act_scale(amax);
-        reinterpret_cast<uint2 *>(p.q + (size_t)m * p.dim)[t] = quant8(n, s);
+        emit_codes(p.q, (size_t)m * p.dim, p.dim, t, quant8(n, s), true, lane);
         if (t == 0) p.s[m] = s;
     }
 }
@@ -181,7 +217,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
 // shared memory between the absmax pass and the quantisation pass.
 // =============================================================================
 __global__ void __launch_bounds__(kRowThreads) silu_mul_quant_kernel(
-    const uint16_t *__restrict__ gu, int F, int8_t *__restrict__ q, float *__restrict__ s_out,
+    const uint16_t *__restrict__ gu, int F, QuantSink sink, float *__restrict__ s_out,
     uint16_t *__restrict__ inner_out, int pdl) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float sh[kRowThreads / 32];
@@ -208,11 +244,12 @@ __global__ void __launch_bounds__(kRowThreads) silu_mul_quant_kernel(
     }
     amax = block_max(amax, sh, lane, warp, kRowThreads / 32);
     const float s = bm_act_scale(amax);
-    uint2 *qr = reinterpret_cast<uint2 *>(q + (size_t)m * F);
-    for (int i = threadIdx.x; i < units; i += kRowThreads) {
-        float v[8];
-        unpack8(inner[i], v);
-        qr[i] = quant8(v, s);
+    for (int i0 = 0; i0 < units; i0 += kRowThreads) {
+        const int i = i0 + threadIdx.x;
+        const bool active = i < units;
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (active) unpack8(inner[i], v);
+        emit_codes(sink, (size_t)m * F, F, i, quant8(v, s), active, lane);
     }
     if (threadIdx.x == 0) s_out[m] = s;
 }

@@ -51,7 +51,8 @@ constexpr int kActPad = 16;        // bytes appended to each staged activation r
 constexpr int kMaxStages = 8;
 
 struct GemvParams {
-    const int8_t *A;        // [W, K]
+    const int8_t *A;        // [W, K]; natural order, or 4x4-transposed 16-runs when asum != nullptr
+    const int32_t *asum;    // [W, K/128] group sums of A, or nullptr (the kernel then permutes and sums)
     const uint8_t *B;       // [N, K/4]
     const uint16_t *ws;     // [N, K/128] bf16 bits
     const float *s;         // [W]
@@ -371,24 +372,25 @@ struct AFrag {
     int nb0, nb8;     // -2 * sum(A) over the group, tokens r and r+8
 };
 
+// Fragments of group g for tokens r and r+8 from rows of `stride` bytes (shared-memory
+// staging area, or the caller's GEMV-ready activations in global memory).  Tokens >= W
+// give zeros.
 template <bool HALF>
-__device__ __forceinline__ void load_afrag(AFrag<HALF> &f, const unsigned char *smem,
-                                           const MmaSmem &L, int ng, int g, int r, int q) {
-    const uint4 *ap = reinterpret_cast<const uint4 *>(smem + L.act_off + r * L.act_stride +
-                                                      BM_GROUP * g + 32 * q);
-    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
-    f.lo0 = ap[0];
-    f.hi0 = ap[1];
-    f.nb0 = -2 * asum[r * ng + g];
-    if (!HALF) {
-        const uint4 *ap8 = reinterpret_cast<const uint4 *>(
-            smem + L.act_off + (r + 8) * L.act_stride + BM_GROUP * g + 32 * q);
+__device__ __forceinline__ void load_afrag(AFrag<HALF> &f, const unsigned char *rows, int stride,
+                                           const int *asum, int W, int ng, int g, int r, int q) {
+    f.lo0 = f.hi0 = f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
+    f.nb0 = f.nb8 = 0;
+    if (r < W) {
+        const uint4 *ap = reinterpret_cast<const uint4 *>(rows + (size_t)r * stride + BM_GROUP * g + 32 * q);
+        f.lo0 = ap[0];
+        f.hi0 = ap[1];
+        f.nb0 = -2 * asum[r * ng + g];
+    }
+    if (!HALF && r + 8 < W) {
+        const uint4 *ap8 = reinterpret_cast<const uint4 *>(rows + (size_t)(r + 8) * stride + BM_GROUP * g + 32 * q);
         f.lo8 = ap8[0];
         f.hi8 = ap8[1];
         f.nb8 = -2 * asum[(r + 8) * ng + g];
-    } else {
-        f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
-        f.nb8 = 0;
     }
 }
 
@@ -429,6 +431,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < p.stages; ++i) mbar_init(&bars[i], 1);
+        mbar_init(&bars[kMaxStages], 1);              // activation rows (several-chunk, prepared)
         mbar_fence_init();
     }
     __syncthreads();
@@ -445,21 +448,47 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
     }
     if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    const bool prepared = p.asum != nullptr;
+    // Where fragments come from: the caller's GEMV-ready rows (one chunk: straight from
+    // global memory, nothing is staged), or the shared-memory staging area.
+    const unsigned char *arows = smem + L.act_off;
+    int astride = L.act_stride;
+    const int *asum = reinterpret_cast<const int *>(smem + L.asum_off);
+    uint64_t *abar = bars + kMaxStages;
+    bool a_ok = true;
     {
-        GemvSmem LA;
-        LA.act_off = L.act_off;
-        LA.act_stride = L.act_stride;
-        LA.asum_off = L.asum_off;
-        gemv_stage_activations(p, smem, LA, WROWS);
-        float *invs = reinterpret_cast<float *>(smem + L.invs_off);
-        if (threadIdx.x < 16) invs[threadIdx.x] = threadIdx.x < p.W ? 1.0f / p.s[threadIdx.x] : 0.0f;
+        float *invs_w = reinterpret_cast<float *>(smem + L.invs_off);
+        if (threadIdx.x < 16) invs_w[threadIdx.x] = threadIdx.x < p.W ? 1.0f / p.s[threadIdx.x] : 0.0f;
+        if (!prepared) {
+            GemvSmem LA;
+            LA.act_off = L.act_off;
+            LA.act_stride = L.act_stride;
+            LA.asum_off = L.asum_off;
+            gemv_stage_activations(p, smem, LA, WROWS);
+        } else if (ONECHUNK) {
+            arows = reinterpret_cast<const unsigned char *>(p.A);
+            astride = p.K;
+            asum = p.asum;
+        } else {
+            // several chunks: the rows are copied in bulk (no permutation left to do)
+            if (warp == 1) {
+                if (lane == 0) mbar_expect_tx(abar, (uint32_t)p.W * (uint32_t)p.K);
+                __syncwarp();
+                if (lane < p.W)
+                    bulk_g2s(smem + L.act_off + lane * L.act_stride, p.A + (size_t)lane * p.K,
+                             (uint32_t)p.K, abar);
+            }
+            int *as = reinterpret_cast<int *>(smem + L.asum_off);
+            for (int i2 = threadIdx.x; i2 < p.W * ng; i2 += kGemvThreads) as[i2] = p.asum[i2];
+            a_ok = mbar_wait_bounded(abar, 0u);
+        }
     }
     __syncthreads();
 
     AFrag<HALF> fA, fB;
     if (ONECHUNK) {
-        load_afrag<HALF>(fA, smem, L, ng, 2 * warp, r, q);
-        load_afrag<HALF>(fB, smem, L, ng, 2 * warp + 1, r, q);
+        load_afrag<HALF>(fA, arows, astride, asum, p.W, ng, 2 * warp, r, q);
+        load_afrag<HALF>(fB, arows, astride, asum, p.W, ng, 2 * warp + 1, r, q);
     }
     float *part = reinterpret_cast<float *>(smem + L.part_off);
     const float *invs = reinterpret_cast<const float *>(smem + L.invs_off);
@@ -471,7 +500,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
 
     for (int i = 0; i < my_tiles; ++i) {
         const int st = i % p.stages;
-        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1));
+        const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1)) && a_ok;
         const unsigned char *stage = smem + L.stage_off + st * L.stage_bytes;
         const int n0 = (blockIdx.x + i * gridDim.x) * R;
 
@@ -488,8 +517,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
                 const int g0 = c * BM_SLOTS + 2 * warp;
                 if (!ONECHUNK) {
                     if (g0 >= ng) break;              // warp-uniform
-                    load_afrag<HALF>(fA, smem, L, ng, g0, r, q);
-                    load_afrag<HALF>(fB, smem, L, ng, g0 + 1, r, q);
+                    load_afrag<HALF>(fA, arows, astride, asum, p.W, ng, g0, r, q);
+                    load_afrag<HALF>(fB, arows, astride, asum, p.W, ng, g0 + 1, r, q);
                 }
                 const unsigned char *wp = stage + woff + c * (32 * BM_SLOTS);
                 const unsigned char *sp = stage + soff + c * (2 * BM_SLOTS);

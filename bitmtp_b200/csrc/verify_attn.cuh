@@ -47,7 +47,7 @@ struct AttnParams {
     unsigned int *amax;
     float *pm, *pl, *po;
     uint16_t *att;            // [M, H*128] bf16 attention output
-    int8_t *q_out;            // [M, H*128] INT8 of att
+    QuantSink q_out;          // [M, H*128] INT8 of att (natural and/or GEMV-ready)
     float *s_out;             // [M]
     int pdl;
 };
@@ -167,6 +167,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_chunk_kernel(const AttnP
 // ---- kernel 2: merge chunks for (row m, head pair); last CTA of a row quantises it --
 __global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnParams p) {
     __shared__ float w_s[2][160];        // merge weights per head of the pair (NC <= 160 => sigma <= 5088)
+    __shared__ float pl_s[2][160];
     __shared__ float l_s[2];
     __shared__ float red[kAttnThreads / 32];
     __shared__ int is_last;
@@ -180,24 +181,26 @@ __global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnPara
 
     if (warp < 2) {                                   // warp w: weights of head h0 + w
         const size_t base = ((size_t)m * p.H + h0 + warp) * p.NC;
+        // chunk maxima and sums come into shared memory with independent loads; the ordered
+        // sum below then runs on shared-memory operands
         float gmax = -INFINITY;
         for (int i = lane; i < nv; i += 32) {
             const int j = i < n_hist ? i : p.NC - 1;
-            gmax = fmaxf(gmax, p.pm[base + j]);
+            const float mj = p.pm[base + j];
+            w_s[warp][i] = mj;
+            pl_s[warp][i] = p.pl[base + j];
+            gmax = fmaxf(gmax, mj);
         }
         gmax = warp_max(gmax);
         for (int i = lane; i < nv; i += 32) {
-            const int j = i < n_hist ? i : p.NC - 1;
-            const float mj = p.pm[base + j];
+            const float mj = w_s[warp][i];
             w_s[warp][i] = mj > -INFINITY ? bm_expf(mj - gmax) : 0.0f;
         }
         __syncwarp();
         if (lane == 0) {
             float l = 0.0f;
-            for (int i = 0; i < nv; ++i) {
-                const int j = i < n_hist ? i : p.NC - 1;
-                if (p.pm[base + j] > -INFINITY) l = fmaf(p.pl[base + j], w_s[warp][i], l);
-            }
+            // a chunk without a visible key has weight 0 and sum 0: fma(0, 0, l) == l
+            for (int i = 0; i < nv; ++i) l = fmaf(pl_s[warp][i], w_s[warp][i], l);
             l_s[warp] = l;
         }
     }
@@ -205,6 +208,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnPara
     const int hh = tid >> 7, d = tid & 127, h = h0 + hh;
     const size_t obase = ((size_t)m * p.H + h) * p.NC;
     float o = 0.0f;
+#pragma unroll 4
     for (int i = 0; i < nv; ++i) {
         const int j = i < n_hist ? i : p.NC - 1;
         const float w = w_s[hh][i];
@@ -229,10 +233,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnPara
     const float amax = __uint_as_float(atomicOr(&p.amax[m], 0u));
     const float s = bm_act_scale(amax);
     const int units = p.H * 128 / 8;
-    for (int u = tid; u < units; u += kAttnThreads) {
-        float f[8];
-        unpack8(__ldcg(reinterpret_cast<const uint4 *>(p.att + row) + u), f);
-        reinterpret_cast<uint2 *>(p.q_out + row)[u] = quant8(f, s);
+    for (int u0 = 0; u0 < units; u0 += kAttnThreads) {
+        const int u = u0 + tid;
+        const bool active = u < units;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (active) unpack8(__ldcg(reinterpret_cast<const uint4 *>(p.att + row) + u), f);
+        emit_codes(p.q_out, row, p.H * 128, u, quant8(f, s), active, lane);
     }
     if (tid == 0) {
         p.s_out[m] = s;

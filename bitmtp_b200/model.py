@@ -321,6 +321,12 @@ class StepWorkspace:
         self.ffn_out = buf((M, args.dim), bf)
         self.hq = buf((M, args.dim), i8)
         self.hs = buf((M, 1), f32)
+        # per-128-group sums that travel with the GEMV-ready codes in q / att_q / iq / hq
+        i32 = torch.int32
+        self.q_sum = buf((M, args.dim // 128), i32)
+        self.att_sum = buf((M, q_dim // 128), i32)
+        self.i_sum = buf((M, args.ffn_dim // 128), i32)
+        self.h_sum = buf((M, args.dim // 128), i32)
         self.n_pad = n_pad
 
 
@@ -437,34 +443,41 @@ class Transformer(nn.Module):
             logits_buf = torch.empty((rows, W.n_pad), dtype=torch.float32, device=dev)
         eps = a.norm_eps
         L0 = self.layers[0]
+        # INT8 activations go from their producer to the next GEMV in GEMV-ready order
+        # (16-runs transposed 4x4, plus per-group sums), so no GEMV CTA permutes or sums them.
+        qsink = {"h": W.h, "qp": W.q, "asum": W.q_sum, "s": W.s}
         ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
-                          gather=token_values, pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
+                          gather=token_values, pdl=pdl, out=qsink)
         for i, layer in enumerate(self.layers):
             at, ff = layer.attention, layer.feed_forward
             if i > 0:
                 ops.rmsnorm_fused(W.ffn_out, layer.input_layernorm.weight.data, eps, M=M, res=W.h,
-                                  pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
-            ops.t2_gemv(W.q, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv, ldc=W.xqkv.shape[1], pdl=pdl)
+                                  pdl=pdl, out=qsink)
+            ops.t2_gemv_prepared(W.q, W.q_sum, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv,
+                                 ldc=W.xqkv.shape[1], pdl=pdl)
             k_l, v_l = kv_full[i]
             ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
                                      at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
                                      _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
                                      pdl=pdl, q_out=W.qrot)
             ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                 attn_mask, attn_scratch, pdl=pdl, out=(W.att, W.att_q, W.att_s))
-            ops.t2_gemv(W.att_q, at.o_proj.weight.data, W.att_s, at.o_proj.weight_scale,
-                        out=W.attn_out, ldc=a.dim, pdl=pdl)
+                                 attn_mask, attn_scratch, pdl=pdl, out=(W.att, None, W.att_s),
+                                 prep=(W.att_q, W.att_sum))
+            ops.t2_gemv_prepared(W.att_q, W.att_sum, at.o_proj.weight.data, W.att_s,
+                                 at.o_proj.weight_scale, out=W.attn_out, ldc=a.dim, pdl=pdl)
             ops.rmsnorm_fused(W.h, layer.post_attention_layernorm.weight.data, eps, M=M,
-                              res=W.attn_out, pdl=pdl, out={"h": W.h, "q": W.q, "s": W.s})
-            ops.t2_gemv(W.q, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu, ldc=W.gu.shape[1], pdl=pdl)
-            ops.silu_mul_quant(W.gu, pdl=pdl, out=(W.iq, W.is_))
-            ops.t2_gemv(W.iq, ff.down_proj.weight.data, W.is_, ff.down_proj.weight_scale,
-                        out=W.ffn_out, ldc=a.dim, pdl=pdl)
+                              res=W.attn_out, pdl=pdl, out=qsink)
+            ops.t2_gemv_prepared(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu,
+                                 ldc=W.gu.shape[1], pdl=pdl)
+            ops.silu_mul_quant(W.gu, pdl=pdl, out=(None, W.is_), prep=(W.iq, W.i_sum))
+            ops.t2_gemv_prepared(W.iq, W.i_sum, ff.down_proj.weight.data, W.is_,
+                                 ff.down_proj.weight_scale, out=W.ffn_out, ldc=a.dim, pdl=pdl)
         # h + ffn_out, final norm of the logit rows, INT8 quantisation for the packed head
         ops.rmsnorm_fused(W.h, self.norm.weight.data, eps, M=rows, res=W.ffn_out, row0=logits_start,
-                          pdl=pdl, out={"q": W.hq, "s": W.hs})
-        ops.t2_gemv(W.hq[:rows], self._lm_head_t2_w, W.hs[:rows], self._lm_head_t2_scale,
-                    out_kind=native.OUT_F32_OF_BF16, out=logits_buf, ldc=W.n_pad, pdl=pdl)
+                          pdl=pdl, out={"qp": W.hq, "asum": W.h_sum, "s": W.hs})
+        ops.t2_gemv_prepared(W.hq[:rows], W.h_sum[:rows], self._lm_head_t2_w, W.hs[:rows],
+                             self._lm_head_t2_scale, out_kind=native.OUT_F32_OF_BF16, out=logits_buf,
+                             ldc=W.n_pad, pdl=pdl)
         return logits_buf[:, : self._lm_head_t2_vocab]
 
     @torch.no_grad()

@@ -92,14 +92,15 @@ def _declare_optional(L) -> None:
     """Prototypes of the fused operators, the attention and the logit reductions."""
     vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     protos = {
-        "bm_quant_rows": [vp, ci, ci, vp, vp, ci, vp],
-        "bm_rmsnorm_fused": [vp, vp, vp, vp, cf, ci, ci, ci, vp, vp, vp, vp, ci, vp],
-        "bm_silu_mul_quant": [vp, ci, ci, vp, vp, vp, ci, vp],
+        "bm_quant_rows": [vp, ci, ci, vp, vp, vp, vp, ci, vp],
+        "bm_rmsnorm_fused": [vp, vp, vp, vp, cf, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
+        "bm_silu_mul_quant": [vp, ci, ci, vp, vp, vp, vp, vp, ci, vp],
         "bm_qknorm_rope_kvappend": [vp, vp, vp, cf, vp, vp, vp, ci, ci, ci, vp, vp, ci, ci, vp, ci, vp],
         "bm_set_step_state": [vp, ci, ci, ci, ci, vp],
         "bm_kv_copy_rows": [vp, ci, ci, ci, ci, ci, vp],
         "bm_verify_attention_scratch_bytes": [ci, ci, ci],
-        "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, ci, vp],
+        "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
+        "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],
         "bm_verify_accept": [vp, vp, ci, vp, vp],

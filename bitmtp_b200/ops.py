@@ -65,28 +65,48 @@ def t2_gemv(a_int8: torch.Tensor, b_packed: torch.Tensor, s: torch.Tensor, ws: t
     return (out, G) if want_groups else out
 
 
+def t2_gemv_prepared(a_prep: torch.Tensor, a_sums: torch.Tensor, b_packed: torch.Tensor,
+                     s: torch.Tensor, ws: torch.Tensor, *, out: torch.Tensor, ldc: Optional[int] = None,
+                     out_kind: int = native.OUT_BF16, pdl: bool = False) -> torch.Tensor:
+    """The GEMV on GEMV-ready activations (q_prep / asum of a quantising operator)."""
+    W, K = a_prep.shape
+    N = b_packed.shape[0]
+    rc = native.lib().bm_t2_gemv_prepared(_ptr(a_prep), _ptr(a_sums), _ptr(b_packed), _ptr(out), _ptr(s),
+                                          _ptr(ws), W, N, K, ldc if ldc is not None else out.stride(0),
+                                          out_kind, int(pdl), _stream(a_prep.device))
+    check(rc, f"bm_t2_gemv_prepared(W={W}, N={N}, K={K})")
+    return out
+
+
 def gemv_bytes(W: int, N: int, K: int, out_kind: int = native.OUT_BF16) -> int:
     return int(native.lib().bm_t2_gemv_bytes(W, N, K, out_kind))
 
 
 # --------------------------------------------------------------------------- fused operators
-def quant_rows(x: torch.Tensor, *, pdl: bool = False):
-    """bf16 [M, K] -> (int8 [M, K], fp32 [M, 1])."""
+def quant_rows(x: torch.Tensor, *, pdl: bool = False, prepared: bool = False):
+    """bf16 [M, K] -> (int8 [M, K], fp32 [M, 1]); with `prepared`, the GEMV-ready form
+    (q_prep int8 [M, K], asum int32 [M, K/128], s fp32 [M, 1]) instead."""
     _require_cuda(x)
     M, K = x.shape
-    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
     s = torch.empty((M, 1), dtype=torch.float32, device=x.device)
-    check(native.lib().bm_quant_rows(_ptr(x), M, K, _ptr(q), _ptr(s), int(pdl), _stream(x.device)),
-          "bm_quant_rows")
-    return q, s
+    q = qp = asum = None
+    if prepared:
+        qp = torch.empty((M, K), dtype=torch.int8, device=x.device)
+        asum = torch.empty((M, K // 128), dtype=torch.int32, device=x.device)
+    else:
+        q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    check(native.lib().bm_quant_rows(_ptr(x), M, K, _ptr(q), _ptr(qp), _ptr(asum), _ptr(s), int(pdl),
+                                     _stream(x.device)), "bm_quant_rows")
+    return (qp, asum, s) if prepared else (q, s)
 
 
 def rmsnorm_fused(x: torch.Tensor, w: torch.Tensor, eps: float, *, M: Optional[int] = None,
                   gather: Optional[torch.Tensor] = None, res: Optional[torch.Tensor] = None,
                   row0: int = 0, want_h: bool = False, want_q: bool = True, want_n: bool = False,
-                  pdl: bool = False, out=None):
+                  want_prep: bool = False, pdl: bool = False, out=None):
     """(gather | residual add) + RMSNorm + (quantise | store).  Returns a dict with the
-    requested outputs among h (bf16), q (int8), s (fp32 [M,1]), n (bf16)."""
+    requested outputs among h (bf16), q (int8), qp + asum (GEMV-ready int8 + int32 group
+    sums), s (fp32 [M,1]), n (bf16).  Buffers passed in `out` are used as they are."""
     dim = x.shape[-1]
     if M is None:
         M = gather.shape[0] if gather is not None else x.shape[0] - row0
@@ -94,30 +114,41 @@ def rmsnorm_fused(x: torch.Tensor, w: torch.Tensor, eps: float, *, M: Optional[i
     out = dict(out) if out else {}
     if want_h and "h" not in out:
         out["h"] = torch.empty((M, dim), dtype=torch.bfloat16, device=dev)
-    if want_q and "q" not in out:
+    if want_prep and "qp" not in out:
+        out["qp"] = torch.empty((M, dim), dtype=torch.int8, device=dev)
+        out["asum"] = torch.empty((M, dim // 128), dtype=torch.int32, device=dev)
+    if want_q and "q" not in out and "qp" not in out:
         out["q"] = torch.empty((M, dim), dtype=torch.int8, device=dev)
+    if ("q" in out or "qp" in out) and "s" not in out:
         out["s"] = torch.empty((M, 1), dtype=torch.float32, device=dev)
     if want_n and "n" not in out:
         out["n"] = torch.empty((M, dim), dtype=torch.bfloat16, device=dev)
     rc = native.lib().bm_rmsnorm_fused(_ptr(x), _ptr(gather), _ptr(res), _ptr(w), float(eps), M, dim,
-                                       row0, _ptr(out.get("h")), _ptr(out.get("q")),
-                                       _ptr(out.get("s")), _ptr(out.get("n")), int(pdl), _stream(dev))
+                                       row0, _ptr(out.get("h")), _ptr(out.get("q")), _ptr(out.get("qp")),
+                                       _ptr(out.get("asum")), _ptr(out.get("s")), _ptr(out.get("n")),
+                                       int(pdl), _stream(dev))
     check(rc, f"bm_rmsnorm_fused(M={M}, dim={dim})")
     return out
 
 
-def silu_mul_quant(gu: torch.Tensor, *, want_inner: bool = False, pdl: bool = False, out=None):
+def silu_mul_quant(gu: torch.Tensor, *, want_inner: bool = False, pdl: bool = False, out=None,
+                   prep=None):
+    """gate|up bf16 [M, 2F] -> INT8 codes of silu(gate)*up + multiplier.  `out` = (q, s)
+    buffers (natural order), `prep` = (qp, asum) buffers (GEMV-ready); either or both."""
     _require_cuda(gu)
     M, F2 = gu.shape
     F = F2 // 2
+    q = s = None
     if out is not None:
         q, s = out
-    else:
+    elif prep is None:
         q = torch.empty((M, F), dtype=torch.int8, device=gu.device)
+    if s is None:
         s = torch.empty((M, 1), dtype=torch.float32, device=gu.device)
+    qp, asum = prep if prep is not None else (None, None)
     inner = torch.empty((M, F), dtype=torch.bfloat16, device=gu.device) if want_inner else None
-    check(native.lib().bm_silu_mul_quant(_ptr(gu), M, F, _ptr(q), _ptr(s), _ptr(inner), int(pdl),
-                                         _stream(gu.device)), "bm_silu_mul_quant")
+    check(native.lib().bm_silu_mul_quant(_ptr(gu), M, F, _ptr(q), _ptr(qp), _ptr(asum), _ptr(s),
+                                         _ptr(inner), int(pdl), _stream(gu.device)), "bm_silu_mul_quant")
     return (q, s, inner) if want_inner else (q, s)
 
 
@@ -157,8 +188,11 @@ def attention_scratch(M: int, H: int, sigma: int, device) -> torch.Tensor:
     return torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=device)
 
 
-def verify_attention(q, k_layer, v_layer, sigma, state, scratch, *, pdl: bool = False, out=None):
-    """Returns (att bf16 [M, H*128], q int8 [M, H*128], s fp32 [M, 1])."""
+def verify_attention(q, k_layer, v_layer, sigma, state, scratch, *, pdl: bool = False, out=None,
+                     prep=None):
+    """Returns (att bf16 [M, H*128], q int8 [M, H*128] or None, s fp32 [M, 1]).  `prep` =
+    (qp, asum) buffers additionally (or, with out[1] None, instead) receive the GEMV-ready
+    codes."""
     M, H, _ = q.shape
     Hkv, kv_rows = k_layer.shape[-3], k_layer.shape[-2]
     dev = q.device
@@ -166,9 +200,11 @@ def verify_attention(q, k_layer, v_layer, sigma, state, scratch, *, pdl: bool = 
         out = (torch.empty((M, H * 128), dtype=torch.bfloat16, device=dev),
                torch.empty((M, H * 128), dtype=torch.int8, device=dev),
                torch.empty((M, 1), dtype=torch.float32, device=dev))
+    qp, asum = prep if prep is not None else (None, None)
     rc = native.lib().bm_verify_attention(_ptr(q), _ptr(k_layer), _ptr(v_layer), M, H, Hkv, kv_rows,
                                           sigma, _ptr(state), _ptr(scratch), _ptr(out[0]),
-                                          _ptr(out[1]), _ptr(out[2]), int(pdl), _stream(dev))
+                                          _ptr(out[1]), _ptr(qp), _ptr(asum), _ptr(out[2]), int(pdl),
+                                          _stream(dev))
     check(rc, "bm_verify_attention")
     return out
 

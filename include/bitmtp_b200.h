@@ -71,6 +71,16 @@ void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, 
 int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void *ws, int W, int N,
                int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream);
 
+/* The same product on GEMV-ready activations (q_prep / asum of the quantising operators):
+ * the kernel then skips its own byte permutation and group sums, and for K == 2048 reads
+ * its fragments straight from A_prep without staging them.  K % 256 == 0.  Results are
+ * bit-identical to bm_t2_gemv on the natural-order codes.  No counterpart in the
+ * reference, whose kernel re-reads natural-order activations from global memory for
+ * every output row. */
+int bm_t2_gemv_prepared(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s,
+                        const void *ws, int W, int N, int K, int ldc, int out_kind, int pdl,
+                        void *stream);
+
 /* Algorithmic bytes one bm_t2_gemv call moves (codes + scales + A + s + C), the
  * numerator of the roofline figure. Host-only arithmetic. */
 int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind);
@@ -82,8 +92,16 @@ int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind);
 
 /* Per-row absmax INT8 quantisation: x bf16 [M, K] -> q int8 [M, K], s fp32 [M]
  * with s = 127 / max(absmax, 1e-5), q = clamp(rint(x * s), -128, 127).
- * Replaces T2LinearKernel.quant_input (src/bonsai_sft/gpu/model.py:632-636). */
-int bm_quant_rows(const void *x, int M, int K, void *q, void *s, int pdl, void *stream);
+ * Replaces T2LinearKernel.quant_input (src/bonsai_sft/gpu/model.py:632-636).
+ *
+ * Every quantising operator below takes the same trio of outputs, any of which may be
+ * NULL (at least one of q / q_prep must be given; q_prep and asum go together):
+ *   q       int8 [M, K] in natural order, what the reference's operator returns
+ *   q_prep  int8 [M, K] GEMV-ready: each run of 16 codes stored as its 4x4 byte
+ *           transpose (q_prep[4t+e] = q[4e+t]), the order bm_t2_gemv_prepared consumes
+ *   asum    int32 [M, K/128]: the sum of the codes of each 128-group (K % 128 == 0) */
+int bm_quant_rows(const void *x, int M, int K, void *q, void *q_prep, void *asum, void *s, int pdl,
+                  void *stream);
 
 /* (gather | residual add) + RMSNorm + (INT8 quantisation | bf16 store), one row per CTA.
  *   x       bf16 [*, dim]; row m is x[gather[m]] when gather (int64 [M]) is given,
@@ -91,20 +109,20 @@ int bm_quant_rows(const void *x, int M, int K, void *q, void *s, int pdl, void *
  *   res     optional bf16 [*, dim], read at row0 + m: h = bf16(x + res)
  *   w       bf16 [dim] norm weight;  dim a multiple of 256, <= 8192
  *   h_out   optional bf16 [M, dim]: the row before the norm
- *   q, s    optional int8 [M, dim] + fp32 [M] (both or neither)
+ *   q, q_prep, asum, s   optional quantised outputs (see bm_quant_rows) + fp32 [M]
  *   n_out   optional bf16 [M, dim]: the normed row
  * Replaces _fused_norm_quant, _fused_add_norm_quant, RMSNorm.forward on the logit
  * rows and the embedding gather (src/bonsai_sft/gpu/model.py:307-336, 290-295,
  * 1386, 1401-1402). */
 int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps,
-                     int M, int dim, int row0, void *h_out, void *q, void *s, void *n_out, int pdl,
-                     void *stream);
+                     int M, int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s,
+                     void *n_out, int pdl, void *stream);
 
 /* inner = bf16(bf16(silu(gate)) * up), then the quantisation of bm_quant_rows.
  * gu bf16 [M, 2F] = gate | up; q int8 [M, F]; s fp32 [M]; inner_out optional bf16 [M, F].
  * Replaces src/bonsai_sft/gpu/model.py:1059-1061. */
-int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *s, void *inner_out, int pdl,
-                      void *stream);
+int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *q_prep, void *asum, void *s,
+                      void *inner_out, int pdl, void *stream);
 
 /* Split qkv, per-head RMSNorm of q and k, RoPE from bf16 tables, append K / V rows.
  *   xqkv bf16 [M, (H + 2*Hkv)*128]; q_w, k_w bf16 [128]; cos_t, sin_t bf16 [max_pos, 128];
@@ -137,14 +155,16 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma);
  *   state: the record written by bm_set_step_state;
  *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned; its first 256
  *   bytes must be zero before the first call and are left zero by every call;
- *   att_out bf16 [M, H*128]; q_out int8 [M, H*128]; s_out fp32 [M].
+ *   att_out bf16 [M, H*128]; q_out / q_prep / asum: the quantised rows (see
+ *   bm_quant_rows); s_out fp32 [M].
  * Visibility follows the reference's draft / verify / ar masks.  Replaces the
  * attention and o-projection input quantisation of
  * Attention.forward_sdlm_graph_kernel (src/bonsai_sft/gpu/model.py:989-1005) and the
  * mask tensors of src/bonsai_sft/gpu/fast_runtime.py:345-372, 423-465. */
 int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H,
                         int Hkv, int kv_rows, int sigma, const void *state, void *scratch,
-                        void *att_out, void *q_out, void *s_out, int pdl, void *stream);
+                        void *att_out, void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
+                        void *stream);
 
 /* Row argmax (lowest index on ties): logits fp32 [rows, ld] -> idx int64 [rows],
  * optional max_out fp32 [rows].  Replaces `.argmax(dim=-1)` on the logit rows

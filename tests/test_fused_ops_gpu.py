@@ -183,3 +183,73 @@ def test_logit_reductions(oracle):
     a = torch.tensor([1, 2, 3, 4, 5, 6, 7, 8], dtype=torch.int64)
     b = torch.tensor([1, 2, 3, 9, 5, 6, 7, 8, 0], dtype=torch.int64)
     assert int(ops.verify_accept(a.to(DEV), b.to(DEV), 8).item()) == oracle.verify_accept(a.numpy(), b.numpy(), 8) == 3
+
+
+def _permute16(q_nat: np.ndarray) -> np.ndarray:
+    """Natural-order codes -> GEMV-ready order: every run of 16 transposed 4x4."""
+    M, K = q_nat.shape
+    return q_nat.reshape(M, K // 16, 4, 4).transpose(0, 1, 3, 2).reshape(M, K).copy()
+
+
+@pytest.mark.parametrize("M,K", [(1, 2048), (16, 6144), (9, 2560), (5, 256)])
+def test_prepared_outputs_and_prepared_gemv(oracle, M, K):
+    """q_prep is the 4x4 transpose of q per 16-run, asum the per-group code sums, and the
+    GEMV on them equals the GEMV on natural-order codes bit for bit."""
+    from bitmtp_b200 import synthetic
+    gen = torch.Generator().manual_seed(M + K)
+    x = _bf16(gen, M, K, scale=2.0)
+    q, s = ops.quant_rows(x.to(DEV))
+    qp, asum, s2 = ops.quant_rows(x.to(DEV), prepared=True)
+    qn = q.cpu().numpy()
+    assert np.array_equal(qp.cpu().numpy(), _permute16(qn))
+    assert np.array_equal(asum.cpu().numpy(), qn.astype(np.int32).reshape(M, K // 128, 128).sum(-1))
+    assert torch.equal(s, s2)
+    N = 512
+    packed, scale, _ = synthetic.ternary_weight(N, K, gen)
+    Bd, wsd = packed.to(DEV), scale.to(DEV)
+    want = ops.t2_gemv(q, Bd, s, wsd, out_kind=native.OUT_F32)
+    got = torch.empty_like(want)
+    ops.t2_gemv_prepared(qp, asum, Bd, s, wsd, out=got, out_kind=native.OUT_F32)
+    assert torch.equal(got, want)
+    y32, _, _ = oracle.t2_gemv(qn, packed.numpy().view(np.uint8), oracle.torch_to_u16(scale),
+                               s.cpu().numpy().reshape(-1))
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), y32.view(np.uint32))
+
+
+def test_prepared_from_norm_silu_attention(oracle):
+    gen = torch.Generator().manual_seed(77)
+    # rmsnorm
+    x = _bf16(gen, 9, 2048, scale=2.0)
+    w = (1.0 + 0.1 * torch.randn(2048, generator=gen)).to(torch.bfloat16)
+    a = ops.rmsnorm_fused(x.to(DEV), w.to(DEV), 1e-6)
+    b = ops.rmsnorm_fused(x.to(DEV), w.to(DEV), 1e-6, want_q=False, want_prep=True)
+    qn = a["q"].cpu().numpy()
+    assert np.array_equal(b["qp"].cpu().numpy(), _permute16(qn))
+    assert np.array_equal(b["asum"].cpu().numpy(), qn.astype(np.int32).reshape(9, 16, 128).sum(-1))
+    # silu
+    gu = _bf16(gen, 5, 2 * 6144, scale=3.0).to(DEV)
+    q, s = ops.silu_mul_quant(gu)
+    qp = torch.empty_like(q)
+    asum = torch.empty(5, 48, dtype=torch.int32, device=DEV)
+    s2 = torch.empty_like(s)
+    ops.silu_mul_quant(gu, out=(None, s2), prep=(qp, asum))
+    qn = q.cpu().numpy()
+    assert np.array_equal(qp.cpu().numpy(), _permute16(qn)) and torch.equal(s, s2)
+    assert np.array_equal(asum.cpu().numpy(), qn.astype(np.int32).reshape(5, 48, 128).sum(-1))
+    # attention
+    M, H, Hkv, sigma = 9, 16, 8, 256
+    qv = _bf16(gen, M, H, 128).to(DEV)
+    k = _bf16(gen, Hkv, sigma + 17, 128).to(DEV)
+    v = _bf16(gen, Hkv, sigma + 17, 128).to(DEV)
+    st = ops.new_step_state(DEV)
+    ops.set_step_state(st, 100, 1, 0, 1)
+    scr = ops.attention_scratch(M, H, sigma, DEV)
+    att, qq, ss = ops.verify_attention(qv, k, v, sigma, st, scr)
+    qp = torch.empty_like(qq)
+    asum = torch.empty(M, H, dtype=torch.int32, device=DEV)
+    out2 = (torch.empty_like(att), None, torch.empty_like(ss))
+    ops.verify_attention(qv, k, v, sigma, st, scr, out=out2, prep=(qp, asum))
+    qn = qq.cpu().numpy()
+    assert torch.equal(out2[0], att) and torch.equal(out2[2], ss)
+    assert np.array_equal(qp.cpu().numpy(), _permute16(qn))
+    assert np.array_equal(asum.cpu().numpy(), qn.astype(np.int32).reshape(M, H, 128).sum(-1))
