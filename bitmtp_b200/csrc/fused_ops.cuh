@@ -119,8 +119,8 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(const uint16_t 
                                                                  float *__restrict__ s_out,
                                                                  int pdl) {
     __shared__ float sh[kRowThreads / 32];
-    if (pdl) pdl_wait();
     pdl_launch_dependents();
+    if (pdl) pdl_wait();
     const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)m * K);
     const int units = K / 8;
@@ -174,8 +174,8 @@ struct NormParams {
 
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
     __shared__ float sh[32];
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     const int m = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int nwarps = blockDim.x >> 5;
     const size_t src_row = p.gather ? (size_t)p.gather[m] : (size_t)(p.row0 + m);
@@ -221,8 +221,8 @@ __global__ void __launch_bounds__(kRowThreads) silu_mul_quant_kernel(
     uint16_t *__restrict__ inner_out, int pdl) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float sh[kRowThreads / 32];
-    if (pdl) pdl_wait();
     pdl_launch_dependents();
+    if (pdl) pdl_wait();
     uint4 *inner = reinterpret_cast<uint4 *>(dyn);
     const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4 *g = reinterpret_cast<const uint4 *>(gu + (size_t)m * 2 * F);
@@ -274,8 +274,8 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(128) qknorm_rope_kvappend_kernel(const RopeParams p) {
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = p.H + 2 * p.Hkv;
     const int m = blockIdx.y;

@@ -188,8 +188,8 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_dp4a_kernel(const GemvPa
                             min(R, p.N - n0), lane);
         }
     }
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     gemv_stage_activations(p, smem, L, p.W);
     __syncthreads();
 
@@ -446,8 +446,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
             gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, LS, &bars[i],
                             (blockIdx.x + i * gridDim.x) * R, R, lane);
     }
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     const bool prepared = p.asum != nullptr;
     // Where fragments come from: the caller's GEMV-ready rows (one chunk: straight from
     // global memory, nothing is staged), or the shared-memory staging area.

@@ -60,8 +60,8 @@ __host__ __device__ inline size_t attn_scratch_bytes(int M, int H, int sigma) {
 // ---- kernel 1: one (chunk, kv head) ------------------------------------------------
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_chunk_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     const int j = blockIdx.x, hk = blockIdx.y;
     const int cache_len = p.state->cache_len, n_pend = p.state->n_pend, role = p.state->role,
               P = p.state->P;
@@ -171,8 +171,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnPara
     __shared__ float l_s[2];
     __shared__ float red[kAttnThreads / 32];
     __shared__ int is_last;
-    if (p.pdl) pdl_wait();
     pdl_launch_dependents();
+    if (p.pdl) pdl_wait();
     const int m = blockIdx.y, h0 = blockIdx.x * 2;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cache_len = p.state->cache_len;

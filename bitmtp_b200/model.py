@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -342,7 +343,10 @@ class Transformer(nn.Module):
         self._lm_head_weight_ref = None
         self._lm_head_t2_w = None
         self._workspaces = {}
-        self.use_pdl = False
+        # Programmatic dependent launch between the kernels of a replay: every kernel lets its
+        # successor start early (GEMVs then request their weight tiles while the predecessor
+        # is still running) and waits for its predecessor before touching activations.
+        self.use_pdl = os.environ.get("BM_PDL", "1") != "0"
 
     def tie_weights(self) -> None:
         # plain attribute, not a registered parameter: the state dict keeps the reference's keys
