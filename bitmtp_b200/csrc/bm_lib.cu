@@ -398,11 +398,11 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma) {
 int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv, int kv_rows,
                         int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *q_prep,
                         void *asum, void *s_out, int pdl, void *stream) {
-    if (!q || !k_base || !v_base || !state || !scratch || !att_out || (!q_out && !q_prep) || !s_out) return BM_EINVAL;
+    if (!q || !k_base || !v_base || !state || !scratch || (!q_out && !q_prep) || !s_out) return BM_EINVAL;
     if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
-    if (M < 1 || M > BM_MAX_W || H < 2 || (H % 2) != 0 || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
+    if (M < 1 || M > BM_MAX_W || H < 1 || H > bm::kMergeMaxHeads || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
     if (sigma < 0 || sigma + M > kv_rows || !aligned16(q) || !aligned16(k_base) || !aligned16(v_base) ||
-        !aligned16(scratch) || !aligned16(att_out))
+        !aligned16(scratch) || (att_out && !aligned16(att_out)))
         return BM_EINVAL;
     const int NC = (sigma + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK + 1;
     if (NC > 160) return BM_EINVAL;
@@ -425,9 +425,20 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
     p.pdl = pdl;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
-    int rc = launch_ex(bm::attn_chunk_kernel, dim3(NC, Hkv), dim3(bm::kAttnThreads), smem, st, pdl, p);
+    const int nq = bm::attn_nq(QV);
+    int warps = (QV + nq - 1) / nq;
+    if (warps > bm::kAttnThreads / 32) warps = bm::kAttnThreads / 32;
+    const int threads = 32 * warps < bm::kAttnMinThreads ? bm::kAttnMinThreads : 32 * warps;
+    const size_t msmem = (size_t)H * 128 * 2 + (size_t)H * NC * sizeof(float);
+    if (smem > 200 * 1024 || msmem > 200 * 1024) return BM_EINVAL;
+    int rc;
+    if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
+    else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
+    else rc = launch_ex(bm::attn_chunk_kernel<8>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
     if (rc != BM_OK) return rc;
-    return launch_ex(bm::attn_merge_kernel, dim3(H / 2, M), dim3(bm::kAttnThreads), 0, st, pdl, p);
+    int mthreads = H * 64 < bm::kMergeThreads ? H * 64 : bm::kMergeThreads;
+    mthreads = (mthreads + 31) / 32 * 32;
+    return launch_ex(bm::attn_merge_kernel, dim3(M), dim3(mthreads), msmem, st, pdl, p);
 }
 
 // ---------------------------------------------------------------------------- logits

@@ -162,6 +162,9 @@ BM_HD int bm_perm16(int k) { return ((k & 3) << 2) | (k >> 2); }
 #define BM_ROLE_DRAFT 0
 #define BM_ROLE_VERIFY 1
 #define BM_ROLE_AR 2
+#ifndef BM_PDL_STABLE_STATE
+#define BM_PDL_STABLE_STATE 2      /* pdl bit: step record and history rows predate the launch chain */
+#endif
 
 BM_HD int bm_visible(int role, int r, int c, int sigma, int cache_len, int n_pend, int P) {
     if (role == BM_ROLE_DRAFT) {

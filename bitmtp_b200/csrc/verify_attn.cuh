@@ -13,7 +13,8 @@
 //   * only history rows [0, cache_len) and the M rows of this replay are read,
 //     not the whole padded buffer of sigma + M rows;
 //   * the work is split over (kv head, 32-key chunk) CTAs and merged by a
-//     second kernel (split-KV), whose last CTA per row quantises the row.
+//     second kernel (split-KV) with one CTA per query row, which also quantises
+//     the row.
 //
 // Arithmetic and order: see bmo_attention in oracle/bm_oracle.c; the two agree
 // bit for bit.  All accumulation is fp32 on the CUDA cores in a fixed order;
@@ -21,9 +22,7 @@
 // could not be mirrored on the CPU.
 //
 // Scratch (caller-allocated, bm_verify_attention_scratch_bytes):
-//   ctr  int32 [32]            per-row arrival counters, must be zero on entry; the
-//                              kernel leaves them zero
-//   amax uint32 [32]           per-row absmax bits, same rule
+//   256 reserved bytes        (unused; kept zero)
 //   pm, pl fp32 [M, H, NC]     chunk max / chunk sum
 //   po   fp32 [M, H, NC, 128]  chunk numerators
 //   NC = ceil(sigma/32) + 1; chunk NC-1 holds the rows appended by this replay.
@@ -57,11 +56,120 @@ __host__ __device__ inline size_t attn_scratch_bytes(int M, int H, int sigma) {
     return 256 + (size_t)M * H * NC * 4 * 2 + (size_t)M * H * NC * 128 * 4;
 }
 
-// ---- kernel 1: one (chunk, kv head) ------------------------------------------------
-__global__ void __launch_bounds__(kAttnThreads, 1) attn_chunk_kernel(const AttnParams p) {
+// ---- kernel 1: one (chunk, kv head); a warp serves NQ query vectors at a time --------
+// lane = key in the score phase (NQ independent fma chains, one per query vector, each in
+// ascending d), lane = 4 output dims in the numerator phase (4*NQ independent chains, each
+// in ascending key order).  Shared memory: the chunk's K rows (padded), V rows, the query
+// vectors of this kv head as fp32, and the bf16-rounded softmax weights.
+constexpr int kAttnMinThreads = 128;           // staging uses at least 4 warps
+
+__host__ __device__ inline int attn_nq(int QV) {
+    return QV <= 16 ? 2 : (QV <= 32 ? 4 : 8);  // keeps ceil(QV/NQ) <= 8 warps up to QV = 64
+}
+
+template <int NQ>
+__device__ __forceinline__ void attn_chunk_pass(const AttnParams &p, const uint16_t *Ks, const uint16_t *Vs,
+                                                const float *Qs, float *Ps, int q0, int QV, int G,
+                                                int hk, int j, int c0, int cn, int lane, int role,
+                                                int cache_len, int n_pend, int P) {
+    // rows past QV repeat the last query vector; their results are dropped
+    const float *qrow[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) qrow[t] = Qs + (size_t)min(q0 + t, QV - 1) * 128;
+    float acc[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) acc[t] = 0.0f;
+    const uint16_t *krow = Ks + (lane < cn ? lane : 0) * kKeyStride;
+#pragma unroll 4
+    for (int u = 0; u < 16; ++u) {
+        float kf[8];
+        unpack8(*reinterpret_cast<const uint4 *>(krow + 8 * u), kf);
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {
+            const float4 qa = *reinterpret_cast<const float4 *>(qrow[t] + 8 * u);
+            const float4 qb = *reinterpret_cast<const float4 *>(qrow[t] + 8 * u + 4);
+            acc[t] = fmaf(qa.x, kf[0], acc[t]);
+            acc[t] = fmaf(qa.y, kf[1], acc[t]);
+            acc[t] = fmaf(qa.z, kf[2], acc[t]);
+            acc[t] = fmaf(qa.w, kf[3], acc[t]);
+            acc[t] = fmaf(qb.x, kf[4], acc[t]);
+            acc[t] = fmaf(qb.y, kf[5], acc[t]);
+            acc[t] = fmaf(qb.z, kf[6], acc[t]);
+            acc[t] = fmaf(qb.w, kf[7], acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+        const int qv = q0 + t;
+        if (qv >= QV) break;                           // warp-uniform
+        const int g = qv / p.M, m = qv - g * p.M;
+        const bool vis = lane < cn && bm_visible(role, m, c0 + lane, p.sigma, cache_len, n_pend, P);
+        const float sc = vis ? acc[t] * 0.08838834764831845f : -INFINITY;
+        const float mj = warp_max(sc);
+        const float pr = vis ? bm_expf(sc - mj) : 0.0f;
+        const float lj = warp_sum_butterfly(pr);
+        Ps[qv * 32 + lane] = bm_bf16_rn(pr);
+        if (lane == 0) {
+            const size_t o = ((size_t)m * p.H + hk * G + g) * p.NC + j;
+            p.pm[o] = mj;
+            p.pl[o] = lj;
+        }
+    }
+    __syncwarp();
+    // numerators: lane owns dims 4*lane .. 4*lane+3 of the NQ query vectors
+    const float *prow[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) prow[t] = Ps + min(q0 + t, QV - 1) * 32;
+    float o[NQ][4];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[t][e] = 0.0f;
+    for (int cb = 0; cb < cn; cb += 4) {
+        float v[4][4];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            // keys past cn have weight 0 and are given value 0
+            const uint2 raw = (cb + cc < cn)
+                                  ? *reinterpret_cast<const uint2 *>(Vs + (cb + cc) * 128 + 4 * lane)
+                                  : make_uint2(0u, 0u);
+            v[cc][0] = __uint_as_float(raw.x << 16);
+            v[cc][1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[cc][2] = __uint_as_float(raw.y << 16);
+            v[cc][3] = __uint_as_float(raw.y & 0xffff0000u);
+        }
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {
+            const float4 w = *reinterpret_cast<const float4 *>(prow[t] + cb);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[t][e] = fmaf(w.x, v[0][e], o[t][e]);
+                o[t][e] = fmaf(w.y, v[1][e], o[t][e]);
+                o[t][e] = fmaf(w.z, v[2][e], o[t][e]);
+                o[t][e] = fmaf(w.w, v[3][e], o[t][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+        const int qv = q0 + t;
+        if (qv >= QV) break;
+        const int g = qv / p.M, m = qv - g * p.M;
+        *reinterpret_cast<float4 *>(p.po + (((size_t)m * p.H + hk * G + g) * p.NC + j) * 128 + 4 * lane) =
+            make_float4(o[t][0], o[t][1], o[t][2], o[t][3]);
+    }
+    __syncwarp();
+}
+
+template <int NQ>
+__global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     pdl_launch_dependents();
-    if (p.pdl) pdl_wait();
+    // BM_PDL_STABLE_STATE: the step record and the history rows were written by launches
+    // that had completed before this call's chain of overlapped launches began, so they
+    // may be read while the predecessor is still running.
+    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
+    if (p.pdl && !early) pdl_wait();
     const int j = blockIdx.x, hk = blockIdx.y;
     const int cache_len = p.state->cache_len, n_pend = p.state->n_pend, role = p.state->role,
               P = p.state->P;
@@ -70,23 +178,25 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_chunk_kernel(const AttnP
     if (j == p.NC - 1) { c0 = p.sigma; cn = p.M; }
     else if (j < n_hist) { c0 = j * BM_ATTN_CHUNK; cn = min(BM_ATTN_CHUNK, cache_len - c0); }
     else return;
+    const bool fresh_rows = j == p.NC - 1;            // rows the predecessor appended
+    if (early && fresh_rows) pdl_wait();
 
     const int G = p.H / p.Hkv, QV = G * p.M;
     uint16_t *Ks = reinterpret_cast<uint16_t *>(dyn);                    // [32][136]
     uint16_t *Vs = Ks + 32 * kKeyStride;                                  // [32][128]
     float *Qs = reinterpret_cast<float *>(Vs + 32 * 128);                 // [QV][128]
-    float *Ss = Qs + (size_t)QV * 128;                                    // [QV][32]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *Ps = Qs + (size_t)QV * 128;                                    // [QV][32]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
 
     const uint16_t *kg = p.k_base + ((size_t)hk * p.kv_rows + c0) * 128;
     const uint16_t *vg = p.v_base + ((size_t)hk * p.kv_rows + c0) * 128;
-    for (int i = tid; i < cn * 16; i += kAttnThreads) {
+    for (int i = tid; i < cn * 16; i += nthr) {
         const int c = i >> 4, u = i & 15;
-        *reinterpret_cast<uint4 *>(Ks + c * kKeyStride + 8 * u) =
-            reinterpret_cast<const uint4 *>(kg)[i];
+        *reinterpret_cast<uint4 *>(Ks + c * kKeyStride + 8 * u) = reinterpret_cast<const uint4 *>(kg)[i];
         reinterpret_cast<uint4 *>(Vs)[i] = reinterpret_cast<const uint4 *>(vg)[i];
     }
-    for (int i = tid; i < QV * 16; i += kAttnThreads) {
+    if (early && !fresh_rows) pdl_wait();             // the query rows come from the predecessor
+    for (int i = tid; i < QV * 16; i += nthr) {
         const int qv = i >> 4, u = i & 15;
         const int g = qv / p.M, m = qv - g * p.M;
         float f[8];
@@ -97,154 +207,125 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_chunk_kernel(const AttnP
     }
     __syncthreads();
 
-    // Scores: lane = key, the key row in registers, query vectors broadcast.
-    {
-        float kf[128];
-        if (lane < cn) {
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-                float f[8];
-                unpack8(*reinterpret_cast<const uint4 *>(Ks + lane * kKeyStride + 8 * u), f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) kf[8 * u + e] = f[e];
-            }
-        } else {
-#pragma unroll
-            for (int d = 0; d < 128; ++d) kf[d] = 0.0f;
-        }
-        for (int qv = warp; qv < QV; qv += kAttnThreads / 32) {
-            const float4 *qp = reinterpret_cast<const float4 *>(Qs + (size_t)qv * 128);
-            float acc = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 32; ++u) {
-                const float4 qq = qp[u];
-                acc = fmaf(qq.x, kf[4 * u], acc);
-                acc = fmaf(qq.y, kf[4 * u + 1], acc);
-                acc = fmaf(qq.z, kf[4 * u + 2], acc);
-                acc = fmaf(qq.w, kf[4 * u + 3], acc);
-            }
-            const int m = qv % p.M;
-            const bool vis = lane < cn && bm_visible(role, m, c0 + lane, p.sigma, cache_len, n_pend, P);
-            const float sc = vis ? acc * 0.08838834764831845f : -INFINITY;
-            const float mj = warp_max(sc);
-            const float pr = vis ? bm_expf(sc - mj) : 0.0f;
-            const float lj = warp_sum_butterfly(pr);
-            Ss[qv * 32 + lane] = bm_bf16_rn(pr);
-            if (lane == 0) {
-                const int g = qv / p.M;
-                const size_t o = ((size_t)m * p.H + hk * G + g) * p.NC + j;
-                p.pm[o] = mj;
-                p.pl[o] = lj;
-            }
-        }
-    }
-    __syncthreads();
-
-    // Numerators: thread = (d, half of the query vectors), the V column in registers.
-    {
-        const int d = tid & 127, half = tid >> 7;
-        float vf[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) vf[c] = c < cn ? bf16_bits_to_f32(Vs[c * 128 + d]) : 0.0f;
-        for (int qv = half; qv < QV; qv += 2) {
-            const float4 *pp = reinterpret_cast<const float4 *>(Ss + qv * 32);
-            float acc = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float4 w = pp[u];
-                // Positions >= cn hold weight 0 and value 0: fma(0, 0, acc) == acc.
-                acc = fmaf(w.x, vf[4 * u], acc);
-                acc = fmaf(w.y, vf[4 * u + 1], acc);
-                acc = fmaf(w.z, vf[4 * u + 2], acc);
-                acc = fmaf(w.w, vf[4 * u + 3], acc);
-            }
-            const int g = qv / p.M, m = qv - g * p.M;
-            p.po[(((size_t)m * p.H + hk * G + g) * p.NC + j) * 128 + d] = acc;
-        }
-    }
+    const int nwarps = nthr >> 5;
+    for (int q0 = warp * NQ; q0 < QV; q0 += nwarps * NQ)
+        attn_chunk_pass<NQ>(p, Ks, Vs, Qs, Ps, q0, QV, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P);
 }
 
-// ---- kernel 2: merge chunks for (row m, head pair); last CTA of a row quantises it --
-__global__ void __launch_bounds__(kAttnThreads) attn_merge_kernel(const AttnParams p) {
-    __shared__ float w_s[2][160];        // merge weights per head of the pair (NC <= 160 => sigma <= 5088)
-    __shared__ float pl_s[2][160];
-    __shared__ float l_s[2];
-    __shared__ float red[kAttnThreads / 32];
-    __shared__ int is_last;
+// ---- kernel 2: one CTA per query row merges the chunks of every head and quantises ----
+// Thread = 2 consecutive dims of one head.  The chunk numerators of a batch of up to 16
+// chunks are requested first, so that their latencies overlap each other and the weight
+// computation: per head (one warp each) the merge weights exp(m_j - max) and the ordered sum
+// of l_j * w_j.  Then the numerators are merged in ascending chunk order, divided by l and
+// rounded to bf16; the row's absmax is a block reduction and the INT8 codes follow from a
+// shared-memory copy of the row.  No cross-CTA hand-off.
+constexpr int kMergeMaxHeads = 32;
+constexpr int kMergeThreads = 1024;
+constexpr int kMergeBatch = 16;
+
+__global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ float l_s[kMergeMaxHeads];
+    __shared__ float red[kMergeThreads / 32];
     pdl_launch_dependents();
-    if (p.pdl) pdl_wait();
-    const int m = blockIdx.y, h0 = blockIdx.x * 2;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
+    if (p.pdl && !early) pdl_wait();
+    const int m = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
     const int cache_len = p.state->cache_len;
+    if (early) pdl_wait();
     const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
     const int nv = n_hist + 1;                        // valid chunks: history, then NC-1
+    uint16_t *row_s = reinterpret_cast<uint16_t *>(dyn);                  // [H*128] bf16 row
+    float *w_s = reinterpret_cast<float *>(row_s + (size_t)p.H * 128);    // [H][nv] weights
+    const int pairs = p.H * 64;                       // 2-dim units of the row
+    const int nwarps = nthr >> 5;
 
-    if (warp < 2) {                                   // warp w: weights of head h0 + w
-        const size_t base = ((size_t)m * p.H + h0 + warp) * p.NC;
-        // chunk maxima and sums come into shared memory with independent loads; the ordered
-        // sum below then runs on shared-memory operands
-        float gmax = -INFINITY;
-        for (int i = lane; i < nv; i += 32) {
-            const int j = i < n_hist ? i : p.NC - 1;
-            const float mj = p.pm[base + j];
-            w_s[warp][i] = mj;
-            pl_s[warp][i] = p.pl[base + j];
-            gmax = fmaxf(gmax, mj);
+    float amax = 0.0f;
+    for (int base = 0; base < pairs; base += nthr) {
+        const int u = base + tid;
+        const bool live = u < pairs;
+        const int h = live ? (u >> 6) : 0, d0 = (u & 63) * 2;
+        const float *src = p.po + ((size_t)m * p.H + h) * p.NC * 128 + d0;
+        float o0 = 0.0f, o1 = 0.0f;
+        for (int b0 = 0; b0 < nv; b0 += kMergeBatch) {
+            const int nb = min(kMergeBatch, nv - b0);
+            float2 part[kMergeBatch];
+#pragma unroll
+            for (int i = 0; i < kMergeBatch; ++i) {
+                const int c = b0 + i;
+                const int j = c < n_hist ? c : p.NC - 1;
+                part[i] = (live && i < nb) ? *reinterpret_cast<const float2 *>(src + (size_t)j * 128)
+                                           : make_float2(0.0f, 0.0f);
+            }
+            if (base == 0 && b0 == 0) {
+                // weights of every head, while the numerators are in flight
+                for (int hh = warp; hh < p.H; hh += nwarps) {
+                    const size_t pb = ((size_t)m * p.H + hh) * p.NC;
+                    float gmax = -INFINITY;
+                    float pl0 = 0.0f;                  // chunk sum of this lane's first chunk
+                    for (int i = lane; i < nv; i += 32) {
+                        const int jj = i < n_hist ? i : p.NC - 1;
+                        const float mj = p.pm[pb + jj];
+                        if (i < 32) pl0 = p.pl[pb + jj];
+                        w_s[hh * nv + i] = mj;
+                        gmax = fmaxf(gmax, mj);
+                    }
+                    gmax = warp_max(gmax);
+                    float l = 0.0f;
+                    for (int i0 = 0; i0 < nv; i0 += 32) {
+                        const int i = i0 + lane;
+                        float w = 0.0f, pl = 0.0f;
+                        if (i < nv) {
+                            const float mj = w_s[hh * nv + i];
+                            w = mj > -INFINITY ? bm_expf(mj - gmax) : 0.0f;
+                            pl = i0 == 0 ? pl0 : p.pl[pb + (i < n_hist ? i : p.NC - 1)];
+                            w_s[hh * nv + i] = w;
+                        }
+                        // ordered sum; a chunk without a visible key has weight 0 and sum 0
+                        const int cnt = min(32, nv - i0);
+                        for (int k = 0; k < cnt; ++k)
+                            l = fmaf(__shfl_sync(0xffffffffu, pl, k), __shfl_sync(0xffffffffu, w, k), l);
+                    }
+                    if (lane == 0) l_s[hh] = l;
+                }
+                __syncthreads();
+            }
+#pragma unroll
+            for (int i = 0; i < kMergeBatch; ++i) {
+                if (i < nb) {
+                    // a chunk without a visible key has weight 0 and a zero numerator
+                    const float w = w_s[h * nv + b0 + i];
+                    o0 = fmaf(part[i].x, w, o0);
+                    o1 = fmaf(part[i].y, w, o1);
+                }
+            }
         }
-        gmax = warp_max(gmax);
-        for (int i = lane; i < nv; i += 32) {
-            const float mj = w_s[warp][i];
-            w_s[warp][i] = mj > -INFINITY ? bm_expf(mj - gmax) : 0.0f;
-        }
-        __syncwarp();
-        if (lane == 0) {
-            float l = 0.0f;
-            // a chunk without a visible key has weight 0 and sum 0: fma(0, 0, l) == l
-            for (int i = 0; i < nv; ++i) l = fmaf(pl_s[warp][i], w_s[warp][i], l);
-            l_s[warp] = l;
+        if (live) {
+            const float l = l_s[h];
+            const float v0 = bm_bf16_rn(o0 / l), v1 = bm_bf16_rn(o1 / l);
+            amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+            reinterpret_cast<uint32_t *>(row_s)[u] =
+                (uint32_t)bm_f32_to_bf16(v0) | ((uint32_t)bm_f32_to_bf16(v1) << 16);
         }
     }
-    __syncthreads();
-    const int hh = tid >> 7, d = tid & 127, h = h0 + hh;
-    const size_t obase = ((size_t)m * p.H + h) * p.NC;
-    float o = 0.0f;
-#pragma unroll 4
-    for (int i = 0; i < nv; ++i) {
-        const int j = i < n_hist ? i : p.NC - 1;
-        const float w = w_s[hh][i];
-        // A chunk without a visible key has weight 0 and a zero numerator; skipping it
-        // and adding 0 * 0 are the same value, so no branch is needed.
-        o = fmaf(p.po[(obase + j) * 128 + d], w, o);
-    }
-    const float val = bm_bf16_rn(o / l_s[hh]);
-    const size_t row = (size_t)m * p.H * 128;
-    p.att[row + h * 128 + d] = bm_f32_to_bf16(val);
-    __threadfence();                                  // publish before this CTA is counted
-    const float a = block_max(fabsf(val), red, lane, warp, kAttnThreads / 32);
-    if (tid == 0) {
-        atomicMax(&p.amax[m], __float_as_uint(a));
-        __threadfence();
-        const int arrived = atomicAdd(&p.ctr[m], 1);
-        is_last = (arrived == (int)gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    const float amax = __uint_as_float(atomicOr(&p.amax[m], 0u));
+    amax = block_max(amax, red, lane, warp, nwarps);   // also orders the row_s writes
     const float s = bm_act_scale(amax);
-    const int units = p.H * 128 / 8;
-    for (int u0 = 0; u0 < units; u0 += kAttnThreads) {
-        const int u = u0 + tid;
+    const int units = p.H * 16;                       // 8-dim units of the row
+    const size_t row = (size_t)m * p.H * 128;
+    for (int base = 0; base < units; base += nthr) {
+        if (base + warp * 32 >= units) break;          // warp-uniform
+        const int u = base + tid;
         const bool active = u < units;
         float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (active) unpack8(__ldcg(reinterpret_cast<const uint4 *>(p.att + row) + u), f);
+        if (active) {
+            const uint4 raw = reinterpret_cast<const uint4 *>(row_s)[u];
+            unpack8(raw, f);
+            if (p.att) reinterpret_cast<uint4 *>(p.att + row)[u] = raw;
+        }
         emit_codes(p.q_out, row, p.H * 128, u, quant8(f, s), active, lane);
     }
-    if (tid == 0) {
-        p.s_out[m] = s;
-        p.amax[m] = 0u;
-        p.ctr[m] = 0;
-    }
+    if (tid == 0) p.s_out[m] = s;
 }
 
 }  // namespace bm

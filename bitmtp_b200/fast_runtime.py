@@ -156,7 +156,7 @@ class GraphAtlas:
             return self.model.forward_sdlm_decode_graph_kernel(
                 token_values=tokens_buf, positions=positions_buf, kv_full=kv_full, block_size=M,
                 attn_mask=state, logits_start=ls, logits_end=le, lm_head_precision="t2",
-                attn_scratch=scratch, logits_buf=logits_buf)
+                attn_scratch=scratch, logits_buf=logits_buf, stable_state=True)
 
         # One eager pass on a side stream (sets kernel attributes, proves the launch
         # sequence), then capture.

@@ -417,6 +417,7 @@ class Transformer(nn.Module):
         *,
         attn_scratch: Optional[torch.Tensor] = None,
         logits_buf: Optional[torch.Tensor] = None,
+        stable_state: bool = False,
     ) -> torch.Tensor:
         """The replay body (reference: model.py:1363-1404, 1119-1137, 958-1009, 1053-1064).
 
@@ -427,6 +428,10 @@ class Transformer(nn.Module):
         place at rows [sigma, sigma+M) of every layer's views.  Returns fp32 logits
         [logits_end - logits_start, vocab] holding bf16-rounded values, as the reference's
         `.float()` of a bf16 head output does.
+
+        `stable_state`: the caller guarantees that `attn_mask` and the history rows were
+        written by launches that finished before this forward's first launch (a captured
+        replay); the attention then reads them without waiting for the preceding kernel.
         """
         if lm_head_precision not in ("t2",):
             raise RuntimeError(f"unsupported lm_head precision: {lm_head_precision!r}")
@@ -437,6 +442,7 @@ class Transformer(nn.Module):
         rows = logits_end - logits_start
         W = self.workspace(M)
         pdl = self.use_pdl
+        attn_pdl = (native.PDL_OVERLAP | native.PDL_STABLE_STATE) if (pdl and stable_state) else int(pdl)
         k0 = kv_full[0][0]
         kv_rows = k0.stride(-3) // a.head_dim
         sigma = k0.shape[-2] - M
@@ -465,7 +471,7 @@ class Transformer(nn.Module):
                                      _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
                                      pdl=pdl, q_out=W.qrot)
             ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                 attn_mask, attn_scratch, pdl=pdl, out=(W.att, None, W.att_s),
+                                 attn_mask, attn_scratch, pdl=attn_pdl, out=(W.att, None, W.att_s),
                                  prep=(W.att_q, W.att_sum))
             ops.t2_gemv_prepared(W.att_q, W.att_sum, at.o_proj.weight.data, W.att_s,
                                  at.o_proj.weight_scale, out=W.attn_out, ldc=a.dim, pdl=pdl)

@@ -31,6 +31,7 @@ BM_EINVAL = 22
 OUT_BF16, OUT_F32, OUT_F32_OF_BF16 = 0, 1, 2
 PATH_AUTO, PATH_DP4A, PATH_MMA = 0, 1, 2
 ROLE_DRAFT, ROLE_VERIFY, ROLE_AR = 0, 1, 2
+PDL_OVERLAP, PDL_STABLE_STATE = 1, 2
 
 _lib = None
 

@@ -29,6 +29,15 @@ extern "C" {
 #define BM_OUT_F32_OF_BF16 2   /* C is fp32 holding the bf16-rounded value (logits) */
 
 /* consumer selection for bm_t2_gemv */
+/* `pdl` values (bit mask).  BM_PDL_OVERLAP: the launch may start before the previous kernel
+ * of the stream has finished and waits for it on the device before reading its output.
+ * BM_PDL_STABLE_STATE (bm_verify_attention only, with BM_PDL_OVERLAP): the caller promises
+ * that the step record and the history rows [0, cache_len) were written by launches that
+ * completed before the current run of overlapped launches began (true for a captured
+ * replay whose record is set before the graph launch), so they are read without waiting. */
+#define BM_PDL_OVERLAP 1
+#define BM_PDL_STABLE_STATE 2
+
 #define BM_PATH_AUTO 0
 #define BM_PATH_DP4A 1
 #define BM_PATH_MMA 2
@@ -153,9 +162,9 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma);
  *   q bf16 [M, H, 128]; k_base, v_base bf16 [Hkv, kv_rows, 128]; history rows are
  *   [0, cache_len), the M rows of this replay sit at [sigma, sigma + M);
  *   state: the record written by bm_set_step_state;
- *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned; its first 256
- *   bytes must be zero before the first call and are left zero by every call;
- *   att_out bf16 [M, H*128]; q_out / q_prep / asum: the quantised rows (see
+ *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned, contents
+ *   irrelevant on entry (every word read by a call is written by that call);
+ *   att_out bf16 [M, H*128] or NULL; q_out / q_prep / asum: the quantised rows (see
  *   bm_quant_rows); s_out fp32 [M].
  * Visibility follows the reference's draft / verify / ar masks.  Replaces the
  * attention and o-projection input quantisation of
