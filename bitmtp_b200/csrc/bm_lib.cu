@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/bitmtp_b200.h"
 #include "bm_common.cuh"
 
@@ -468,6 +470,62 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------- attention without allocation
+// Some hosts cannot give the attention a scratch buffer: a C or Go service that owns no
+// device allocator of its own, a plugin that runs where the embedding runtime has handed
+// all free device memory to its pool, or a latency-critical loop in which a device
+// allocation is unwelcome because it synchronises the whole device.  For them the partial
+// results of the split-KV attention go into a fixed array that is part of the loaded module,
+// so nothing is allocated or freed by the call, by this library or by a library under it.
+//
+// The array is shared by every call on a device: two calls whose execution can overlap
+// (different streams, or different host threads) race on it and must be serialised by the
+// caller.  No word of it has to be initialised; each call writes what it later reads.
+constexpr size_t kStaticAttnScratchBytes = BM_STATIC_ATTN_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void *g_static_attn_ptr[kMaxDevices];      // device address of the array, per device
+static std::mutex g_static_attn_mutex;
+
+// Looks the array's address up on the current device, once per device.  The look-up is a
+// runtime call, so the first call on a device should be made outside stream capture.
+static int static_attn_scratch(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (dev < 0 || dev >= kMaxDevices) return BM_EINVAL;
+    std::lock_guard<std::mutex> lock(g_static_attn_mutex);
+    if (g_static_attn_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
+        if (e != cudaSuccess) return cuda_status(e);
+        if (ptr == nullptr) return BM_EINVAL;
+        g_static_attn_ptr[dev] = ptr;
+    }
+    *out = g_static_attn_ptr[dev];
+    return BM_OK;
+}
+
+int bm_verify_attention_static(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv,
+                               int kv_rows, int sigma, const void *state, void *att_out, void *q_out,
+                               void *q_prep, void *asum, void *s_out, int pdl, void *stream) {
+    if (M < 1 || H < 1 || sigma < 0) return BM_EINVAL;
+    const size_t need = bm::attn_scratch_bytes(M, H, sigma);
+    if (need > kStaticAttnScratchBytes) {
+        fprintf(stderr,
+                "bm_verify_attention_static: M=%d H=%d sigma=%d needs %zu scratch bytes, the built-in array "
+                "holds %zu; use bm_verify_attention with caller scratch\n",
+                M, H, sigma, need, kStaticAttnScratchBytes);
+        return BM_ETOOBIG;
+    }
+    void *scratch = nullptr;
+    const int rc = static_attn_scratch(&scratch);
+    if (rc != BM_OK) return rc;
+    return bm_verify_attention(q, k_base, v_base, M, H, Hkv, kv_rows, sigma, state, scratch, att_out, q_out,
+                               q_prep, asum, s_out, pdl, stream);
 }
 
 }  // extern "C"

@@ -28,6 +28,8 @@ NVCC_FLAGS = [
 
 BM_OK = 0
 BM_EINVAL = 22
+BM_ETOOBIG = 27
+STATIC_ATTN_SCRATCH_BYTES = 8 << 20     # BM_STATIC_ATTN_SCRATCH_BYTES of the header
 OUT_BF16, OUT_F32, OUT_F32_OF_BF16 = 0, 1, 2
 PATH_AUTO, PATH_DP4A, PATH_MMA = 0, 1, 2
 ROLE_DRAFT, ROLE_VERIFY, ROLE_AR = 0, 1, 2
@@ -101,6 +103,7 @@ def _declare_optional(L) -> None:
         "bm_kv_copy_rows": [vp, ci, ci, ci, ci, ci, vp],
         "bm_verify_attention_scratch_bytes": [ci, ci, ci],
         "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
+        "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],

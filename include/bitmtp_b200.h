@@ -21,6 +21,7 @@ extern "C" {
 
 #define BM_OK 0
 #define BM_EINVAL 22
+#define BM_ETOOBIG 27          /* the request exceeds a built-in limit               */
 #define BM_ECUDA_BASE 1000
 
 /* out_kind for bm_t2_gemv */
@@ -174,6 +175,21 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
                         int Hkv, int kv_rows, int sigma, const void *state, void *scratch,
                         void *att_out, void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
                         void *stream);
+
+/* bm_verify_attention for callers that cannot provide scratch memory; it has no
+ * counterpart in the reference.  Same arguments without `scratch`: the chunk partials go to
+ * an array built into the library (BM_STATIC_ATTN_SCRATCH_BYTES per device), so the call
+ * allocates and frees nothing.  Requests whose
+ * bm_verify_attention_scratch_bytes(M, H, sigma) exceeds that size return BM_ETOOBIG
+ * (16 rows x 16 heads fit up to sigma = 1984; 1 row x 16 heads up to sigma = 32224).
+ * The first call on a device looks the array's address up and should therefore be made
+ * before any stream capture on that device.  All calls on a device share the one array:
+ * calls that may execute at the same time must be serialised by the caller. */
+#define BM_STATIC_ATTN_SCRATCH_BYTES (8u << 20)
+int bm_verify_attention_static(const void *q, const void *k_base, const void *v_base, int M, int H,
+                               int Hkv, int kv_rows, int sigma, const void *state, void *att_out,
+                               void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
+                               void *stream);
 
 /* Row argmax (lowest index on ties): logits fp32 [rows, ld] -> idx int64 [rows],
  * optional max_out fp32 [rows].  Replaces `.argmax(dim=-1)` on the logit rows
