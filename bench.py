@@ -43,11 +43,14 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["decode", "gemv", "gemv-one"])
+    ap.add_argument("--workload", default=None, choices=["decode", "gemv", "gemv-one", "gemv-nsplit"])
     ap.add_argument("--shape", default="151936x2048", help="gemv-one: NxK")
     ap.add_argument("--w", type=int, default=1, help="gemv-one: width")
-    ap.add_argument("--path", default="auto", choices=["auto", "dp4a", "mma"])
+    ap.add_argument("--path", default="auto", choices=["auto", "dp4a", "mma", "rowwarp"])
     ap.add_argument("--calls", type=int, default=0, help="gemv-one: launches per step")
+    ap.add_argument("--pdl", action="store_true",
+                    help="gemv workloads: programmatic dependent launch between the calls, as in the decode replay")
+    ap.add_argument("--tune", type=int, default=0, help="gemv-one: tuning value passed in bits 8.. of the path")
     ap.add_argument("--mode", default="hybrid", choices=["ar", "conf", "spec", "hybrid"])
     ap.add_argument("--model", default="1p7b", choices=["1p7b", "4b", "tiny"])
     ap.add_argument("--prompt-len", type=int, default=None)
@@ -169,10 +172,10 @@ class GemvSet:
     """Device-resident GEMV problems whose weights together exceed L2 several times over,
     so that back-to-back calls always stream from HBM."""
 
-    def __init__(self, device, shapes_w, min_bytes=512 << 20, path=0, seed=0):
+    def __init__(self, device, shapes_w, min_bytes=512 << 20, path=0, seed=0, pdl=False):
         import torch
         from bitmtp_b200 import native, ops
-        self.ops, self.native, self.path = ops, native, path
+        self.ops, self.native, self.path, self.pdl = ops, native, path, pdl
         self.calls = []
         gen = torch.Generator(device="cpu").manual_seed(seed)
         per_pass = sum(n * k // 4 for (_, n, k, _) in shapes_w)
@@ -190,7 +193,7 @@ class GemvSet:
 
     def run_pass(self):
         for (A, B, s, ws, C, w, n, k) in self.calls:
-            self.ops.t2_gemv(A, B, s, ws, path=self.path, out=C, ldc=n)
+            self.ops.t2_gemv(A, B, s, ws, path=self.path, out=C, ldc=n, pdl=self.pdl)
 
 
 def capture(fn, device):
@@ -255,7 +258,7 @@ def run_gemv(args, world, rank, local, dist):
     from bitmtp_b200 import native, ops
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    path = {"auto": 0, "dp4a": 1, "mma": 2}[args.path]
+    path = {"auto": 0, "dp4a": 1, "mma": 2, "rowwarp": 3}[args.path] | (args.tune << 8)
     if args.workload == "gemv-one":
         n, k = (int(x) for x in args.shape.lower().split("x"))
         shapes_w = [("one", n, k, args.w)]
@@ -265,7 +268,7 @@ def run_gemv(args, world, rank, local, dist):
         shapes_w = [(nm, n, k, w) for w in SWEEP_W for (nm, n, k) in LAYER_SHAPES]
         min_bytes = 768 << 20
         label = "T2-g128 GEMV sweep, Qwen3-1.7B layer shapes, W in {1,2,4,8}"
-    gs = GemvSet(device, shapes_w, min_bytes=min_bytes, path=path)
+    gs = GemvSet(device, shapes_w, min_bytes=min_bytes, path=path, pdl=args.pdl)
     if args.calls:
         gs.calls = gs.calls[: args.calls]
         gs.bytes_per_pass = sum(ops.gemv_bytes(w, n, k) for (_, _, _, _, _, w, n, k) in gs.calls)
@@ -313,7 +316,7 @@ def run_gemv(args, world, rank, local, dist):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8 x ternary -> s32",
         "data": "synthetic", "config": {"workload": label, "l2": "weights rotate over "
                                         f"{gs.copies} distinct copies ({gs.copies * sum(n * k // 4 for (_, n, k, _) in shapes_w) >> 20} MiB) > L2",
-                                        "timing": "CUDA events around graph replays"},
+                                        "timing": "CUDA events around graph replays", "pdl": bool(args.pdl)},
         "gpu_launches": launches, "clocks": clocks,
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
@@ -338,6 +341,8 @@ def run_reference_gemv(args, rank):
     if args.workload == "gemv-one":
         n, k = (int(x) for x in args.shape.lower().split("x"))
         shapes_w = [("one", n, k, args.w)]
+    elif args.workload == "gemv-nsplit":
+        shapes_w = [("wide", 28672, 8192, 1), ("wide", 28672, 8192, 8)]
     else:
         shapes_w = [(nm, n, k, w) for w in SWEEP_W for (nm, n, k) in LAYER_SHAPES]
     import numpy as np
@@ -392,6 +397,9 @@ def main():
     if args.workload == "decode":
         from bitmtp_b200.benchmarks import run_decode
         out = run_decode(args, world, rank, local, dist)
+    elif args.workload == "gemv-nsplit":
+        from bitmtp_b200.benchmarks import run_nsplit
+        out = run_nsplit(args, world, rank, local, dist)
     else:
         out = run_gemv(args, world, rank, local, dist)
     if rank == 0:

@@ -240,6 +240,105 @@ def cpu_decode_baseline(model_name: str, M: int, layers: int = 1, more_layers: i
                       f"({t_full * 1e3:.0f} ms per replay)"}
 
 
+def run_nsplit(args, world, rank, local, dist):
+    """Wide-layer stress shape (K = 8192 -> N = 28672) split by output rows over the ranks:
+    every rank streams its own N/world rows and the [W, N/world] slices are all-gathered
+    with NCCL, so that every rank ends with the full output.  Total work is fixed (strong
+    scaling); value = algorithmic bytes of the whole layer / time per call (max over ranks).
+    Each rank rotates over enough distinct copies of its shard to exceed L2."""
+    import bench
+    from . import native, ops, synthetic
+    from .nsplit import NSplitLinear, shard_rows
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    N, K = 28672, 8192
+    widths = (1, 8)
+    steps = args.steps or 20
+    warmup = args.warmup if args.warmup is not None else 5
+    n0, n1 = shard_rows(N, world, rank)
+    rows = n1 - n0
+    shard_bytes = rows * K // 4
+    copies = max(2, -(-(256 << 20) // shard_bytes))
+    gen = torch.Generator(device=device).manual_seed(1 + rank)
+
+    def gemv(a, s_, weight, scale, out):
+        ops.t2_gemv(a, weight, s_, scale, out=out, ldc=out.shape[1])
+
+    layers = []
+    for _ in range(copies):
+        w_, sc = synthetic.device_ternary(rows, K, gen, device)
+        layers.append(NSplitLinear(w_, sc, rank=rank, world=world, gemv=gemv, sharded=True))
+    gen_cpu = torch.Generator().manual_seed(7)          # activations are replicated: same seed everywhere
+    acts = {w: (torch.randint(-127, 128, (w, K), generator=gen_cpu, dtype=torch.int8),
+                (torch.rand(w, generator=gen_cpu) * 40 + 20)) for w in widths}
+    dev_acts = {w: (a.to(device), s_.to(device)) for w, (a, s_) in acts.items()}
+    host_acts = {w: (a.pin_memory(), s_.pin_memory()) for w, (a, s_) in acts.items()}
+
+    def one_pass():
+        for w in widths:
+            a, s_ = dev_acts[w]
+            for lin in layers:
+                lin.forward(a, s_)
+
+    def e2e_pass():
+        outs = []
+        for w in widths:
+            ha, hs = host_acts[w]
+            a, s_ = ha.to(device, non_blocking=True), hs.to(device, non_blocking=True)
+            for lin in layers:
+                outs.append(lin.forward(a, s_)[:, :8].float().sum().cpu())   # result read back every call
+        return outs
+
+    for _ in range(warmup):
+        one_pass()
+    bench.barrier(dist)
+    sampler = bench.ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_pass()
+    e1.record()
+    bench.barrier(dist)
+    clocks = sampler.stop()
+    ms = bench.max_over_ranks(dist, e0.elapsed_time(e1), device)
+    calls = len(widths) * copies
+    layer_bytes = sum(ops.gemv_bytes(w, N, K) for w in widths) * copies     # whole layer, all ranks
+    value = layer_bytes * steps / (ms * 1e-3) / 1e9
+    shard_alg = sum(ops.gemv_bytes(w, rows, K) for w in widths) * copies
+    gbs_rank = shard_alg * steps / (ms * 1e-3) / 1e9
+
+    e2e_pass()
+    bench.barrier(dist)
+    t0 = time.time()
+    e2e_steps = max(1, min(steps, 5))
+    for _ in range(e2e_steps):
+        e2e_pass()
+    bench.barrier(dist)
+    e2e_s = bench.max_over_ranks(dist, time.time() - t0, device)
+    err = native.lib().bm_device_error()
+    if err:
+        raise RuntimeError(f"device error word = {err}")
+    peak, peak_kind = bench.peaks()
+    return {
+        "metric": "T2-g128 GEMV algorithmic HBM GB/s", "value": round(value, 2), "unit": "GB/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8 x ternary -> s32",
+        "data": "synthetic",
+        "config": {"workload": f"N-split of the 8192->28672 layer over {world} GPU(s), W in {{1,8}}, bf16 outputs "
+                               "all-gathered with NCCL after every GEMV",
+                   "l2": f"each rank rotates over {copies} copies of its {shard_bytes >> 20} MiB shard (> L2)",
+                   "timing": "CUDA events around eager launches, max over ranks"},
+        "gpu_launches": calls * steps, "clocks": clocks,
+        "e2e": {"value": round(layer_bytes * e2e_steps / e2e_s / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": sum(w * K + 4 * w for w in widths), "d2h_bytes_per_step": 4 * calls},
+        "roofline": {"bound": "hbm", "achieved": round(gbs_rank, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(gbs_rank / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                     "kernel": f"t2_gemv on this rank's {rows} x {K} shard, all-gather time included",
+                     "frac_of_8TBps": round(gbs_rank / 8000.0, 4)},
+    }
+
+
 def run_reference_decode(args) -> dict:
     """CPU arm of bench.py: the oracle port of the reference path on all host threads, on a
     bounded sample of the same workload (see cpu_decode_baseline)."""

@@ -13,6 +13,11 @@
 #include "t2_gemv.cuh"
 #include "fused_ops.cuh"
 #include "verify_attn.cuh"
+#include "t2_gemv_rowwarp.cuh"
+
+#include <cudaTypedefs.h>
+#include <map>
+#include <tuple>
 
 namespace {
 
@@ -231,6 +236,101 @@ int gemv_launch_mma(const bm::GemvParams &p0, int sms, int pdl, int force_rb, cu
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- row-per-warp GEMV: tensor maps ------------------------------------------------
+// A tiled TMA copy needs a 128-byte descriptor of the weight matrix.  It is encoded by the
+// driver on first use of a (device, pointer, N, K) and kept; the encode routine is looked up
+// through the runtime, so the library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+int weight_tensor_map(const void *B, int N, int K, CUtensorMap *out) {
+    static std::mutex mu;
+    static EncodeTiledFn encode = nullptr;
+    static std::map<std::tuple<int, const void *, int, int>, CUtensorMap> cache;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e);
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_tuple(dev, B, N, K);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return BM_OK; }
+    if (encode == nullptr) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return cuda_status(e);
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return BM_EINVAL;
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    CUtensorMap tm;
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 4), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 4)};
+    const cuuint32_t box[2] = {(cuuint32_t)bm::kRwPanelBytes, (cuuint32_t)bm::kRwRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(B), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return BM_ECUDA_BASE + 999;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = tm;
+    *out = tm;
+    return BM_OK;
+}
+
+// Warps per CTA and panels per stage of the row-per-warp kernel.  `force` (tuning aid) packs
+// warps in bits 0..4 and log2(panels per stage) + 1 in bits 5..6; 0 = defaults.
+struct RowWarpCfg { int warps, pb; };
+
+inline RowWarpCfg rowwarp_cfg(int W, int K, int force) {
+    RowWarpCfg c;
+    const int pcode = (force >> 5) & 3;
+    c.pb = pcode == 1 ? 1 : (pcode == 2 ? 2 : (pcode == 3 ? 4 : 2));
+    int warps = force & 31;
+    if (warps < 1 || warps > bm::kRwMaxWarps) warps = bm::kRwMaxWarps;
+    // keep at least two stages per warp
+    while (warps > 4 && bm::rowwarp_smem_layout(W, K, warps, c.pb).stages < 2) --warps;
+    c.warps = warps;
+    return c;
+}
+
+bool rowwarp_fits(int W, int N, int K, int force = 0) {
+    if (W > 8 || (K % 512) != 0 || (N % bm::kRwRows) != 0) return false;
+    const RowWarpCfg c = rowwarp_cfg(W, K, force);
+    return bm::rowwarp_smem_layout(W, K, c.warps, c.pb).stages >= 2;
+}
+
+template <int NTOK, int PB>
+int launch_rowwarp(const bm::RowWarpParams &P, int warps, int sms, int pdl, cudaStream_t stream) {
+    const bm::RowWarpSmem L = bm::rowwarp_smem_layout(P.g.W, P.g.K, warps, PB);
+    const int blocks = P.g.N / bm::kRwRows;
+    int grid = (blocks + warps - 1) / warps;
+    if (grid > sms) grid = sms;
+    const size_t smem = (size_t)L.total + 1024;
+    if (P.g.G != nullptr)
+        return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, true>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
+    return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, false>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
+}
+
+int gemv_launch_rowwarp(const bm::GemvParams &p0, int sms, int pdl, int force, cudaStream_t stream) {
+    if (!rowwarp_fits(p0.W, p0.N, p0.K, force)) return BM_EINVAL;
+    bm::RowWarpParams P;
+    const int rc = weight_tensor_map(p0.B, p0.N, p0.K, &P.tmap);
+    if (rc != BM_OK) return rc;
+    P.g = p0;
+    P.g.pdl = pdl;
+    const RowWarpCfg c = rowwarp_cfg(p0.W, p0.K, force);
+    if (p0.W == 1) {
+        if (c.pb == 1) return launch_rowwarp<1, 1>(P, c.warps, sms, pdl, stream);
+        if (c.pb == 2) return launch_rowwarp<1, 2>(P, c.warps, sms, pdl, stream);
+        return launch_rowwarp<1, 4>(P, c.warps, sms, pdl, stream);
+    }
+    if (c.pb == 1) return launch_rowwarp<2, 1>(P, c.warps, sms, pdl, stream);
+    if (c.pb == 2) return launch_rowwarp<2, 2>(P, c.warps, sms, pdl, stream);
+    return launch_rowwarp<2, 4>(P, c.warps, sms, pdl, stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -267,7 +367,7 @@ int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void 
 int bm_t2_gemv_prepared(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s,
                         const void *ws, int W, int N, int K, int ldc, int out_kind, int pdl, void *stream) {
     if (!a_sums || (K % 256) != 0) return BM_EINVAL;
-    return gemv_common(A_prep, a_sums, B, C, s, ws, W, N, K, ldc, out_kind, BM_PATH_MMA, nullptr, pdl, stream);
+    return gemv_common(A_prep, a_sums, B, C, s, ws, W, N, K, ldc, out_kind, BM_PATH_AUTO, nullptr, pdl, stream);
 }
 
 static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
@@ -297,7 +397,13 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     // has it.  Odd group counts go to the lanes-across-K consumer.
     const int force_rb = (path >> 8) & 0xff;          // tuning aid: BM_PATH_MMA | (rows_per_tile/8 << 8)
     path &= 0xff;
-    if (path == BM_PATH_AUTO) path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
+    if (path == BM_PATH_AUTO) {
+        // Many rows and at most 8 tokens: every warp streams its own rows.  With fewer than about
+        // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner.
+        if (rowwarp_fits(W, N, K) && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
+        else path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
+    }
+    if (path == BM_PATH_ROWWARP) return gemv_launch_rowwarp(p, sms, pdl, force_rb, st);
     if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
     if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, force_rb, st) : BM_EINVAL;
     return BM_EINVAL;

@@ -42,6 +42,7 @@ extern "C" {
 #define BM_PATH_AUTO 0
 #define BM_PATH_DP4A 1
 #define BM_PATH_MMA 2
+#define BM_PATH_ROWWARP 3      /* W <= 8, K % 512 == 0, N % 16 == 0: a warp per 16-row block */
 
 /* Library / build identification: returns a static string. */
 const char *bm_version(void);

@@ -163,3 +163,42 @@ def test_linearity_property_full_size():
     _, g2 = ops.t2_gemv(a2, B, one, ws, want_groups=True)
     _, g12 = ops.t2_gemv((a1 + a2).contiguous(), B, one, ws, want_groups=True)
     assert torch.equal(g12, g1 + g2)
+
+
+ROWWARP = [(1, 16, 512), (2, 64, 512), (3, 48, 1024), (8, 2048, 2048), (5, 2048, 6144), (4, 6144, 2560),
+           (8, 2560, 9728), (7, 12288, 2048), (1, 151936, 2048), (8, 28672, 8192), (6, 4096, 4096)]
+
+
+@pytest.mark.parametrize("W,N,K", ROWWARP)
+def test_row_per_warp_consumer(oracle, W, N, K):
+    """The W <= 8 streaming kernel (a warp per 16-row block, tiled TMA panels), forced at
+    every size: group sums, fp32 and bf16 outputs bit for bit."""
+    _check(oracle, synthetic.gemv_case(W, N, K, seed=W * 77 + N + K), native.PATH_ROWWARP)
+
+
+def test_row_per_warp_rejects_what_it_cannot_serve():
+    dev = torch.device("cuda:0")
+    for (W, N, K) in [(9, 64, 512), (2, 24, 512), (2, 64, 256)]:
+        case = synthetic.gemv_case(W, N, K, seed=1)
+        A, B, ws, s = (case[k].to(dev) for k in ("A", "B", "ws", "s"))
+        with pytest.raises(native.NativeError):
+            ops.t2_gemv(A, B, s, ws, path=native.PATH_ROWWARP)
+
+
+def test_prepared_activations_on_the_head_shape(oracle):
+    """GEMV-ready activations through the automatic choice, which is the row-per-warp kernel
+    for the 151936-row head at W <= 8 and the cooperative tiles at W = 16."""
+    dev = torch.device("cuda:0")
+    for W in (1, 8, 16):
+        case = synthetic.gemv_case(W, 151936, 2048, seed=50 + W)
+        y32, _, _ = oracle.t2_gemv(case["A"].numpy(), case["B"].numpy().view(np.uint8),
+                                   oracle.torch_to_u16(case["ws"]), case["s"].numpy())
+        A = case["A"].to(dev)
+        # GEMV-ready form of the same codes: 4x4 byte transpose per 16-run + group sums
+        prep = A.view(W, -1, 4, 4).transpose(2, 3).contiguous().view(W, -1)
+        asum = A.view(W, -1, 128).to(torch.int32).sum(-1).to(torch.int32).contiguous()
+        out = torch.empty(W, 151936, dtype=torch.float32, device=dev)
+        ops.t2_gemv_prepared(prep, asum, case["B"].to(dev), case["s"].to(dev), case["ws"].to(dev), out=out,
+                             out_kind=native.OUT_F32)
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), y32.view(np.uint32))
+    assert native.lib().bm_device_error() == 0
