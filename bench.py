@@ -348,7 +348,8 @@ def run_reference_gemv(args, rank):
     import numpy as np
     from oracle import oracle as O
     from bitmtp_b200 import synthetic
-    from bitmtp_b200.native import lib  # noqa: F401  (byte formula only)
+    # every host core, also under a launcher that exports OMP_NUM_THREADS=1 for its ranks
+    O.lib().bmo_set_num_threads(len(os.sched_getaffinity(0)))
     cases = []
     for (name, n, k, w) in shapes_w:
         c = synthetic.gemv_case(w, n, k, seed=0)

@@ -209,6 +209,8 @@ def cpu_decode_baseline(model_name: str, M: int, layers: int = 1, more_layers: i
     geometry = dict(getattr(synthetic, GEOMETRIES[model_name]))
     full_layers = geometry["n_layers"]
     sigma = 1024
+    # every host core, also under a launcher that exports OMP_NUM_THREADS=1 for its ranks
+    O.lib().bmo_set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
 
     def best_time(n_layers: int) -> float:
         cfg = synthetic.make_config(dict(geometry, n_layers=n_layers), block_size=8)
