@@ -14,6 +14,7 @@
 #include "fused_ops.cuh"
 #include "verify_attn.cuh"
 #include "t2_gemv_rowwarp.cuh"
+#include "decode_sweep.cuh"
 
 #include <cudaTypedefs.h>
 #include <map>
@@ -533,16 +534,21 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
     p.pdl = pdl;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
-    const int nq = bm::attn_nq(QV);
-    int warps = (QV + nq - 1) / nq;
+    // Many query vectors: two CTAs per (chunk, kv head), each with half of them, so that more
+    // warps are resident per chunk (the per-warp instruction stream is what bounds this kernel).
+    const int qsplit = QV >= 16 ? 2 : 1;
+    const int qv_cta = (QV + qsplit - 1) / qsplit;
+    const int nq = bm::attn_nq(qv_cta);
+    int warps = (qv_cta + nq - 1) / nq;
     if (warps > bm::kAttnThreads / 32) warps = bm::kAttnThreads / 32;
     const int threads = 32 * warps < bm::kAttnMinThreads ? bm::kAttnMinThreads : 32 * warps;
     const size_t msmem = (size_t)H * 128 * 2 + (size_t)H * NC * sizeof(float);
     if (smem > 200 * 1024 || msmem > 200 * 1024) return BM_EINVAL;
     int rc;
-    if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
-    else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
-    else rc = launch_ex(bm::attn_chunk_kernel<8>, dim3(NC, Hkv), dim3(threads), smem, st, pdl, p);
+    const dim3 grid(NC, Hkv, qsplit);
+    if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, grid, dim3(threads), smem, st, pdl, p);
+    else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, grid, dim3(threads), smem, st, pdl, p);
+    else rc = launch_ex(bm::attn_chunk_kernel<8>, grid, dim3(threads), smem, st, pdl, p);
     if (rc != BM_OK) return rc;
     int mthreads = H * 64 < bm::kMergeThreads ? H * 64 : bm::kMergeThreads;
     mthreads = (mthreads + 31) / 32 * 32;
@@ -576,6 +582,78 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------- layer sweep
+int bm_decode_sweep(const bm_sweep_args *a, void *stream) {
+    if (!a || !a->layers || !a->tokens || !a->positions || !a->embed || !a->cos_t || !a->sin_t || !a->state ||
+        !a->attn_scratch || !a->h || !a->xq || !a->xsum || !a->xs || !a->xqkv || !a->attq || !a->attsum ||
+        !a->atts || !a->attn_out || !a->inner || !a->inner_amax || !a->iq || !a->isum || !a->is_ ||
+        !a->ffn_out || !a->barrier)
+        return BM_EINVAL;
+    if (a->n_layers < 1 || a->M < 1 || a->M > 16 || a->dim != 2048 || a->H * 128 != 2048 || a->ffn != 6144 ||
+        a->Hkv < 1 || (a->H % a->Hkv) != 0 || a->sigma < 0 || a->kv_rows < a->sigma + a->M)
+        return BM_EINVAL;
+    bm::SweepParams p;
+    p.layers = static_cast<const bm::SweepLayer *>(a->layers);
+    p.n_layers = a->n_layers; p.M = a->M; p.dim = a->dim; p.H = a->H; p.Hkv = a->Hkv; p.ffn = a->ffn;
+    p.kv_rows = a->kv_rows; p.sigma = a->sigma;
+    p.NC = (a->sigma + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK + 1;
+    p.eps = a->eps;
+    p.tokens = static_cast<const int64_t *>(a->tokens);
+    p.positions = static_cast<const int64_t *>(a->positions);
+    p.embed = static_cast<const uint16_t *>(a->embed);
+    p.cos_t = static_cast<const uint16_t *>(a->cos_t);
+    p.sin_t = static_cast<const uint16_t *>(a->sin_t);
+    p.state = static_cast<const bm::StepState *>(a->state);
+    p.h = static_cast<uint16_t *>(a->h);
+    p.xq = static_cast<int8_t *>(a->xq);
+    p.xsum = static_cast<int32_t *>(a->xsum);
+    p.xs = static_cast<float *>(a->xs);
+    p.xqkv = static_cast<uint16_t *>(a->xqkv);
+    char *sc = static_cast<char *>(a->attn_scratch);
+    p.pm = reinterpret_cast<float *>(sc + 256);
+    p.pl = p.pm + (size_t)a->M * a->H * p.NC;
+    p.po = p.pl + (size_t)a->M * a->H * p.NC;
+    p.attq = static_cast<int8_t *>(a->attq);
+    p.attsum = static_cast<int32_t *>(a->attsum);
+    p.atts = static_cast<float *>(a->atts);
+    p.attn_out = static_cast<uint16_t *>(a->attn_out);
+    p.inner = static_cast<uint16_t *>(a->inner);
+    p.inner_amax = static_cast<unsigned int *>(a->inner_amax);
+    p.iq = static_cast<int8_t *>(a->iq);
+    p.isum = static_cast<int32_t *>(a->isum);
+    p.is_ = static_cast<float *>(a->is_);
+    p.ffn_out = static_cast<uint16_t *>(a->ffn_out);
+    p.bar = static_cast<unsigned int *>(a->barrier);
+    p.timing = static_cast<unsigned long long *>(a->timing);
+    const int G = a->H / a->Hkv, QV = G * a->M;
+    size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;   // attention
+    const size_t merge = (size_t)a->H * 128 * 2 + (size_t)a->H * p.NC * sizeof(float);
+    const size_t gemv = (size_t)bm::kGemvWarps * 16 * 40 * sizeof(float);
+    if (merge > smem) smem = merge;
+    if (gemv > smem) smem = gemv;
+    if (smem > 200 * 1024) return BM_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaFuncSetAttribute(bm::decode_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bm::decode_sweep_kernel, bm::kSweepThreads, smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (per_sm < 1) return BM_EINVAL;
+    e = cudaMemsetAsync(a->barrier, 0, 8, st);
+    if (e != cudaSuccess) return cuda_status(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(current_device().sm_count);
+    cfg.blockDim = dim3(bm::kSweepThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once: the barrier needs it
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, bm::decode_sweep_kernel, p));
 }
 
 // ---------------------------------------------------------- attention without allocation

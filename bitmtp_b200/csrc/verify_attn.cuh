@@ -196,7 +196,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnPara
         reinterpret_cast<uint4 *>(Vs)[i] = reinterpret_cast<const uint4 *>(vg)[i];
     }
     if (early && !fresh_rows) pdl_wait();             // the query rows come from the predecessor
-    for (int i = tid; i < QV * 16; i += nthr) {
+    const int qs_per = (QV + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int qs_lo = (int)blockIdx.z * qs_per, qs_hi = min(QV, qs_lo + qs_per);
+    for (int i = qs_lo * 16 + tid; i < qs_hi * 16; i += nthr) {
         const int qv = i >> 4, u = i & 15;
         const int g = qv / p.M, m = qv - g * p.M;
         float f[8];
@@ -207,9 +209,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnPara
     }
     __syncthreads();
 
+    // The query vectors of the kv head are dealt to gridDim.z CTAs (more resident warps per
+    // chunk when there are many of them): this CTA serves [q_lo, q_hi).
+    const int per = (QV + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int q_lo = (int)blockIdx.z * per, q_hi = min(QV, q_lo + per);
     const int nwarps = nthr >> 5;
-    for (int q0 = warp * NQ; q0 < QV; q0 += nwarps * NQ)
-        attn_chunk_pass<NQ>(p, Ks, Vs, Qs, Ps, q0, QV, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P);
+    for (int q0 = q_lo + warp * NQ; q0 < q_hi; q0 += nwarps * NQ)
+        attn_chunk_pass<NQ>(p, Ks, Vs, Qs, Ps, q0, q_hi, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P);
 }
 
 // ---- kernel 2: one CTA per query row merges the chunks of every head and quantises ----
@@ -223,17 +229,12 @@ constexpr int kMergeMaxHeads = 32;
 constexpr int kMergeThreads = 1024;
 constexpr int kMergeBatch = 16;
 
-__global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnParams p) {
-    extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ float l_s[kMergeMaxHeads];
-    __shared__ float red[kMergeThreads / 32];
-    pdl_launch_dependents();
-    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
-    if (p.pdl && !early) pdl_wait();
-    const int m = blockIdx.x;
+// Row m of the merge: all threads of the CTA (any multiple of 32 up to kMergeThreads); `dyn` holds
+// H*128 bf16 + H*nv floats, `l_s` kMergeMaxHeads floats, `red` one float per warp.  The chunk
+// partials are read through L2 (ld.global.cg): in the persistent decode kernel another SM wrote them.
+__device__ __forceinline__ void attn_merge_row(const AttnParams &p, int m, int cache_len, unsigned char *dyn,
+                                               float *l_s, float *red) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
-    const int cache_len = p.state->cache_len;
-    if (early) pdl_wait();
     const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
     const int nv = n_hist + 1;                        // valid chunks: history, then NC-1
     uint16_t *row_s = reinterpret_cast<uint16_t *>(dyn);                  // [H*128] bf16 row
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnPar
             for (int i = 0; i < kMergeBatch; ++i) {
                 const int c = b0 + i;
                 const int j = c < n_hist ? c : p.NC - 1;
-                part[i] = (live && i < nb) ? *reinterpret_cast<const float2 *>(src + (size_t)j * 128)
+                part[i] = (live && i < nb) ? __ldcg(reinterpret_cast<const float2 *>(src + (size_t)j * 128))
                                            : make_float2(0.0f, 0.0f);
             }
             if (base == 0 && b0 == 0) {
@@ -266,8 +267,8 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnPar
                     float pl0 = 0.0f;                  // chunk sum of this lane's first chunk
                     for (int i = lane; i < nv; i += 32) {
                         const int jj = i < n_hist ? i : p.NC - 1;
-                        const float mj = p.pm[pb + jj];
-                        if (i < 32) pl0 = p.pl[pb + jj];
+                        const float mj = __ldcg(p.pm + pb + jj);
+                        if (i < 32) pl0 = __ldcg(p.pl + pb + jj);
                         w_s[hh * nv + i] = mj;
                         gmax = fmaxf(gmax, mj);
                     }
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnPar
                         if (i < nv) {
                             const float mj = w_s[hh * nv + i];
                             w = mj > -INFINITY ? bm_expf(mj - gmax) : 0.0f;
-                            pl = i0 == 0 ? pl0 : p.pl[pb + (i < n_hist ? i : p.NC - 1)];
+                            pl = i0 == 0 ? pl0 : __ldcg(p.pl + pb + (i < n_hist ? i : p.NC - 1));
                             w_s[hh * nv + i] = w;
                         }
                         // ordered sum; a chunk without a visible key has weight 0 and sum 0
@@ -326,6 +327,19 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnPar
         emit_codes(p.q_out, row, p.H * 128, u, quant8(f, s), active, lane);
     }
     if (tid == 0) p.s_out[m] = s;
+}
+
+
+__global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ float l_s[kMergeMaxHeads];
+    __shared__ float red[kMergeThreads / 32];
+    pdl_launch_dependents();
+    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
+    if (p.pdl && !early) pdl_wait();
+    const int cache_len = p.state->cache_len;
+    if (early) pdl_wait();
+    attn_merge_row(p, blockIdx.x, cache_len, dyn, l_s, red);
 }
 
 }  // namespace bm

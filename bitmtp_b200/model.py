@@ -328,6 +328,10 @@ class StepWorkspace:
         self.att_sum = buf((M, q_dim // 128), i32)
         self.i_sum = buf((M, args.ffn_dim // 128), i32)
         self.h_sum = buf((M, args.dim // 128), i32)
+        # extra buffers of the persistent layer kernel
+        self.inner = buf((M, args.ffn_dim), bf)
+        self.inner_amax = torch.zeros((M,), dtype=i32, device=device)
+        self.sweep_barrier = torch.zeros((2,), dtype=i32, device=device)
         self.n_pad = n_pad
 
 
@@ -347,6 +351,12 @@ class Transformer(nn.Module):
         # successor start early (GEMVs then request their weight tiles while the predecessor
         # is still running) and waits for its predecessor before touching activations.
         self.use_pdl = os.environ.get("BM_PDL", "1") != "0"
+        # One persistent kernel for the whole layer stack of a replay (bm_decode_sweep), where the
+        # geometry allows it.  Bit-identical to the operator-by-operator launches but measured
+        # slower on B200 (one 8-warp CTA per SM hides less latency than several resident CTAs of
+        # the stand-alone kernels), so it is opt-in: BM_SWEEP=1.
+        self.use_sweep = os.environ.get("BM_SWEEP", "0") == "1"
+        self._sweep_tables = {}
 
     def tie_weights(self) -> None:
         # plain attribute, not a registered parameter: the state dict keeps the reference's keys
@@ -394,6 +404,81 @@ class Transformer(nn.Module):
             layer.attention.prepare_merged_weights(max_positions, tables=tables)
             layer.feed_forward.prepare_merged_weights()
         self.max_positions = max_positions
+
+    def _layers_by_operator(self, W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
+                            pdl, attn_pdl) -> None:
+        """The layer stack as ten launches per layer (every geometry, every width)."""
+        a = self.args
+        M = W.M
+        eps = a.norm_eps
+        L0 = self.layers[0]
+        # INT8 activations go from their producer to the next GEMV in GEMV-ready order
+        # (16-runs transposed 4x4, plus per-group sums), so no GEMV CTA permutes or sums them.
+        qsink = {"h": W.h, "qp": W.q, "asum": W.q_sum, "s": W.s}
+        ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
+                          gather=token_values, pdl=pdl, out=qsink)
+        for i, layer in enumerate(self.layers):
+            at, ff = layer.attention, layer.feed_forward
+            if i > 0:
+                ops.rmsnorm_fused(W.ffn_out, layer.input_layernorm.weight.data, eps, M=M, res=W.h,
+                                  pdl=pdl, out=qsink)
+            ops.t2_gemv_prepared(W.q, W.q_sum, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv,
+                                 ldc=W.xqkv.shape[1], pdl=pdl)
+            k_l, v_l = kv_full[i]
+            ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
+                                     at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                     _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                     pdl=pdl, q_out=W.qrot)
+            ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                 attn_mask, attn_scratch, pdl=attn_pdl, out=(W.att, None, W.att_s),
+                                 prep=(W.att_q, W.att_sum))
+            ops.t2_gemv_prepared(W.att_q, W.att_sum, at.o_proj.weight.data, W.att_s,
+                                 at.o_proj.weight_scale, out=W.attn_out, ldc=a.dim, pdl=pdl)
+            ops.rmsnorm_fused(W.h, layer.post_attention_layernorm.weight.data, eps, M=M,
+                              res=W.attn_out, pdl=pdl, out=qsink)
+            ops.t2_gemv_prepared(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu,
+                                 ldc=W.gu.shape[1], pdl=pdl)
+            ops.silu_mul_quant(W.gu, pdl=pdl, out=(None, W.is_), prep=(W.iq, W.i_sum))
+            ops.t2_gemv_prepared(W.iq, W.i_sum, ff.down_proj.weight.data, W.is_,
+                                 ff.down_proj.weight_scale, out=W.ffn_out, ldc=a.dim, pdl=pdl)
+
+    def _sweep_layer_table(self, kv_full, kv_rows: int) -> torch.Tensor:
+        """Device table of the 14 pointers per layer bm_decode_sweep reads, for one KV buffer.
+        Built on first use (outside graph capture: the atlas runs one eager pass first)."""
+        key = (kv_full[0][0].data_ptr(), kv_full[0][1].data_ptr(), kv_rows, len(kv_full))
+        tab = self._sweep_tables.get(key)
+        if tab is not None:
+            return tab
+        rows = []
+        for layer, (k_l, v_l) in zip(self.layers, kv_full):
+            at, ff = layer.attention, layer.feed_forward
+            tensors = (at.wqkv_weight, at.o_proj.weight.data, ff.w_gu, ff.down_proj.weight.data,
+                       at.wqkv_scale, at.o_proj.weight_scale, ff.w_gu_scale, ff.down_proj.weight_scale,
+                       layer.input_layernorm.weight.data, layer.post_attention_layernorm.weight.data,
+                       at.q_norm.weight.data, at.k_norm.weight.data, k_l, v_l)
+            rows.append([t.data_ptr() for t in tensors])
+        if len(self._sweep_tables) > 64:
+            self._sweep_tables.clear()
+        tab = torch.tensor(rows, dtype=torch.int64).to(self.embed_tokens.weight.device)
+        self._sweep_tables[key] = tab
+        return tab
+
+    def _sweep_layers(self, W: "StepWorkspace", token_values, positions, kv_full, kv_rows: int, sigma: int,
+                      attn_mask, attn_scratch) -> None:
+        a = self.args
+        L0 = self.layers[0].attention
+        sa = native.SweepArgs()
+        sa.layers = self._sweep_layer_table(kv_full, kv_rows).data_ptr()
+        sa.n_layers, sa.M, sa.dim, sa.H, sa.Hkv, sa.ffn = a.n_layers, W.M, a.dim, a.n_heads, a.n_kv_heads, a.ffn_dim
+        sa.kv_rows, sa.sigma, sa.eps = kv_rows, sigma, a.norm_eps
+        for name, t in (("tokens", token_values), ("positions", positions), ("embed", self.embed_tokens.weight.data),
+                        ("cos_t", L0.rope_cos), ("sin_t", L0.rope_sin), ("state", attn_mask),
+                        ("attn_scratch", attn_scratch), ("h", W.h), ("xq", W.q), ("xsum", W.q_sum), ("xs", W.s),
+                        ("xqkv", W.xqkv), ("attq", W.att_q), ("attsum", W.att_sum), ("atts", W.att_s),
+                        ("attn_out", W.attn_out), ("inner", W.inner), ("inner_amax", W.inner_amax), ("iq", W.iq),
+                        ("isum", W.i_sum), ("is_", W.is_), ("ffn_out", W.ffn_out), ("barrier", W.sweep_barrier)):
+            setattr(sa, name, t.data_ptr())
+        ops.decode_sweep(sa, token_values.device)
 
     def workspace(self, M: int) -> StepWorkspace:
         ws = self._workspaces.get(M)
@@ -452,36 +537,12 @@ class Transformer(nn.Module):
         if logits_buf is None:
             logits_buf = torch.empty((rows, W.n_pad), dtype=torch.float32, device=dev)
         eps = a.norm_eps
-        L0 = self.layers[0]
-        # INT8 activations go from their producer to the next GEMV in GEMV-ready order
-        # (16-runs transposed 4x4, plus per-group sums), so no GEMV CTA permutes or sums them.
-        qsink = {"h": W.h, "qp": W.q, "asum": W.q_sum, "s": W.s}
-        ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
-                          gather=token_values, pdl=pdl, out=qsink)
-        for i, layer in enumerate(self.layers):
-            at, ff = layer.attention, layer.feed_forward
-            if i > 0:
-                ops.rmsnorm_fused(W.ffn_out, layer.input_layernorm.weight.data, eps, M=M, res=W.h,
-                                  pdl=pdl, out=qsink)
-            ops.t2_gemv_prepared(W.q, W.q_sum, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv,
-                                 ldc=W.xqkv.shape[1], pdl=pdl)
-            k_l, v_l = kv_full[i]
-            ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
-                                     at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
-                                     _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                     pdl=pdl, q_out=W.qrot)
-            ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                 attn_mask, attn_scratch, pdl=attn_pdl, out=(W.att, None, W.att_s),
-                                 prep=(W.att_q, W.att_sum))
-            ops.t2_gemv_prepared(W.att_q, W.att_sum, at.o_proj.weight.data, W.att_s,
-                                 at.o_proj.weight_scale, out=W.attn_out, ldc=a.dim, pdl=pdl)
-            ops.rmsnorm_fused(W.h, layer.post_attention_layernorm.weight.data, eps, M=M,
-                              res=W.attn_out, pdl=pdl, out=qsink)
-            ops.t2_gemv_prepared(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu,
-                                 ldc=W.gu.shape[1], pdl=pdl)
-            ops.silu_mul_quant(W.gu, pdl=pdl, out=(None, W.is_), prep=(W.iq, W.i_sum))
-            ops.t2_gemv_prepared(W.iq, W.i_sum, ff.down_proj.weight.data, W.is_,
-                                 ff.down_proj.weight_scale, out=W.ffn_out, ldc=a.dim, pdl=pdl)
+        if self.use_sweep and ops.sweep_supported(a.dim, a.n_heads, a.head_dim, a.ffn_dim, M) \
+                and token_values.is_contiguous() and positions.is_contiguous():
+            self._sweep_layers(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch)
+        else:
+            self._layers_by_operator(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
+                                     pdl, attn_pdl)
         # h + ffn_out, final norm of the logit rows, INT8 quantisation for the packed head
         ops.rmsnorm_fused(W.h, self.norm.weight.data, eps, M=rows, res=W.ffn_out, row0=logits_start,
                           pdl=pdl, out={"qp": W.hq, "asum": W.h_sum, "s": W.hs})

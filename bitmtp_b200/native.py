@@ -17,7 +17,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO_PATH = os.path.join(HERE, "libbitmtp_b200.so")
 SOURCES = ["bm_lib.cu"]
-HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh"]
+HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh",
+           "decode_sweep.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -62,6 +63,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return SO_PATH
 
 
+class SweepArgs(ctypes.Structure):
+    """bm_sweep_args of include/bitmtp_b200.h."""
+    _fields_ = ([("layers", ctypes.c_void_p)]
+                + [(n, ctypes.c_int) for n in ("n_layers", "M", "dim", "H", "Hkv", "ffn", "kv_rows", "sigma")]
+                + [("eps", ctypes.c_float), ("reserved", ctypes.c_int)]
+                + [(n, ctypes.c_void_p) for n in (
+                    "tokens", "positions", "embed", "cos_t", "sin_t", "state", "attn_scratch", "h", "xq", "xsum",
+                    "xs", "xqkv", "attq", "attsum", "atts", "attn_out", "inner", "inner_amax", "iq", "isum", "is_",
+                    "ffn_out", "barrier", "timing")])
+
+
 class NativeError(RuntimeError):
     pass
 
@@ -104,6 +116,7 @@ def _declare_optional(L) -> None:
         "bm_verify_attention_scratch_bytes": [ci, ci, ci],
         "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
+        "bm_decode_sweep": [ctypes.POINTER(SweepArgs), vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],

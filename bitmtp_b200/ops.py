@@ -235,3 +235,17 @@ def verify_accept(draft: torch.Tensor, verify: torch.Tensor, D: int, *, out=None
     check(native.lib().bm_verify_accept(_ptr(draft), _ptr(verify), D, _ptr(n), _stream(draft.device)),
           "bm_verify_accept")
     return n
+
+
+# --------------------------------------------------------------------------- layer sweep
+SWEEP_LAYER_FIELDS = 14
+
+
+def sweep_supported(dim: int, n_heads: int, head_dim: int, ffn_dim: int, M: int) -> bool:
+    """Geometry the persistent layer kernel serves (bm_decode_sweep)."""
+    return dim == 2048 and head_dim == 128 and n_heads * head_dim == 2048 and ffn_dim == 6144 and 1 <= M <= 16
+
+
+def decode_sweep(args: "native.SweepArgs", device) -> None:
+    """All layers of one replay in one launch; `args` is a filled native.SweepArgs."""
+    check(native.lib().bm_decode_sweep(ctypes.byref(args), _stream(device)), "bm_decode_sweep")

@@ -192,6 +192,40 @@ int bm_verify_attention_static(const void *q, const void *k_base, const void *v_
                                void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
                                void *stream);
 
+/* All transformer layers of one decode replay in ONE persistent kernel launch: per layer
+ * (residual add +) RMSNorm + quant, qkv GEMV, q/k norm + RoPE + KV append + block-verify attention,
+ * o GEMV, residual add + RMSNorm + quant, gate|up GEMV + SiLU*up + quant, down GEMV — the body of
+ * the layer loop of Transformer.forward_sdlm_decode_graph_kernel
+ * (src/bonsai_sft/gpu/model.py:1386-1399 with 1119-1137, 958-1009, 1053-1064).  Results are
+ * bit-identical to calling the operators above one by one.
+ *   layers   device array, 14 pointers per layer: packed codes of wqkv [(H+2Hkv)*128, dim/4],
+ *            wo [dim, H*128/4], gate|up [2*ffn, dim/4], down [dim, ffn/4]; their bf16 scales in
+ *            the same order; input_layernorm, post_attention_layernorm, q_norm, k_norm weights
+ *            (bf16); the layer's K and V planes [Hkv, kv_rows, 128] (bf16)
+ *   tokens, positions int64 [M]; embed bf16 [vocab, dim]; cos_t / sin_t bf16 [max_pos, 128];
+ *   state: bm_set_step_state record; attn_scratch: bm_verify_attention_scratch_bytes(M, H, sigma)
+ *   workspace (caller-allocated, contents irrelevant on entry): h, attn_out, ffn_out bf16 [M, dim];
+ *   xq int8 [M, dim] + xsum int32 [M, dim/128] + xs fp32 [M]; xqkv bf16 [M, (H+2Hkv)*128];
+ *   attq int8 [M, H*128] + attsum + atts; inner bf16 [M, ffn]; inner_amax uint32 [M];
+ *   iq int8 [M, ffn] + isum + is; barrier: 8 bytes (zeroed by the call).
+ * On return (stream order) h and ffn_out hold the residual stream and the last down projection,
+ * i.e. the inputs of the final norm, and the K/V rows [sigma, sigma+M) of every layer are written.
+ * Serves dim == 2048, H*128 == 2048, ffn == 6144, head_dim 128, M <= 16; anything else is
+ * BM_EINVAL and the caller uses the operators.  One CTA per SM, launched cooperatively; the
+ * stages are separated by a bounded software grid barrier (bm_device_error() = 3 on expiry). */
+typedef struct bm_sweep_args {
+    const void *layers;
+    int n_layers, M, dim, H, Hkv, ffn, kv_rows, sigma;
+    float eps;
+    int reserved;
+    const void *tokens, *positions, *embed, *cos_t, *sin_t, *state;
+    void *attn_scratch;
+    void *h, *xq, *xsum, *xs, *xqkv, *attq, *attsum, *atts, *attn_out, *inner, *inner_amax, *iq, *isum,
+        *is_, *ffn_out, *barrier;
+    void *timing; /* optional uint64 [19]: %globaltimer (ns) of CTA 0 in layer 1: [2k] stage k starts, [2k+1] its work is done, [18] end */
+} bm_sweep_args;
+int bm_decode_sweep(const bm_sweep_args *args, void *stream);
+
 /* Row argmax (lowest index on ties): logits fp32 [rows, ld] -> idx int64 [rows],
  * optional max_out fp32 [rows].  Replaces `.argmax(dim=-1)` on the logit rows
  * (src/bonsai_sft/gpu/fast_generate.py:786, 809, 1079). */
