@@ -60,24 +60,29 @@ def _gemv_roofline(model, M: int, device, steps: int = 20):
     from . import native, ops
     a = model.args
     W = model.workspace(M)
-    rows = min(M, a.block_size + 1)
+    rows = a.block_size if M > a.block_size + 1 else M     # logit rows of a draft / verify / AR replay
     logits = torch.empty((rows, W.n_pad), dtype=torch.float32, device=device)
     calls, nbytes = 0, 0
 
+    pdl = model.use_pdl
+
     def gemvs():
+        # the GEMV launches of one replay as the replay issues them: GEMV-ready activations,
+        # programmatic dependent launch between consecutive kernels
         nonlocal calls, nbytes
         calls, nbytes = 0, 0
         for layer in model.layers:
             at, ff = layer.attention, layer.feed_forward
-            for (A, s, w, ws, out) in ((W.q, W.s, at.wqkv_weight, at.wqkv_scale, W.xqkv),
-                                       (W.att_q, W.att_s, at.o_proj.weight.data, at.o_proj.weight_scale, W.attn_out),
-                                       (W.q, W.s, ff.w_gu, ff.w_gu_scale, W.gu),
-                                       (W.iq, W.is_, ff.down_proj.weight.data, ff.down_proj.weight_scale, W.ffn_out)):
-                ops.t2_gemv(A, w, s, ws, out=out, ldc=out.shape[1])
+            for (A, asum, s, w, ws, out) in (
+                    (W.q, W.q_sum, W.s, at.wqkv_weight, at.wqkv_scale, W.xqkv),
+                    (W.att_q, W.att_sum, W.att_s, at.o_proj.weight.data, at.o_proj.weight_scale, W.attn_out),
+                    (W.q, W.q_sum, W.s, ff.w_gu, ff.w_gu_scale, W.gu),
+                    (W.iq, W.i_sum, W.is_, ff.down_proj.weight.data, ff.down_proj.weight_scale, W.ffn_out)):
+                ops.t2_gemv_prepared(A, asum, w, s, ws, out=out, ldc=out.shape[1], pdl=pdl)
                 calls += 1
                 nbytes += ops.gemv_bytes(M, w.shape[0], w.shape[1] * 4)
-        ops.t2_gemv(W.hq[:rows], model._lm_head_t2_w, W.hs[:rows], model._lm_head_t2_scale,
-                    out_kind=native.OUT_F32_OF_BF16, out=logits, ldc=W.n_pad)
+        ops.t2_gemv_prepared(W.hq[:rows], W.h_sum[:rows], model._lm_head_t2_w, W.hs[:rows], model._lm_head_t2_scale,
+                             out_kind=native.OUT_F32_OF_BF16, out=logits, ldc=W.n_pad, pdl=pdl)
         calls += 1
         nbytes += ops.gemv_bytes(rows, W.n_pad, a.dim, native.OUT_F32)
 
@@ -85,6 +90,8 @@ def _gemv_roofline(model, M: int, device, steps: int = 20):
         t.random_(-127, 128)
     for t in (W.s, W.att_s, W.is_, W.hs):
         t.fill_(30.0)
+    for t in (W.q_sum, W.att_sum, W.i_sum, W.h_sum):      # any integers: only the timing matters here
+        t.random_(-4000, 4000)
     gemvs()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -179,14 +186,14 @@ def run_decode(args, world, rank, local, dist):
                    "timing": "value = timed decode tokens / decode seconds as the reference defines them "
                              "(first token and prefill excluded, host clock between device synchronisations); "
                              "ms_per_step and e2e = CUDA events around whole generate calls",
-                   "l2": "376 MB of packed weights are streamed per replay (3x L2)",
+                   "l2": f"{rf['bytes'] / 1e6:.0f} MB of packed weights and scales are streamed per replay (> 3x L2)",
                    "one_request_stream_per_gpu": world > 1},
         "gpu_launches": launches, "clocks": clocks,
         "e2e": {"value": round(e2e, 2), "unit": "tok/s (prefill + all new tokens, host prompt in, tokens out)",
                 "h2d_bytes_per_step": prompt_len * 8, "d2h_bytes_per_step": new_tokens * 8},
         "roofline": {"bound": "hbm", "achieved": round(rf["gbs"], 1), "peak": peak, "unit": "GB/s",
                      "frac": round(rf["gbs"] / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                     "kernel": f"t2_gemv_mma_kernel, the {rf['calls']} GEMV launches of one width-{roof_m} "
+                     "kernel": f"t2_gemv (cooperative-tile and row-per-warp kernels), the {rf['calls']} GEMV launches of one width-{roof_m} "
                                f"replay ({rf['bytes'] / 1e6:.1f} MB algorithmic, {rf['us_per_launch']:.2f} us "
                                "average per launch)",
                      "frac_of_8TBps": round(rf["gbs"] / 8000.0, 4)},
