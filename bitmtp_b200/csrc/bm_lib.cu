@@ -357,8 +357,17 @@ int64_t bm_t2_gemv_bytes(int W, int N, int K, int out_kind) {
            esz * W * N;
 }
 
+struct PeerArgs {
+    int world, rank;
+    void *const *peer_C0;      // first output buffer of every rank
+    void *const *peer_C1;      // second output buffer of every rank
+    void *const *peer_flags;
+    void *done;                // uint32 [2]
+};
+
 static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
-                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream);
+                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream,
+                       const PeerArgs *peer = nullptr);
 
 int bm_t2_gemv(const void *A, const void *B, void *C, const void *s, const void *ws, int W, int N,
                int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
@@ -372,7 +381,8 @@ int bm_t2_gemv_prepared(const void *A_prep, const void *a_sums, const void *B, v
 }
 
 static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
-                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream) {
+                       int W, int N, int K, int ldc, int out_kind, int path, void *G_out, int pdl, void *stream,
+                       const PeerArgs *peer) {
     if (!A || !B || !C || !s || !ws) return BM_EINVAL;
     if (W < 1 || W > BM_MAX_W || N < 8 || (N % 8) != 0 || K < 128 || (K % 128) != 0) return BM_EINVAL;
     if (ldc < N || (ldc % 4) != 0 || out_kind < 0 || out_kind > 2) return BM_EINVAL;
@@ -392,6 +402,24 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     p.out_kind = out_kind;
     p.stages = 2;
     p.pdl = 0;
+    p.world = 0;
+    p.rank = 0;
+    p.done = nullptr;
+    for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
+    if (peer != nullptr && peer->world > 1) {
+        if (peer->world > 8 || peer->rank < 0 || peer->rank >= peer->world || out_kind != BM_OUT_BF16 || G_out != nullptr ||
+            W > 16 || (K % 256) != 0 || !peer->peer_C0 || !peer->peer_C1 || !peer->peer_flags || !peer->done)
+            return BM_EINVAL;
+        p.world = peer->world;
+        p.rank = peer->rank;
+        p.done = static_cast<unsigned int *>(peer->done);
+        for (int i = 0; i < peer->world; ++i) {
+            if (!peer->peer_C0[i] || !peer->peer_C1[i] || !peer->peer_flags[i]) return BM_EINVAL;
+            p.peer_C[0][i] = static_cast<uint16_t *>(peer->peer_C0[i]);
+            p.peer_C[1][i] = static_cast<uint16_t *>(peer->peer_C1[i]);
+            p.peer_flags[i] = static_cast<unsigned int *>(peer->peer_flags[i]);
+        }
+    }
     const int sms = current_device().sm_count;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The MMA consumer needs an even number of groups (K % 256 == 0); every model shape
@@ -400,7 +428,8 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     path &= 0xff;
     if (path == BM_PATH_AUTO) {
         // Many rows and at most 8 tokens: every warp streams its own rows.  With fewer than about
-        // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner.
+        // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner
+        // (measured on 14336 x 8192, 12288 x 2048 and smaller).
         if (rowwarp_fits(W, N, K) && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
         else path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     }
@@ -582,6 +611,25 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------- N-split GEMV
+int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *ws, int W, int N_shard, int K, int ldc,
+                      int col0, int world, int rank, void *const *peer_C0, void *const *peer_C1,
+                      void *const *peer_flags, void *state, int pdl, void *stream) {
+    if (world < 2 || world > 8 || rank < 0 || rank >= world || col0 < 0 || (col0 % 8) != 0 || col0 + N_shard > ldc ||
+        !peer_C0 || !peer_C1 || !peer_flags || !state)
+        return BM_EINVAL;
+    // every rank writes columns [col0, col0 + N_shard) of every rank's [W, ldc] buffers
+    void *s0[8], *s1[8];
+    for (int i = 0; i < world; ++i) {
+        if (!peer_C0[i] || !peer_C1[i]) return BM_EINVAL;
+        s0[i] = static_cast<uint16_t *>(peer_C0[i]) + col0;
+        s1[i] = static_cast<uint16_t *>(peer_C1[i]) + col0;
+    }
+    PeerArgs peer{world, rank, s0, s1, peer_flags, state};
+    return gemv_common(A, nullptr, B, s0[rank], s, ws, W, N_shard, K, ldc, BM_OUT_BF16, BM_PATH_AUTO, nullptr, pdl,
+                       stream, &peer);
 }
 
 // ---------------------------------------------------------------------------- layer sweep

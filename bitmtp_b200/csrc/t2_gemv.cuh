@@ -62,6 +62,15 @@ struct GemvParams {
     int out_kind;           // 0 bf16, 1 fp32, 2 fp32 holding the bf16-rounded value
     int stages;             // tiles in flight per CTA
     int pdl;                // 1: wait for the previous grid before reading A / s
+    // N-split over the GPUs of a node (bf16 output only): this launch computes rows of one shard;
+    // every value is also stored into the same place of each peer's output buffer over NVLink, and
+    // the last CTA to finish tells the peers and waits for their shards.  world <= 1: unused.
+    int world, rank;
+    uint16_t *peer_C[2][8];         // the two output buffers of every rank, used in turn ([b][rank] == C's twin)
+    unsigned int *peer_flags[8];    // flag arrays [world] of the ranks; [rank] = the local one
+    unsigned int *done;             // local: [0] counter of finished CTAs (zero between launches),
+                                    //        [1] number of completed calls (the epoch; device-resident so
+                                    //        that a captured graph can be replayed)
 };
 
 struct GemvSmem {
@@ -147,12 +156,56 @@ __device__ __forceinline__ void gemv_stage_activations(const GemvParams &p, unsi
 }
 
 __device__ __forceinline__ void gemv_store(const GemvParams &p, int m, int n, float y) {
-    if (p.out_kind == 0)
-        reinterpret_cast<uint16_t *>(p.C)[(size_t)m * p.ldc + n] = bm_f32_to_bf16(y);
-    else if (p.out_kind == 1)
+    if (p.out_kind == 0) {
+        const uint16_t v = bm_f32_to_bf16(y);
+        if (p.world > 1) {
+            const int b = (int)((p.done[1] + 1u) & 1u);       // buffer of this call
+            for (int r = 0; r < p.world; ++r) p.peer_C[b][r][(size_t)m * p.ldc + n] = v;
+        } else {
+            reinterpret_cast<uint16_t *>(p.C)[(size_t)m * p.ldc + n] = v;
+        }
+        return;
+    }
+    if (p.out_kind == 1)
         reinterpret_cast<float *>(p.C)[(size_t)m * p.ldc + n] = y;
     else
         reinterpret_cast<float *>(p.C)[(size_t)m * p.ldc + n] = bm_bf16_rn(y);
+}
+
+// ---- N-split hand-off ------------------------------------------------------------------------------
+// Called by every CTA at the end of a launch with world > 1.  The last CTA to arrive knows that the
+// whole shard has been stored (locally and into the peers' buffers), publishes `epoch` in its slot of
+// every peer's flag array with system-scope release, and waits, with a limit, until every peer has
+// published the same epoch here: when the kernel ends, the full output is in this GPU's buffer.
+enum : int { kErrPeerWaitTimeout = 4 };
+
+__device__ __forceinline__ void gemv_peer_finish(const GemvParams &p) {
+    if (p.world <= 1) return;
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    __threadfence_system();
+    const unsigned int old = atomicAdd(&p.done[0], 1u);
+    if (old != gridDim.x - 1) return;
+    // last CTA: every other CTA has stored its part (and read the epoch) before it arrived
+    atomicExch(&p.done[0], 0u);
+    const unsigned int epoch = p.done[1] + 1u;
+    __threadfence_system();
+    for (int r = 0; r < p.world; ++r)
+        if (r != p.rank)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[r] + p.rank), "r"(epoch) : "memory");
+    for (int r = 0; r < p.world; ++r) {
+        if (r == p.rank) continue;
+        const unsigned int *flag = p.peer_flags[p.rank] + r;
+        unsigned int spins = 0;
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if ((int)(v - epoch) >= 0) break;
+            if (++spins > (1u << 22)) { report_error(kErrPeerWaitTimeout); break; }
+            __nanosleep(100);
+        }
+    }
+    p.done[1] = epoch;                               // the next launch (stream order) uses the other buffer
 }
 
 // =============================================================================
@@ -587,7 +640,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
             if (p.out_kind == 0) {
                 const uint32_t lo = (uint32_t)bm_f32_to_bf16(y[0]) | ((uint32_t)bm_f32_to_bf16(y[1]) << 16);
                 const uint32_t hi = (uint32_t)bm_f32_to_bf16(y[2]) | ((uint32_t)bm_f32_to_bf16(y[3]) << 16);
-                *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.C) + dst) = make_uint2(lo, hi);
+                if (p.world > 1) {
+                    const int b = (int)((p.done[1] + 1u) & 1u);   // buffer of this call
+                    for (int pr = 0; pr < p.world; ++pr)
+                        *reinterpret_cast<uint2 *>(p.peer_C[b][pr] + dst) = make_uint2(lo, hi);
+                } else {
+                    *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.C) + dst) = make_uint2(lo, hi);
+                }
             } else {
                 if (p.out_kind == 2) {
 #pragma unroll
@@ -599,6 +658,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
         }
     }
     (void)failed;
+    gemv_peer_finish(p);
 }
 
 }  // namespace bm

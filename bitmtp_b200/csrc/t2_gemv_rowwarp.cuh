@@ -409,6 +409,7 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
             }
         }
     }
+    gemv_peer_finish(p);
 }
 
 }  // namespace bm

@@ -117,6 +117,8 @@ def _declare_optional(L) -> None:
         "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_decode_sweep": [ctypes.POINTER(SweepArgs), vp],
+        "bm_t2_gemv_nsplit": [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp),
+                              ctypes.POINTER(vp), vp, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],

@@ -192,6 +192,23 @@ int bm_verify_attention_static(const void *q, const void *k_base, const void *v_
                                void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
                                void *stream);
 
+/* N-split of one wide layer over the GPUs of a node, GEMV and exchange in one kernel: this rank
+ * computes the N_shard output rows of its shard (B, ws: the shard's codes and scales) and stores every
+ * value at columns [col0, col0 + N_shard) of EVERY rank's bf16 [W, ldc] output buffer over NVLink
+ * (peer_C0[i] / peer_C1[i]: the two buffers of rank i as mapped into this process, e.g. by torch
+ * symmetric memory; calls use them in turn, so a rank that is one call ahead never writes into rows a
+ * peer's consumers still read).  The last CTA to finish publishes the call number in slot [rank] of
+ * every peer's flag array (peer_flags[i]: uint32 [world] of rank i) and waits, with a limit, until all
+ * peers have published the same number in the local array: when the kernel ends the full [W, ldc]
+ * block is in this GPU's buffer, bit-identical to the single-GPU product.  state: local uint32 [2],
+ * zero before the first call ([0] CTA counter, [1] completed calls; device-resident, so a captured
+ * graph can be replayed).  The result of call k (k = 1, 2, ...) is in buffer k & 1.  All ranks make
+ * the same sequence of calls.  The reference has no multi-GPU inference path; this is the exchange
+ * step of the wide-layer configuration.  bm_device_error() = 4 when a peer did not answer in time. */
+int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *ws, int W, int N_shard,
+                      int K, int ldc, int col0, int world, int rank, void *const *peer_C0,
+                      void *const *peer_C1, void *const *peer_flags, void *state, int pdl, void *stream);
+
 /* All transformer layers of one decode replay in ONE persistent kernel launch: per layer
  * (residual add +) RMSNorm + quant, qkv GEMV, q/k norm + RoPE + KV append + block-verify attention,
  * o GEMV, residual add + RMSNorm + quant, gate|up GEMV + SiLU*up + quant, down GEMV — the body of
