@@ -402,6 +402,8 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     p.out_kind = out_kind;
     p.stages = 2;
     p.pdl = 0;
+    p.silu_F = 0;
+    p.amax_out = nullptr;
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
@@ -478,6 +480,64 @@ int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const v
     return launch_ex(bm::rmsnorm_kernel, dim3(M), dim3(dim / 8), 0, static_cast<cudaStream_t>(stream), pdl, p);
 }
 
+int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *B, const void *ws, const void *s, int W,
+                            int F, int K, void *inner_out, void *amax_out, int pdl, void *stream) {
+    if (!A_prep || !a_sums || !B || !ws || !s || !inner_out || !amax_out) return BM_EINVAL;
+    if (W < 1 || W > 16 || F < 16 || (F % 16) != 0 || (K % 256) != 0 || K < 256) return BM_EINVAL;
+    if (!aligned16(A_prep) || !aligned16(B) || !aligned16(ws) || !aligned16(inner_out)) return BM_EINVAL;
+    bm::GemvParams p;
+    p.A = static_cast<const int8_t *>(A_prep);
+    p.asum = static_cast<const int32_t *>(a_sums);
+    p.B = static_cast<const uint8_t *>(B);
+    p.ws = static_cast<const uint16_t *>(ws);
+    p.s = static_cast<const float *>(s);
+    p.C = inner_out;
+    p.G = nullptr;
+    p.W = W;
+    p.N = F;
+    p.K = K;
+    p.ldc = F;
+    p.out_kind = BM_OUT_BF16;
+    p.pdl = pdl;
+    p.silu_F = F;
+    p.amax_out = static_cast<unsigned int *>(amax_out);
+    p.world = 0;
+    p.rank = 0;
+    p.done = nullptr;
+    for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
+    const int sms = current_device().sm_count;
+    const bool half = W <= 8, one = K == 2048;
+    MmaPlan pl;
+    // the planner sees the 2F weight rows; a tile of 8*RB rows is 4*RB gate rows and their 4*RB up rows
+    if (!make_mma_plan(2 * F, K, half, sms, 0, &pl)) return BM_EINVAL;
+    if (pl.rb < 2 || (F % (4 * pl.rb)) != 0) {
+        if (!make_mma_plan(2 * F, K, half, sms, 2, &pl) || (F % 8) != 0) return BM_EINVAL;
+    }
+    p.stages = pl.stages;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (half) return one ? launch_mma_rb<true, true>(pl, st, pdl, p) : launch_mma_rb<true, false>(pl, st, pdl, p);
+    return one ? launch_mma_rb<false, true>(pl, st, pdl, p) : launch_mma_rb<false, false>(pl, st, pdl, p);
+}
+
+int bm_zero_words(void *p, int n, void *stream) {
+    if (!p || n < 1) return BM_EINVAL;
+    return cuda_status(cudaMemsetAsync(p, 0, (size_t)n * 4, static_cast<cudaStream_t>(stream)));
+}
+
+int bm_quant_rows_amax(const void *x, const void *amax_in, void *amax_zero, int M, int K, void *q, void *q_prep,
+                       void *asum, void *s, int pdl, void *stream) {
+    if (!x || !amax_in || !s || (!q && !q_prep) || M < 1 || M > 32 || K < 256 || (K % 256) != 0 || !aligned16(x))
+        return BM_EINVAL;
+    if ((q_prep == nullptr) != (asum == nullptr) || amax_zero == amax_in) return BM_EINVAL;
+    bm::QuantSink sink{static_cast<int8_t *>(q), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
+    const int units = M * (K / 8);
+    const int grid = (units + bm::kQuantAmaxThreads - 1) / bm::kQuantAmaxThreads;
+    return launch_ex(bm::quant_rows_amax_kernel, dim3(grid), dim3(bm::kQuantAmaxThreads), 0,
+                     static_cast<cudaStream_t>(stream), pdl, static_cast<const uint16_t *>(x),
+                     static_cast<const unsigned int *>(amax_in), static_cast<unsigned int *>(amax_zero), M, K, sink,
+                     static_cast<float *>(s), pdl);
+}
+
 int bm_silu_mul_quant(const void *gu, int M, int F, void *q, void *q_prep, void *asum, void *s, void *inner_out,
                       int pdl, void *stream) {
     if (!gu || !s || (!q && !q_prep) || M < 1 || F < 8 || (F % 8) != 0 || !aligned16(gu)) return BM_EINVAL;
@@ -533,9 +593,35 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma) {
     return (int64_t)bm::attn_scratch_bytes(M, H, sigma);
 }
 
-int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv, int kv_rows,
-                        int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *q_prep,
-                        void *asum, void *s_out, int pdl, void *stream) {
+}  // extern "C"
+
+namespace {
+// Inputs of the chunk kernel with the q/k norm, RoPE and KV append folded in (null: rotated queries in `q`).
+struct RopeInputs {
+    const void *xqkv, *q_w, *k_w, *cos_t, *sin_t, *positions;
+    float eps;
+};
+
+int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_base, const void *v_base, int M, int H,
+                          int Hkv, int kv_rows, int sigma, const void *state, void *scratch, void *att_out,
+                          void *q_out, void *q_prep, void *asum, void *s_out, int pdl, void *stream,
+                          void *amax_rows = nullptr) {
+    // amax_rows != null: rows only (bf16 att_out + absmax bits per row), quantisation left to the caller
+    int dummy_s = 0;
+    if (amax_rows != nullptr) {
+        if (!att_out || (H % 4) != 0) return BM_EINVAL;
+        q_prep = nullptr;
+        asum = nullptr;
+        q_out = att_out;                              // satisfies the "some sink" check; not written
+        s_out = &dummy_s;
+    }
+    if (rope != nullptr) {
+        if (!rope->xqkv || !rope->q_w || !rope->k_w || !rope->cos_t || !rope->sin_t || !rope->positions) return BM_EINVAL;
+        if ((reinterpret_cast<uintptr_t>(rope->xqkv) & 7u) || (reinterpret_cast<uintptr_t>(rope->cos_t) & 7u) ||
+            (reinterpret_cast<uintptr_t>(rope->sin_t) & 7u))
+            return BM_EINVAL;
+        q = rope->xqkv;                               // only for the null / alignment checks below
+    }
     if (!q || !k_base || !v_base || !state || !scratch || (!q_out && !q_prep) || !s_out) return BM_EINVAL;
     if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
     if (M < 1 || M > BM_MAX_W || H < 1 || H > bm::kMergeMaxHeads || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
@@ -575,13 +661,62 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
     if (smem > 200 * 1024 || msmem > 200 * 1024) return BM_EINVAL;
     int rc;
     const dim3 grid(NC, Hkv, qsplit);
-    if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, grid, dim3(threads), smem, st, pdl, p);
+    if (rope != nullptr) {
+        bm::AttnRopeParams rp;
+        rp.a = p;
+        rp.xqkv = static_cast<const uint16_t *>(rope->xqkv);
+        rp.q_w = static_cast<const uint16_t *>(rope->q_w);
+        rp.k_w = static_cast<const uint16_t *>(rope->k_w);
+        rp.cos_t = static_cast<const uint16_t *>(rope->cos_t);
+        rp.sin_t = static_cast<const uint16_t *>(rope->sin_t);
+        rp.positions = static_cast<const int64_t *>(rope->positions);
+        rp.k_out = const_cast<uint16_t *>(p.k_base);
+        rp.v_out = const_cast<uint16_t *>(p.v_base);
+        rp.eps = rope->eps;
+        if (nq == 2) rc = launch_ex(bm::attn_chunk_rope_kernel<2>, grid, dim3(threads), smem, st, pdl, rp);
+        else if (nq == 4) rc = launch_ex(bm::attn_chunk_rope_kernel<4>, grid, dim3(threads), smem, st, pdl, rp);
+        else rc = launch_ex(bm::attn_chunk_rope_kernel<8>, grid, dim3(threads), smem, st, pdl, rp);
+    } else if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, grid, dim3(threads), smem, st, pdl, p);
     else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, grid, dim3(threads), smem, st, pdl, p);
     else rc = launch_ex(bm::attn_chunk_kernel<8>, grid, dim3(threads), smem, st, pdl, p);
     if (rc != BM_OK) return rc;
+    if (amax_rows != nullptr) {
+        const int hpc = 4;
+        return launch_ex(bm::attn_merge_part_kernel, dim3(M, H / hpc), dim3(hpc * 64), (size_t)hpc * NC * sizeof(float),
+                         st, pdl, p, static_cast<unsigned int *>(amax_rows), hpc);
+    }
     int mthreads = H * 64 < bm::kMergeThreads ? H * 64 : bm::kMergeThreads;
     mthreads = (mthreads + 31) / 32 * 32;
     return launch_ex(bm::attn_merge_kernel, dim3(M), dim3(mthreads), msmem, st, pdl, p);
+}
+}  // namespace
+
+extern "C" {
+
+int bm_verify_attention(const void *q, const void *k_base, const void *v_base, int M, int H, int Hkv, int kv_rows,
+                        int sigma, const void *state, void *scratch, void *att_out, void *q_out, void *q_prep,
+                        void *asum, void *s_out, int pdl, void *stream) {
+    return verify_attention_impl(q, nullptr, k_base, v_base, M, H, Hkv, kv_rows, sigma, state, scratch, att_out, q_out,
+                                 q_prep, asum, s_out, pdl, stream);
+}
+
+int bm_rope_verify_attention_rows(const void *xqkv, const void *q_w, const void *k_w, float eps, const void *cos_t,
+                                  const void *sin_t, const void *positions, void *k_base, void *v_base, int M, int H,
+                                  int Hkv, int kv_rows, int sigma, const void *state, void *scratch, void *att_out,
+                                  void *amax_out, int pdl, void *stream) {
+    if (!amax_out) return BM_EINVAL;
+    const RopeInputs rope{xqkv, q_w, k_w, cos_t, sin_t, positions, eps};
+    return verify_attention_impl(nullptr, &rope, k_base, v_base, M, H, Hkv, kv_rows, sigma, state, scratch, att_out,
+                                 nullptr, nullptr, nullptr, nullptr, pdl, stream, amax_out);
+}
+
+int bm_rope_verify_attention(const void *xqkv, const void *q_w, const void *k_w, float eps, const void *cos_t,
+                             const void *sin_t, const void *positions, void *k_base, void *v_base, int M, int H,
+                             int Hkv, int kv_rows, int sigma, const void *state, void *scratch, void *att_out,
+                             void *q_out, void *q_prep, void *asum, void *s_out, int pdl, void *stream) {
+    const RopeInputs rope{xqkv, q_w, k_w, cos_t, sin_t, positions, eps};
+    return verify_attention_impl(nullptr, &rope, k_base, v_base, M, H, Hkv, kv_rows, sigma, state, scratch, att_out,
+                                 q_out, q_prep, asum, s_out, pdl, stream);
 }
 
 // ---------------------------------------------------------------------------- logits

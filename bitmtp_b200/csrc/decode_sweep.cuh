@@ -414,36 +414,11 @@ __device__ __forceinline__ void sweep_stamp(const SweepParams &p, int layer, int
 }
 
 // ---- stage: q/k norm + RoPE + KV append + attention chunks --------------------------------------
-// One warp per 128-wide head vector, as qknorm_rope_kvappend_kernel: lane l owns elements
-// 4l..4l+3, the RoPE partner lives in lane l ^ 16.  `raw` holds the lane's four bf16 inputs, `wraw`
-// its four norm weights, cos_row / sin_row the position's table rows (shared-memory copies made once
-// per launch).  o[] receives the sums before the final bf16 rounding.
+// rope_head_vector (verify_attn.cuh) with the table rows read from shared memory.
 __device__ __forceinline__ void sweep_rope_vec(uint2 raw, uint2 wraw, const uint16_t *cos_row, const uint16_t *sin_row,
                                                float eps, int lane, float (&o)[4]) {
-    const float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
-    float acc = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc = fmaf(x[i], x[i], acc);
-    const float total = warp_sum_butterfly(acc);
-    const float r = bm_rsqrtf((0.0f + total) / 128.0f + eps);
-    const uint2 craw = *reinterpret_cast<const uint2 *>(cos_row + 4 * lane);
-    const uint2 sraw = *reinterpret_cast<const uint2 *>(sin_row + 4 * lane);
-    const float wv[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u),
-                         __uint_as_float(wraw.y << 16), __uint_as_float(wraw.y & 0xffff0000u)};
-    const float c[4] = {__uint_as_float(craw.x << 16), __uint_as_float(craw.x & 0xffff0000u),
-                        __uint_as_float(craw.y << 16), __uint_as_float(craw.y & 0xffff0000u)};
-    const float sn[4] = {__uint_as_float(sraw.x << 16), __uint_as_float(sraw.x & 0xffff0000u),
-                         __uint_as_float(sraw.y << 16), __uint_as_float(sraw.y & 0xffff0000u)};
-    float n[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) n[i] = bm_bf16_rn(wv[i] * bm_bf16_rn(x[i] * r));
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
-        const float rot = lane < 16 ? -partner : partner;
-        o[i] = bm_bf16_rn(n[i] * c[i]) + bm_bf16_rn(rot * sn[i]);
-    }
+    rope_head_vector(raw, wraw, *reinterpret_cast<const uint2 *>(cos_row + 4 * lane),
+                     *reinterpret_cast<const uint2 *>(sin_row + 4 * lane), eps, lane, o);
 }
 
 // Work items are (live chunk, kv head) pairs dealt round-robin to the CTAs.  The item that holds

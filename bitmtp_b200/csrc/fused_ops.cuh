@@ -144,6 +144,36 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(const uint16_t 
 }
 
 // =============================================================================
+// quant_rows with the row absmax already known: the gate|up projection with the SiLU epilogue
+// (t2_gemv.cuh) leaves bf16 `inner` rows and, by atomic max, the bits of each row's absmax; this kernel
+// turns them into INT8 codes for the down projection.  Replaces the quant_input half of
+// `inner = F.silu(g) * u; quant_input(inner)` (model.py:1059-1061).  Units of 8 elements are dealt to
+// the threads of a flat grid, so the work spreads over many SMs instead of one CTA per row.
+// `amax_zero` (optional): M words cleared for the next producer (a different array from amax_in).
+// =============================================================================
+constexpr int kQuantAmaxThreads = 256;
+
+__global__ void __launch_bounds__(kQuantAmaxThreads) quant_rows_amax_kernel(
+    const uint16_t *__restrict__ x, const unsigned int *__restrict__ amax_in, unsigned int *amax_zero, int M, int K,
+    QuantSink sink, float *__restrict__ s_out, int pdl) {
+    pdl_launch_dependents();
+    if (pdl) pdl_wait();
+    const int units = K / 8, lane = threadIdx.x & 31;
+    const int u = blockIdx.x * kQuantAmaxThreads + threadIdx.x;   // whole warps stay inside one row (units % 32 == 0)
+    const bool active = u < M * units;
+    const int m = active ? u / units : 0, i = active ? u - m * units : 0;
+    float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float s = 0.0f;
+    if (active) {
+        unpack8(reinterpret_cast<const uint4 *>(x + (size_t)m * K)[i], v);
+        s = bm_act_scale(__uint_as_float(amax_in[m]));
+        if (i == 0) s_out[m] = s;
+    }
+    emit_codes(sink, (size_t)m * K, K, i, quant8(v, s), active, lane);
+    if (amax_zero != nullptr && blockIdx.x == 0 && threadIdx.x < M) amax_zero[threadIdx.x] = 0u;
+}
+
+// =============================================================================
 // (gather | residual add) + RMSNorm + (INT8 quantisation | bf16 store).
 // Replaces _fused_norm_quant (model.py:307-319), _fused_add_norm_quant
 // (model.py:322-336), RMSNorm.forward on the logit rows (model.py:290-295,

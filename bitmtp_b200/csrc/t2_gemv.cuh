@@ -62,6 +62,12 @@ struct GemvParams {
     int out_kind;           // 0 bf16, 1 fp32, 2 fp32 holding the bf16-rounded value
     int stages;             // tiles in flight per CTA
     int pdl;                // 1: wait for the previous grid before reading A / s
+    // gate|up projection with SiLU(gate) * up in the epilogue (MMA consumer, bf16 output): B has
+    // 2 * silu_F rows (gate rows, then up rows), N == silu_F output columns; a tile pairs 4*RB gate
+    // rows with the 4*RB up rows of the same columns.  amax_out[m] receives, by atomic max, the bits of
+    // max |output| of row m (zero before the launch).  silu_F == 0: plain projection.
+    int silu_F;
+    unsigned int *amax_out;
     // N-split over the GPUs of a node (bf16 output only): this launch computes rows of one shard;
     // every value is also stored into the same place of each peer's output buffer over NVLink, and
     // the last CTA to finish tells the peers and waits for their shards.  world <= 1: unused.
@@ -113,16 +119,24 @@ __device__ __forceinline__ void gemv_issue_tile(const GemvParams &p, unsigned ch
     const uint32_t row_bytes = (uint32_t)(p.K / 4);
     if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes + (uint32_t)(rows * ng * 2));
     __syncwarp();
-#ifdef BM_EXP_DENSE_TILE_COPY
-    // Timing experiment only (wrong results): the whole tile as one copy, no row padding.
-    if (lane == 0) bulk_g2s(stage, p.B + (size_t)n0 * row_bytes, (uint32_t)rows * row_bytes, bar);
-#else
-    for (int r = lane; r < rows; r += 32)
-        bulk_g2s(stage + r * L.row_stride, p.B + (size_t)(n0 + r) * row_bytes, row_bytes, bar);
-#endif
-    if (lane == 0)
-        bulk_g2s(stage + L.scale_off_in_stage, p.ws + (size_t)n0 * ng, (uint32_t)(rows * ng * 2),
-                 bar);
+    if (p.silu_F == 0) {
+        for (int r = lane; r < rows; r += 32)
+            bulk_g2s(stage + r * L.row_stride, p.B + (size_t)(n0 + r) * row_bytes, row_bytes, bar);
+        if (lane == 0)
+            bulk_g2s(stage + L.scale_off_in_stage, p.ws + (size_t)n0 * ng, (uint32_t)(rows * ng * 2), bar);
+    } else {
+        // paired tile: rows [0, rows/2) are gate rows n0.., rows [rows/2, rows) the up rows of the same columns
+        const int half = rows >> 1;
+        for (int r = lane; r < rows; r += 32) {
+            const size_t src = r < half ? (size_t)(n0 + r) : (size_t)(p.silu_F + n0 + r - half);
+            bulk_g2s(stage + r * L.row_stride, p.B + src * row_bytes, row_bytes, bar);
+        }
+        if (lane == 0) {
+            bulk_g2s(stage + L.scale_off_in_stage, p.ws + (size_t)n0 * ng, (uint32_t)(half * ng * 2), bar);
+            bulk_g2s(stage + L.scale_off_in_stage + half * ng * 2, p.ws + (size_t)(p.silu_F + n0) * ng,
+                     (uint32_t)(half * ng * 2), bar);
+        }
+    }
 }
 
 // ---- activation staging --------------------------------------------------------
@@ -479,8 +493,11 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = lane >> 2, q = lane & 3;
-    const int n_tiles = p.N / R;
+    const int R_out = p.silu_F ? R / 2 : R;            // output columns per tile
+    const int n_tiles = p.N / R_out;
     const int nch = ONECHUNK ? 1 : (ng + BM_SLOTS - 1) / BM_SLOTS;
+    __shared__ unsigned int amax_sh[16];
+    if (p.silu_F && threadIdx.x < 16) amax_sh[threadIdx.x] = 0u;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < p.stages; ++i) mbar_init(&bars[i], 1);
@@ -497,7 +514,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
     if (warp == 0) {
         for (int i = 0; i < p.stages && i < my_tiles; ++i)
             gemv_issue_tile(p, smem + L.stage_off + i * L.stage_bytes, LS, &bars[i],
-                            (blockIdx.x + i * gridDim.x) * R, R, lane);
+                            (blockIdx.x + i * gridDim.x) * R_out, R, lane);
     }
     pdl_launch_dependents();
     if (p.pdl) pdl_wait();
@@ -555,7 +572,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
         const int st = i % p.stages;
         const bool ok = mbar_wait_bounded(&bars[st], (uint32_t)((i / p.stages) & 1)) && a_ok;
         const unsigned char *stage = smem + L.stage_off + st * L.stage_bytes;
-        const int n0 = (blockIdx.x + i * gridDim.x) * R;
+        const int n0 = (blockIdx.x + i * gridDim.x) * R_out;
 
         float acc[RB][2][4];
 #pragma unroll
@@ -622,9 +639,41 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
         // Every warp is done with stage `st`: refill it with the tile `stages` ahead.
         if (warp == 0 && i + p.stages < my_tiles)
             gemv_issue_tile(p, smem + L.stage_off + st * L.stage_bytes, LS, &bars[st],
-                            (blockIdx.x + (i + p.stages) * gridDim.x) * R, R, lane);
+                            (blockIdx.x + (i + p.stages) * gridDim.x) * R_out, R, lane);
         // Remaining tree levels, reciprocal multiply, store.  Thread = (token, 4 rows).
         const float *pr = part + (i & 1) * L.part_buf_floats;
+        if (p.silu_F) {
+            // rows [0, R/2) of the tile are gate rows, rows [R/2, R) the up rows of the same columns:
+            // inner = bf16(silu(bf16 gate) * bf16 up), as the stand-alone SiLU kernel computes it from
+            // the bf16 projection outputs
+            for (int o = threadIdx.x; o < p.W * (R / 8); o += kGemvThreads) {
+                const int m = o / (R / 8), rq = o - m * (R / 8);
+                float4 vg[kGemvWarps], vu[kGemvWarps];
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) {
+                    vg[w] = *reinterpret_cast<const float4 *>(&pr[(w * WROWS + m) * RP + 4 * rq]);
+                    vu[w] = *reinterpret_cast<const float4 *>(&pr[(w * WROWS + m) * RP + R / 2 + 4 * rq]);
+                }
+                const float is = invs[m];
+                float g[4], u[4], v[4];
+#define BM_TREE(V, F) (((V[0].F + V[1].F) + (V[2].F + V[3].F)) + ((V[4].F + V[5].F) + (V[6].F + V[7].F))) * is
+                g[0] = BM_TREE(vg, x); g[1] = BM_TREE(vg, y); g[2] = BM_TREE(vg, z); g[3] = BM_TREE(vg, w);
+                u[0] = BM_TREE(vu, x); u[1] = BM_TREE(vu, y); u[2] = BM_TREE(vu, z); u[3] = BM_TREE(vu, w);
+#undef BM_TREE
+                float amax = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v[e] = bm_bf16_rn(bm_silu_bf16(bm_bf16_rn(g[e])) * bm_bf16_rn(u[e]));
+                    amax = fmaxf(amax, fabsf(v[e]));
+                }
+                const uint32_t lo = (uint32_t)bm_f32_to_bf16(v[0]) | ((uint32_t)bm_f32_to_bf16(v[1]) << 16);
+                const uint32_t hi = (uint32_t)bm_f32_to_bf16(v[2]) | ((uint32_t)bm_f32_to_bf16(v[3]) << 16);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.C) + (size_t)m * p.ldc + n0 + 4 * rq) =
+                    make_uint2(lo, hi);
+                atomicMax(&amax_sh[m], __float_as_uint(amax));
+            }
+            continue;
+        }
         for (int o = threadIdx.x; o < p.W * (R / 4); o += kGemvThreads) {
             const int m = o / (R / 4), rq = o - m * (R / 4);
             float4 v[kGemvWarps];
@@ -658,6 +707,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
         }
     }
     (void)failed;
+    if (p.silu_F) {
+        __syncthreads();
+        if (threadIdx.x < p.W && amax_sh[threadIdx.x] != 0u) atomicMax(&p.amax_out[threadIdx.x], amax_sh[threadIdx.x]);
+    }
     gemv_peer_finish(p);
 }
 

@@ -161,6 +161,164 @@ __device__ __forceinline__ void attn_chunk_pass(const AttnParams &p, const uint1
     __syncwarp();
 }
 
+// q/k head norm + RoPE of one 128-wide head vector by one warp, as qknorm_rope_kvappend_kernel does it:
+// lane l owns elements 4l..4l+3 (`raw`: its four bf16 inputs, `wraw`: its norm weights, `craw` / `sraw`:
+// its cos / sin table entries), the RoPE partner lives in lane l ^ 16.  o[] receives the sums before
+// the final bf16 rounding.
+__device__ __forceinline__ void rope_head_vector(uint2 raw, uint2 wraw, uint2 craw, uint2 sraw, float eps, int lane,
+                                                 float (&o)[4]) {
+    const float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc = fmaf(x[i], x[i], acc);
+    const float total = warp_sum_butterfly(acc);
+    const float r = bm_rsqrtf((0.0f + total) / 128.0f + eps);
+    const float wv[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u),
+                         __uint_as_float(wraw.y << 16), __uint_as_float(wraw.y & 0xffff0000u)};
+    const float c[4] = {__uint_as_float(craw.x << 16), __uint_as_float(craw.x & 0xffff0000u),
+                        __uint_as_float(craw.y << 16), __uint_as_float(craw.y & 0xffff0000u)};
+    const float sn[4] = {__uint_as_float(sraw.x << 16), __uint_as_float(sraw.x & 0xffff0000u),
+                         __uint_as_float(sraw.y << 16), __uint_as_float(sraw.y & 0xffff0000u)};
+    float n[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n[i] = bm_bf16_rn(wv[i] * bm_bf16_rn(x[i] * r));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
+        const float rot = lane < 16 ? -partner : partner;
+        o[i] = bm_bf16_rn(n[i] * c[i]) + bm_bf16_rn(rot * sn[i]);
+    }
+}
+
+// ---- kernel 1b: kernel 1 with the q/k norm, RoPE and KV append of the replay's rows folded in ----
+// Reads the qkv projection output instead of rotated queries: every CTA rotates the query vectors it
+// serves, the CTAs of the chunk that holds the replay's own rows compute their K rows (norm + RoPE),
+// copy their V rows, and the z == 0 one appends both to the layer's planes.  Replaces
+// qknorm_rope_kvappend_kernel + attn_chunk_kernel (one launch less per layer); same arithmetic.
+struct AttnRopeParams {
+    AttnParams a;
+    const uint16_t *xqkv;            // [M, (H + 2 Hkv) * 128] bf16
+    const uint16_t *q_w, *k_w;       // head-norm weights, bf16 [128]
+    const uint16_t *cos_t, *sin_t;   // bf16 [max_pos, 128]
+    const int64_t *positions;        // [M]
+    uint16_t *k_out, *v_out;         // the layer's planes (same memory as a.k_base / a.v_base)
+    float eps;
+};
+
+constexpr int kRopeBatch = 4;        // head vectors a warp rotates per batch (loads issued together)
+
+template <int NQ>
+__global__ void __launch_bounds__(kAttnThreads) attn_chunk_rope_kernel(const AttnRopeParams P) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    const AttnParams &p = P.a;
+    pdl_launch_dependents();
+    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
+    if (p.pdl && !early) pdl_wait();
+    const int j = blockIdx.x, hk = blockIdx.y;
+    const int cache_len = p.state->cache_len, n_pend = p.state->n_pend, role = p.state->role, P_ = p.state->P;
+    const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
+    int c0, cn;
+    if (j == p.NC - 1) { c0 = p.sigma; cn = p.M; }
+    else if (j < n_hist) { c0 = j * BM_ATTN_CHUNK; cn = min(BM_ATTN_CHUNK, cache_len - c0); }
+    else return;
+    const bool fresh = j == p.NC - 1;
+
+    const int G = p.H / p.Hkv, QV = G * p.M, heads = p.H + 2 * p.Hkv;
+    uint16_t *Ks = reinterpret_cast<uint16_t *>(dyn);                    // [32][136]
+    uint16_t *Vs = Ks + 32 * kKeyStride;                                  // [32][128]
+    float *Qs = reinterpret_cast<float *>(Vs + 32 * 128);                 // [QV][128]
+    float *Ps = Qs + (size_t)QV * 128;                                    // [QV][32]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x, nwarps = nthr >> 5;
+    const int per = (QV + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int q_lo = (int)blockIdx.z * per, q_hi = min(QV, q_lo + per);
+
+    // Nothing below depends on the previous kernel until the wait: history rows, positions, tables.
+    uint4 kreg[4], vreg[4];                                               // up to 512 pieces over >= 128 threads
+    if (!fresh) {
+        const uint4 *kg = reinterpret_cast<const uint4 *>(p.k_base + ((size_t)hk * p.kv_rows + c0) * 128);
+        const uint4 *vg = reinterpret_cast<const uint4 *>(p.v_base + ((size_t)hk * p.kv_rows + c0) * 128);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = tid + k * nthr;
+            if (i < cn * 16) { kreg[k] = kg[i]; vreg[k] = vg[i]; }
+        }
+    }
+    const uint2 qw = *reinterpret_cast<const uint2 *>(P.q_w + 4 * lane);
+    const uint2 kw = *reinterpret_cast<const uint2 *>(P.k_w + 4 * lane);
+    if (early) pdl_wait();                                                // xqkv comes from the predecessor
+
+    if (fresh) {
+        for (int m0 = warp; m0 < p.M; m0 += nwarps * kRopeBatch) {
+            uint2 kraw[kRopeBatch], vraw[kRopeBatch], cr[kRopeBatch], sr[kRopeBatch];
+#pragma unroll
+            for (int k = 0; k < kRopeBatch; ++k) {
+                const int m = m0 + k * nwarps;
+                if (m < p.M) {
+                    const size_t pos = (size_t)P.positions[m];
+                    kraw[k] = *reinterpret_cast<const uint2 *>(P.xqkv + ((size_t)m * heads + p.H + hk) * 128 + 4 * lane);
+                    vraw[k] = *reinterpret_cast<const uint2 *>(P.xqkv + ((size_t)m * heads + p.H + p.Hkv + hk) * 128 + 4 * lane);
+                    cr[k] = *reinterpret_cast<const uint2 *>(P.cos_t + pos * 128 + 4 * lane);
+                    sr[k] = *reinterpret_cast<const uint2 *>(P.sin_t + pos * 128 + 4 * lane);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kRopeBatch; ++k) {
+                const int m = m0 + k * nwarps;
+                if (m >= p.M) break;                                       // warp-uniform
+                float o[4];
+                rope_head_vector(kraw[k], kw, cr[k], sr[k], P.eps, lane, o);
+                const uint2 kbits = make_uint2(
+                    (uint32_t)bm_f32_to_bf16(o[0]) | ((uint32_t)bm_f32_to_bf16(o[1]) << 16),
+                    (uint32_t)bm_f32_to_bf16(o[2]) | ((uint32_t)bm_f32_to_bf16(o[3]) << 16));
+                *reinterpret_cast<uint2 *>(Ks + m * kKeyStride + 4 * lane) = kbits;
+                *reinterpret_cast<uint2 *>(Vs + m * 128 + 4 * lane) = vraw[k];
+                if (blockIdx.z == 0) {
+                    const size_t row = ((size_t)hk * p.kv_rows + p.sigma + m) * 128 + 4 * lane;
+                    *reinterpret_cast<uint2 *>(P.k_out + row) = kbits;
+                    *reinterpret_cast<uint2 *>(P.v_out + row) = vraw[k];
+                }
+            }
+        }
+    }
+    for (int v0 = q_lo + warp; v0 < q_hi; v0 += nwarps * kRopeBatch) {
+        uint2 qraw[kRopeBatch], cr[kRopeBatch], sr[kRopeBatch];
+#pragma unroll
+        for (int k = 0; k < kRopeBatch; ++k) {
+            const int qv = v0 + k * nwarps;
+            if (qv < q_hi) {
+                const int g = qv / p.M, m = qv - g * p.M;
+                const size_t pos = (size_t)P.positions[m];
+                qraw[k] = *reinterpret_cast<const uint2 *>(P.xqkv + ((size_t)m * heads + hk * G + g) * 128 + 4 * lane);
+                cr[k] = *reinterpret_cast<const uint2 *>(P.cos_t + pos * 128 + 4 * lane);
+                sr[k] = *reinterpret_cast<const uint2 *>(P.sin_t + pos * 128 + 4 * lane);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kRopeBatch; ++k) {
+            const int qv = v0 + k * nwarps;
+            if (qv >= q_hi) break;                                         // warp-uniform
+            float o[4];
+            rope_head_vector(qraw[k], qw, cr[k], sr[k], P.eps, lane, o);
+            *reinterpret_cast<float4 *>(Qs + (size_t)qv * 128 + 4 * lane) =
+                make_float4(bm_bf16_rn(o[0]), bm_bf16_rn(o[1]), bm_bf16_rn(o[2]), bm_bf16_rn(o[3]));
+        }
+    }
+    if (!fresh) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = tid + k * nthr;
+            if (i < cn * 16) {
+                *reinterpret_cast<uint4 *>(Ks + (i >> 4) * kKeyStride + 8 * (i & 15)) = kreg[k];
+                reinterpret_cast<uint4 *>(Vs)[i] = vreg[k];
+            }
+        }
+    }
+    __syncthreads();
+    for (int q0 = q_lo + warp * NQ; q0 < q_hi; q0 += nwarps * NQ)
+        attn_chunk_pass<NQ>(p, Ks, Vs, Qs, Ps, q0, q_hi, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P_);
+}
+
 template <int NQ>
 __global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -329,6 +487,89 @@ __device__ __forceinline__ void attn_merge_row(const AttnParams &p, int m, int c
     if (tid == 0) p.s_out[m] = s;
 }
 
+
+// ---- kernel 2b: the merge spread over (row, head group) CTAs, without the quantisation ----
+// Same merge as attn_merge_row for `hpc` heads of one row per CTA (thread = 2 dims of one head, up to
+// 32 chunk numerators per thread in flight): writes the bf16 attention row and folds its absmax into
+// amax_out[m] by atomic max (float bits; zero on entry).  The INT8 codes then come from
+// quant_rows_amax_kernel.  With M rows alone only M SMs would merge; this uses M * H / hpc of them.
+constexpr int kMergePartBatch = 32;
+
+__global__ void __launch_bounds__(256) attn_merge_part_kernel(const AttnParams p, unsigned int *amax_out, int hpc) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ float l_s[8];
+    __shared__ float red[8];
+    pdl_launch_dependents();
+    const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
+    if (p.pdl && !early) pdl_wait();
+    const int cache_len = p.state->cache_len;
+    if (early) pdl_wait();
+    const int m = blockIdx.x, h0 = blockIdx.y * hpc;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x, nwarps = nthr >> 5;
+    const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
+    const int nv = n_hist + 1;
+    float *w_s = reinterpret_cast<float *>(dyn);      // [hpc][nv] merge weights
+    const int hl = tid >> 6, d0 = (tid & 63) * 2;     // local head, first of the two dims
+    const int h = h0 + hl;
+    const float *src = p.po + ((size_t)m * p.H + h) * p.NC * 128 + d0;
+    float o0 = 0.0f, o1 = 0.0f;
+    for (int b0 = 0; b0 < nv; b0 += kMergePartBatch) {
+        const int nb = min(kMergePartBatch, nv - b0);
+        float2 part[kMergePartBatch];
+#pragma unroll
+        for (int i = 0; i < kMergePartBatch; ++i) {
+            const int c = b0 + i;
+            const int j = c < n_hist ? c : p.NC - 1;
+            part[i] = i < nb ? __ldcg(reinterpret_cast<const float2 *>(src + (size_t)j * 128)) : make_float2(0.0f, 0.0f);
+        }
+        if (b0 == 0) {
+            // weights of this CTA's heads (one warp each), while the numerators are in flight
+            for (int hh = warp; hh < hpc; hh += nwarps) {
+                const size_t pb = ((size_t)m * p.H + h0 + hh) * p.NC;
+                float gmax = -INFINITY;
+                float pl0 = 0.0f;
+                for (int i = lane; i < nv; i += 32) {
+                    const int jj = i < n_hist ? i : p.NC - 1;
+                    const float mj = __ldcg(p.pm + pb + jj);
+                    if (i < 32) pl0 = __ldcg(p.pl + pb + jj);
+                    w_s[hh * nv + i] = mj;
+                    gmax = fmaxf(gmax, mj);
+                }
+                gmax = warp_max(gmax);
+                float l = 0.0f;
+                for (int i0 = 0; i0 < nv; i0 += 32) {
+                    const int i = i0 + lane;
+                    float w = 0.0f, pl = 0.0f;
+                    if (i < nv) {
+                        const float mj = w_s[hh * nv + i];
+                        w = mj > -INFINITY ? bm_expf(mj - gmax) : 0.0f;
+                        pl = i0 == 0 ? pl0 : __ldcg(p.pl + pb + (i < n_hist ? i : p.NC - 1));
+                        w_s[hh * nv + i] = w;
+                    }
+                    const int cnt = min(32, nv - i0);
+                    for (int k = 0; k < cnt; ++k)
+                        l = fmaf(__shfl_sync(0xffffffffu, pl, k), __shfl_sync(0xffffffffu, w, k), l);
+                }
+                if (lane == 0) l_s[hh] = l;
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < kMergePartBatch; ++i) {
+            if (i < nb) {
+                const float w = w_s[hl * nv + b0 + i];
+                o0 = fmaf(part[i].x, w, o0);
+                o1 = fmaf(part[i].y, w, o1);
+            }
+        }
+    }
+    const float l = l_s[hl];
+    const float v0 = bm_bf16_rn(o0 / l), v1 = bm_bf16_rn(o1 / l);
+    reinterpret_cast<uint32_t *>(p.att + (size_t)m * p.H * 128 + h * 128)[tid & 63] =
+        (uint32_t)bm_f32_to_bf16(v0) | ((uint32_t)bm_f32_to_bf16(v1) << 16);
+    const float amax = block_max(fmaxf(fabsf(v0), fabsf(v1)), red, lane, warp, nwarps);
+    if (tid == 0 && amax != 0.0f) atomicMax(&amax_out[m], __float_as_uint(amax));
+}
 
 __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];

@@ -330,7 +330,8 @@ class StepWorkspace:
         self.h_sum = buf((M, args.dim // 128), i32)
         # extra buffers of the persistent layer kernel
         self.inner = buf((M, args.ffn_dim), bf)
-        self.inner_amax = torch.zeros((M,), dtype=i32, device=device)
+        self.inner_amax = torch.zeros((2, M), dtype=i32, device=device)   # row absmax bits, two slots used in turn
+        self.att_amax = torch.zeros((2, M), dtype=i32, device=device)
         self.sweep_barrier = torch.zeros((2,), dtype=i32, device=device)
         self.n_pad = n_pad
 
@@ -356,6 +357,13 @@ class Transformer(nn.Module):
         # slower on B200 (one 8-warp CTA per SM hides less latency than several resident CTAs of
         # the stand-alone kernels), so it is opt-in: BM_SWEEP=1.
         self.use_sweep = os.environ.get("BM_SWEEP", "0") == "1"
+        # SiLU(gate) * up inside the gate|up GEMV + a flat quantisation kernel instead of GEMV + one SiLU
+        # CTA per row (BM_FUSED_FFN=0 restores the latter)
+        self.fused_ffn = os.environ.get("BM_FUSED_FFN", "1") != "0"
+        # q/k norm + RoPE + KV append folded into the attention's chunk kernel (BM_FUSED_ROPE=0: own launch)
+        self.fused_rope = os.environ.get("BM_FUSED_ROPE", "1") != "0"
+        # attention merge over (row, 4 heads) CTAs + flat quantisation (BM_SPLIT_MERGE=0: one merge CTA per row)
+        self.split_merge = os.environ.get("BM_SPLIT_MERGE", "1") != "0"
         self._sweep_tables = {}
 
     def tie_weights(self) -> None:
@@ -415,6 +423,12 @@ class Transformer(nn.Module):
         # INT8 activations go from their producer to the next GEMV in GEMV-ready order
         # (16-runs transposed 4x4, plus per-group sums), so no GEMV CTA permutes or sums them.
         qsink = {"h": W.h, "qp": W.q, "asum": W.q_sum, "s": W.s}
+        fused_ffn = self.fused_ffn and M <= 16 and a.ffn_dim % 16 == 0 and a.dim % 256 == 0
+        split_merge = self.split_merge and a.n_heads % 4 == 0 and (a.n_heads * a.head_dim) % 256 == 0
+        if fused_ffn:
+            ops.zero_words(W.inner_amax[0])           # slot of layer 0; every layer clears the next one's
+        if self.fused_rope and split_merge:
+            ops.zero_words(W.att_amax[0])
         ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
                           gather=token_values, pdl=pdl, out=qsink)
         for i, layer in enumerate(self.layers):
@@ -425,20 +439,46 @@ class Transformer(nn.Module):
             ops.t2_gemv_prepared(W.q, W.q_sum, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv,
                                  ldc=W.xqkv.shape[1], pdl=pdl)
             k_l, v_l = kv_full[i]
-            ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
-                                     at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
-                                     _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                     pdl=pdl, q_out=W.qrot)
-            ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
-                                 attn_mask, attn_scratch, pdl=attn_pdl, out=(W.att, None, W.att_s),
-                                 prep=(W.att_q, W.att_sum))
+            if self.fused_rope and split_merge:
+                # chunk kernel with the RoPE folded in, merge spread over (row, 4 heads) CTAs with the row
+                # absmax by atomic max, INT8 codes from the flat quantisation kernel
+                ops.rope_verify_attention_rows(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
+                                               at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                               _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma, attn_mask,
+                                               attn_scratch, att=W.att, amax=W.att_amax[i & 1], pdl=attn_pdl)
+                ops.quant_rows_amax(W.att, W.att_amax[i & 1], prep=(W.att_q, W.att_sum), s=W.att_s,
+                                    amax_zero=W.att_amax[(i + 1) & 1], pdl=pdl)
+            elif self.fused_rope:
+                # q/k norm + RoPE + KV append inside the attention's chunk kernel: one launch less
+                ops.rope_verify_attention(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps, at.rope_cos,
+                                          at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                          _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma, attn_mask,
+                                          attn_scratch, out=(None, None, W.att_s), prep=(W.att_q, W.att_sum),
+                                          pdl=attn_pdl)
+            else:
+                ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
+                                         at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                         _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                         pdl=pdl, q_out=W.qrot)
+                ops.verify_attention(W.qrot, _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma,
+                                     attn_mask, attn_scratch, pdl=attn_pdl, out=(None, None, W.att_s),
+                                     prep=(W.att_q, W.att_sum))
             ops.t2_gemv_prepared(W.att_q, W.att_sum, at.o_proj.weight.data, W.att_s,
                                  at.o_proj.weight_scale, out=W.attn_out, ldc=a.dim, pdl=pdl)
             ops.rmsnorm_fused(W.h, layer.post_attention_layernorm.weight.data, eps, M=M,
                               res=W.attn_out, pdl=pdl, out=qsink)
-            ops.t2_gemv_prepared(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu,
-                                 ldc=W.gu.shape[1], pdl=pdl)
-            ops.silu_mul_quant(W.gu, pdl=pdl, out=(None, W.is_), prep=(W.iq, W.i_sum))
+            if fused_ffn:
+                # SiLU(gate) * up in the GEMV epilogue (the row absmax gathered by atomic max), then
+                # the INT8 codes from a flat grid: the work of the one-CTA-per-row SiLU kernel spread
+                # over all SMs
+                ops.gate_up_silu(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, inner=W.inner,
+                                 amax=W.inner_amax[i & 1], pdl=pdl)
+                ops.quant_rows_amax(W.inner, W.inner_amax[i & 1], prep=(W.iq, W.i_sum), s=W.is_,
+                                    amax_zero=W.inner_amax[(i + 1) & 1], pdl=pdl)
+            else:
+                ops.t2_gemv_prepared(W.q, W.q_sum, ff.w_gu, W.s, ff.w_gu_scale, out=W.gu,
+                                     ldc=W.gu.shape[1], pdl=pdl)
+                ops.silu_mul_quant(W.gu, pdl=pdl, out=(None, W.is_), prep=(W.iq, W.i_sum))
             ops.t2_gemv_prepared(W.iq, W.i_sum, ff.down_proj.weight.data, W.is_,
                                  ff.down_proj.weight_scale, out=W.ffn_out, ldc=a.dim, pdl=pdl)
 
@@ -475,7 +515,7 @@ class Transformer(nn.Module):
                         ("cos_t", L0.rope_cos), ("sin_t", L0.rope_sin), ("state", attn_mask),
                         ("attn_scratch", attn_scratch), ("h", W.h), ("xq", W.q), ("xsum", W.q_sum), ("xs", W.s),
                         ("xqkv", W.xqkv), ("attq", W.att_q), ("attsum", W.att_sum), ("atts", W.att_s),
-                        ("attn_out", W.attn_out), ("inner", W.inner), ("inner_amax", W.inner_amax), ("iq", W.iq),
+                        ("attn_out", W.attn_out), ("inner", W.inner), ("inner_amax", W.inner_amax[0]), ("iq", W.iq),
                         ("isum", W.i_sum), ("is_", W.is_), ("ffn_out", W.ffn_out), ("barrier", W.sweep_barrier)):
             setattr(sa, name, t.data_ptr())
         ops.decode_sweep(sa, token_values.device)

@@ -117,6 +117,12 @@ def _declare_optional(L) -> None:
         "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_decode_sweep": [ctypes.POINTER(SweepArgs), vp],
+        "bm_zero_words": [vp, ci, vp],
+        "bm_rope_verify_attention_rows": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, ci, vp],
+        "bm_rope_verify_attention": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp,
+                                     ci, vp],
+        "bm_t2_gemv_gate_up_silu": [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, ci, vp],
+        "bm_quant_rows_amax": [vp, vp, vp, ci, ci, vp, vp, vp, vp, ci, vp],
         "bm_t2_gemv_nsplit": [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp),
                               ctypes.POINTER(vp), vp, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],

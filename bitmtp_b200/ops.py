@@ -249,3 +249,57 @@ def sweep_supported(dim: int, n_heads: int, head_dim: int, ffn_dim: int, M: int)
 def decode_sweep(args: "native.SweepArgs", device) -> None:
     """All layers of one replay in one launch; `args` is a filled native.SweepArgs."""
     check(native.lib().bm_decode_sweep(ctypes.byref(args), _stream(device)), "bm_decode_sweep")
+
+
+# --------------------------------------------------------------------------- fused SwiGLU
+def gate_up_silu(a_prep: torch.Tensor, a_sums: torch.Tensor, w_gu: torch.Tensor, s: torch.Tensor,
+                 w_gu_scale: torch.Tensor, *, inner: torch.Tensor, amax: torch.Tensor, pdl: bool = False) -> None:
+    """inner[W, F] = bf16(silu(g) * u) straight from the merged gate|up GEMV; amax[W] (uint32 bits, zero
+    on entry) collects the row absmax."""
+    W, K = a_prep.shape
+    F = w_gu.shape[0] // 2
+    rc = native.lib().bm_t2_gemv_gate_up_silu(_ptr(a_prep), _ptr(a_sums), _ptr(w_gu), _ptr(w_gu_scale), _ptr(s), W, F,
+                                              K, _ptr(inner), _ptr(amax), int(pdl), _stream(a_prep.device))
+    check(rc, f"bm_t2_gemv_gate_up_silu(W={W}, F={F}, K={K})")
+
+
+def quant_rows_amax(x: torch.Tensor, amax: torch.Tensor, *, prep: Tuple[torch.Tensor, torch.Tensor], s: torch.Tensor,
+                    amax_zero: Optional[torch.Tensor] = None, q: Optional[torch.Tensor] = None,
+                    pdl: bool = False) -> None:
+    """INT8 codes of bf16 rows whose absmax bits are in `amax`; clears `amax_zero` for the next producer."""
+    M, K = x.shape
+    rc = native.lib().bm_quant_rows_amax(_ptr(x), _ptr(amax), _ptr(amax_zero), M, K, _ptr(q), _ptr(prep[0]),
+                                         _ptr(prep[1]), _ptr(s), int(pdl), _stream(x.device))
+    check(rc, f"bm_quant_rows_amax(M={M}, K={K})")
+
+
+def rope_verify_attention(xqkv, q_w, k_w, eps, cos_t, sin_t, positions, H, Hkv, k_layer, v_layer, sigma, state,
+                          scratch, *, out, prep=None, pdl=False):
+    """qknorm_rope_kvappend + verify_attention with the first folded into the attention's chunk kernel.
+    `out` = (att or None, q or None, s), `prep` = (qp, asum)."""
+    M = xqkv.shape[0]
+    kv_rows = k_layer.shape[-2]
+    qp, asum = prep if prep is not None else (None, None)
+    rc = native.lib().bm_rope_verify_attention(
+        _ptr(xqkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos_t), _ptr(sin_t), _ptr(positions), _ptr(k_layer),
+        _ptr(v_layer), M, H, Hkv, kv_rows, sigma, _ptr(state), _ptr(scratch), _ptr(out[0]), _ptr(out[1]), _ptr(qp),
+        _ptr(asum), _ptr(out[2]), int(pdl), _stream(xqkv.device))
+    check(rc, "bm_rope_verify_attention")
+
+
+def rope_verify_attention_rows(xqkv, q_w, k_w, eps, cos_t, sin_t, positions, H, Hkv, k_layer, v_layer, sigma, state,
+                               scratch, *, att, amax, pdl=False):
+    """rope_verify_attention without the quantisation: bf16 rows into `att`, row absmax bits into `amax`
+    (uint32 [M], zero on entry); follow with quant_rows_amax(att, amax, ...)."""
+    M = xqkv.shape[0]
+    kv_rows = k_layer.shape[-2]
+    rc = native.lib().bm_rope_verify_attention_rows(
+        _ptr(xqkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos_t), _ptr(sin_t), _ptr(positions), _ptr(k_layer),
+        _ptr(v_layer), M, H, Hkv, kv_rows, sigma, _ptr(state), _ptr(scratch), _ptr(att), _ptr(amax), int(pdl),
+        _stream(xqkv.device))
+    check(rc, "bm_rope_verify_attention_rows")
+
+
+def zero_words(t: torch.Tensor) -> None:
+    """Stream-ordered clear of a 32-bit tensor (no torch in-place op: workspaces may be inference tensors)."""
+    check(native.lib().bm_zero_words(_ptr(t), t.numel(), _stream(t.device)), "bm_zero_words")

@@ -192,6 +192,24 @@ int bm_verify_attention_static(const void *q, const void *k_base, const void *v_
                                void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
                                void *stream);
 
+/* gate|up projection with SiLU(gate) * up in the epilogue: B [2F, K/4] holds the gate rows, then the
+ * up rows (scales ws [2F, K/128] likewise); inner_out bf16 [W, F] = bf16(silu(bf16 g) * bf16 u), the value
+ * bm_silu_mul_quant forms from the bf16 projection outputs; amax_out uint32 [W] receives, by atomic
+ * max, the bits of max |inner| per row and must be zero on entry.  GEMV-ready activations as for
+ * bm_t2_gemv_prepared; W <= 16.  With bm_quant_rows_amax it replaces the gate/up projections and
+ * `F.silu(g) * u` + quant_input of FeedForward (src/bonsai_sft/gpu/model.py:1053-1064), bit for bit. */
+int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *B, const void *ws,
+                            const void *s, int W, int F, int K, void *inner_out, void *amax_out, int pdl,
+                            void *stream);
+
+/* Clears n 32-bit words (stream-ordered memset): the absmax words of the first layer of a forward. */
+int bm_zero_words(void *p, int n, void *stream);
+
+/* bm_quant_rows for rows whose absmax is already known (amax_in uint32 [M]: float bits).  amax_zero
+ * (optional, another array): M words cleared for the next producer.  K % 256 == 0. */
+int bm_quant_rows_amax(const void *x, const void *amax_in, void *amax_zero, int M, int K, void *q,
+                       void *q_prep, void *asum, void *s, int pdl, void *stream);
+
 /* N-split of one wide layer over the GPUs of a node, GEMV and exchange in one kernel: this rank
  * computes the N_shard output rows of its shard (B, ws: the shard's codes and scales) and stores every
  * value at columns [col0, col0 + N_shard) of EVERY rank's bf16 [W, ldc] output buffer over NVLink
@@ -242,6 +260,26 @@ typedef struct bm_sweep_args {
     void *timing; /* optional uint64 [19]: %globaltimer (ns) of CTA 0 in layer 1: [2k] stage k starts, [2k+1] its work is done, [18] end */
 } bm_sweep_args;
 int bm_decode_sweep(const bm_sweep_args *args, void *stream);
+
+/* bm_qknorm_rope_kvappend + bm_verify_attention in two launches instead of three: the attention's chunk
+ * kernel reads the qkv projection output (xqkv bf16 [M, (H + 2 Hkv) * 128]) and does the q/k head norm, the
+ * RoPE and the append of the replay's K and V rows at [sigma, sigma + M) of the planes itself.  Other
+ * arguments and results as for those two calls; bit-identical to them. */
+int bm_rope_verify_attention(const void *xqkv, const void *q_w, const void *k_w, float eps, const void *cos_t,
+                             const void *sin_t, const void *positions, void *k_base, void *v_base, int M,
+                             int H, int Hkv, int kv_rows, int sigma, const void *state, void *scratch,
+                             void *att_out, void *q_out, void *q_prep, void *asum, void *s_out, int pdl,
+                             void *stream);
+
+/* bm_rope_verify_attention without the quantisation and with the merge spread over (row, 4 heads) CTAs:
+ * writes the bf16 rows att_out [M, H*128] and folds each row's absmax into amax_out uint32 [M] by atomic
+ * max (float bits; zero on entry).  bm_quant_rows_amax(att_out, amax_out, ...) then yields exactly the
+ * codes and multipliers of bm_rope_verify_attention.  H % 4 == 0. */
+int bm_rope_verify_attention_rows(const void *xqkv, const void *q_w, const void *k_w, float eps,
+                                  const void *cos_t, const void *sin_t, const void *positions, void *k_base,
+                                  void *v_base, int M, int H, int Hkv, int kv_rows, int sigma,
+                                  const void *state, void *scratch, void *att_out, void *amax_out, int pdl,
+                                  void *stream);
 
 /* Row argmax (lowest index on ties): logits fp32 [rows, ld] -> idx int64 [rows],
  * optional max_out fp32 [rows].  Replaces `.argmax(dim=-1)` on the logit rows

@@ -253,3 +253,97 @@ def test_prepared_from_norm_silu_attention(oracle):
     assert torch.equal(out2[0], att) and torch.equal(out2[2], ss)
     assert np.array_equal(qp.cpu().numpy(), _permute16(qn))
     assert np.array_equal(asum.cpu().numpy(), qn.astype(np.int32).reshape(M, H, 128).sum(-1))
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 6144, 2048), (9, 6144, 2048), (16, 6144, 2048), (8, 9728, 2560), (16, 768, 512),
+                                   (5, 512, 256)])
+def test_gate_up_silu_gemv_and_amax_quant(M, F, K):
+    """SiLU(gate)*up in the GEMV epilogue + quantisation with the gathered absmax against the unfused
+    chain GEMV -> bm_silu_mul_quant (each checked against the oracle elsewhere): inner rows, absmax,
+    codes, GEMV-ready codes, group sums and multipliers bit for bit; two calls on reused buffers."""
+    from bitmtp_b200 import synthetic
+    case = synthetic.gemv_case(M, 2 * F, K, seed=M + F)
+    A, B, ws, s = (case[k].to(DEV) for k in ("A", "B", "ws", "s"))
+    prep = A.view(M, -1, 4, 4).transpose(2, 3).contiguous().view(M, -1)
+    asum = A.view(M, -1, 128).to(torch.int32).sum(-1).to(torch.int32).contiguous()
+    gu = torch.empty(M, 2 * F, dtype=torch.bfloat16, device=DEV)
+    ops.t2_gemv_prepared(prep, asum, B, s, ws, out=gu)
+    ref_qp = torch.empty(M, F, dtype=torch.int8, device=DEV)
+    ref_sum = torch.empty(M, F // 128, dtype=torch.int32, device=DEV)
+    ref_q = torch.empty(M, F, dtype=torch.int8, device=DEV)
+    ref_s = torch.empty(M, 1, dtype=torch.float32, device=DEV)
+    _, _, ref_inner = ops.silu_mul_quant(gu, want_inner=True, out=(ref_q, ref_s), prep=(ref_qp, ref_sum))
+
+    amax = torch.zeros(2, M, dtype=torch.int32, device=DEV)
+    inner = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    q = torch.empty(M, F, dtype=torch.int8, device=DEV)
+    qp = torch.empty(M, F, dtype=torch.int8, device=DEV)
+    isum = torch.empty(M, F // 128, dtype=torch.int32, device=DEV)
+    s_out = torch.empty(M, 1, dtype=torch.float32, device=DEV)
+    for rep in range(2):
+        slot, nxt = rep & 1, (rep + 1) & 1
+        ops.gate_up_silu(prep, asum, B, s, ws, inner=inner, amax=amax[slot])
+        ops.quant_rows_amax(inner, amax[slot], prep=(qp, isum), s=s_out, amax_zero=amax[nxt], q=q)
+        torch.cuda.synchronize()
+        assert int(amax[nxt].abs().sum()) == 0, "the other slot was not cleared"
+        assert torch.equal(inner.view(torch.int16), ref_inner.view(torch.int16)), f"inner rows differ (call {rep})"
+        assert torch.equal(amax[slot].view(torch.float32), ref_inner.float().abs().amax(dim=1)), "absmax differs"
+        assert torch.equal(q, ref_q) and torch.equal(qp, ref_qp), "codes differ"
+        assert torch.equal(isum, ref_sum), "group sums differ"
+        assert torch.equal(s_out.view(torch.int32), ref_s.view(torch.int32)), "multipliers differ"
+    assert native.lib().bm_device_error() == 0
+
+
+@pytest.mark.parametrize("M,H,Hkv,sigma,cache_len,n_pend,D,role", ATTN_CASES)
+def test_rope_folded_into_attention(oracle, M, H, Hkv, sigma, cache_len, n_pend, D, role):
+    """bm_rope_verify_attention (q/k norm + RoPE + KV append inside the chunk kernel) against the two
+    separate calls: attention rows, codes, multipliers and the KV planes bit for bit."""
+    gen = torch.Generator().manual_seed(M * 17 + cache_len + H)
+    kv_rows = sigma + 17
+    xqkv = _bf16(gen, M, (H + 2 * Hkv) * 128, scale=2.0).to(DEV)
+    qw = (1.0 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16).to(DEV)
+    kw = (1.0 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16).to(DEV)
+    cos, sin = _rope_tables(oracle, sigma + 40)
+    cos, sin = oracle.u16_to_torch(cos).to(DEV), oracle.u16_to_torch(sin).to(DEV)
+    pos = (torch.arange(M) + max(cache_len - 1, 0)).to(torch.int64).to(DEV)
+    k0 = _bf16(gen, Hkv, kv_rows, 128, scale=1.5)
+    v0 = _bf16(gen, Hkv, kv_rows, 128)
+    rid = oracle.ROLE_IDS[role]
+    state = ops.new_step_state(DEV)
+    ops.set_step_state(state, cache_len, n_pend, rid, M - D)
+    scratch = ops.attention_scratch(M, H, sigma, DEV)
+
+    ka, va = k0.to(DEV), v0.to(DEV)
+    q = ops.qknorm_rope_kvappend(xqkv, qw, kw, 1e-6, cos, sin, pos, H, Hkv, ka, va, sigma)
+    att_a, q_a, s_a = ops.verify_attention(q, ka, va, sigma, state, scratch)
+
+    kb, vb = k0.to(DEV), v0.to(DEV)
+    att_b = torch.empty_like(att_a)
+    q_b = torch.empty_like(q_a)
+    s_b = torch.empty_like(s_a)
+    for rep in range(2):
+        ops.rope_verify_attention(xqkv, qw, kw, 1e-6, cos, sin, pos, H, Hkv, kb, vb, sigma, state, scratch,
+                                  out=(att_b, q_b, s_b))
+        torch.cuda.synchronize()
+        assert torch.equal(att_a.view(torch.int16), att_b.view(torch.int16)), f"attention rows differ (call {rep})"
+        assert torch.equal(q_a, q_b) and torch.equal(s_a.view(torch.int32), s_b.view(torch.int32))
+        assert torch.equal(ka.view(torch.int16), kb.view(torch.int16)), "K planes differ"
+        assert torch.equal(va.view(torch.int16), vb.view(torch.int16)), "V planes differ"
+    if H % 4 == 0:
+        # rows-only variant (merge spread over head groups) + quantisation with the gathered absmax
+        kc, vc = k0.to(DEV), v0.to(DEV)
+        amax = torch.zeros(2, M, dtype=torch.int32, device=DEV)
+        att_c = torch.zeros_like(att_a)
+        q_c, s_c = torch.empty_like(q_a), torch.empty_like(s_a)
+        qp_c = torch.empty_like(q_a)
+        sum_c = torch.empty(M, H, dtype=torch.int32, device=DEV)
+        for rep in range(2):
+            slot = rep & 1
+            ops.rope_verify_attention_rows(xqkv, qw, kw, 1e-6, cos, sin, pos, H, Hkv, kc, vc, sigma, state, scratch,
+                                           att=att_c, amax=amax[slot])
+            ops.quant_rows_amax(att_c, amax[slot], prep=(qp_c, sum_c), s=s_c, amax_zero=amax[1 - slot], q=q_c)
+            torch.cuda.synchronize()
+            assert torch.equal(att_a.view(torch.int16), att_c.view(torch.int16)), f"rows differ (split merge, call {rep})"
+            assert torch.equal(q_a, q_c) and torch.equal(s_a.view(torch.int32), s_c.view(torch.int32))
+            assert torch.equal(ka.view(torch.int16), kc.view(torch.int16)) and torch.equal(va.view(torch.int16), vc.view(torch.int16))
+    assert native.lib().bm_device_error() == 0
