@@ -205,9 +205,11 @@ struct NormParams {
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
     __shared__ float sh[32];
     pdl_launch_dependents();
-    if (p.pdl) pdl_wait();
     const int m = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int nwarps = blockDim.x >> 5;
+    // the norm weights do not depend on the previous kernel: requested before the wait, used after the sum
+    const uint4 wraw = reinterpret_cast<const uint4 *>(p.w)[t];
+    if (p.pdl) pdl_wait();
     const size_t src_row = p.gather ? (size_t)p.gather[m] : (size_t)(p.row0 + m);
     float h[8];
     unpack8(reinterpret_cast<const uint4 *>(p.x + src_row * p.dim)[t], h);
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
     const float total = block_sum_ordered(warp_sum_butterfly(acc), sh, lane, warp, nwarps);
     const float r = bm_rsqrtf(total / (float)p.dim + p.eps);
     float wv[8], n[8];
-    unpack8(reinterpret_cast<const uint4 *>(p.w)[t], wv);
+    unpack8(wraw, wv);
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

@@ -646,31 +646,21 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
             // rows [0, R/2) of the tile are gate rows, rows [R/2, R) the up rows of the same columns:
             // inner = bf16(silu(bf16 gate) * bf16 up), as the stand-alone SiLU kernel computes it from
             // the bf16 projection outputs
-            for (int o = threadIdx.x; o < p.W * (R / 8); o += kGemvThreads) {
-                const int m = o / (R / 8), rq = o - m * (R / 8);
-                float4 vg[kGemvWarps], vu[kGemvWarps];
+            // one output element per thread: the SiLU (own exp, IEEE division) is a long dependent chain
+            for (int o = threadIdx.x; o < p.W * (R / 2); o += kGemvThreads) {
+                const int m = o / (R / 2), c = o - m * (R / 2);
+                float vg[kGemvWarps], vu[kGemvWarps];
 #pragma unroll
                 for (int w = 0; w < kGemvWarps; ++w) {
-                    vg[w] = *reinterpret_cast<const float4 *>(&pr[(w * WROWS + m) * RP + 4 * rq]);
-                    vu[w] = *reinterpret_cast<const float4 *>(&pr[(w * WROWS + m) * RP + R / 2 + 4 * rq]);
+                    vg[w] = pr[(w * WROWS + m) * RP + c];
+                    vu[w] = pr[(w * WROWS + m) * RP + R / 2 + c];
                 }
                 const float is = invs[m];
-                float g[4], u[4], v[4];
-#define BM_TREE(V, F) (((V[0].F + V[1].F) + (V[2].F + V[3].F)) + ((V[4].F + V[5].F) + (V[6].F + V[7].F))) * is
-                g[0] = BM_TREE(vg, x); g[1] = BM_TREE(vg, y); g[2] = BM_TREE(vg, z); g[3] = BM_TREE(vg, w);
-                u[0] = BM_TREE(vu, x); u[1] = BM_TREE(vu, y); u[2] = BM_TREE(vu, z); u[3] = BM_TREE(vu, w);
-#undef BM_TREE
-                float amax = 0.0f;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    v[e] = bm_bf16_rn(bm_silu_bf16(bm_bf16_rn(g[e])) * bm_bf16_rn(u[e]));
-                    amax = fmaxf(amax, fabsf(v[e]));
-                }
-                const uint32_t lo = (uint32_t)bm_f32_to_bf16(v[0]) | ((uint32_t)bm_f32_to_bf16(v[1]) << 16);
-                const uint32_t hi = (uint32_t)bm_f32_to_bf16(v[2]) | ((uint32_t)bm_f32_to_bf16(v[3]) << 16);
-                *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.C) + (size_t)m * p.ldc + n0 + 4 * rq) =
-                    make_uint2(lo, hi);
-                atomicMax(&amax_sh[m], __float_as_uint(amax));
+                const float g = (((vg[0] + vg[1]) + (vg[2] + vg[3])) + ((vg[4] + vg[5]) + (vg[6] + vg[7]))) * is;
+                const float u = (((vu[0] + vu[1]) + (vu[2] + vu[3])) + ((vu[4] + vu[5]) + (vu[6] + vu[7]))) * is;
+                const float v = bm_bf16_rn(bm_silu_bf16(bm_bf16_rn(g)) * bm_bf16_rn(u));
+                reinterpret_cast<uint16_t *>(p.C)[(size_t)m * p.ldc + n0 + c] = bm_f32_to_bf16(v);
+                atomicMax(&amax_sh[m], __float_as_uint(fabsf(v)));
             }
             continue;
         }
