@@ -519,6 +519,23 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
     return one ? launch_mma_rb<false, true>(pl, st, pdl, p) : launch_mma_rb<false, false>(pl, st, pdl, p);
 }
 
+int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n_pend, int cache_len, int M, int D,
+                           long long mask_id, int role, int P, void *tok, void *pos, void *state, void *stream) {
+    if (kind < 0 || kind > 2 || !src_a || !tok || !pos || !state || M < 1 || M > BM_MAX_W) return BM_EINVAL;
+    if (kind == 0 && (n_pend < 1 || n_pend > P || P + D != M)) return BM_EINVAL;
+    if (kind == 1 && (!src_b || n_pend < 1 || M != D + 1)) return BM_EINVAL;
+    if (kind == 2 && M != 1) return BM_EINVAL;
+    int sp = n_pend < 0 ? 0 : n_pend;
+    const int pmax = P > 0 ? P : 0;
+    if (sp > pmax) sp = pmax;
+    if (kind != 0) sp = 0;
+    bm::stage_replay_inputs_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        kind, static_cast<const int64_t *>(src_a), static_cast<const int64_t *>(src_b), n_pend, cache_len, M, D,
+        (int64_t)mask_id, role, P, sp, static_cast<int64_t *>(tok), static_cast<int64_t *>(pos),
+        static_cast<bm::StepState *>(state));
+    return cuda_status(cudaGetLastError());
+}
+
 int bm_zero_words(void *p, int n, void *stream) {
     if (!p || n < 1) return BM_EINVAL;
     return cuda_status(cudaMemsetAsync(p, 0, (size_t)n * 4, static_cast<cudaStream_t>(stream)));

@@ -368,6 +368,43 @@ __global__ void set_step_state_kernel(StepState *st, int cache_len, int n_pend, 
     }
 }
 
+// Token ids, positions and the step record of one replay in ONE launch (the reference fills them with
+// half a dozen tensor ops per step, fast_generate.py:1015-1037 draft, 1040-1055 verify, 247-256 AR).
+//   kind 0  draft of width M = P + D:  tok = pending[0..n_pend) | 0.. | pending[n_pend-1] | MASK..,
+//           pos = cache_len + i for the pending rows, 0 for the padding rows,
+//           cache_len + n_pend - 1 + k for the D block rows
+//   kind 1  verify of width M = D + 1: tok = pending[n_pend-1] | draft[0..D), pos = cache_len - 1 + i
+//   kind 2  AR (M = 1): tok = src_a[0], pos = cache_len
+// `src_a` = pending tokens, `src_b` = draft tokens (kind 1).  The record is what bm_set_step_state writes.
+__global__ void stage_replay_inputs_kernel(int kind, const int64_t *__restrict__ src_a,
+                                           const int64_t *__restrict__ src_b, int n_pend, int cache_len, int M, int D,
+                                           int64_t mask_id, int role, int P, int state_n_pend,
+                                           int64_t *__restrict__ tok, int64_t *__restrict__ pos, StepState *st) {
+    const int i = threadIdx.x;
+    if (i == 0) {
+        st->cache_len = cache_len;
+        st->n_pend = state_n_pend;
+        st->role = role;
+        st->P = P;
+    }
+    if (i >= M) return;
+    if (kind == 0) {
+        int64_t t, q;
+        if (i > P) { t = mask_id; q = cache_len + n_pend - 1 + (i - P); }
+        else if (i == P) { t = src_a[n_pend - 1]; q = cache_len + n_pend - 1; }
+        else if (i < n_pend) { t = src_a[i]; q = cache_len + i; }
+        else { t = 0; q = 0; }
+        tok[i] = t;
+        pos[i] = q;
+    } else if (kind == 1) {
+        tok[i] = i == 0 ? src_a[n_pend - 1] : src_b[i - 1];
+        pos[i] = cache_len - 1 + i;
+    } else {
+        tok[i] = src_a[0];
+        pos[i] = cache_len;
+    }
+}
+
 // Copies rows [src_row, src_row + n) to [dst_row, dst_row + n) in every
 // (k|v, layer, kv head) plane of the shared buffer [planes, kv_rows, 128] bf16.
 // Replaces GraphAtlas.commit_kv / commit_kv_from_verify

@@ -188,12 +188,15 @@ class _Session:
     def ar_step(self, token, position: int) -> CapturedGraph:
         atlas = self.atlas
         g = atlas.get_graph(1, self.sigma, "ar")
-        if isinstance(token, torch.Tensor):
-            g.tokens_buf[0:1].copy_(token.reshape(1))
+        if isinstance(token, torch.Tensor) and token.dtype == torch.int64 and g.tokens_buf.is_cuda:
+            atlas.stage_ar(g, token.reshape(1), position)      # token, position and step record in one launch
         else:
-            g.tokens_buf[0] = int(token)
-        g.positions_buf[0] = position
-        atlas.prepare_step(g, position, n_pend=0)
+            if isinstance(token, torch.Tensor):
+                g.tokens_buf[0:1].copy_(token.reshape(1))
+            else:
+                g.tokens_buf[0] = int(token)
+            g.positions_buf[0] = position
+            atlas.prepare_step(g, position, n_pend=0)
         g.cuda_graph.replay()
         atlas.commit_kv(g, position, n_accept=1)
         return g
@@ -205,6 +208,12 @@ class _Session:
         P = M - D
         self.ensure_room()
         g = atlas.get_graph(M, self.sigma, role)
+        if g.tokens_buf.is_cuda and 1 <= n_pend <= P:
+            atlas.stage_draft(g, bufs.pending_buf, n_pend, self.cache_len, D, self.MASK)
+            g.cuda_graph.replay()
+            atlas.commit_kv(g, self.cache_len, n_pend)
+            self.cache_len += n_pend
+            return g
         tok, pos = g.tokens_buf, g.positions_buf
         tok[:n_pend].copy_(bufs.pending_buf[:n_pend])
         if n_pend < P:
@@ -225,6 +234,9 @@ class _Session:
     def stage_verify(self, n_pend: int, draft_tokens: torch.Tensor, role: str) -> CapturedGraph:
         atlas, bufs, D = self.atlas, self.bufs, self.D
         gv = atlas.get_graph(D + 1, self.sigma, role)
+        if gv.tokens_buf.is_cuda and draft_tokens.dtype == torch.int64 and draft_tokens.is_contiguous():
+            atlas.stage_verify(gv, bufs.pending_buf, n_pend, draft_tokens, self.cache_len, D)
+            return gv
         gv.tokens_buf[0:1].copy_(bufs.pending_buf[n_pend - 1:n_pend])
         gv.tokens_buf[1:1 + D].copy_(draft_tokens)
         torch.add(bufs.pos_arange[:D + 1], self.cache_len - 1, out=gv.positions_buf[:D + 1])
@@ -295,14 +307,18 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
         return bufs.gen_buf[:0].clone(), _empty_stats(prefill_time, ses.seq_len, with_draft=False)
     gen_count = 1
     t1 = time.time()
+    tok_dev = bufs.gen_buf[0:1]                    # the token of the next replay, kept on the device
     while gen_count < max_gen_len:
         ses.ensure_room()
-        g = ses.ar_step(next_tok, ses.cache_len)
+        g = ses.ar_step(tok_dev, ses.cache_len)
         ses.cache_len += 1
-        next_tok = int(_argmax_rows(g.logits_out)[-1].item())
+        tok_dev = _argmax_rows(g.logits_out)[-1:]
+        # queued before the host read below, so it does not sit in the GPU-idle window; an EOS token
+        # written here lies past gen_count and is never returned
+        bufs.gen_buf[gen_count:gen_count + 1].copy_(tok_dev)
+        next_tok = int(tok_dev.item())
         if bufs.has_eos and next_tok in eos_ids:
             break
-        bufs.gen_buf[gen_count] = next_tok
         gen_count += 1
         if (stop_strings and tokenizer is not None
                 and _decode_hits_stop(tokenizer, bufs.gen_buf[:gen_count].tolist(), stop_strings)):

@@ -196,6 +196,24 @@ class GraphAtlas:
         n_pend_clamp = max(0, min(int(n_pend), max(graph.P, 0)))
         ops.set_step_state(graph.attn_mask, int(cache_len), n_pend_clamp, _ROLE_ID[graph.role], graph.P)
 
+    # One launch instead of the tensor fills + prepare_step of a step.  The decode loops use these for
+    # graphs whose buffers live on the GPU (a CPU stand-in atlas for host-logic tests keeps the fills).
+    def stage_draft(self, graph: CapturedGraph, pending: torch.Tensor, n_pend: int, cache_len: int, D: int,
+                    mask_id: int) -> None:
+        ops.stage_replay_inputs(0, pending, None, n_pend, cache_len, graph.M, D, mask_id, _ROLE_ID[graph.role],
+                                graph.P, graph.tokens_buf, graph.positions_buf, graph.attn_mask)
+
+    def stage_verify(self, graph: CapturedGraph, pending: torch.Tensor, n_pend: int, draft_tokens: torch.Tensor,
+                     cache_len: int, D: int) -> None:
+        if cache_len <= 0:
+            raise RuntimeError("batched verifier requires a committed anchor")
+        ops.stage_replay_inputs(1, pending, draft_tokens, n_pend, cache_len, graph.M, D, 0, _ROLE_ID[graph.role],
+                                graph.P, graph.tokens_buf, graph.positions_buf, graph.attn_mask)
+
+    def stage_ar(self, graph: CapturedGraph, token: torch.Tensor, position: int) -> None:
+        ops.stage_replay_inputs(2, token, None, 0, position, 1, 0, 0, _ROLE_ID[graph.role], graph.P,
+                                graph.tokens_buf, graph.positions_buf, graph.attn_mask)
+
     def commit_kv(self, graph: CapturedGraph, cache_len: int, n_accept: int) -> None:
         """Rows [sigma, sigma+n_accept) -> history rows [cache_len, cache_len+n_accept) in
         every layer of the segment's buffer (fast_runtime.py:467-484)."""

@@ -303,3 +303,13 @@ def rope_verify_attention_rows(xqkv, q_w, k_w, eps, cos_t, sin_t, positions, H, 
 def zero_words(t: torch.Tensor) -> None:
     """Stream-ordered clear of a 32-bit tensor (no torch in-place op: workspaces may be inference tensors)."""
     check(native.lib().bm_zero_words(_ptr(t), t.numel(), _stream(t.device)), "bm_zero_words")
+
+
+def stage_replay_inputs(kind: int, src_a: torch.Tensor, src_b: Optional[torch.Tensor], n_pend: int, cache_len: int,
+                        M: int, D: int, mask_id: int, role: int, P: int, tok: torch.Tensor, pos: torch.Tensor,
+                        state: torch.Tensor) -> None:
+    """Tokens, positions and the step record of one replay in one launch (bm_stage_replay_inputs)."""
+    rc = native.lib().bm_stage_replay_inputs(int(kind), _ptr(src_a), _ptr(src_b), int(n_pend), int(cache_len), int(M),
+                                             int(D), int(mask_id), int(role), int(P), _ptr(tok), _ptr(pos), _ptr(state),
+                                             _stream(tok.device))
+    check(rc, "bm_stage_replay_inputs")
