@@ -1,9 +1,11 @@
 #!/usr/bin/env python
 """Generate the golden fixtures of tests/golden/ from the reference's own Python code.
 
-Run in a container that has the reference checked out (default /root/reference):
+Run where the reference project is checked out (its root is the directory that holds `src/bonsai_sft`):
 
-    python tests/golden/make_golden.py [--ref /root/reference] [--only ops,masks,kats,forward,streams]
+    python tests/golden/make_golden.py --ref REFERENCE_ROOT [--only ops,masks,kats,forward,streams]
+
+(`--ref` defaults to the environment variable BITMTP_REFERENCE.)
 
 The script imports `bonsai_sft.gpu` from the reference under its eager profile
 (`orin-d8`, so every `compile_helper` is the identity and the tensor expressions
@@ -531,7 +533,8 @@ def make_streams(ref, out_path, full=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("BITMTP_REFERENCE"), required="BITMTP_REFERENCE" not in os.environ,
+                    help="root of the reference checkout")
     ap.add_argument("--only", default="ops,masks,kats,forward,streams")
     a = ap.parse_args()
     ref = load_reference(a.ref)
