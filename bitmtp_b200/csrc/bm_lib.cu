@@ -404,6 +404,13 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     p.pdl = 0;
     p.silu_F = 0;
     p.amax_out = nullptr;
+    p.src_mode = 0;
+    p.xb = p.res = p.norm_w = nullptr;
+    p.gather = nullptr;
+    p.h_out = nullptr;
+    p.eps = 0.0f;
+    p.amax_in = nullptr;
+    p.amax_zero = nullptr;
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
@@ -501,6 +508,13 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
     p.pdl = pdl;
     p.silu_F = F;
     p.amax_out = static_cast<unsigned int *>(amax_out);
+    p.src_mode = 0;
+    p.xb = p.res = p.norm_w = nullptr;
+    p.gather = nullptr;
+    p.h_out = nullptr;
+    p.eps = 0.0f;
+    p.amax_in = nullptr;
+    p.amax_zero = nullptr;
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
@@ -534,6 +548,57 @@ int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n
         (int64_t)mask_id, role, P, sp, static_cast<int64_t *>(tok), static_cast<int64_t *>(pos),
         static_cast<bm::StepState *>(state));
     return cuda_status(cudaGetLastError());
+}
+
+int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const void *res, const void *norm_w, float eps,
+                         void *h_out, const void *amax_in, void *amax_zero, const void *B, const void *ws, int N, int K,
+                         void *C, int ldc, int out_kind, int silu, void *amax_out, int pdl, void *stream) {
+    if ((src_mode != 1 && src_mode != 2) || !x || !B || !ws || !C || N < 8 || (N % 8) != 0 || (K % 256) != 0 || K < 256)
+        return BM_EINVAL;
+    if (src_mode == 1 && !amax_in) return BM_EINVAL;
+    if (src_mode == 2 && (!norm_w || K != 8 * bm::kGemvThreads)) return BM_EINVAL;
+    if (silu && (!amax_out || out_kind != BM_OUT_BF16 || (N % 16) != 0)) return BM_EINVAL;
+    if (ldc < N || (ldc % 4) != 0 || out_kind < 0 || out_kind > 2) return BM_EINVAL;
+    if (!aligned16(x) || !aligned16(B) || !aligned16(ws) || !aligned16(C) || (res && !aligned16(res)) ||
+        (norm_w && !aligned16(norm_w)) || (h_out && !aligned16(h_out)))
+        return BM_EINVAL;
+    bm::GemvParams p;
+    p.A = nullptr;
+    p.asum = nullptr;
+    p.B = static_cast<const uint8_t *>(B);
+    p.ws = static_cast<const uint16_t *>(ws);
+    p.s = nullptr;
+    p.C = C;
+    p.G = nullptr;
+    p.W = 1;
+    p.N = N;
+    p.K = K;
+    p.ldc = ldc;
+    p.out_kind = out_kind;
+    p.pdl = pdl;
+    p.silu_F = silu ? N : 0;
+    p.amax_out = static_cast<unsigned int *>(amax_out);
+    p.src_mode = src_mode;
+    p.xb = static_cast<const uint16_t *>(x);
+    p.res = static_cast<const uint16_t *>(res);
+    p.norm_w = static_cast<const uint16_t *>(norm_w);
+    p.gather = static_cast<const int64_t *>(gather);
+    p.h_out = static_cast<uint16_t *>(h_out);
+    p.eps = eps;
+    p.amax_in = static_cast<const unsigned int *>(amax_in);
+    p.amax_zero = static_cast<unsigned int *>(amax_zero);
+    p.world = 0;
+    p.rank = 0;
+    p.done = nullptr;
+    for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
+    const int sms = current_device().sm_count;
+    const bool one = K == 2048;
+    MmaPlan pl;
+    if (!make_mma_plan(silu ? 2 * N : N, K, true, sms, 0, &pl)) return BM_EINVAL;
+    if (silu && (N % (4 * pl.rb)) != 0 && !make_mma_plan(2 * N, K, true, sms, 1, &pl)) return BM_EINVAL;
+    p.stages = pl.stages;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return one ? launch_mma_rb<true, true>(pl, st, pdl, p) : launch_mma_rb<true, false>(pl, st, pdl, p);
 }
 
 int bm_zero_words(void *p, int n, void *stream) {

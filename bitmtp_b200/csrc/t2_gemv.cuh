@@ -41,6 +41,7 @@
 #pragma once
 
 #include "bm_common.cuh"
+#include "fused_ops.cuh"
 
 namespace bm {
 
@@ -68,6 +69,19 @@ struct GemvParams {
     // max |output| of row m (zero before the launch).  silu_F == 0: plain projection.
     int silu_F;
     unsigned int *amax_out;
+    // Width-1 launches that make their own activations (MMA consumer): instead of INT8 codes the
+    // kernel is given the bf16 row and every CTA quantises it itself (a few thousand elements), which
+    // removes a launch from the dependency chain of an AR replay.
+    //   src_mode 1  x bf16 [K] + the bits of its absmax (amax_in[0]); amax_zero[0] is cleared
+    //   src_mode 2  (gather | residual add) + RMSNorm of x (K == 2048 == 8 * threads), then the codes:
+    //               the arithmetic of rmsnorm_kernel; CTA 0 stores the summed row to h_out
+    int src_mode;
+    const uint16_t *xb, *res, *norm_w;
+    const int64_t *gather;
+    uint16_t *h_out;
+    float eps;
+    const unsigned int *amax_in;
+    unsigned int *amax_zero;
     // N-split over the GPUs of a node (bf16 output only): this launch computes rows of one shard;
     // every value is also stored into the same place of each peer's output buffer over NVLink, and
     // the last CTA to finish tells the peers and waits for their shards.  world <= 1: unused.
@@ -372,6 +386,55 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_dp4a_kernel(const GemvPa
     }
 }
 
+// ---- width-1 activations made by the GEMV itself (src_mode 1 / 2) -------------------------------
+// All kGemvThreads threads call this.  Leaves the GEMV-ready codes of token 0 in the staging row, its
+// group sums and 1/s in shared memory.  `sh`: 32 floats of scratch.
+__device__ __forceinline__ void gemv_stage_row_from_bf16(const GemvParams &p, unsigned char *smem, int act_off,
+                                                         int asum_off, int invs_off, float *sh) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = kGemvThreads / 32;
+    const QuantSink sink{nullptr, reinterpret_cast<int8_t *>(smem + act_off), reinterpret_cast<int32_t *>(smem + asum_off)};
+    float *invs = reinterpret_cast<float *>(smem + invs_off);
+    float s;
+    if (p.src_mode == 2) {
+        const uint4 wraw = reinterpret_cast<const uint4 *>(p.norm_w)[t];
+        const size_t src_row = p.gather ? (size_t)p.gather[0] : 0;
+        float h[8];
+        unpack8(reinterpret_cast<const uint4 *>(p.xb + src_row * p.K)[t], h);
+        if (p.res) {
+            float rr[8];
+            unpack8(reinterpret_cast<const uint4 *>(p.res)[t], rr);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = bm_bf16_rn(h[i] + rr[i]);
+        }
+        if (blockIdx.x == 0 && p.h_out) reinterpret_cast<uint4 *>(p.h_out)[t] = pack8(h);
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(h[i], h[i], acc);
+        const float total = block_sum_ordered(warp_sum_butterfly(acc), sh, lane, warp, nwarps);
+        const float rs = bm_rsqrtf(total / (float)p.K + p.eps);
+        float wv[8], n[8];
+        unpack8(wraw, wv);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            n[i] = bm_bf16_rn(wv[i] * bm_bf16_rn(h[i] * rs));
+            amax = fmaxf(amax, fabsf(n[i]));
+        }
+        amax = block_max(amax, sh, lane, warp, nwarps);
+        s = bm_act_scale(amax);
+        emit_codes(sink, 0, p.K, t, quant8(n, s), true, lane);
+    } else {
+        s = bm_act_scale(__uint_as_float(p.amax_in[0]));
+        for (int i = t; i < p.K / 8; i += kGemvThreads) {          // K % 256 == 0: whole warps
+            float v[8];
+            unpack8(reinterpret_cast<const uint4 *>(p.xb)[i], v);
+            emit_codes(sink, 0, p.K, i, quant8(v, s), true, lane);
+        }
+        if (blockIdx.x == 0 && t == 0 && p.amax_zero) p.amax_zero[0] = 0u;
+    }
+    if (t < 16) invs[t] = t == 0 ? 1.0f / s : 0.0f;
+}
+
 // =============================================================================
 // Consumer 2: tokens as the MMA rows, mma.sync.m16n8k32 s8 x u8 -> s32.
 //
@@ -528,8 +591,11 @@ __global__ void __launch_bounds__(kGemvThreads, 2) t2_gemv_mma_kernel(const Gemv
     bool a_ok = true;
     {
         float *invs_w = reinterpret_cast<float *>(smem + L.invs_off);
-        if (threadIdx.x < 16) invs_w[threadIdx.x] = threadIdx.x < p.W ? 1.0f / p.s[threadIdx.x] : 0.0f;
-        if (!prepared) {
+        if (p.src_mode == 0 && threadIdx.x < 16) invs_w[threadIdx.x] = threadIdx.x < p.W ? 1.0f / p.s[threadIdx.x] : 0.0f;
+        if (p.src_mode != 0) {
+            __shared__ float stage_sh[32];
+            gemv_stage_row_from_bf16(p, smem, L.act_off, L.asum_off, L.invs_off, stage_sh);
+        } else if (!prepared) {
             GemvSmem LA;
             LA.act_off = L.act_off;
             LA.act_stride = L.act_stride;

@@ -332,6 +332,7 @@ class StepWorkspace:
         self.inner = buf((M, args.ffn_dim), bf)
         self.inner_amax = torch.zeros((2, M), dtype=i32, device=device)   # row absmax bits, two slots used in turn
         self.att_amax = torch.zeros((2, M), dtype=i32, device=device)
+        self.h2 = buf((M, args.dim), bf)            # second residual buffer of the width-1 fused path
         self.sweep_barrier = torch.zeros((2,), dtype=i32, device=device)
         self.n_pad = n_pad
 
@@ -364,6 +365,9 @@ class Transformer(nn.Module):
         self.fused_rope = os.environ.get("BM_FUSED_ROPE", "1") != "0"
         # attention merge over (row, 4 heads) CTAs + flat quantisation (BM_SPLIT_MERGE=0: one merge CTA per row)
         self.split_merge = os.environ.get("BM_SPLIT_MERGE", "1") != "0"
+        # width-1 replays: RMSNorm / quantisation inside the consuming GEMV, 6 launches per layer instead
+        # of 10 (BM_FUSED_AR=0: the general sequence)
+        self.fused_ar = os.environ.get("BM_FUSED_AR", "1") != "0"
         self._sweep_tables = {}
 
     def tie_weights(self) -> None:
@@ -412,6 +416,42 @@ class Transformer(nn.Module):
             layer.attention.prepare_merged_weights(max_positions, tables=tables)
             layer.feed_forward.prepare_merged_weights()
         self.max_positions = max_positions
+
+    def _ar_fused_supported(self, M: int) -> bool:
+        a = self.args
+        return (self.fused_ar and M == 1 and a.dim == 2048 and a.n_heads % 4 == 0 and a.head_dim == 128
+                and (a.n_heads * a.head_dim) % 256 == 0 and a.ffn_dim % 256 == 0)
+
+    def _layers_ar_fused(self, W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
+                         pdl, attn_pdl) -> None:
+        """Width-1 layer stack in six launches per layer: each projection quantises (and, for qkv and
+        gate|up, normalises) its own input row.  The residual stream alternates between W.h2 and W.h and
+        ends in W.h, where the final norm expects it."""
+        a = self.args
+        eps = a.norm_eps
+        ops.zero_words(W.inner_amax[0])
+        ops.zero_words(W.att_amax[0])
+        for i, layer in enumerate(self.layers):
+            at, ff = layer.attention, layer.feed_forward
+            k_l, v_l = kv_full[i]
+            if i == 0:
+                ops.gemv_row_fused(2, self.embed_tokens.weight.data, at.wqkv_weight, at.wqkv_scale, out=W.xqkv,
+                                   gather=token_values, norm_w=layer.input_layernorm.weight.data, eps=eps,
+                                   h_out=W.h2, pdl=pdl)
+            else:
+                ops.gemv_row_fused(2, W.ffn_out, at.wqkv_weight, at.wqkv_scale, out=W.xqkv, res=W.h,
+                                   norm_w=layer.input_layernorm.weight.data, eps=eps, h_out=W.h2, pdl=pdl)
+            ops.rope_verify_attention_rows(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps, at.rope_cos,
+                                           at.rope_sin, positions, a.n_heads, a.n_kv_heads,
+                                           _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma, attn_mask,
+                                           attn_scratch, att=W.att, amax=W.att_amax[i & 1], pdl=attn_pdl)
+            ops.gemv_row_fused(1, W.att, at.o_proj.weight.data, at.o_proj.weight_scale, out=W.attn_out,
+                               amax_in=W.att_amax[i & 1], amax_zero=W.att_amax[(i + 1) & 1], pdl=pdl)
+            ops.gemv_row_fused(2, W.h2, ff.w_gu, ff.w_gu_scale, out=W.inner, res=W.attn_out,
+                               norm_w=layer.post_attention_layernorm.weight.data, eps=eps, h_out=W.h, silu=True,
+                               amax_out=W.inner_amax[i & 1], pdl=pdl)
+            ops.gemv_row_fused(1, W.inner, ff.down_proj.weight.data, ff.down_proj.weight_scale, out=W.ffn_out,
+                               amax_in=W.inner_amax[i & 1], amax_zero=W.inner_amax[(i + 1) & 1], pdl=pdl)
 
     def _layers_by_operator(self, W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
                             pdl, attn_pdl) -> None:
@@ -580,6 +620,9 @@ class Transformer(nn.Module):
         if self.use_sweep and ops.sweep_supported(a.dim, a.n_heads, a.head_dim, a.ffn_dim, M) \
                 and token_values.is_contiguous() and positions.is_contiguous():
             self._sweep_layers(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch)
+        elif self._ar_fused_supported(M) and token_values.is_contiguous() and positions.is_contiguous():
+            self._layers_ar_fused(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
+                                  pdl, attn_pdl)
         else:
             self._layers_by_operator(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
                                      pdl, attn_pdl)

@@ -118,6 +118,7 @@ def _declare_optional(L) -> None:
         "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_decode_sweep": [ctypes.POINTER(SweepArgs), vp],
         "bm_zero_words": [vp, ci, vp],
+        "bm_t2_gemv_row_fused": [ci, vp, vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, vp, ci, ci, ci, vp, ci, vp],
         "bm_stage_replay_inputs": [ci, vp, vp, ci, ci, ci, ci, ctypes.c_longlong, ci, ci, vp, vp, vp, vp],
         "bm_rope_verify_attention_rows": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, ci, vp],
         "bm_rope_verify_attention": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp,

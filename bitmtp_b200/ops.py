@@ -313,3 +313,19 @@ def stage_replay_inputs(kind: int, src_a: torch.Tensor, src_b: Optional[torch.Te
                                              int(D), int(mask_id), int(role), int(P), _ptr(tok), _ptr(pos), _ptr(state),
                                              _stream(tok.device))
     check(rc, "bm_stage_replay_inputs")
+
+
+def gemv_row_fused(src_mode: int, x: torch.Tensor, w: torch.Tensor, ws: torch.Tensor, *, out: torch.Tensor,
+                   gather: Optional[torch.Tensor] = None, res: Optional[torch.Tensor] = None,
+                   norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, h_out: Optional[torch.Tensor] = None,
+                   amax_in: Optional[torch.Tensor] = None, amax_zero: Optional[torch.Tensor] = None, silu: bool = False,
+                   amax_out: Optional[torch.Tensor] = None, out_kind: int = native.OUT_BF16, pdl: bool = False) -> None:
+    """Width-1 GEMV that quantises its own bf16 input row (bm_t2_gemv_row_fused): src_mode 1 = row with known
+    absmax, 2 = (gather | add) + RMSNorm; `silu`: merged gate|up weights with the SiLU epilogue."""
+    K = w.shape[1] * 4
+    N = w.shape[0] // 2 if silu else w.shape[0]
+    rc = native.lib().bm_t2_gemv_row_fused(
+        int(src_mode), _ptr(x), _ptr(gather), _ptr(res), _ptr(norm_w), float(eps), _ptr(h_out), _ptr(amax_in),
+        _ptr(amax_zero), _ptr(w), _ptr(ws), N, K, _ptr(out), out.shape[-1], int(out_kind), int(silu), _ptr(amax_out),
+        int(pdl), _stream(x.device))
+    check(rc, f"bm_t2_gemv_row_fused(mode={src_mode}, N={N}, K={K})")

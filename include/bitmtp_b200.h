@@ -213,6 +213,22 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
 int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n_pend, int cache_len, int M, int D,
                            long long mask_id, int role, int P, void *tok, void *pos, void *state, void *stream);
 
+/* Width-1 GEMV that makes its own INT8 activations from a bf16 row, for the AR replay (one launch per
+ * projection instead of two): every CTA quantises the row itself.
+ *   src_mode 1: x bf16 [K] with the bits of its absmax in amax_in[0] (as left by
+ *               bm_rope_verify_attention_rows or bm_t2_gemv_gate_up_silu); amax_zero[0] (optional, another
+ *               word) is cleared.  Equals bm_quant_rows_amax + bm_t2_gemv_prepared.
+ *   src_mode 2: h = bf16(x_row + res) (x_row = x[gather[0]] when gather is given, res optional), stored to
+ *               h_out [K] (must not alias x or res), then RMSNorm with norm_w and eps and the codes.
+ *               K == 2048.  Equals bm_rmsnorm_fused + bm_t2_gemv_prepared.
+ *   silu != 0: B holds 2N rows (gate, then up), C bf16 [N] = bf16(silu(g) * u), amax_out[0] gathers its
+ *               absmax (zero on entry), as bm_t2_gemv_gate_up_silu.
+ * Other arguments as bm_t2_gemv.  Bit-identical to the chains named above. */
+int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const void *res, const void *norm_w,
+                         float eps, void *h_out, const void *amax_in, void *amax_zero, const void *B,
+                         const void *ws, int N, int K, void *C, int ldc, int out_kind, int silu, void *amax_out,
+                         int pdl, void *stream);
+
 /* Clears n 32-bit words (stream-ordered memset): the absmax words of the first layer of a forward. */
 int bm_zero_words(void *p, int n, void *stream);
 

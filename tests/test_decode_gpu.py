@@ -147,3 +147,37 @@ def test_layer_sweep_kernel_equals_operator_path(oracle, role, M, cache_len, n_p
         want = om.forward(tokens.cpu().numpy(), positions.cpu().numpy(), kv_np, sigma, rid, cache_len, n_pend, ls, le)
         assert np.array_equal(outs[True][0].cpu().numpy().view(np.uint32), want.view(np.uint32))
         assert np.array_equal(oracle.torch_to_u16(outs[True][1].cpu()), kv_np)
+
+
+@pytest.mark.parametrize("cache_len", [0, 37, 200])
+def test_width1_fused_layers_equal_operator_path(cache_len):
+    """The six-launch width-1 layer (RMSNorm / quantisation inside the consuming GEMV) against the general
+    launch sequence on the 1.7B layer geometry: logits, residual stream and KV rows bit for bit."""
+    geometry = dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096)
+    cfg = synthetic.make_config(geometry, block_size=8)
+    sigma, m_max = 256, 17
+    model, _ = _model(cfg, 5, sigma + m_max)
+    assert model._ar_fused_supported(1)
+    L, Hkv, M = cfg["n_layers"], cfg["n_kv_heads"], 1
+    gen = torch.Generator().manual_seed(cache_len + 1)
+    kv = (torch.randn(2, L, 1, Hkv, sigma + m_max, 128, generator=gen) * 0.5).to(torch.bfloat16)
+    tokens = torch.randint(0, cfg["vocab_size"], (M,), generator=gen).to(DEV)
+    positions = torch.arange(cache_len, cache_len + M).to(DEV)
+    state_t = ops.new_step_state(DEV)
+    ops.set_step_state(state_t, cache_len, 0, native.ROLE_AR, M - 8)
+    outs = {}
+    for fused in (False, True):
+        kvd = kv.to(DEV)
+        kv_full = [(kvd[0, i][:, :, : sigma + M, :], kvd[1, i][:, :, : sigma + M, :]) for i in range(L)]
+        model.fused_ar = fused
+        try:
+            for rep in range(2):
+                logits = model.forward_sdlm_decode_graph_kernel(tokens, positions, kv_full, M, state_t, 0, M, "t2")
+        finally:
+            model.fused_ar = True
+        torch.cuda.synchronize()
+        assert native.lib().bm_device_error() == 0
+        outs[fused] = (logits.clone(), kvd.clone(), model.workspace(M).h.clone())
+    assert torch.equal(outs[True][0].view(torch.int32), outs[False][0].view(torch.int32)), "logits differ"
+    assert torch.equal(outs[True][1].view(torch.int16), outs[False][1].view(torch.int16)), "KV rows differ"
+    assert torch.equal(outs[True][2].view(torch.int16), outs[False][2].view(torch.int16)), "residual stream differs"
