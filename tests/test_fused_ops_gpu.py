@@ -347,3 +347,44 @@ def test_rope_folded_into_attention(oracle, M, H, Hkv, sigma, cache_len, n_pend,
             assert torch.equal(q_a, q_c) and torch.equal(s_a.view(torch.int32), s_c.view(torch.int32))
             assert torch.equal(ka.view(torch.int16), kc.view(torch.int16)) and torch.equal(va.view(torch.int16), vc.view(torch.int16))
     assert native.lib().bm_device_error() == 0
+
+
+@pytest.mark.parametrize("M,D,n_pend,cache_len", [(9, 8, 1, 40), (10, 8, 2, 7), (12, 8, 3, 100), (16, 8, 8, 300),
+                                                  (17, 8, 9, 12), (16, 8, 5, 1), (5, 4, 1, 9), (9, 4, 5, 64)])
+def test_stage_replay_inputs_matches_the_tensor_fills(M, D, n_pend, cache_len):
+    """bm_stage_replay_inputs against the per-step tensor fills of the decode loops (draft, verify, AR)."""
+    MASK = 151654
+    P = M - D
+    gen = torch.Generator().manual_seed(M * 31 + n_pend)
+    pending = torch.randint(0, 150000, (18,), generator=gen, dtype=torch.int64).to(DEV)
+    draft = torch.randint(0, 150000, (D,), generator=gen, dtype=torch.int64).to(DEV)
+    ar = torch.arange(32, dtype=torch.int64, device=DEV)
+    # draft
+    tok = torch.full((M,), -7, dtype=torch.int64, device=DEV)
+    pos = torch.full((M,), -7, dtype=torch.int64, device=DEV)
+    tok[:n_pend] = pending[:n_pend]
+    if n_pend < P:
+        tok[n_pend:P] = 0
+        pos[n_pend:P] = 0
+    tok[P:P + 1] = pending[n_pend - 1:n_pend]
+    if P + 1 < M:
+        tok[P + 1:] = MASK
+    pos[:n_pend] = ar[:n_pend] + cache_len
+    pos[P:P + D] = ar[:D] + (cache_len + n_pend - 1)
+    tok2, pos2 = torch.full_like(tok, -1), torch.full_like(pos, -1)
+    st = ops.new_step_state(DEV)
+    ops.stage_replay_inputs(0, pending, None, n_pend, cache_len, M, D, MASK, native.ROLE_DRAFT, P, tok2, pos2, st)
+    assert torch.equal(tok, tok2) and torch.equal(pos, pos2)
+    assert st.cpu().tolist() == [cache_len, max(0, min(n_pend, max(P, 0))), native.ROLE_DRAFT, P]
+    # verify (width D + 1)
+    tokv = torch.cat([pending[n_pend - 1:n_pend], draft])
+    posv = ar[:D + 1] + (cache_len - 1)
+    tok3, pos3 = torch.empty_like(tokv), torch.empty_like(posv)
+    ops.stage_replay_inputs(1, pending, draft, n_pend, cache_len, D + 1, D, 0, native.ROLE_VERIFY, 1, tok3, pos3, st)
+    assert torch.equal(tokv, tok3) and torch.equal(posv, pos3)
+    assert st.cpu().tolist() == [cache_len, 0, native.ROLE_VERIFY, 1]
+    # AR
+    tok4, pos4 = torch.empty(1, dtype=torch.int64, device=DEV), torch.empty(1, dtype=torch.int64, device=DEV)
+    ops.stage_replay_inputs(2, draft[2:3], None, 0, cache_len, 1, 0, 0, native.ROLE_AR, 1 - D, tok4, pos4, st)
+    assert int(tok4) == int(draft[2]) and int(pos4) == cache_len
+    assert st.cpu().tolist() == [cache_len, 0, native.ROLE_AR, 1 - D]
