@@ -9,6 +9,8 @@ Prints ONE JSON line (rank 0).  Workloads:
             full-block acceptance, 256-token prompt, 512 new tokens, batch 1,
             CUDA-graph replay (the configuration the headline metric is quoted
             on).  A step is one full generation; value = decode tokens/s.
+            --model 4b --accept categorical is the 4B configuration (accepted
+            length per step drawn from a seeded categorical with mean 4).
   gemv      Width-specialised GEMV sweep over every Qwen3-1.7B-style layer shape
             and W in {1,2,4,8}; a step is one pass over the sweep;
             value = aggregate algorithmic GB/s.
@@ -52,6 +54,9 @@ def parse_args():
                     help="gemv workloads: programmatic dependent launch between the calls, as in the decode replay")
     ap.add_argument("--tune", type=int, default=0, help="gemv-one: tuning value passed in bits 8.. of the path")
     ap.add_argument("--mode", default="hybrid", choices=["ar", "conf", "spec", "hybrid"])
+    ap.add_argument("--accept", default="forced", choices=["forced", "categorical", "free"],
+                    help="decode: accepted length per step (forced = whole block; categorical = seeded "
+                         "draw over 1..8 with mean 4; free = measured)")
     ap.add_argument("--model", default="1p7b", choices=["1p7b", "4b", "tiny"])
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--new-tokens", type=int, default=None)

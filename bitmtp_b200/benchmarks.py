@@ -17,17 +17,37 @@ GEOMETRIES = {"1p7b": "BONSAI_1P7B", "4b": "BONSAI_4B", "tiny": "TINY"}
 D8_WIDTHS = (1, 8, 9, 10, 12, 16, 17)
 
 
-def _forced_hooks(FG, D):
+def acceptance_hooks(FG, policy):
+    """Replacements for the loops' confidence-chain and prefix-accept reductions that apply
+    a synthetic.AcceptancePolicy.  The kernels still run; their counts are overwritten in
+    place, so they stay part of the record the loop reads in one copy."""
     chain, accept = FG._fused_draft_chain, FG._fused_verify_accept
 
-    def forced_chain(logits, threshold):
-        idx, n = chain(logits, threshold)
-        return idx, torch.full_like(n, D)
+    def hooked_chain(logits, threshold, out=None):
+        idx, n = chain(logits, threshold, out)
+        a = policy.chain_count()
+        return idx, (n if a is None else n.fill_(a))
 
-    def forced_accept(draft, verify, Dd):
-        return torch.full_like(accept(draft, verify, Dd), Dd)
+    def hooked_accept(draft, verify, Dd, out=None):
+        n = accept(draft, verify, Dd, out)
+        a = policy.accept_count()
+        return n if a is None else n.fill_(a)
 
-    return forced_chain, forced_accept
+    return hooked_chain, hooked_accept
+
+
+class _ReplayCounter:
+    """Stands in for a CapturedGraph's cuda_graph: forwards replay() and counts the calls."""
+
+    def __init__(self, graph):
+        self.graph, self.replays = graph, 0
+
+    def replay(self):
+        self.replays += 1
+        self.graph.replay()
+
+    def __getattr__(self, name):
+        return getattr(self.graph, name)
 
 
 def build_decode(model_name: str, device, prompt_len: int, new_tokens: int, seed: int = 0):
@@ -124,8 +144,10 @@ def run_decode(args, world, rank, local, dist):
     warmup = args.warmup if args.warmup is not None else 3
     model, atlas, cfg = build_decode(args.model, device, prompt_len, new_tokens, seed=rank)
     D = cfg["block_size"]
-    fc, fa = _forced_hooks(FG, D)
-    FG._fused_draft_chain, FG._fused_verify_accept = fc, fa
+    policy = synthetic.AcceptancePolicy(args.accept, D, seed=rank)
+    FG._fused_draft_chain, FG._fused_verify_accept = acceptance_hooks(FG, policy)
+    for g in atlas.graphs.values():
+        g.cuda_graph = _ReplayCounter(g.cuda_graph)
     fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
           "hybrid": FG.fast_hybrid_generate, "conf": FG.fast_confidence_generate}[args.mode]
     prompt_host = synthetic.random_prompt(prompt_len, cfg["vocab_size"], seed=100 + rank).pin_memory()
@@ -143,6 +165,9 @@ def run_decode(args, world, rank, local, dist):
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tok = dec_t = tot_t = iters = 0.0
+    for g in atlas.graphs.values():
+        g.cuda_graph.replays = 0
+    eager_before = native.lib().bm_launch_count()
     e0.record()
     for _ in range(steps):
         out, st = one()
@@ -164,13 +189,18 @@ def run_decode(args, world, rank, local, dist):
     value = tok_all / dec_t_max
     e2e = new_all / (ms * 1e-3)
 
-    # kernels launched inside the timed region: graph nodes per replay x replays + per-step ops
-    L = cfg["n_layers"]
-    nodes = 1 + L * 11 - 1 + 2                   # norm/gemv/rope/attn(2)/gemv/norm/gemv/silu/gemv + final norm + head
-    launches = int(iters * (nodes + 8) + steps * (prompt_len // 16) * nodes)
+    # this library's kernels inside the timed region: launches it issued eagerly (prefill slabs,
+    # staging, argmax / chain / accept, KV promotion) + its kernel nodes in every replayed graph
+    launches = int(native.lib().bm_launch_count() - eager_before
+                   + sum(g.cuda_graph.replays * g.n_kernels for g in atlas.graphs.values()))
+    replays = {f"{r}:M{M}": g.cuda_graph.replays for (M, _, r), g in sorted(atlas.graphs.items())
+               if g.cuda_graph.replays}
     roof_m = 16 if args.mode in ("hybrid", "conf") else (1 if args.mode == "ar" else 9)
     rf = _gemv_roofline(model, roof_m, device)
     peak, peak_kind = bench.peaks()
+    accept_words = {"forced": "forced full-block acceptance", "free": "measured acceptance",
+                    "categorical": "accepted length per step drawn from a seeded categorical over 1..8 "
+                                   "(p ~ 0.9083^k, mean 4)"}[args.accept]
     res = {
         "metric": "decode tok/s (Bonsai-1.7B-arch D8, bs1)" if args.model == "1p7b" else
                   f"decode tok/s (Bonsai-{args.model}-arch D8, bs1 per GPU)",
@@ -179,7 +209,7 @@ def run_decode(args, world, rank, local, dist):
         "vs_baseline": None, "dtype": "s8 x ternary -> s32 (bf16 activations in memory)",
         "data": "synthetic",
         "config": {"workload": f"Bonsai-{args.model}-architecture {args.mode} MTP decode, random-init ternary "
-                               f"weights, block 8, forced full-block acceptance, {prompt_len}-token random "
+                               f"weights, block 8, {accept_words}, {prompt_len}-token random "
                                f"prompt, {new_tokens} new tokens, batch 1, CUDA-graph replay, native T2 head "
                                "for draft and verify",
                    "segment": atlas.segment_ladder[0], "widths": list(atlas.m_set),
@@ -198,7 +228,9 @@ def run_decode(args, world, rank, local, dist):
                                "average per launch)",
                      "frac_of_8TBps": round(rf["gbs"] / 8000.0, 4)},
         "decode": {"iters_per_generation": iters / steps, "decode_ms_per_generation": dec_t / steps * 1e3,
-                   "total_ms_per_generation": tot_t / steps * 1e3},
+                   "total_ms_per_generation": tot_t / steps * 1e3,
+                   "graph_replays_timed": replays,
+                   "tokens_per_iteration": round(tok / max(iters - steps, 1.0), 3)},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         res["cpu_baseline"] = cpu_decode_baseline(args.model, roof_m)

@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/bitmtp_b200.h"
@@ -43,6 +44,11 @@ DeviceInfo current_device() {
 
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? BM_OK : BM_ECUDA_BASE + (int)e; }
 
+// Kernel launches issued by this library since it was loaded (launches recorded into a
+// stream capture count once, at capture).  Diagnostic only: read through bm_launch_count.
+std::atomic<unsigned long long> g_launches{0};
+inline void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 // Generic launch with the optional programmatic-serialisation attribute.
 template <typename Kernel, typename... Args>
 int launch_ex(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int pdl,
@@ -61,6 +67,7 @@ int launch_ex(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    count_launch();
     return cuda_status(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
 
@@ -79,6 +86,7 @@ int launch(Kernel kernel, int grid, int block, int smem, cudaStream_t stream, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    count_launch();
     return cuda_status(cudaLaunchKernelEx(&cfg, kernel, p));
 }
 
@@ -340,6 +348,8 @@ const char *bm_version(void) { return "bitmtp_b200 0.1 (sm_100a)"; }
 
 int bm_sm_count(void) { return current_device().sm_count; }
 
+unsigned long long bm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
 int bm_device_error(void) {
     int v = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
@@ -543,6 +553,7 @@ int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n
     const int pmax = P > 0 ? P : 0;
     if (sp > pmax) sp = pmax;
     if (kind != 0) sp = 0;
+    count_launch();
     bm::stage_replay_inputs_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         kind, static_cast<const int64_t *>(src_a), static_cast<const int64_t *>(src_b), n_pend, cache_len, M, D,
         (int64_t)mask_id, role, P, sp, static_cast<int64_t *>(tok), static_cast<int64_t *>(pos),
@@ -656,6 +667,7 @@ int bm_qknorm_rope_kvappend(const void *xqkv, const void *q_w, const void *k_w, 
 
 int bm_set_step_state(void *state, int cache_len, int n_pend, int role, int P, void *stream) {
     if (!state || cache_len < 0 || role < 0 || role > 2) return BM_EINVAL;
+    count_launch();
     bm::set_step_state_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<bm::StepState *>(state), cache_len, n_pend, role, P);
     return cuda_status(cudaGetLastError());
@@ -666,6 +678,7 @@ int bm_kv_copy_rows(void *kv, int planes, int kv_rows, int src_row, int dst_row,
         return BM_EINVAL;
     if (n == 0) return BM_OK;
     if (!(src_row >= dst_row + n || dst_row >= src_row + n)) return BM_EINVAL;   // ranges must not overlap
+    count_launch();
     bm::kv_copy_rows_kernel<<<planes, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint16_t *>(kv), planes, kv_rows, src_row, dst_row, n);
     return cuda_status(cudaGetLastError());
@@ -804,6 +817,7 @@ int bm_rope_verify_attention(const void *xqkv, const void *q_w, const void *k_w,
 // ---------------------------------------------------------------------------- logits
 int bm_argmax_rows(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out, void *stream) {
     if (!logits || !idx || rows < 1 || vocab < 1 || ld < vocab) return BM_EINVAL;
+    count_launch();
     bm::argmax_rows_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float *>(logits), vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_out));
     return cuda_status(cudaGetLastError());
@@ -815,16 +829,20 @@ int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void
         vocab > bm::kConfMaxChunks * 256)
         return BM_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    count_launch();
     bm::argmax_rows_kernel<<<D, 1024, 0, st>>>(static_cast<const float *>(logits), vocab, ld,
                                                static_cast<int64_t *>(idx), static_cast<float *>(max_buf));
+    count_launch();
     bm::row_confidence_kernel<<<D, 256, 0, st>>>(static_cast<const float *>(logits), vocab, ld,
                                                  static_cast<const float *>(max_buf), static_cast<float *>(conf));
+    count_launch();
     bm::chain_length_kernel<<<1, 32, 0, st>>>(static_cast<const float *>(conf), D, tau, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
 }
 
 int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, void *stream) {
     if (!draft || !verify || !n_out || D < 1) return BM_EINVAL;
+    count_launch();
     bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
@@ -918,6 +936,7 @@ int bm_decode_sweep(const bm_sweep_args *a, void *stream) {
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     return cuda_status(cudaLaunchKernelEx(&cfg, bm::decode_sweep_kernel, p));
 }
 

@@ -46,23 +46,46 @@ def _decode_hits_stop(tokenizer, token_ids: Sequence[int], stop_strings) -> bool
     return _first_stop_index(text, stop_strings) < len(text)
 
 
-def _argmax_rows(logits: torch.Tensor) -> torch.Tensor:
-    """Row argmax, lowest index on ties (native kernel)."""
-    return ops.argmax_rows(logits)
+def _argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row argmax, lowest index on ties (native kernel); written into `out` when given."""
+    return ops.argmax_rows(logits, out=out)
 
 
-def _fused_draft_chain(logits: torch.Tensor, threshold: float) -> Tuple[torch.Tensor, torch.Tensor]:
+def _fused_draft_chain(logits: torch.Tensor, threshold: float,
+                       out: Optional[Tuple[torch.Tensor, ...]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(draft ids [D], iter_accept) with iter_accept = 1 + the number of leading rows
     r >= 1 whose confidence exp(max - logsumexp) exceeds the threshold
-    (fast_generate.py:111-130).  Row 0 is always committed."""
-    idx, n, _ = ops.draft_chain(logits, threshold)
+    (fast_generate.py:111-130).  Row 0 is always committed.  `out` = (ids, max work area,
+    confidences, count) places the results in the caller's buffers."""
+    idx, n, _ = ops.draft_chain(logits, threshold, bufs=out)
     return idx, n
 
 
-def _fused_verify_accept(draft_tokens: torch.Tensor, verify_tokens: torch.Tensor, D: int) -> torch.Tensor:
+def _fused_verify_accept(draft_tokens: torch.Tensor, verify_tokens: torch.Tensor, D: int,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Length of the longest prefix of identical token ids (fast_generate.py:133-146);
     logits are deliberately not an input."""
-    return ops.verify_accept(draft_tokens, verify_tokens, D)
+    return ops.verify_accept(draft_tokens, verify_tokens, D, out=out)
+
+
+def _read_record(rec: torch.Tensor, *parts: torch.Tensor) -> List[List[int]]:
+    """Host copies of `parts` as lists.  When the parts tile the front of `rec` in order
+    (the decode buffers are laid out that way) this is ONE device-to-host copy and one
+    synchronisation; otherwise one per part."""
+    addr, total = rec.data_ptr(), 0
+    tiled = rec.is_contiguous()
+    for p in parts:
+        tiled = (tiled and p.dtype == rec.dtype and p.is_contiguous()
+                 and p.data_ptr() == addr + total * rec.element_size())
+        total += p.numel()
+    if not tiled or total > rec.numel():
+        return [p.reshape(-1).tolist() for p in parts]
+    flat = rec[:total].tolist()
+    out, at = [], 0
+    for p in parts:
+        out.append(flat[at:at + p.numel()])
+        at += p.numel()
+    return out
 
 
 def _select_M_for_pending(atlas, n_pend: int) -> int:
@@ -102,12 +125,24 @@ class _DecodeBufs:
     pos_arange: torch.Tensor    # int64 [max(M_max + 1, prompt_len)]
     has_eos: bool
     M_max: int
+    # Result records, each read by the host in one copy.  The count slots are int64 words whose
+    # low half the kernels write as int32 (the high half stays zero).
+    chain_rec: torch.Tensor     # int64 [D + 1]: draft ids | confidence-chain length
+    chain_work: torch.Tensor    # fp32 [2, D]: row maxima and confidences of the chain kernel
+    verify_rec: torch.Tensor    # int64 [2D + 2]: verifier ids (D + 1) | accepted count | draft ids (D)
+
+    def chain_out(self, D: int):
+        return self.chain_rec[:D], self.chain_work[0], self.chain_work[1], self.chain_rec[D:D + 1]
 
 
 def _alloc_decode_bufs(atlas, max_gen_len: int, eos_ids, prompt_len: int = 0) -> _DecodeBufs:
     dev = atlas.device
     m_max = max(atlas.M_max, 1)
+    D = max(int(atlas.D), 1)
     return _DecodeBufs(
+        chain_rec=torch.zeros(D + 1, dtype=torch.long, device=dev),
+        chain_work=torch.zeros((2, D), dtype=torch.float32, device=dev),
+        verify_rec=torch.zeros(2 * D + 2, dtype=torch.long, device=dev),
         gen_buf=torch.zeros(max_gen_len + m_max + 1, dtype=torch.long, device=dev),
         pending_buf=torch.zeros(m_max + 1, dtype=torch.long, device=dev),
         commit_buf=torch.zeros(m_max + 1, dtype=torch.long, device=dev),
@@ -115,12 +150,14 @@ def _alloc_decode_bufs(atlas, max_gen_len: int, eos_ids, prompt_len: int = 0) ->
         has_eos=bool(eos_ids), M_max=m_max)
 
 
-def _commit_and_eos(bufs: _DecodeBufs, n_commit: int, eos_set) -> Tuple[List[int], bool, int]:
-    """One bulk device-to-host copy of the committed ids, then a host scan for EOS; the EOS
-    token itself is not kept (fast_generate.py:149-171)."""
+def _commit_and_eos(bufs: _DecodeBufs, n_commit: int, eos_set,
+                    host_tokens: Optional[List[int]] = None) -> Tuple[List[int], bool, int]:
+    """Host scan of the committed ids for EOS; the EOS token itself is not kept
+    (fast_generate.py:149-171).  The ids come from `host_tokens` when the caller has already
+    read them, else from one bulk device-to-host copy of commit_buf."""
     if n_commit <= 0:
         return [], False, 0
-    toks = bufs.commit_buf[:n_commit].tolist()
+    toks = host_tokens[:n_commit] if host_tokens is not None else bufs.commit_buf[:n_commit].tolist()
     if not eos_set:
         return toks, False, n_commit
     for kept, t in enumerate(toks):
@@ -243,20 +280,29 @@ class _Session:
         atlas.prepare_step(gv, self.cache_len, n_pend=0)
         return gv
 
-    def verify_and_commit(self, gv: CapturedGraph, draft_tokens: torch.Tensor) -> int:
+    def verify_and_commit(self, gv: CapturedGraph, draft_tokens: torch.Tensor,
+                          draft_host: Optional[List[int]] = None) -> Tuple[int, List[int]]:
         """Replay the verifier, accept the longest matching prefix, build
-        commit_buf = draft[:acc] | verify[acc], promote the accepted rows.  Returns acc."""
+        commit_buf = draft[:acc] | verify[acc], promote the accepted rows.  Returns
+        (acc, the acc + 1 committed ids on the host).  The verifier's ids, the count and (when
+        the caller has not read them yet) the draft ids come back in one host read."""
         atlas, bufs, D = self.atlas, self.bufs, self.D
         gv.cuda_graph.replay()
-        verify_tokens = _argmax_rows(gv.logits_out)
-        acc = int(_fused_verify_accept(draft_tokens, verify_tokens, D).item())
+        rec = bufs.verify_rec
+        verify_tokens = _argmax_rows(gv.logits_out, rec[:D + 1])
+        acc_t = _fused_verify_accept(draft_tokens, verify_tokens, D, rec[D + 1:D + 2])
+        if draft_host is None:
+            verify_host, acc_host, draft_host = _read_record(rec, verify_tokens, acc_t, draft_tokens)
+        else:
+            verify_host, acc_host = _read_record(rec, verify_tokens, acc_t)
+        acc = int(acc_host[0])
         if acc > 0:
             bufs.commit_buf[:acc].copy_(draft_tokens[:acc])
         bufs.commit_buf[acc:acc + 1].copy_(verify_tokens[acc:acc + 1])
         if acc > 0:
             atlas.commit_kv_from_verify(gv, self.cache_len, acc)
             self.cache_len += acc
-        return acc
+        return acc, [int(t) for t in draft_host[:acc]] + [int(verify_host[acc])]
 
     def exact_m1_verify(self, n_pend: int, draft_tokens: torch.Tensor) -> Tuple[int, int]:
         """Verify with the width-1 graph accelerated AR uses, stopping at the first mismatch
@@ -365,6 +411,8 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
     n_conf_path = n_verify_path = draft_iters = drafted_total = 0
     accepted_draft_total = verifier_bonus_total = 0
 
+    chain_out = bufs.chain_out(D)
+    spec_draft_out = bufs.verify_rec[D + 2:2 * D + 2]
     t1 = time.time()
     while gen_count < max_gen_len and not eos_found:
         n_iters += 1
@@ -372,23 +420,29 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
         drafted_total += D
         gd = ses.draft_step(n_pend, draft_role)
 
+        draft_host = None                    # the D draft ids on the host, once read
         if policy == "spec":
-            draft_tokens = _argmax_rows(gd.logits_out)
+            # the draft ids go beside the verifier's in the record that the host reads once
+            draft_tokens = _argmax_rows(gd.logits_out, spec_draft_out)
             use_verify = True
             iter_accept = 0
             gv = None if exact_m1_verify else ses.stage_verify(n_pend, draft_tokens, verify_role)
         else:
-            draft_tokens, iter_accept_t = _fused_draft_chain(gd.logits_out, threshold)
+            draft_tokens, iter_accept_t = _fused_draft_chain(gd.logits_out, threshold, chain_out)
             # Verifier inputs are queued before the host reads the chain length, so the
             # read overlaps their preparation (fast_generate.py:1040-1055).
             gv = None
             if policy == "hybrid" and not exact_m1_verify:
                 gv = ses.stage_verify(n_pend, draft_tokens, verify_role)
-            iter_accept = int(iter_accept_t.item())
+            draft_host, n_host = _read_record(bufs.chain_rec, draft_tokens, iter_accept_t)
+            iter_accept = int(n_host[0])
             use_verify = policy == "hybrid" and iter_accept < hybrid_m
 
+        commit_src = bufs.commit_buf          # device ids of this iteration's commit
+        commit_host = None                    # the same ids on the host, when already read
         if not use_verify:
-            bufs.commit_buf[:iter_accept].copy_(draft_tokens[:iter_accept])
+            commit_src = draft_tokens
+            commit_host = [int(t) for t in draft_host[:iter_accept]]
             n_commit = accepted_this_iter = iter_accept
             bonus_this_iter = 0
             n_conf_path += 1
@@ -399,12 +453,12 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
                     bufs.commit_buf[:acc].copy_(draft_tokens[:acc])
                 bufs.commit_buf[acc] = bonus
             else:
-                acc = ses.verify_and_commit(gv, draft_tokens)
+                acc, commit_host = ses.verify_and_commit(gv, draft_tokens, draft_host)
             n_commit = acc + 1
             accepted_this_iter, bonus_this_iter = acc, 1
             n_verify_path += 1
 
-        _, eos_hit, n_kept = _commit_and_eos(bufs, n_commit, eos_ids)
+        _, eos_hit, n_kept = _commit_and_eos(bufs, n_commit, eos_ids, commit_host)
         if eos_hit:
             eos_found = True
             n_commit = n_kept
@@ -422,7 +476,7 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
         verifier_bonus_total += bonus_emitted
 
         if n_commit > 0:
-            bufs.gen_buf[gen_count:gen_count + n_commit].copy_(bufs.commit_buf[:n_commit])
+            bufs.gen_buf[gen_count:gen_count + n_commit].copy_(commit_src[:n_commit])
             gen_count += n_commit
         elif policy != "spec":
             eos_found = True
@@ -431,11 +485,11 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
 
         if use_verify:
             # verified rows were promoted; only the bonus token is pending
-            bufs.pending_buf[0:1].copy_(bufs.commit_buf[n_commit - 1:n_commit])
+            bufs.pending_buf[0:1].copy_(commit_src[n_commit - 1:n_commit])
             n_pend = 1
         else:
             # confidence commit: the committed block is recomputed as pending next time
-            bufs.pending_buf[:n_commit].copy_(bufs.commit_buf[:n_commit])
+            bufs.pending_buf[:n_commit].copy_(commit_src[:n_commit])
             n_pend = n_commit
         if ses.out_of_room(n_pend):
             break

@@ -52,6 +52,7 @@ class CapturedGraph:
     logits_end: int
     lm_head_precision: str
     flex_attn_fn: Optional[object] = None  # kept for field compatibility; always None
+    n_kernels: int = 0                     # this library's kernel nodes in the graph (bm_launch_count at capture)
 
 
 def role_logit_rows(role: str, M: int, D: int) -> Tuple[int, int]:
@@ -167,11 +168,14 @@ class GraphAtlas:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        launches_before = native.lib().bm_launch_count()
         with torch.cuda.graph(graph):
             logits = body()
+        n_kernels = int(native.lib().bm_launch_count() - launches_before)
         return CapturedGraph(cuda_graph=graph, tokens_buf=tokens_buf, positions_buf=positions_buf,
                              attn_mask=state, logits_out=logits, kv_full=kv_full, M=M, sigma=sigma,
-                             role=role, P=P, logits_start=ls, logits_end=le, lm_head_precision="t2")
+                             role=role, P=P, logits_start=ls, logits_end=le, lm_head_precision="t2",
+                             n_kernels=n_kernels)
 
     # ------------------------------------------------------------------ selection
     def select_segment(self, needed_kv_len: int) -> int:

@@ -92,6 +92,7 @@ def lib() -> ctypes.CDLL:
     L.bm_version.restype = ctypes.c_char_p
     L.bm_sm_count.restype = ci
     L.bm_device_error.restype = ci
+    L.bm_launch_count.restype = ctypes.c_ulonglong
     L.bm_t2_gemv.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, ci, vp]
     L.bm_t2_gemv.restype = ci
     L.bm_t2_gemv_bytes.argtypes = [ci, ci, ci, ci]

@@ -110,6 +110,71 @@ def write_checkpoint(out_dir: str, cfg: Dict, seed: int = 0) -> str:
     return out_dir
 
 
+class AcceptancePolicy:
+    """How many draft tokens a benchmark or test run accepts per step, in place of the measured
+    confidence chain / prefix match (random-init weights accept almost nothing by themselves).
+
+    kind  "free"         keep the measured counts
+          "forced"       the whole block: chain length D, verifier accepts D
+          "categorical"  a seeded draw a in 1..D per step with p(k) proportional to r**k
+                         (r = 0.9082925: mean 4.0 at D = 8); the chain length becomes a, and
+                         a verifier replay in the same step accepts a - 1 (+ its own token =
+                         a committed).  A verifier replay with no chain before it (the
+                         speculative policy) draws its own a.
+    The draws come from a splitmix64 stream, so every host reproduces them from the seed."""
+
+    R = 0.9082925
+
+    def __init__(self, kind: str, D: int, seed: int = 0):
+        if kind not in ("free", "forced", "categorical"):
+            raise ValueError(f"unknown acceptance policy {kind!r}")
+        self.kind, self.D = kind, int(D)
+        self._state = (int(seed) * 0x9E3779B97F4A7C15 + 0x1234567) & 0xFFFFFFFFFFFFFFFF
+        self._a = None
+        w = [self.R ** k for k in range(1, self.D + 1)]
+        tot = sum(w)
+        self.p = [x / tot for x in w]
+        self.draws: list = []
+
+    def _uniform(self) -> float:
+        self._state = (self._state + 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+        z = self._state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+        z ^= z >> 31
+        return (z >> 11) / float(1 << 53)
+
+    def _draw(self) -> int:
+        u, acc = self._uniform(), 0.0
+        a = self.D
+        for k, pk in enumerate(self.p, start=1):
+            acc += pk
+            if u < acc:
+                a = k
+                break
+        self.draws.append(a)
+        return a
+
+    def chain_count(self):
+        """Replacement for the confidence-chain length of this step, or None to keep it."""
+        if self.kind == "free":
+            return None
+        if self.kind == "forced":
+            return self.D
+        self._a = self._draw()
+        return self._a
+
+    def accept_count(self):
+        """Replacement for the verifier's accepted-prefix length, or None to keep it."""
+        if self.kind == "free":
+            return None
+        if self.kind == "forced":
+            return self.D
+        a = self._a if self._a is not None else self._draw()
+        self._a = None
+        return a - 1
+
+
 def random_prompt(length: int, vocab: int, seed: int = 0) -> torch.Tensor:
     gen = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (1, length), generator=gen, dtype=torch.int64)

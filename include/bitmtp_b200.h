@@ -50,6 +50,11 @@ const char *bm_version(void);
 /* Number of SMs the launch heuristics were sized for on the current device. */
 int bm_sm_count(void);
 
+/* Kernel launches this library has issued in this process (a launch recorded into a
+ * stream capture counts once, at capture time; replays of the graph are the caller's to
+ * count).  Host-side diagnostic counter; no reference counterpart. */
+unsigned long long bm_launch_count(void);
+
 /* Reads and clears the per-device error word that kernels set when a bounded
  * wait runs out (0 = none, 1 = a GEMV weight tile never arrived). Synchronises
  * the device. */

@@ -101,25 +101,30 @@ class CpuAtlas(GraphAtlas):
 
 class patched_host_ops:
     """Context manager: route the loops' three device reductions to the oracle and make
-    torch.cuda.synchronize a no-op, optionally forcing full acceptance."""
+    torch.cuda.synchronize a no-op; `policy` (synthetic.AcceptancePolicy) may replace the
+    measured counts."""
 
-    def __init__(self, D, forced):
-        self.D, self.forced = D, forced
+    def __init__(self, D, policy):
+        self.D, self.policy = D, policy
 
     def __enter__(self):
         self.saved = (FG._argmax_rows, FG._fused_draft_chain, FG._fused_verify_accept,
                       torch.cuda.synchronize)
-        D, forced = self.D, self.forced
+        policy = self.policy
 
-        def argmax_rows(logits):
+        # The loops offer result buffers (`out`); these stand-ins return fresh tensors instead, which
+        # takes the loops through their one-read-per-part path.
+        def argmax_rows(logits, out=None):
             return torch.from_numpy(O.argmax_rows(logits.numpy()))
 
-        def chain(logits, threshold):
+        def chain(logits, threshold, out=None):
             idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
-            return torch.from_numpy(idx), torch.tensor(D if forced else n)
+            a = policy.chain_count()
+            return torch.from_numpy(idx), torch.tensor([n if a is None else a])
 
-        def accept(draft, verify, Dd):
-            return torch.tensor(Dd if forced else O.verify_accept(draft.numpy(), verify.numpy(), Dd))
+        def accept(draft, verify, Dd, out=None):
+            a = policy.accept_count()
+            return torch.tensor([O.verify_accept(draft.numpy(), verify.numpy(), Dd) if a is None else a])
 
         FG._argmax_rows, FG._fused_draft_chain, FG._fused_verify_accept = argmax_rows, chain, accept
         torch.cuda.synchronize = lambda *a, **k: None

@@ -469,7 +469,7 @@ def make_cpu_atlas(ref, om, args, segment_ladder, m_set, roles, check_masks=True
     return atlas
 
 
-def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, forced, ladder, m_set):
+def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind, ladder, m_set, accept_seed=0):
     RG = ref.generate
     om = O.OracleModel(cfg, state, max_positions=max(ladder) + max(m_set))
     args = ref.model.ModelArgs(dim=cfg["dim"], n_layers=cfg["n_layers"], n_heads=cfg["n_heads"],
@@ -484,13 +484,17 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, forced, lad
     torch.cuda.synchronize = lambda *a, **k: None
     torch.cuda.empty_cache = lambda *a, **k: None
     orig_chain, orig_accept = RG._fused_draft_chain, RG._fused_verify_accept
+    from bitmtp_b200 import synthetic
+    policy = synthetic.AcceptancePolicy(accept_kind, D, seed=accept_seed)
 
     def chain(logits, threshold):
         idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
-        return torch.from_numpy(idx), torch.tensor(D if forced else n)
+        a = policy.chain_count()
+        return torch.from_numpy(idx), torch.tensor(n if a is None else a)
 
     def accept(draft_tokens, verify_tokens, Dd):
-        return torch.tensor(Dd) if forced else orig_accept(draft_tokens, verify_tokens, Dd)
+        a = policy.accept_count()
+        return orig_accept(draft_tokens, verify_tokens, Dd) if a is None else torch.tensor(a)
 
     RG._fused_draft_chain, RG._fused_verify_accept = chain, accept
     try:
@@ -510,22 +514,26 @@ def make_streams(ref, out_path, full=False):
     records = []
     geoms = {"tiny": synthetic.TINY,
              "tiny_g4": dict(synthetic.TINY, n_heads=4, n_kv_heads=1, dim=512, ffn_dim=768)}
-    plans = [("tiny", 8, "ar", False, 24, 20), ("tiny", 8, "spec", False, 40, 48),
-             ("tiny", 8, "hybrid", False, 40, 48), ("tiny", 8, "hybrid", True, 40, 64),
-             ("tiny", 8, "spec", True, 33, 40), ("tiny_g4", 8, "hybrid", True, 50, 40),
-             ("tiny_g4", 8, "hybrid", False, 50, 40), ("tiny", 4, "hybrid", True, 21, 30),
-             ("tiny", 4, "spec", False, 21, 30)]
-    for (gname, D, mode, forced, plen, ntok) in plans:
+    # acceptance: "free" = measured, "forced" = whole block, "categorical" = seeded draw per step
+    # (synthetic.AcceptancePolicy, seed = prompt length)
+    plans = [("tiny", 8, "ar", "free", 24, 20), ("tiny", 8, "spec", "free", 40, 48),
+             ("tiny", 8, "hybrid", "free", 40, 48), ("tiny", 8, "hybrid", "forced", 40, 64),
+             ("tiny", 8, "spec", "forced", 33, 40), ("tiny_g4", 8, "hybrid", "forced", 50, 40),
+             ("tiny_g4", 8, "hybrid", "free", 50, 40), ("tiny", 4, "hybrid", "forced", 21, 30),
+             ("tiny", 4, "spec", "free", 21, 30), ("tiny", 8, "hybrid", "categorical", 37, 96),
+             ("tiny_g4", 8, "spec", "categorical", 29, 60), ("tiny", 4, "hybrid", "categorical", 19, 40)]
+    for (gname, D, mode, accept_kind, plen, ntok) in plans:
         cfg = synthetic.make_config(geoms[gname], block_size=D)
         state = synthetic.make_state(cfg, seed=7)
         prompt = synthetic.random_prompt(plen, cfg["vocab_size"], seed=plen)
         m_set = (1, 8, 9, 10, 12, 16, 17) if D == 8 else (1, 4, 5, 6, 7, 8, 9)
-        toks, stats = run_reference_loop(ref, O, cfg, state, mode, prompt, ntok, forced, (64, 256), m_set)
+        toks, stats = run_reference_loop(ref, O, cfg, state, mode, prompt, ntok, accept_kind, (64, 256), m_set,
+                                         accept_seed=plen)
         records.append(dict(geometry=gname, cfg=cfg, state_seed=7, prompt_seed=plen, prompt_len=plen,
-                            new_tokens=ntok, mode=mode, forced=forced, ladder=[64, 256],
-                            m_set=list(m_set), tokens=toks, stats=stats))
-        print(gname, D, mode, "forced" if forced else "free", len(toks), "tokens",
-              "iters", stats.get("n_iters"))
+                            new_tokens=ntok, mode=mode, forced=accept_kind == "forced", accept=accept_kind,
+                            accept_seed=plen, ladder=[64, 256], m_set=list(m_set), tokens=toks, stats=stats))
+        print(gname, D, mode, accept_kind, len(toks), "tokens", "iters", stats.get("n_iters"),
+              "verify paths", stats.get("n_verify_path"))
     with open(out_path, "w") as f:
         json.dump(records, f)
     print("wrote", out_path)

@@ -9,6 +9,7 @@ import pytest
 import torch
 
 from bitmtp_b200 import fast_generate as FG, generate, native, ops, synthetic
+from bitmtp_b200.benchmarks import acceptance_hooks
 from bitmtp_b200.fast_runtime import GraphAtlas
 
 pytestmark = pytest.mark.gpu
@@ -64,29 +65,17 @@ def test_forward_matches_oracle(oracle, geom, role, M, cache_len, n_pend):
     assert np.array_equal(oracle.torch_to_u16(kvd.cpu()), kv_np), "KV buffer differs"
 
 
-def _forced(D):
-    chain, accept = FG._fused_draft_chain, FG._fused_verify_accept
-
-    def forced_chain(logits, threshold):
-        idx, n = chain(logits, threshold)
-        return idx, torch.full_like(n, D)
-
-    def forced_accept(draft, verify, Dd):
-        return torch.full_like(accept(draft, verify, Dd), Dd)
-
-    return forced_chain, forced_accept
-
-
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
-                                                         f"{'forced' if r['forced'] else 'free'}")
+                                                         f"{r['accept']}")
 def test_token_streams_match_reference_loops(rec, monkeypatch):
     cfg = rec["cfg"]
     model, _ = _model(cfg, rec["state_seed"], max(rec["ladder"]) + max(rec["m_set"]))
     roles = ("ar",) if rec["mode"] == "ar" else ("ar", "draft", "verify")
     atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=tuple(rec["ladder"]),
                        m_set=tuple(rec["m_set"]), roles=roles, capture_verbose=False)
-    if rec["forced"]:
-        fc, fa = _forced(cfg["block_size"])
+    if rec["accept"] != "free":
+        policy = synthetic.AcceptancePolicy(rec["accept"], cfg["block_size"], seed=rec["accept_seed"])
+        fc, fa = acceptance_hooks(FG, policy)
         monkeypatch.setattr(FG, "_fused_draft_chain", fc)
         monkeypatch.setattr(FG, "_fused_verify_accept", fa)
     prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
@@ -181,3 +170,38 @@ def test_width1_fused_layers_equal_operator_path(cache_len):
     assert torch.equal(outs[True][0].view(torch.int32), outs[False][0].view(torch.int32)), "logits differ"
     assert torch.equal(outs[True][1].view(torch.int16), outs[False][1].view(torch.int16)), "KV rows differ"
     assert torch.equal(outs[True][2].view(torch.int16), outs[False][2].view(torch.int16)), "residual stream differs"
+
+
+def test_confidence_stream_with_categorical_acceptance_equals_cpu_loop(oracle):
+    """Confidence-only decode with a seeded accepted length per step walks the draft widths
+    9, 10, 12 and 16 (n_pend = 1..8).  The captured graphs must produce the token stream the same
+    loop produces over the CPU oracle forward, with the same draws."""
+    from tests.cpu_atlas import CpuAtlas, OracleModel, patched_host_ops
+    cfg = synthetic.make_config(synthetic.TINY, block_size=8)
+    ladder, m_set, roles = (256,), (1, 8, 9, 10, 12, 16, 17), ("ar", "draft", "verify")
+    model, state = _model(cfg, 7, max(ladder) + max(m_set))
+    prompt = synthetic.random_prompt(31, cfg["vocab_size"], seed=31)
+    new_tokens = 120
+
+    om = oracle.OracleModel(cfg, state, max_positions=max(ladder) + max(m_set))
+    cpu_atlas = CpuAtlas(om, model.args, ladder, m_set, roles)
+    policy = synthetic.AcceptancePolicy("categorical", 8, seed=5)
+    with patched_host_ops(8, policy):
+        want, want_stats = FG.fast_confidence_generate(OracleModel(om, model.args), cpu_atlas, prompt,
+                                                       max_gen_len=new_tokens, eos_ids=())
+    widths = {M for (_, M, _, _, _) in cpu_atlas.log}
+    assert {9, 10, 12, 16} <= widths, widths
+
+    atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=ladder, m_set=m_set, roles=roles,
+                       capture_verbose=False)
+    policy = synthetic.AcceptancePolicy("categorical", 8, seed=5)
+    saved = FG._fused_draft_chain, FG._fused_verify_accept
+    FG._fused_draft_chain, FG._fused_verify_accept = acceptance_hooks(FG, policy)
+    try:
+        got, stats = FG.fast_confidence_generate(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=())
+    finally:
+        FG._fused_draft_chain, FG._fused_verify_accept = saved
+    assert native.lib().bm_device_error() == 0
+    assert got.cpu().tolist() == want.tolist()
+    for key in ("n_iters", "draft_iters", "accepted_drafts", "n_conf_path", "n_verify_path", "decode_tokens"):
+        assert stats[key] == want_stats[key], key

@@ -19,7 +19,7 @@ MODES = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
 
 
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
-                                                         f"{'forced' if r['forced'] else 'free'}")
+                                                         f"{r['accept']}")
 def test_stream_matches_reference_loops(rec):
     cfg = rec["cfg"]
     state = synthetic.make_state(cfg, seed=rec["state_seed"])
@@ -28,7 +28,8 @@ def test_stream_matches_reference_loops(rec):
     roles = ("ar",) if rec["mode"] == "ar" else ("ar", "draft", "verify")
     atlas = CpuAtlas(om, args, rec["ladder"], rec["m_set"], roles)
     prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
-    with patched_host_ops(cfg["block_size"], rec["forced"]):
+    policy = synthetic.AcceptancePolicy(rec["accept"], cfg["block_size"], seed=rec["accept_seed"])
+    with patched_host_ops(cfg["block_size"], policy):
         out, stats = MODES[rec["mode"]](OracleModel(om, args), atlas, prompt,
                                         max_gen_len=rec["new_tokens"], eos_ids=())
     assert out.tolist() == rec["tokens"]
@@ -36,3 +37,19 @@ def test_stream_matches_reference_loops(rec):
         assert stats[key] == pytest.approx(want), key
     # the run crossed a segment boundary where the record says so
     assert {s for (_, _, s, _, _) in atlas.log} <= set(rec["ladder"])
+
+
+def test_read_record_single_copy_and_fallback():
+    """_read_record returns the same lists whether the parts tile the record (one copy) or
+    are separate tensors (one copy each); a count written as int32 into the low half of an
+    int64 slot reads back as that count."""
+    rec = torch.zeros(12, dtype=torch.long)
+    rec[:5] = torch.tensor([7, 8, 9, 10, 11])
+    rec[5:6].view(torch.int32)[0] = 3                      # what the kernels write
+    rec[6:11] = torch.tensor([1, 2, 3, 4, 5])
+    ids, n, more = FG._read_record(rec, rec[:5], rec[5:6], rec[6:11])
+    assert (ids, n, more) == ([7, 8, 9, 10, 11], [3], [1, 2, 3, 4, 5])
+    # parts that do not start at the record, are out of order, or live elsewhere
+    assert FG._read_record(rec, rec[1:5], rec[5:6]) == [[8, 9, 10, 11], [3]]
+    assert FG._read_record(rec, rec[5:6], rec[:5]) == [[3], [7, 8, 9, 10, 11]]
+    assert FG._read_record(rec, torch.tensor([4, 5]), torch.tensor(6)) == [[4, 5], [6]]
