@@ -146,7 +146,8 @@ def run_decode(args, world, rank, local, dist):
     D = cfg["block_size"]
     policy = synthetic.AcceptancePolicy(args.accept, D, seed=rank)
     FG._fused_draft_chain, FG._fused_verify_accept = acceptance_hooks(FG, policy)
-    for g in atlas.graphs.values():
+    counted = list(atlas.graphs.values()) + list(atlas.prefill_graphs.values())
+    for g in counted:
         g.cuda_graph = _ReplayCounter(g.cuda_graph)
     fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
           "hybrid": FG.fast_hybrid_generate, "conf": FG.fast_confidence_generate}[args.mode]
@@ -165,7 +166,7 @@ def run_decode(args, world, rank, local, dist):
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tok = dec_t = tot_t = iters = 0.0
-    for g in atlas.graphs.values():
+    for g in counted:
         g.cuda_graph.replays = 0
     eager_before = native.lib().bm_launch_count()
     e0.record()
@@ -192,9 +193,10 @@ def run_decode(args, world, rank, local, dist):
     # this library's kernels inside the timed region: launches it issued eagerly (prefill slabs,
     # staging, argmax / chain / accept, KV promotion) + its kernel nodes in every replayed graph
     launches = int(native.lib().bm_launch_count() - eager_before
-                   + sum(g.cuda_graph.replays * g.n_kernels for g in atlas.graphs.values()))
+                   + sum(g.cuda_graph.replays * g.n_kernels for g in counted))
     replays = {f"{r}:M{M}": g.cuda_graph.replays for (M, _, r), g in sorted(atlas.graphs.items())
                if g.cuda_graph.replays}
+    replays["prompt-slab:M16"] = sum(g.cuda_graph.replays for g in atlas.prefill_graphs.values())
     roof_m = 16 if args.mode in ("hybrid", "conf") else (1 if args.mode == "ar" else 9)
     rf = _gemv_roofline(model, roof_m, device)
     peak, peak_kind = bench.peaks()

@@ -545,10 +545,11 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
 
 int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n_pend, int cache_len, int M, int D,
                            long long mask_id, int role, int P, void *tok, void *pos, void *state, void *stream) {
-    if (kind < 0 || kind > 2 || !src_a || !tok || !pos || !state || M < 1 || M > BM_MAX_W) return BM_EINVAL;
+    if (kind < 0 || kind > 3 || !src_a || !tok || !pos || !state || M < 1 || M > BM_MAX_W) return BM_EINVAL;
     if (kind == 0 && (n_pend < 1 || n_pend > P || P + D != M)) return BM_EINVAL;
     if (kind == 1 && (!src_b || n_pend < 1 || M != D + 1)) return BM_EINVAL;
     if (kind == 2 && M != 1) return BM_EINVAL;
+    if (kind == 3 && (n_pend < 1 || n_pend > M)) return BM_EINVAL;
     int sp = n_pend < 0 ? 0 : n_pend;
     const int pmax = P > 0 ? P : 0;
     if (sp > pmax) sp = pmax;

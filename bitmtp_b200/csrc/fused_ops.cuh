@@ -375,7 +375,8 @@ __global__ void set_step_state_kernel(StepState *st, int cache_len, int n_pend, 
 //           cache_len + n_pend - 1 + k for the D block rows
 //   kind 1  verify of width M = D + 1: tok = pending[n_pend-1] | draft[0..D), pos = cache_len - 1 + i
 //   kind 2  AR (M = 1): tok = src_a[0], pos = cache_len
-// `src_a` = pending tokens, `src_b` = draft tokens (kind 1).  The record is what bm_set_step_state writes.
+//   kind 3  prompt slab of width M with n_pend real rows: tok = src_a[0..n_pend) | 0.., pos = cache_len + i | 0..
+// `src_a` = pending tokens (prompt rows for kind 3), `src_b` = draft tokens (kind 1).  The record is what bm_set_step_state writes.
 __global__ void stage_replay_inputs_kernel(int kind, const int64_t *__restrict__ src_a,
                                            const int64_t *__restrict__ src_b, int n_pend, int cache_len, int M, int D,
                                            int64_t mask_id, int role, int P, int state_n_pend,
@@ -399,9 +400,12 @@ __global__ void stage_replay_inputs_kernel(int kind, const int64_t *__restrict__
     } else if (kind == 1) {
         tok[i] = i == 0 ? src_a[n_pend - 1] : src_b[i - 1];
         pos[i] = cache_len - 1 + i;
-    } else {
+    } else if (kind == 2) {
         tok[i] = src_a[0];
         pos[i] = cache_len;
+    } else {
+        tok[i] = i < n_pend ? src_a[i] : 0;
+        pos[i] = i < n_pend ? cache_len + i : 0;
     }
 }
 

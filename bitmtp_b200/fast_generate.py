@@ -191,19 +191,23 @@ class _Session:
         the prompt's last row; the prompt's K/V is placed in the chosen segment."""
         atlas, bufs = self.atlas, self.bufs
         t0 = time.time()
-        cache = make_sdlm_cache(self.args, device=self.device)
-        logits = self.model.forward_sdlm_prefill(
-            token_values=self.prompt_ids, cache=cache, positions=bufs.pos_arange[: self.seq_len],
-            block_size=1, fast=False, causal_attn=True)
-        bufs.gen_buf[0:1].copy_(_argmax_rows(logits[-1:].contiguous()))
-        self.cache_len = self.seq_len
-        self.sigma = atlas.select_segment(self.cache_len + self.max_gen_len + atlas.M_max)
+        self.sigma = atlas.select_segment(self.seq_len + self.max_gen_len + atlas.M_max)
         shared = atlas.kv_buffers[self.sigma]
         shared.zero_()
-        for i, (ck, cv) in enumerate(cache):
-            shared[0, i, :, :, : self.cache_len, :].copy_(ck[0])
-            shared[1, i, :, :, : self.cache_len, :].copy_(cv[0])
-        del cache
+        if getattr(atlas, "prefill_graphs", None) and self.seq_len <= self.sigma:
+            # captured slab graphs write the prompt's rows straight into the segment
+            logits = atlas.prefill(self.prompt_ids, self.sigma)
+        else:
+            cache = make_sdlm_cache(self.args, device=self.device)
+            logits = self.model.forward_sdlm_prefill(
+                token_values=self.prompt_ids, cache=cache, positions=bufs.pos_arange[: self.seq_len],
+                block_size=1, fast=False, causal_attn=True)
+            for i, (ck, cv) in enumerate(cache):
+                shared[0, i, :, :, : self.seq_len, :].copy_(ck[0])
+                shared[1, i, :, :, : self.seq_len, :].copy_(cv[0])
+            del cache
+        bufs.gen_buf[0:1].copy_(_argmax_rows(logits[-1:].contiguous()))
+        self.cache_len = self.seq_len
         torch.cuda.synchronize()
         prefill_time = time.time() - t0
         return prefill_time, int(bufs.gen_buf[0].item()), t0

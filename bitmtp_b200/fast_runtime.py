@@ -25,7 +25,7 @@ import torch
 
 from . import native, ops
 from .contracts import validate_graph_roles
-from .model import ModelArgs, SDLMLayerCache, Transformer, make_sdlm_cache
+from .model import PREFILL_CHUNK, ModelArgs, SDLMLayerCache, Transformer, make_sdlm_cache
 
 DEFAULT_SEGMENT_LADDER = (256, 1024, 4096)
 DEFAULT_M_SET = (1, 8, 9, 10, 12, 16, 17)
@@ -138,17 +138,31 @@ class GraphAtlas:
                 for role in self.roles:
                     if role != "ar":
                         self.graphs[(M, sigma, role)] = self._capture_one(M, sigma, role)
+        # Prompt slabs: one AR-causal graph of PREFILL_CHUNK rows per segment, layers only (the one
+        # logit row a prompt needs is taken afterwards).  Kept apart from `graphs`, whose key set
+        # mirrors the reference's.  Needs workspace rows for a whole slab.
+        self.prefill_graphs: Dict[int, CapturedGraph] = {}
+        if self.M_max >= PREFILL_CHUNK:
+            self.prefill_tokens = torch.zeros(PREFILL_CHUNK, device=self.device, dtype=torch.int64)
+            self.prefill_positions = torch.zeros(PREFILL_CHUNK, device=self.device, dtype=torch.int64)
+            self.prefill_logits = torch.zeros((1, self.model.workspace(PREFILL_CHUNK).n_pad),
+                                              dtype=torch.float32, device=self.device)
+            for sigma in self.segment_ladder:
+                self.prefill_graphs[sigma] = self._capture_one(
+                    PREFILL_CHUNK, sigma, "ar", logit_rows=(0, 0),
+                    buffers=(self.prefill_tokens, self.prefill_positions))
 
-    def _capture_one(self, M: int, sigma: int, role: str) -> CapturedGraph:
+    def _capture_one(self, M: int, sigma: int, role: str, logit_rows: Optional[Tuple[int, int]] = None,
+                     buffers: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> CapturedGraph:
         D = self.D
         P = M - D
-        ls, le = role_logit_rows(role, M, D)
+        ls, le = logit_rows if logit_rows is not None else role_logit_rows(role, M, D)
         shared = self.kv_buffers[sigma]
         slot = shared[:, :, :, :, : sigma + M, :]
         kv_full = [(slot[0, i], slot[1, i]) for i in range(self.n_layers)]
         state = ops.new_step_state(self.device)
         ops.set_step_state(state, 0, 0, _ROLE_ID[role], P)
-        tokens_buf, positions_buf = self.tokens_m[M], self.positions_m[M]
+        tokens_buf, positions_buf = buffers if buffers is not None else (self.tokens_m[M], self.positions_m[M])
         ws = self.model.workspace(M)
         logits_buf = torch.zeros((le - ls, ws.n_pad), dtype=torch.float32, device=self.device)
         scratch = self.attn_scratch[sigma]
@@ -234,6 +248,27 @@ class GraphAtlas:
             return
         sigma = verify_graph.sigma
         ops.kv_copy_rows(self.kv_buffers[sigma], sigma + self.M_max, sigma + 1, cache_len, n_accept)
+
+    def prefill(self, prompt_ids: torch.Tensor, sigma: int) -> torch.Tensor:
+        """The prompt's K/V into history rows [0, len) of segment `sigma`, by replaying the captured
+        slab graph once per PREFILL_CHUNK rows (staging, replay, row promotion: three launches + one
+        graph per slab), then the last row's logits through the packed head.  Same arithmetic as
+        Transformer.forward_sdlm_prefill, which launches every operator of every slab from the host
+        and computes all rows' logits; the decode loops need only the last row (reference:
+        fast_generate.py:203-222 take `logits[-1]`).  Returns fp32 logits [1, vocab]."""
+        g = self.prefill_graphs[sigma]
+        seq = int(prompt_ids.shape[0])
+        if seq < 1 or seq > sigma:
+            raise ValueError(f"prompt of {seq} tokens does not fit segment {sigma}")
+        ids = prompt_ids.to(torch.int64).contiguous()
+        n = 0
+        for c0 in range(0, seq, PREFILL_CHUNK):
+            n = min(PREFILL_CHUNK, seq - c0)
+            ops.stage_replay_inputs(3, ids[c0:], None, n, c0, PREFILL_CHUNK, self.D, 0, native.ROLE_AR, g.P,
+                                    g.tokens_buf, g.positions_buf, g.attn_mask)
+            g.cuda_graph.replay()
+            ops.kv_copy_rows(self.kv_buffers[sigma], sigma + self.M_max, sigma, c0, n)
+        return self.model.head_from_workspace(PREFILL_CHUNK, n - 1, 1, self.prefill_logits)
 
     def migrate_segment(self, src_sigma: int, dst_sigma: int, cache_len: int) -> None:
         """Copy live rows [0, cache_len) into a larger segment (fast_runtime.py:510-521)."""

@@ -626,8 +626,18 @@ class Transformer(nn.Module):
         else:
             self._layers_by_operator(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
                                      pdl, attn_pdl)
-        # h + ffn_out, final norm of the logit rows, INT8 quantisation for the packed head
-        ops.rmsnorm_fused(W.h, self.norm.weight.data, eps, M=rows, res=W.ffn_out, row0=logits_start,
+        if rows == 0:
+            # layers only: the caller takes the logit rows it wants with head_from_workspace
+            return logits_buf[:, : self._lm_head_t2_vocab]
+        return self.head_from_workspace(M, logits_start, rows, logits_buf)
+
+    def head_from_workspace(self, M: int, row0: int, rows: int, logits_buf: torch.Tensor) -> torch.Tensor:
+        """Final norm and packed head over rows [row0, row0 + rows) of the width-M workspace as the
+        layer loop left it: h + ffn_out, RMSNorm, INT8 quantisation, T2 head
+        (reference: model.py:1402-1404, 1245-1296).  Returns fp32 logits [rows, vocab]."""
+        W = self.workspace(M)
+        pdl = self.use_pdl
+        ops.rmsnorm_fused(W.h, self.norm.weight.data, self.args.norm_eps, M=rows, res=W.ffn_out, row0=row0,
                           pdl=pdl, out={"qp": W.hq, "asum": W.h_sum, "s": W.hs})
         ops.t2_gemv_prepared(W.hq[:rows], W.h_sum[:rows], self._lm_head_t2_w, W.hs[:rows],
                              self._lm_head_t2_scale, out_kind=native.OUT_F32_OF_BF16, out=logits_buf,

@@ -211,8 +211,9 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
  *   kind 0 (draft, M = P + D): tok = pending[0..n_pend) | 0 .. | pending[n_pend-1] at row P | mask_id ..;
  *           pos = cache_len + i (pending rows), 0 (padding rows), cache_len + n_pend - 1 + k (block rows);
  *   kind 1 (verify, M = D + 1): tok = pending[n_pend-1] | draft[0..D); pos = cache_len - 1 + i;
- *   kind 2 (AR, M = 1): tok = src_a[0], pos = cache_len.
- * src_a = pending tokens (int64), src_b = draft tokens (kind 1); tok, pos int64 [M]; state as written by
+ *   kind 2 (AR, M = 1): tok = src_a[0], pos = cache_len;
+ *   kind 3 (prompt slab of width M, n_pend real rows): tok = src_a[0..n_pend) | 0 ..; pos = cache_len + i | 0 ...
+ * src_a = pending tokens (int64; the slab's prompt ids for kind 3), src_b = draft tokens (kind 1); tok, pos int64 [M]; state as written by
  * bm_set_step_state (n_pend clamped to [0, P] for a draft, 0 otherwise).  Replaces the per-step tensor
  * fills of src/bonsai_sft/gpu/fast_generate.py:1015-1055, 247-256 and fast_runtime.prepare_step. */
 int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n_pend, int cache_len, int M, int D,

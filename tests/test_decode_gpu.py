@@ -11,6 +11,7 @@ import torch
 from bitmtp_b200 import fast_generate as FG, generate, native, ops, synthetic
 from bitmtp_b200.benchmarks import acceptance_hooks
 from bitmtp_b200.fast_runtime import GraphAtlas
+from bitmtp_b200.model import make_sdlm_cache
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -205,3 +206,32 @@ def test_confidence_stream_with_categorical_acceptance_equals_cpu_loop(oracle):
     assert got.cpu().tolist() == want.tolist()
     for key in ("n_iters", "draft_iters", "accepted_drafts", "n_conf_path", "n_verify_path", "decode_tokens"):
         assert stats[key] == want_stats[key], key
+
+
+@pytest.mark.parametrize("geometry,seq", [("tiny", 37), ("tiny", 16), ("tiny", 5), ("layers3", 70)])
+def test_captured_prompt_slabs_equal_operator_prefill(geometry, seq):
+    """GraphAtlas.prefill (captured 16-row slab graphs writing into the segment, head for the last
+    row only) against Transformer.forward_sdlm_prefill (every operator launched from the host,
+    rows written in place): the prompt's K/V rows in every layer and the last row's logits, bit
+    for bit, for ragged, exact and shorter-than-a-slab prompts."""
+    geo = synthetic.TINY if geometry == "tiny" else dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096)
+    cfg = synthetic.make_config(geo, block_size=8)
+    sigma, m_set = 128, (1, 9, 16)
+    model, _ = _model(cfg, 5, sigma + max(m_set))
+    atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=(sigma,), m_set=m_set,
+                       roles=("ar", "draft", "verify"), capture_verbose=False)
+    assert sigma in atlas.prefill_graphs and atlas.prefill_graphs[sigma].n_kernels > 0
+    prompt = synthetic.random_prompt(seq, cfg["vocab_size"], seed=seq)[0].to(DEV)
+
+    cache = make_sdlm_cache(model.args, device=torch.device(DEV))
+    want_logits = model.forward_sdlm_prefill(token_values=prompt, cache=cache)[-1:].clone()
+    atlas.kv_buffers[sigma].zero_()
+    got_logits = atlas.prefill(prompt, sigma)
+    torch.cuda.synchronize()
+    assert native.lib().bm_device_error() == 0
+    assert torch.equal(got_logits.view(torch.int32), want_logits.view(torch.int32)), "last-row logits differ"
+    shared = atlas.kv_buffers[sigma]
+    for i, (ck, cv) in enumerate(cache):
+        assert torch.equal(shared[0, i, 0, :, :seq, :].view(torch.int16), ck[0].view(torch.int16)), f"K layer {i}"
+        assert torch.equal(shared[1, i, 0, :, :seq, :].view(torch.int16), cv[0].view(torch.int16)), f"V layer {i}"
+        assert not shared[:, i, 0, :, seq:sigma, :].any(), "rows past the prompt were written"

@@ -388,3 +388,9 @@ def test_stage_replay_inputs_matches_the_tensor_fills(M, D, n_pend, cache_len):
     ops.stage_replay_inputs(2, draft[2:3], None, 0, cache_len, 1, 0, 0, native.ROLE_AR, 1 - D, tok4, pos4, st)
     assert int(tok4) == int(draft[2]) and int(pos4) == cache_len
     assert st.cpu().tolist() == [cache_len, 0, native.ROLE_AR, 1 - D]
+    # prompt slab (width M, n_pend real rows taken from an offset of the prompt)
+    tok5, pos5 = torch.full((M,), -1, dtype=torch.int64, device=DEV), torch.full((M,), -1, dtype=torch.int64, device=DEV)
+    ops.stage_replay_inputs(3, pending[1:], None, n_pend, cache_len, M, D, 0, native.ROLE_AR, P, tok5, pos5, st)
+    assert tok5.tolist() == pending[1:1 + n_pend].tolist() + [0] * (M - n_pend)
+    assert pos5.tolist() == [cache_len + i for i in range(n_pend)] + [0] * (M - n_pend)
+    assert st.cpu().tolist() == [cache_len, 0, native.ROLE_AR, P]
