@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--workload", default=None, choices=["decode", "gemv", "gemv-one", "gemv-nsplit"])
     ap.add_argument("--shape", default="151936x2048", help="gemv-one: NxK")
     ap.add_argument("--w", type=int, default=1, help="gemv-one: width")
-    ap.add_argument("--path", default="auto", choices=["auto", "dp4a", "mma", "rowwarp"])
+    ap.add_argument("--path", default="auto", choices=["auto", "dp4a", "mma", "rowwarp", "direct"])
     ap.add_argument("--calls", type=int, default=0, help="gemv-one: launches per step")
     ap.add_argument("--pdl", action="store_true",
                     help="gemv workloads: programmatic dependent launch between the calls, as in the decode replay")
@@ -232,6 +232,70 @@ def time_replays(graph, steps, warmup, dist, device, sampler):
     return ms, clocks
 
 
+def time_cases(gs, launch, device, reps=10):
+    """Per (shape, width) GB/s: for each case a graph of its calls over all weight copies (distinct
+    buffers, together larger than L2), CUDA events around `reps` replays.  `launch(call)` issues
+    one call on the current stream."""
+    import torch
+    from bitmtp_b200 import ops
+    by_case = {}
+    for call in gs.calls:
+        by_case.setdefault((call[6], call[7], call[5]), []).append(call)
+    out = {}
+    for (n, k, w), calls in by_case.items():
+        graph = capture(lambda: [launch(c) for c in calls], device)
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) * 1e-3 / (reps * len(calls))
+        out[f"{n}x{k}:W{w}"] = {"us": round(sec * 1e6, 2), "gbs": round(ops.gemv_bytes(w, n, k) / sec / 1e9, 1)}
+    return out
+
+
+REFERENCE_WIDTHS = (1, 4, 5, 6, 7, 8, 9, 10, 12, 16, 17)      # widths the reference kernel registers
+REFERENCE_SHAPES = {(1024, 2048), (2048, 2048), (4096, 2048), (6144, 2048), (12288, 2048), (2048, 6144),
+                    (151936, 2048)}                           # (N, K) of its 1.7B table
+
+
+def reference_cuda_sweep(shapes_w, device_index=0):
+    """The reference's own CUDA GEMV (built from its source into oracle/_ref by oracle/build.py) timed
+    on the GPU over the cases of the sweep it registers; None when the library or a GPU is absent.
+    Reference arm only: none of this package's kernels run here."""
+    import ctypes
+    import torch
+    from oracle.build import reference_kernel_path
+    path = reference_kernel_path()
+    if not path or not torch.cuda.is_available():
+        return None
+    lib = ctypes.CDLL(path)
+    vp = ctypes.c_void_p
+    lib.t2g128_int8xint2_linear.argtypes = [vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp]
+    lib.t2g128_int8xint2_linear.restype = None
+    device = torch.device("cuda", device_index)
+    torch.cuda.set_device(device)
+    cases = [c for c in shapes_w if c[3] in REFERENCE_WIDTHS and (c[1], c[2]) in REFERENCE_SHAPES]
+    if not cases:
+        return None
+    gs = GemvSet(device, cases, min_bytes=768 << 20)
+
+    def launch(call):
+        A, B, sc, ws, C, w, n, k = call
+        lib.t2g128_int8xint2_linear(A.data_ptr(), B.data_ptr(), C.data_ptr(), sc.data_ptr(), ws.data_ptr(), w, n, k,
+                                    torch.cuda.current_stream(device).cuda_stream)
+
+    per_case = time_cases(gs, launch, device)
+    tot_b = sum(v["gbs"] * v["us"] for v in per_case.values())
+    tot_t = sum(v["us"] for v in per_case.values())
+    return {"gbs": round(tot_b / tot_t, 1), "per_case": per_case,
+            "what": "the reference's t2g128_kernels.cu compiled for sm_100a with its own flags, same buffers "
+                    "and timing protocol as the GPU arm; widths it does not register are left out"}
+
+
 def cpu_gemv_baseline(shapes_w, budget_s=12.0):
     """The CPU oracle timed on this box's host cores over the same sweep (bounded)."""
     import numpy as np
@@ -263,7 +327,7 @@ def run_gemv(args, world, rank, local, dist):
     from bitmtp_b200 import native, ops
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    path = {"auto": 0, "dp4a": 1, "mma": 2, "rowwarp": 3}[args.path] | (args.tune << 8)
+    path = {"auto": 0, "dp4a": 1, "mma": 2, "rowwarp": 3, "direct": 4}[args.path] | (args.tune << 8)
     if args.workload == "gemv-one":
         n, k = (int(x) for x in args.shape.lower().split("x"))
         shapes_w = [("one", n, k, args.w)]
@@ -330,6 +394,9 @@ def run_gemv(args, world, rank, local, dist):
                      "kernel": "t2_gemv (all launches of the pass)",
                      "frac_of_8TBps": round(gbs_rank / 8000.0, 4)},
     }
+    if rank == 0 and world == 1 and args.workload == "gemv":
+        out["per_case"] = time_cases(
+            gs, lambda c: ops.t2_gemv(c[0], c[1], c[2], c[3], path=path, out=c[4], ldc=c[6], pdl=args.pdl), device)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         v, cores, done = cpu_gemv_baseline(shapes_w)
         out["cpu_baseline"] = {"value": round(v, 3), "unit": "GB/s", "cores": cores, "kind": "port",
@@ -373,7 +440,9 @@ def run_reference_gemv(args, rank):
     dt = time.time() - t0
     v = nbytes * steps / dt / 1e9
     cores = O.lib().bmo_num_threads()
-    return {"impl": "reference", "metric": "T2-g128 GEMV algorithmic HBM GB/s", "value": round(v, 3),
+    ref_cuda = reference_cuda_sweep(shapes_w)
+    return {"impl": "reference", "reference_cuda_kernel": ref_cuda,
+            "metric": "T2-g128 GEMV algorithmic HBM GB/s", "value": round(v, 3),
             "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
             "ms_per_step": round(dt / steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "s8 x ternary -> s32", "data": "synthetic",

@@ -404,7 +404,19 @@ def run_reference_decode(args) -> dict:
     t0 = time.time()
     base = cpu_decode_baseline(args.model, M)
     dt = time.time() - t0
-    return {"impl": "reference", "metric": "decode tok/s (Bonsai-1.7B-arch D8, bs1)" if args.model == "1p7b"
+    ref_cuda = None
+    if args.model == "1p7b":
+        # the reference's own CUDA GEMV on the GEMV calls of one width-M replay (28 layers + head)
+        import bench
+        rows = {1: 1, 9: 9, 16: 8}[M]
+        per_layer = [("qkv", 4096, 2048, M), ("o", 2048, 2048, M), ("gate|up", 12288, 2048, M),
+                     ("down", 2048, 6144, M)]
+        ref_cuda = bench.reference_cuda_sweep(per_layer + [("head", 151936, 2048, rows)])
+        if ref_cuda is not None:
+            pc = ref_cuda["per_case"]
+            layer_us = sum(pc[f"{n}x{k}:W{w}"]["us"] for (_, n, k, w) in per_layer)
+            ref_cuda["gemv_us_per_replay"] = round(28 * layer_us + pc[f"151936x2048:W{rows}"]["us"], 1)
+    return {"impl": "reference", "reference_cuda_kernel": ref_cuda, "metric": "decode tok/s (Bonsai-1.7B-arch D8, bs1)" if args.model == "1p7b"
             else f"decode tok/s (Bonsai-{args.model}-arch D8, bs1 per GPU)",
             "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
             "ms_per_step": round(dt * 1e3, 1), "higher_is_better": True, "scaling": "weak",

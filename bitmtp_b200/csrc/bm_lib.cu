@@ -15,6 +15,7 @@
 #include "fused_ops.cuh"
 #include "verify_attn.cuh"
 #include "t2_gemv_rowwarp.cuh"
+#include "t2_gemv_direct.cuh"
 #include "decode_sweep.cuh"
 
 #include <cudaTypedefs.h>
@@ -144,6 +145,19 @@ int gemv_launch_dp4a(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t st
     BM_DP4A_CASE(4, 1) BM_DP4A_CASE(4, 2) BM_DP4A_CASE(4, 4)
 #undef BM_DP4A_CASE
     return BM_EINVAL;
+}
+
+constexpr size_t kDirectMaxBytes = 8u << 20;   // packed weights up to which AUTO prefers the direct kernel
+
+// Row-per-warp kernel without shared-memory staging, for W <= 4 (t2_gemv_direct.cuh).
+int gemv_launch_direct(const bm::GemvParams &p0, int pdl, cudaStream_t stream) {
+    if (!bm::direct_fits(p0.W, p0.N, p0.K) || p0.world > 1 || p0.silu_F != 0 || p0.src_mode != 0) return BM_EINVAL;
+    bm::GemvParams p = p0;
+    p.pdl = pdl;
+    const dim3 grid((unsigned)((p.N + bm::kDirectWarps - 1) / bm::kDirectWarps)), block(bm::kDirectWarps * 32);
+    if (p.W == 1) return launch_ex(bm::t2_gemv_direct_kernel<1>, grid, block, 0, stream, pdl, p);
+    if (p.W == 2) return launch_ex(bm::t2_gemv_direct_kernel<2>, grid, block, 0, stream, pdl, p);
+    return launch_ex(bm::t2_gemv_direct_kernel<4>, grid, block, 0, stream, pdl, p);
 }
 
 struct MmaPlan {
@@ -449,9 +463,16 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
         // Many rows and at most 8 tokens: every warp streams its own rows.  With fewer than about
         // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner
         // (measured on 14336 x 8192, 12288 x 2048 and smaller).
+        // One token over a few MB of weights (two over at most 2 MB): the launch is latency-bound and
+        // the kernel with a single memory round trip wins (2.6-5.6 us against 4.4-7.2 us of the staged
+        // kernels, measured); from four tokens on its dp4a work costs more than it saves.
         if (rowwarp_fits(W, N, K) && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
+        else if (p.world <= 1 && bm::direct_fits(W, N, K) &&
+                 (size_t)N * K / 4 <= (W == 1 ? kDirectMaxBytes : (W == 2 ? kDirectMaxBytes / 4 : 0)))
+            path = BM_PATH_DIRECT;
         else path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     }
+    if (path == BM_PATH_DIRECT) return gemv_launch_direct(p, pdl, st);
     if (path == BM_PATH_ROWWARP) return gemv_launch_rowwarp(p, sms, pdl, force_rb, st);
     if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
     if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, force_rb, st) : BM_EINVAL;

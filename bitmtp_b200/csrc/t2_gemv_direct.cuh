@@ -1,0 +1,159 @@
+// T2-g128 GEMV for few tokens and few rows: a warp per output row, operands straight from
+// global memory into registers.
+//
+// Replaces, for W <= 4 and layers of a few MB, t2g128_mfused of the reference
+// (src/bonsai_sft/gpu/t2g128_kernels/t2g128_kernels.cu:29-92).  A launch over 0.5-6 MB of
+// weights is bound by latency, not by bandwidth: what counts is the number of dependent memory
+// round trips between the start of the grid and its last store.  The cooperative-tile and
+// row-per-warp kernels stage operands in shared memory (barrier initialisation, bulk copies,
+// an activation staging pass, a cross-warp reduction) and need four to five microseconds for
+// any size; this kernel has one round trip: every lane requests its 16 bytes of packed weights,
+// its scale and its 64 activations per token at once, then computes from registers.
+//
+// Work split: row n = one warp.  A pass covers 2048 elements of K: lane l owns elements
+// [2048*pass + 64*l, +64), i.e. half of group 16*pass + l/2; the two lanes of a pair add their
+// integer partial sums, so both hold the exact group sum G.  fp32 order as in every other GEMV of
+// this library (and bmo_t2_gemv of the CPU oracle): group g feeds slot g % 16 with
+// fma((float)G, scale, slot) in ascending g (= ascending pass; slot = l/2), the 16 slots are
+// summed by the xor butterfly with slot offsets 1, 2, 4, 8 (lane offsets 2..16), the sum is
+// multiplied by 1/s[m].
+//
+// Activations: GEMV-ready (16-runs already in the order of the code registers `(word >> 2t) &
+// 0x03030303`, group sums in p.asum), or natural order.  For one natural-order token the kernel
+// transposes the token's 16-runs in registers and sums them with dp4a; for several it transposes
+// the code registers instead and makes them signed, once for all tokens.
+#pragma once
+
+#include "t2_gemv.cuh"
+#include "t2_gemv_rowwarp.cuh"
+
+namespace bm {
+
+constexpr int kDirectWarps = 8;          // rows per CTA
+constexpr int kDirectMaxPasses = 5;      // K <= 10240
+constexpr int kDirectMaxW = 4;
+
+__host__ __device__ inline bool direct_fits(int W, int N, int K) {
+    return W >= 1 && W <= kDirectMaxW && K >= 128 && (K % 128) == 0 && K <= 2048 * kDirectMaxPasses && N >= 1;
+}
+
+__device__ __forceinline__ int dp4a_s8_u8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int WT>
+__global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const GemvParams p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * kDirectWarps + warp;
+    pdl_launch_dependents();
+    if (n >= p.N) return;
+    const int ng = p.K >> 7;
+    const int passes = (p.K + 2047) >> 11;
+    const bool prepared = p.asum != nullptr;
+
+    // Weights and scales do not depend on the previous kernel: request them first.
+    uint4 wv[kDirectMaxPasses];
+    float sc[kDirectMaxPasses];
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(p.B + (size_t)n * (p.K >> 2));
+#pragma unroll
+    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+        const int g = 16 * ps + (lane >> 1);
+        const bool active = ps < passes && g < ng;
+        wv[ps] = active ? __ldg(wrow + 32 * ps + lane) : make_uint4(0u, 0u, 0u, 0u);
+        sc[ps] = active ? bm_bf16_to_f32(__ldg(p.ws + (size_t)n * ng + g)) : 0.0f;
+    }
+    if (p.pdl) pdl_wait();
+    // 1/s of the token this lane will store, requested with the activations
+    const float inv_s = (lane < WT && lane < p.W) ? 1.0f / p.s[lane] : 0.0f;
+
+    float acc[WT];
+#pragma unroll
+    for (int m = 0; m < WT; ++m) acc[m] = 0.0f;
+
+#pragma unroll
+    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+        if (ps >= passes) break;                                   // uniform
+        const int g = 16 * ps + (lane >> 1);
+        const bool active = g < ng;
+        const int k0 = 2048 * ps + 64 * lane;
+        uint4 av[WT][4];
+#pragma unroll
+        for (int m = 0; m < WT; ++m)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                av[m][q] = (active && m < p.W)
+                               ? *reinterpret_cast<const uint4 *>(p.A + (size_t)m * p.K + k0 + 16 * q)
+                               : make_uint4(0u, 0u, 0u, 0u);
+        int asum_g[WT];
+#pragma unroll
+        for (int m = 0; m < WT; ++m) asum_g[m] = (prepared && active && m < p.W) ? p.asum[m * ng + g] : 0;
+
+        const uint32_t wq[4] = {wv[ps].x, wv[ps].y, wv[ps].z, wv[ps].w};
+        int part[WT];
+#pragma unroll
+        for (int m = 0; m < WT; ++m) part[m] = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            // codes of packed bytes 0..3 of this word: register t holds element t of each byte
+            const uint32_t c0 = wq[q] & 0x03030303u, c1 = (wq[q] >> 2) & 0x03030303u,
+                           c2 = (wq[q] >> 4) & 0x03030303u, c3 = (wq[q] >> 6) & 0x03030303u;
+            if (prepared || WT == 1) {
+#pragma unroll
+                for (int m = 0; m < WT; ++m) {
+                    uint4 a = av[m][q];
+                    if (!prepared) {
+                        // one token: cheaper to bring its 16-run into the order of the code registers
+                        int sum = __dp4a((int)a.x, 0x01010101, 0);
+                        sum = __dp4a((int)a.y, 0x01010101, sum);
+                        sum = __dp4a((int)a.z, 0x01010101, sum);
+                        sum = __dp4a((int)a.w, 0x01010101, sum);
+                        part[m] -= 2 * sum;                        // codes are value + 2
+                        a = transpose_run16(a);
+                    }
+                    part[m] = dp4a_s8_u8(a.x, c0, part[m]);
+                    part[m] = dp4a_s8_u8(a.y, c1, part[m]);
+                    part[m] = dp4a_s8_u8(a.z, c2, part[m]);
+                    part[m] = dp4a_s8_u8(a.w, c3, part[m]);
+                }
+            } else {
+                // several tokens in natural order: bring the codes into natural order once instead and
+                // make them signed (code - 2 per byte, no borrow across bytes), shared by all tokens
+                const uint4 nat = transpose_run16(make_uint4(c0, c1, c2, c3));
+                const uint32_t s0 = ((nat.x | 0x80808080u) - 0x02020202u) ^ 0x80808080u;
+                const uint32_t s1 = ((nat.y | 0x80808080u) - 0x02020202u) ^ 0x80808080u;
+                const uint32_t s2 = ((nat.z | 0x80808080u) - 0x02020202u) ^ 0x80808080u;
+                const uint32_t s3 = ((nat.w | 0x80808080u) - 0x02020202u) ^ 0x80808080u;
+#pragma unroll
+                for (int m = 0; m < WT; ++m) {
+                    const uint4 a = av[m][q];
+                    part[m] = __dp4a((int)a.x, (int)s0, part[m]);
+                    part[m] = __dp4a((int)a.y, (int)s1, part[m]);
+                    part[m] = __dp4a((int)a.z, (int)s2, part[m]);
+                    part[m] = __dp4a((int)a.w, (int)s3, part[m]);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < WT; ++m) {
+            const int both = part[m] + __shfl_xor_sync(0xffffffffu, part[m], 1);
+            const int G = both - 2 * asum_g[m];
+            acc[m] = fmaf((float)G, sc[ps], acc[m]);
+            if (p.G != nullptr && active && (lane & 1) == 0 && m < p.W)
+                p.G[((size_t)m * p.N + n) * ng + g] = G;
+        }
+    }
+    // Slot tree: lane bits 1..4 are slot bits 0..3.
+#pragma unroll
+    for (int m = 0; m < WT; ++m) {
+        float v = acc[m];
+        v = v + __shfl_xor_sync(0xffffffffu, v, 2);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 4);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 8);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 16);
+        if (lane == m && m < p.W) gemv_store(p, m, n, v * inv_s);
+    }
+}
+
+}  // namespace bm

@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 SO_PATH = os.path.join(HERE, "libbitmtp_b200.so")
 SOURCES = ["bm_lib.cu"]
 HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh",
-           "decode_sweep.cuh"]
+           "t2_gemv_direct.cuh", "decode_sweep.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -32,7 +32,7 @@ BM_EINVAL = 22
 BM_ETOOBIG = 27
 STATIC_ATTN_SCRATCH_BYTES = 8 << 20     # BM_STATIC_ATTN_SCRATCH_BYTES of the header
 OUT_BF16, OUT_F32, OUT_F32_OF_BF16 = 0, 1, 2
-PATH_AUTO, PATH_DP4A, PATH_MMA, PATH_ROWWARP = 0, 1, 2, 3
+PATH_AUTO, PATH_DP4A, PATH_MMA, PATH_ROWWARP, PATH_DIRECT = 0, 1, 2, 3, 4
 ROLE_DRAFT, ROLE_VERIFY, ROLE_AR = 0, 1, 2
 PDL_OVERLAP, PDL_STABLE_STATE = 1, 2
 

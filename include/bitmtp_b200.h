@@ -43,6 +43,7 @@ extern "C" {
 #define BM_PATH_DP4A 1
 #define BM_PATH_MMA 2
 #define BM_PATH_ROWWARP 3      /* W <= 8, K % 512 == 0, N % 16 == 0: a warp per 16-row block */
+#define BM_PATH_DIRECT 4       /* W <= 4, K <= 10240: a warp per row, operands straight into registers */
 
 /* Library / build identification: returns a static string. */
 const char *bm_version(void);

@@ -45,5 +45,42 @@ def build_oracle(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+# ----------------------------------------------------------------------------- the reference's own kernel
+REF_DIR = os.path.join(HERE, "_ref")
+REF_OUT = os.path.join(REF_DIR, "libbonsai_t2.so")
+REF_SRC_REL = os.path.join("src", "bonsai_sft", "gpu", "t2g128_kernels", "t2g128_kernels.cu")
+
+
+def build_reference_kernel(reference_root: str, force: bool = False, verbose: bool = False) -> str:
+    """Compile the reference's CUDA GEMV (one source file, read where it lies in the reference
+    checkout, never copied) into oracle/_ref/libbonsai_t2.so with the flags of its own
+    compile.sh (-O3 -std=c++17 --use_fast_math -Xcompiler -fPIC -shared), targeting sm_100a,
+    which that script does not list.  The GPU tests compare this library's GEMV outputs with it
+    and the benchmark's reference arm times it; nothing else loads it.  Returns the path, or ""
+    when the reference checkout or nvcc is absent (the prebuilt file, if any, stays in use)."""
+    src = os.path.join(reference_root, REF_SRC_REL)
+    nvcc = "/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else "nvcc"
+    if not os.path.exists(src):
+        return REF_OUT if os.path.exists(REF_OUT) else ""
+    if not force and os.path.exists(REF_OUT) and os.path.getmtime(REF_OUT) >= os.path.getmtime(src):
+        return REF_OUT
+    os.makedirs(REF_DIR, exist_ok=True)
+    cmd = [nvcc, "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC", "-shared",
+           "-gencode", "arch=compute_100a,code=sm_100a", src, "-o", REF_OUT + ".tmp"]
+    if verbose:
+        print(" ".join(cmd), file=sys.stderr)
+    subprocess.run(cmd, check=True)
+    os.replace(REF_OUT + ".tmp", REF_OUT)
+    return REF_OUT
+
+
+def reference_kernel_path() -> str:
+    """Path of the built reference kernel library, "" if it has not been built."""
+    return REF_OUT if os.path.exists(REF_OUT) else ""
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv, verbose=True))
+    root = os.environ.get("BITMTP_REFERENCE", "")
+    if root:
+        print(build_reference_kernel(root, force="--force" in sys.argv, verbose=True) or "reference checkout not found")

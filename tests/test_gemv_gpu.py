@@ -176,6 +176,47 @@ def test_row_per_warp_consumer(oracle, W, N, K):
     _check(oracle, synthetic.gemv_case(W, N, K, seed=W * 77 + N + K), native.PATH_ROWWARP)
 
 
+DIRECT = [(1, 8, 128), (2, 16, 384), (3, 24, 2048), (4, 64, 2560), (1, 1024, 2048), (1, 2048, 2048),
+          (2, 4096, 2048), (4, 6144, 2048), (1, 2048, 6144), (3, 2560, 9728), (1, 12288, 2048), (4, 2048, 10240),
+          (1, 6144, 2560), (2, 104, 8192)]
+
+
+@pytest.mark.parametrize("W,N,K", DIRECT)
+def test_direct_consumer(oracle, W, N, K):
+    """The W <= 4 kernel that works from registers (a warp per row, one memory round trip), forced at
+    every size incl. a single CTA, ragged last CTAs and K that is not a multiple of 2048: group sums,
+    fp32 and bf16 outputs bit for bit."""
+    _check(oracle, synthetic.gemv_case(W, N, K, seed=W * 131 + N + K), native.PATH_DIRECT)
+
+
+@pytest.mark.parametrize("W,N,K", [(1, 2048, 2048), (4, 1024, 2560), (2, 2048, 6144)])
+def test_direct_consumer_on_prepared_activations(oracle, W, N, K):
+    """GEMV-ready activations (4x4-transposed 16-runs + group sums) through the automatic choice,
+    which is the direct kernel at these sizes."""
+    dev = torch.device("cuda:0")
+    case = synthetic.gemv_case(W, N, K, seed=W + N + K)
+    y32, _, _ = oracle.t2_gemv(case["A"].numpy(), case["B"].numpy().view(np.uint8),
+                               oracle.torch_to_u16(case["ws"]), case["s"].numpy())
+    A = case["A"].to(dev)
+    prep = A.view(W, -1, 4, 4).transpose(2, 3).contiguous().view(W, -1)
+    asum = A.view(W, -1, 128).to(torch.int32).sum(-1).to(torch.int32).contiguous()
+    out = torch.empty(W, N, dtype=torch.float32, device=dev)
+    ops.t2_gemv_prepared(prep, asum, case["B"].to(dev), case["s"].to(dev), case["ws"].to(dev), out=out,
+                         out_kind=native.OUT_F32)
+    torch.cuda.synchronize()
+    assert native.lib().bm_device_error() == 0
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), y32.view(np.uint32))
+
+
+def test_direct_rejects_what_it_cannot_serve():
+    dev = torch.device("cuda:0")
+    for (W, N, K) in [(5, 64, 512), (1, 64, 12288)]:
+        case = synthetic.gemv_case(W, N, K, seed=1)
+        A, B, ws, s = (case[k].to(dev) for k in ("A", "B", "ws", "s"))
+        with pytest.raises(native.NativeError):
+            ops.t2_gemv(A, B, s, ws, path=native.PATH_DIRECT)
+
+
 def test_row_per_warp_rejects_what_it_cannot_serve():
     dev = torch.device("cuda:0")
     for (W, N, K) in [(9, 64, 512), (2, 24, 512), (2, 64, 256)]:
