@@ -588,6 +588,8 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
                          void *C, int ldc, int out_kind, int silu, void *amax_out, int pdl, void *stream) {
     if ((src_mode != 1 && src_mode != 2) || !x || !B || !ws || !C || N < 8 || (N % 8) != 0 || (K % 256) != 0 || K < 256)
         return BM_EINVAL;
+    const bool staged = (pdl & BM_PDL_STAGED) != 0;     // testing aid: keep to the shared-memory-staged kernel
+    pdl &= BM_PDL_OVERLAP;
     if (src_mode == 1 && !amax_in) return BM_EINVAL;
     if (src_mode == 2 && (!norm_w || K != 8 * bm::kGemvThreads)) return BM_EINVAL;
     if (silu && (!amax_out || out_kind != BM_OUT_BF16 || (N % 16) != 0)) return BM_EINVAL;
@@ -625,12 +627,18 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
     p.done = nullptr;
     for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
     const int sms = current_device().sm_count;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // A few MB of weights: the register-only kernel (one memory round trip after the row is staged).
+    if (!staged && bm::direct_row_fits(N, K) && (size_t)(silu ? 2 : 1) * N * K / 4 <= kDirectMaxBytes) {
+        const dim3 grid((unsigned)(N / bm::kDirectWarps)), block(bm::kGemvThreads);
+        return silu ? launch_ex(bm::t2_gemv_direct_row_kernel<true>, grid, block, 0, st, pdl, p)
+                    : launch_ex(bm::t2_gemv_direct_row_kernel<false>, grid, block, 0, st, pdl, p);
+    }
     const bool one = K == 2048;
     MmaPlan pl;
     if (!make_mma_plan(silu ? 2 * N : N, K, true, sms, 0, &pl)) return BM_EINVAL;
     if (silu && (N % (4 * pl.rb)) != 0 && !make_mma_plan(2 * N, K, true, sms, 1, &pl)) return BM_EINVAL;
     p.stages = pl.stages;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     return one ? launch_mma_rb<true, true>(pl, st, pdl, p) : launch_mma_rb<true, false>(pl, st, pdl, p);
 }
 

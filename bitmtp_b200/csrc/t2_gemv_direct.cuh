@@ -156,4 +156,106 @@ __global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const
     }
 }
 
+// ---- width 1 with the activation row made in the kernel (src_mode 1 / 2) ------------------------
+// The register-only GEMV for the projections of a width-1 replay: every CTA first turns the bf16 input
+// row into GEMV-ready INT8 codes in shared memory (gemv_stage_row_from_bf16: known absmax, or residual
+// add + RMSNorm, exactly as the cooperative kernel's prologue does), then each of its 8 warps computes
+// one output column from registers.  SILU: a warp computes column n of the gate rows and of the up
+// rows (B holds silu_F gate rows, then silu_F up rows) and stores bf16(silu(bf16 gate) * bf16 up); the
+// row's max |output| goes to p.amax_out by atomic max.  Weight rows are requested before the wait on
+// the previous kernel.  Same results as t2_gemv_mma_kernel with src_mode != 0, bit for bit.
+constexpr int kDirectRowAsumOff = 2048 * kDirectMaxPasses;                 // int32 [K/128]
+constexpr int kDirectRowInvsOff = kDirectRowAsumOff + 4 * 16 * kDirectMaxPasses;   // float [16]
+constexpr int kDirectRowShOff = kDirectRowInvsOff + 64;                    // float [32]
+constexpr int kDirectRowSmem = kDirectRowShOff + 128;
+
+__host__ __device__ inline bool direct_row_fits(int N, int K) {
+    return K >= 256 && (K % 256) == 0 && K <= 2048 * kDirectMaxPasses && N >= 8 && (N % 8) == 0;
+}
+
+template <bool SILU>
+__global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const GemvParams p) {
+    __shared__ __align__(16) unsigned char smem[kDirectRowSmem];
+    __shared__ unsigned int amax_sh;
+    constexpr int NR = SILU ? 2 : 1;                    // weight rows per output column
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * kDirectWarps + warp;     // output column; N % 8 == 0, so every warp has one
+    const int ng = p.K >> 7;
+    const int passes = (p.K + 2047) >> 11;
+    pdl_launch_dependents();
+    if (SILU && threadIdx.x == 0) amax_sh = 0u;
+
+    uint4 wv[NR][kDirectMaxPasses];
+    float sc[NR][kDirectMaxPasses];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const size_t row = (size_t)n + (size_t)r * p.silu_F;
+        const uint4 *wrow = reinterpret_cast<const uint4 *>(p.B + row * (p.K >> 2));
+#pragma unroll
+        for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+            const int g = 16 * ps + (lane >> 1);
+            const bool active = ps < passes && g < ng;
+            wv[r][ps] = active ? __ldg(wrow + 32 * ps + lane) : make_uint4(0u, 0u, 0u, 0u);
+            sc[r][ps] = active ? bm_bf16_to_f32(__ldg(p.ws + row * ng + g)) : 0.0f;
+        }
+    }
+    if (p.pdl) pdl_wait();
+    gemv_stage_row_from_bf16(p, smem, 0, kDirectRowAsumOff, kDirectRowInvsOff,
+                             reinterpret_cast<float *>(smem + kDirectRowShOff));
+    __syncthreads();
+    const int *asum = reinterpret_cast<const int *>(smem + kDirectRowAsumOff);
+    const float inv_s = reinterpret_cast<const float *>(smem + kDirectRowInvsOff)[0];
+
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+#pragma unroll
+    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+        if (ps >= passes) break;                                   // uniform
+        const int g = 16 * ps + (lane >> 1);
+        const bool active = g < ng;
+        uint4 a[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            a[q] = active ? *reinterpret_cast<const uint4 *>(smem + 2048 * ps + 64 * lane + 16 * q)
+                          : make_uint4(0u, 0u, 0u, 0u);
+        const int asum_g = active ? asum[g] : 0;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint32_t wq[4] = {wv[r][ps].x, wv[r][ps].y, wv[r][ps].z, wv[r][ps].w};
+            int part = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                part = dp4a_s8_u8(a[q].x, wq[q] & 0x03030303u, part);
+                part = dp4a_s8_u8(a[q].y, (wq[q] >> 2) & 0x03030303u, part);
+                part = dp4a_s8_u8(a[q].z, (wq[q] >> 4) & 0x03030303u, part);
+                part = dp4a_s8_u8(a[q].w, (wq[q] >> 6) & 0x03030303u, part);
+            }
+            const int G = part + __shfl_xor_sync(0xffffffffu, part, 1) - 2 * asum_g;
+            acc[r] = fmaf((float)G, sc[r][ps], acc[r]);
+        }
+    }
+    float y[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        float v = acc[r];
+        v = v + __shfl_xor_sync(0xffffffffu, v, 2);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 4);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 8);
+        v = v + __shfl_xor_sync(0xffffffffu, v, 16);
+        y[r] = v * inv_s;
+    }
+    if (SILU) {
+        if (lane == 0) {
+            const float v = bm_bf16_rn(bm_silu_bf16(bm_bf16_rn(y[0])) * bm_bf16_rn(y[NR - 1]));
+            reinterpret_cast<uint16_t *>(p.C)[n] = bm_f32_to_bf16(v);
+            atomicMax(&amax_sh, __float_as_uint(fabsf(v)));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && amax_sh != 0u) atomicMax(&p.amax_out[0], amax_sh);
+    } else if (lane == 0) {
+        gemv_store(p, 0, n, y[0]);
+    }
+}
+
 }  // namespace bm

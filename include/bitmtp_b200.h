@@ -38,6 +38,7 @@ extern "C" {
  * replay whose record is set before the graph launch), so they are read without waiting. */
 #define BM_PDL_OVERLAP 1
 #define BM_PDL_STABLE_STATE 2
+#define BM_PDL_STAGED 4        /* bm_t2_gemv_row_fused only: use the shared-memory-staged kernel at every size */
 
 #define BM_PATH_AUTO 0
 #define BM_PATH_DP4A 1

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from bitmtp_b200 import native, ops
+from bitmtp_b200 import native, ops, synthetic
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -394,3 +394,42 @@ def test_stage_replay_inputs_matches_the_tensor_fills(M, D, n_pend, cache_len):
     assert tok5.tolist() == pending[1:1 + n_pend].tolist() + [0] * (M - n_pend)
     assert pos5.tolist() == [cache_len + i for i in range(n_pend)] + [0] * (M - n_pend)
     assert st.cpu().tolist() == [cache_len, 0, native.ROLE_AR, P]
+
+
+ROW_FUSED = [(1, 2048, 2048, False), (1, 2048, 6144, False), (1, 2560, 9728, False), (1, 1024, 2560, False),
+             (2, 4096, 2048, False), (2, 2048, 2048, False), (2, 6144, 2048, True), (2, 512, 2048, True)]
+
+
+@pytest.mark.parametrize("src_mode,N,K,silu", ROW_FUSED)
+def test_width1_row_fused_register_kernel_equals_staged_kernel(src_mode, N, K, silu):
+    """bm_t2_gemv_row_fused picks the register-only kernel for layers of a few MB; BM_PDL_STAGED keeps it
+    on the shared-memory-staged kernel.  Outputs, the stored residual row, the absmax words and the
+    cleared word must be identical."""
+    gen = torch.Generator().manual_seed(N + K + src_mode)
+    rows = 2 * N if silu else N
+    w, ws, _ = synthetic.ternary_weight(rows, K, gen)
+    w, ws = w.to(DEV), ws.to(DEV)
+    x = (torch.randn(1, K, generator=gen) * 1.3).to(torch.bfloat16).to(DEV)
+    res = torch.randn(1, K, generator=gen).to(torch.bfloat16).to(DEV)
+    norm_w = (1.0 + 0.1 * torch.randn(K, generator=gen)).to(torch.bfloat16).to(DEV)
+    amax_in = x.float().abs().max().reshape(1).view(torch.int32).to(DEV)
+
+    def run(pdl):
+        out = torch.zeros(1, N, dtype=torch.bfloat16, device=DEV)
+        h_out = torch.zeros(1, K, dtype=torch.bfloat16, device=DEV)
+        amax_zero = torch.full((1,), 77, dtype=torch.int32, device=DEV)
+        amax_out = torch.zeros(1, dtype=torch.int32, device=DEV)
+        kw = dict(out=out, silu=silu, amax_out=amax_out if silu else None, pdl=pdl)
+        if src_mode == 1:
+            ops.gemv_row_fused(1, x, w, ws, amax_in=amax_in, amax_zero=amax_zero, **kw)
+        else:
+            ops.gemv_row_fused(2, x, w, ws, res=res, norm_w=norm_w, eps=1e-6, h_out=h_out, **kw)
+        torch.cuda.synchronize()
+        return out, h_out, amax_zero, amax_out
+
+    a, b = run(0), run(native.PDL_STAGED)
+    assert native.lib().bm_device_error() == 0
+    for name, u, v in zip(("output", "residual row", "cleared word", "absmax word"), a, b):
+        assert torch.equal(u.view(torch.int16) if u.dtype == torch.bfloat16 else u,
+                           v.view(torch.int16) if v.dtype == torch.bfloat16 else v), name
+    assert float(a[0].float().abs().sum()) > 0
