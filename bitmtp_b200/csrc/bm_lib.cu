@@ -152,12 +152,17 @@ constexpr size_t kDirectMaxBytes = 8u << 20;   // packed weights up to which AUT
 // Row-per-warp kernel without shared-memory staging, for W <= 4 (t2_gemv_direct.cuh).
 int gemv_launch_direct(const bm::GemvParams &p0, int pdl, cudaStream_t stream) {
     if (!bm::direct_fits(p0.W, p0.N, p0.K) || p0.world > 1 || p0.silu_F != 0 || p0.src_mode != 0) return BM_EINVAL;
-    bm::GemvParams p = p0;
-    p.pdl = pdl;
+    const bm::DirectParams p{p0.A, p0.asum, p0.B, p0.ws, p0.s, p0.C, p0.G, p0.W, p0.N, p0.K, p0.ldc, p0.out_kind, pdl};
     const dim3 grid((unsigned)((p.N + bm::kDirectWarps - 1) / bm::kDirectWarps)), block(bm::kDirectWarps * 32);
-    if (p.W == 1) return launch_ex(bm::t2_gemv_direct_kernel<1>, grid, block, 0, stream, pdl, p);
-    if (p.W == 2) return launch_ex(bm::t2_gemv_direct_kernel<2>, grid, block, 0, stream, pdl, p);
-    return launch_ex(bm::t2_gemv_direct_kernel<4>, grid, block, 0, stream, pdl, p);
+    const int maxp = p.K <= 2048 ? 1 : (p.K <= 6144 ? 3 : 5);
+    const int wt = p.W == 1 ? 1 : (p.W == 2 ? 2 : 4);
+#define BM_DIRECT_CASE(WT_, MP_) \
+    if (wt == WT_ && maxp == MP_) return launch_ex(bm::t2_gemv_direct_kernel<WT_, MP_>, grid, block, 0, stream, pdl, p);
+    BM_DIRECT_CASE(1, 1) BM_DIRECT_CASE(1, 3) BM_DIRECT_CASE(1, 5)
+    BM_DIRECT_CASE(2, 1) BM_DIRECT_CASE(2, 3) BM_DIRECT_CASE(2, 5)
+    BM_DIRECT_CASE(4, 1) BM_DIRECT_CASE(4, 3) BM_DIRECT_CASE(4, 5)
+#undef BM_DIRECT_CASE
+    return BM_EINVAL;
 }
 
 struct MmaPlan {
@@ -631,8 +636,12 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
     // A few MB of weights: the register-only kernel (one memory round trip after the row is staged).
     if (!staged && bm::direct_row_fits(N, K) && (size_t)(silu ? 2 : 1) * N * K / 4 <= kDirectMaxBytes) {
         const dim3 grid((unsigned)(N / bm::kDirectWarps)), block(bm::kGemvThreads);
-        return silu ? launch_ex(bm::t2_gemv_direct_row_kernel<true>, grid, block, 0, st, pdl, p)
-                    : launch_ex(bm::t2_gemv_direct_row_kernel<false>, grid, block, 0, st, pdl, p);
+        const int maxp = K <= 2048 ? 1 : (K <= 6144 ? 3 : 5);
+#define BM_ROW_CASE(S_, MP_) \
+        if (silu == S_ && maxp == MP_) return launch_ex(bm::t2_gemv_direct_row_kernel<S_, MP_>, grid, block, 0, st, pdl, p);
+        BM_ROW_CASE(false, 1) BM_ROW_CASE(false, 3) BM_ROW_CASE(false, 5)
+        BM_ROW_CASE(true, 1) BM_ROW_CASE(true, 3) BM_ROW_CASE(true, 5)
+#undef BM_ROW_CASE
     }
     const bool one = K == 2048;
     MmaPlan pl;

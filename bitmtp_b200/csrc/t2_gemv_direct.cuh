@@ -10,13 +10,16 @@
 // any size; this kernel has one round trip: every lane requests its 16 bytes of packed weights,
 // its scale and its 64 activations per token at once, then computes from registers.
 //
-// Work split: row n = one warp.  A pass covers 2048 elements of K: lane l owns elements
-// [2048*pass + 64*l, +64), i.e. half of group 16*pass + l/2; the two lanes of a pair add their
-// integer partial sums, so both hold the exact group sum G.  fp32 order as in every other GEMV of
-// this library (and bmo_t2_gemv of the CPU oracle): group g feeds slot g % 16 with
-// fma((float)G, scale, slot) in ascending g (= ascending pass; slot = l/2), the 16 slots are
-// summed by the xor butterfly with slot offsets 1, 2, 4, 8 (lane offsets 2..16), the sum is
-// multiplied by 1/s[m].
+// Work split: row n = one warp.  A pass covers 2048 elements of K in four steps q: lane l owns the
+// 16-element run at k = 2048*pass + 512*q + 16*l, so a warp's activation loads are 512 contiguous
+// bytes and its weight loads 128 (every sector fetched is used in full; with 64 contiguous elements per
+// lane the activation sectors were fetched twice, which ncu showed as 299 K against 174 K sectors and a
+// third more cycles).  Eight lanes share a group: their integer partial sums are added by shuffles,
+// so every lane holds the exact group sum G of group 16*pass + 4*q + l/8.  fp32 order as in every other
+// GEMV of this library (and bmo_t2_gemv of the CPU oracle): group g feeds slot g % 16 = 4*q + l/8 with
+// fma((float)G, scale, slot) in ascending g (= ascending pass); the 16 slots are summed in the order
+// of the xor butterfly with slot offsets 1, 2 (lane offsets 8, 16), 4, 8 (the q index, in registers);
+// the sum is multiplied by 1/s[m].
 //
 // Activations: GEMV-ready (16-runs already in the order of the code registers `(word >> 2t) &
 // 0x03030303`, group sums in p.asum), or natural order.  For one natural-order token the kernel
@@ -43,8 +46,45 @@ __device__ __forceinline__ int dp4a_s8_u8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
-template <int WT>
-__global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const GemvParams p) {
+// The operands of a plain GEMV call only: a launch this short also pays for the size of its parameter block.
+struct DirectParams {
+    const int8_t *A;
+    const int32_t *asum;
+    const uint8_t *B;
+    const uint16_t *ws;
+    const float *s;
+    void *C;
+    int32_t *G;
+    int W, N, K, ldc, out_kind, pdl;
+};
+
+__device__ __forceinline__ void direct_store(const DirectParams &p, int m, int n, float y) {
+    if (p.out_kind == 0) reinterpret_cast<uint16_t *>(p.C)[(size_t)m * p.ldc + n] = bm_f32_to_bf16(y);
+    else reinterpret_cast<float *>(p.C)[(size_t)m * p.ldc + n] = p.out_kind == 1 ? y : bm_bf16_rn(y);
+}
+
+// Sum over the eight lanes that share a group.
+__device__ __forceinline__ int direct_group_sum(int v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+// The 16 slots (acc[q] of the four lane octets) summed in the canonical order.
+__device__ __forceinline__ float direct_slot_tree(const float (&acc)[4]) {
+    float t[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        t[q] = acc[q] + __shfl_xor_sync(0xffffffffu, acc[q], 8);
+        t[q] = t[q] + __shfl_xor_sync(0xffffffffu, t[q], 16);
+    }
+    return (t[0] + t[1]) + (t[2] + t[3]);
+}
+
+// MAXP: passes the kernel is built for (K <= 2048 * MAXP); registers grow with it.
+template <int WT, int MAXP>
+__global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const DirectParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n = blockIdx.x * kDirectWarps + warp;
     pdl_launch_dependents();
@@ -54,62 +94,63 @@ __global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const
     const bool prepared = p.asum != nullptr;
 
     // Weights and scales do not depend on the previous kernel: request them first.
-    uint4 wv[kDirectMaxPasses];
-    float sc[kDirectMaxPasses];
-    const uint4 *wrow = reinterpret_cast<const uint4 *>(p.B + (size_t)n * (p.K >> 2));
+    uint32_t wv[MAXP][4];
+    float sc[MAXP][4];
+    const uint32_t *wrow = reinterpret_cast<const uint32_t *>(p.B + (size_t)n * (p.K >> 2));
 #pragma unroll
-    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
-        const int g = 16 * ps + (lane >> 1);
-        const bool active = ps < passes && g < ng;
-        wv[ps] = active ? __ldg(wrow + 32 * ps + lane) : make_uint4(0u, 0u, 0u, 0u);
-        sc[ps] = active ? bm_bf16_to_f32(__ldg(p.ws + (size_t)n * ng + g)) : 0.0f;
-    }
+    for (int ps = 0; ps < MAXP; ++ps)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int g = 16 * ps + 4 * q + (lane >> 3);
+            const bool active = ps < passes && g < ng;
+            wv[ps][q] = active ? __ldg(wrow + 128 * ps + 32 * q + lane) : 0u;
+            sc[ps][q] = active ? bm_bf16_to_f32(__ldg(p.ws + (size_t)n * ng + g)) : 0.0f;
+        }
     if (p.pdl) pdl_wait();
     // 1/s of the token this lane will store, requested with the activations
     const float inv_s = (lane < WT && lane < p.W) ? 1.0f / p.s[lane] : 0.0f;
 
-    float acc[WT];
+    float acc[WT][4];
 #pragma unroll
-    for (int m = 0; m < WT; ++m) acc[m] = 0.0f;
+    for (int m = 0; m < WT; ++m)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[m][q] = 0.0f;
 
 #pragma unroll
-    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+    for (int ps = 0; ps < MAXP; ++ps) {
         if (ps >= passes) break;                                   // uniform
-        const int g = 16 * ps + (lane >> 1);
-        const bool active = g < ng;
-        const int k0 = 2048 * ps + 64 * lane;
         uint4 av[WT][4];
+        int asum_g[WT][4];
 #pragma unroll
         for (int m = 0; m < WT; ++m)
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                av[m][q] = (active && m < p.W)
-                               ? *reinterpret_cast<const uint4 *>(p.A + (size_t)m * p.K + k0 + 16 * q)
-                               : make_uint4(0u, 0u, 0u, 0u);
-        int asum_g[WT];
-#pragma unroll
-        for (int m = 0; m < WT; ++m) asum_g[m] = (prepared && active && m < p.W) ? p.asum[m * ng + g] : 0;
-
-        const uint32_t wq[4] = {wv[ps].x, wv[ps].y, wv[ps].z, wv[ps].w};
-        int part[WT];
-#pragma unroll
-        for (int m = 0; m < WT; ++m) part[m] = 0;
+            for (int q = 0; q < 4; ++q) {
+                const int g = 16 * ps + 4 * q + (lane >> 3);
+                const bool on = g < ng && m < p.W;
+                av[m][q] = on ? *reinterpret_cast<const uint4 *>(p.A + (size_t)m * p.K + 2048 * ps + 512 * q + 16 * lane)
+                              : make_uint4(0u, 0u, 0u, 0u);
+                asum_g[m][q] = (prepared && on) ? p.asum[m * ng + g] : 0;
+            }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
+            const int g = 16 * ps + 4 * q + (lane >> 3);
             // codes of packed bytes 0..3 of this word: register t holds element t of each byte
-            const uint32_t c0 = wq[q] & 0x03030303u, c1 = (wq[q] >> 2) & 0x03030303u,
-                           c2 = (wq[q] >> 4) & 0x03030303u, c3 = (wq[q] >> 6) & 0x03030303u;
+            const uint32_t w = wv[ps][q];
+            const uint32_t c0 = w & 0x03030303u, c1 = (w >> 2) & 0x03030303u, c2 = (w >> 4) & 0x03030303u,
+                           c3 = (w >> 6) & 0x03030303u;
+            int part[WT];
             if (prepared || WT == 1) {
 #pragma unroll
                 for (int m = 0; m < WT; ++m) {
                     uint4 a = av[m][q];
+                    part[m] = 0;
                     if (!prepared) {
                         // one token: cheaper to bring its 16-run into the order of the code registers
                         int sum = __dp4a((int)a.x, 0x01010101, 0);
                         sum = __dp4a((int)a.y, 0x01010101, sum);
                         sum = __dp4a((int)a.z, 0x01010101, sum);
                         sum = __dp4a((int)a.w, 0x01010101, sum);
-                        part[m] -= 2 * sum;                        // codes are value + 2
+                        part[m] = -2 * sum;                        // codes are value + 2
                         a = transpose_run16(a);
                     }
                     part[m] = dp4a_s8_u8(a.x, c0, part[m]);
@@ -128,31 +169,25 @@ __global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const
 #pragma unroll
                 for (int m = 0; m < WT; ++m) {
                     const uint4 a = av[m][q];
-                    part[m] = __dp4a((int)a.x, (int)s0, part[m]);
+                    part[m] = __dp4a((int)a.x, (int)s0, 0);
                     part[m] = __dp4a((int)a.y, (int)s1, part[m]);
                     part[m] = __dp4a((int)a.z, (int)s2, part[m]);
                     part[m] = __dp4a((int)a.w, (int)s3, part[m]);
                 }
             }
-        }
 #pragma unroll
-        for (int m = 0; m < WT; ++m) {
-            const int both = part[m] + __shfl_xor_sync(0xffffffffu, part[m], 1);
-            const int G = both - 2 * asum_g[m];
-            acc[m] = fmaf((float)G, sc[ps], acc[m]);
-            if (p.G != nullptr && active && (lane & 1) == 0 && m < p.W)
-                p.G[((size_t)m * p.N + n) * ng + g] = G;
+            for (int m = 0; m < WT; ++m) {
+                const int G = direct_group_sum(part[m]) - 2 * asum_g[m][q];
+                acc[m][q] = fmaf((float)G, sc[ps][q], acc[m][q]);
+                if (p.G != nullptr && g < ng && (lane & 7) == 0 && m < p.W)
+                    p.G[((size_t)m * p.N + n) * ng + g] = G;
+            }
         }
     }
-    // Slot tree: lane bits 1..4 are slot bits 0..3.
 #pragma unroll
     for (int m = 0; m < WT; ++m) {
-        float v = acc[m];
-        v = v + __shfl_xor_sync(0xffffffffu, v, 2);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 4);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 8);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 16);
-        if (lane == m && m < p.W) gemv_store(p, m, n, v * inv_s);
+        const float v = direct_slot_tree(acc[m]);
+        if (lane == m && m < p.W) direct_store(p, m, n, v * inv_s);
     }
 }
 
@@ -173,7 +208,7 @@ __host__ __device__ inline bool direct_row_fits(int N, int K) {
     return K >= 256 && (K % 256) == 0 && K <= 2048 * kDirectMaxPasses && N >= 8 && (N % 8) == 0;
 }
 
-template <bool SILU>
+template <bool SILU, int MAXP>
 __global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const GemvParams p) {
     __shared__ __align__(16) unsigned char smem[kDirectRowSmem];
     __shared__ unsigned int amax_sh;
@@ -185,19 +220,21 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const 
     pdl_launch_dependents();
     if (SILU && threadIdx.x == 0) amax_sh = 0u;
 
-    uint4 wv[NR][kDirectMaxPasses];
-    float sc[NR][kDirectMaxPasses];
+    uint32_t wv[NR][MAXP][4];
+    float sc[NR][MAXP][4];
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
         const size_t row = (size_t)n + (size_t)r * p.silu_F;
-        const uint4 *wrow = reinterpret_cast<const uint4 *>(p.B + row * (p.K >> 2));
+        const uint32_t *wrow = reinterpret_cast<const uint32_t *>(p.B + row * (p.K >> 2));
 #pragma unroll
-        for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
-            const int g = 16 * ps + (lane >> 1);
-            const bool active = ps < passes && g < ng;
-            wv[r][ps] = active ? __ldg(wrow + 32 * ps + lane) : make_uint4(0u, 0u, 0u, 0u);
-            sc[r][ps] = active ? bm_bf16_to_f32(__ldg(p.ws + row * ng + g)) : 0.0f;
-        }
+        for (int ps = 0; ps < MAXP; ++ps)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int g = 16 * ps + 4 * q + (lane >> 3);
+                const bool active = ps < passes && g < ng;
+                wv[r][ps][q] = active ? __ldg(wrow + 128 * ps + 32 * q + lane) : 0u;
+                sc[r][ps][q] = active ? bm_bf16_to_f32(__ldg(p.ws + row * ng + g)) : 0.0f;
+            }
     }
     if (p.pdl) pdl_wait();
     gemv_stage_row_from_bf16(p, smem, 0, kDirectRowAsumOff, kDirectRowInvsOff,
@@ -206,45 +243,36 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const 
     const int *asum = reinterpret_cast<const int *>(smem + kDirectRowAsumOff);
     const float inv_s = reinterpret_cast<const float *>(smem + kDirectRowInvsOff)[0];
 
-    float acc[NR];
+    float acc[NR][4];
 #pragma unroll
-    for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+    for (int r = 0; r < NR; ++r)
 #pragma unroll
-    for (int ps = 0; ps < kDirectMaxPasses; ++ps) {
+        for (int q = 0; q < 4; ++q) acc[r][q] = 0.0f;
+#pragma unroll
+    for (int ps = 0; ps < MAXP; ++ps) {
         if (ps >= passes) break;                                   // uniform
-        const int g = 16 * ps + (lane >> 1);
-        const bool active = g < ng;
-        uint4 a[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-            a[q] = active ? *reinterpret_cast<const uint4 *>(smem + 2048 * ps + 64 * lane + 16 * q)
-                          : make_uint4(0u, 0u, 0u, 0u);
-        const int asum_g = active ? asum[g] : 0;
+        for (int q = 0; q < 4; ++q) {
+            const int g = 16 * ps + 4 * q + (lane >> 3);
+            const bool active = g < ng;
+            const uint4 a = active ? *reinterpret_cast<const uint4 *>(smem + 2048 * ps + 512 * q + 16 * lane)
+                                   : make_uint4(0u, 0u, 0u, 0u);
+            const int asum_g = active ? asum[g] : 0;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-            const uint32_t wq[4] = {wv[r][ps].x, wv[r][ps].y, wv[r][ps].z, wv[r][ps].w};
-            int part = 0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                part = dp4a_s8_u8(a[q].x, wq[q] & 0x03030303u, part);
-                part = dp4a_s8_u8(a[q].y, (wq[q] >> 2) & 0x03030303u, part);
-                part = dp4a_s8_u8(a[q].z, (wq[q] >> 4) & 0x03030303u, part);
-                part = dp4a_s8_u8(a[q].w, (wq[q] >> 6) & 0x03030303u, part);
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t w = wv[r][ps][q];
+                int part = dp4a_s8_u8(a.x, w & 0x03030303u, 0);
+                part = dp4a_s8_u8(a.y, (w >> 2) & 0x03030303u, part);
+                part = dp4a_s8_u8(a.z, (w >> 4) & 0x03030303u, part);
+                part = dp4a_s8_u8(a.w, (w >> 6) & 0x03030303u, part);
+                const int G = direct_group_sum(part) - 2 * asum_g;
+                acc[r][q] = fmaf((float)G, sc[r][ps][q], acc[r][q]);
             }
-            const int G = part + __shfl_xor_sync(0xffffffffu, part, 1) - 2 * asum_g;
-            acc[r] = fmaf((float)G, sc[r][ps], acc[r]);
         }
     }
     float y[NR];
 #pragma unroll
-    for (int r = 0; r < NR; ++r) {
-        float v = acc[r];
-        v = v + __shfl_xor_sync(0xffffffffu, v, 2);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 4);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 8);
-        v = v + __shfl_xor_sync(0xffffffffu, v, 16);
-        y[r] = v * inv_s;
-    }
+    for (int r = 0; r < NR; ++r) y[r] = direct_slot_tree(acc[r]) * inv_s;
     if (SILU) {
         if (lane == 0) {
             const float v = bm_bf16_rn(bm_silu_bf16(bm_bf16_rn(y[0])) * bm_bf16_rn(y[NR - 1]));
