@@ -782,7 +782,10 @@ int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_b
     p.s_out = static_cast<float *>(s_out);
     p.pdl = pdl;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
+    // chunk rows as bf16, or as fp32 in the kernel that also rotates the queries (it widens them once per CTA)
+    const size_t smem = (rope != nullptr ? (size_t)32 * bm::kKeyStrideF * 4 + 32 * 128 * 4
+                                         : (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2) +
+                        (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
     // Many query vectors: two CTAs per (chunk, kv head), each with half of them, so that more
     // warps are resident per chunk (the per-warp instruction stream is what bounds this kernel).
     const int qsplit = QV >= 16 ? 2 : 1;
