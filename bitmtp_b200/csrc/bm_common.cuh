@@ -108,6 +108,14 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (both addresses 16-byte aligned), and the wait for all of a
+// thread's outstanding ones.
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ---- warp reductions in the oracle's butterfly order -------------------------
 __device__ __forceinline__ float warp_sum_butterfly(float v) {
 #pragma unroll

@@ -782,10 +782,7 @@ int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_b
     p.s_out = static_cast<float *>(s_out);
     p.pdl = pdl;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // chunk rows as bf16, or as fp32 in the kernel that also rotates the queries (it widens them once per CTA)
-    const size_t smem = (rope != nullptr ? (size_t)32 * bm::kKeyStrideF * 4 + 32 * 128 * 4
-                                         : (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2) +
-                        (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
+    const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
     // Many query vectors: two CTAs per (chunk, kv head), each with half of them, so that more
     // warps are resident per chunk (the per-warp instruction stream is what bounds this kernel).
     const int qsplit = QV >= 16 ? 2 : 1;
@@ -810,9 +807,15 @@ int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_b
         rp.k_out = const_cast<uint16_t *>(p.k_base);
         rp.v_out = const_cast<uint16_t *>(p.v_base);
         rp.eps = rope->eps;
-        if (nq == 2) rc = launch_ex(bm::attn_chunk_rope_kernel<2>, grid, dim3(threads), smem, st, pdl, rp);
-        else if (nq == 4) rc = launch_ex(bm::attn_chunk_rope_kernel<4>, grid, dim3(threads), smem, st, pdl, rp);
-        else rc = launch_ex(bm::attn_chunk_rope_kernel<8>, grid, dim3(threads), smem, st, pdl, rp);
+        // long segments: several waves of chunk CTAs, so trade a slower pass for three CTAs per SM
+        const bool dense = (long long)NC * Hkv * qsplit > 4LL * current_device().sm_count;
+#define BM_ROPE_CASE(NQ_) \
+        rc = dense ? launch_ex(bm::attn_chunk_rope_kernel<NQ_, 3>, grid, dim3(threads), smem, st, pdl, rp) \
+                   : launch_ex(bm::attn_chunk_rope_kernel<NQ_, 2>, grid, dim3(threads), smem, st, pdl, rp)
+        if (nq == 2) BM_ROPE_CASE(2);
+        else if (nq == 4) BM_ROPE_CASE(4);
+        else BM_ROPE_CASE(8);
+#undef BM_ROPE_CASE
     } else if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, grid, dim3(threads), smem, st, pdl, p);
     else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, grid, dim3(threads), smem, st, pdl, p);
     else rc = launch_ex(bm::attn_chunk_kernel<8>, grid, dim3(threads), smem, st, pdl, p);

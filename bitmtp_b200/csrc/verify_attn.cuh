@@ -35,7 +35,6 @@ namespace bm {
 
 constexpr int kAttnThreads = 256;
 constexpr int kKeyStride = 136;   // bf16 elements per staged key row (128 + 8 pad = 272 bytes)
-constexpr int kKeyStrideF = 132;  // fp32 elements per staged key row when the chunk is widened once per CTA
 
 struct AttnParams {
     const uint16_t *q;        // [M, H, 128]
@@ -68,9 +67,7 @@ __host__ __device__ inline int attn_nq(int QV) {
     return QV <= 16 ? 2 : (QV <= 32 ? 4 : 8);  // keeps ceil(QV/NQ) <= 8 warps up to QV = 64
 }
 
-// F32KV: Ks / Vs hold the chunk already widened to fp32 (rows of kKeyStrideF / 128 floats) instead of bf16
-// rows of kKeyStride / 128 elements, so that the eight warps of a CTA do not each widen it again.
-template <int NQ, bool F32KV = false>
+template <int NQ>
 __device__ __forceinline__ void attn_chunk_pass(const AttnParams &p, const uint16_t *Ks, const uint16_t *Vs,
                                                 const float *Qs, float *Ps, int q0, int QV, int G,
                                                 int hk, int j, int c0, int cn, int lane, int role,
@@ -83,18 +80,10 @@ __device__ __forceinline__ void attn_chunk_pass(const AttnParams &p, const uint1
 #pragma unroll
     for (int t = 0; t < NQ; ++t) acc[t] = 0.0f;
     const uint16_t *krow = Ks + (lane < cn ? lane : 0) * kKeyStride;
-    const float *krowf = reinterpret_cast<const float *>(Ks) + (lane < cn ? lane : 0) * kKeyStrideF;
 #pragma unroll 4
     for (int u = 0; u < 16; ++u) {
         float kf[8];
-        if (F32KV) {
-            const float4 ka = *reinterpret_cast<const float4 *>(krowf + 8 * u);
-            const float4 kb = *reinterpret_cast<const float4 *>(krowf + 8 * u + 4);
-            kf[0] = ka.x; kf[1] = ka.y; kf[2] = ka.z; kf[3] = ka.w;
-            kf[4] = kb.x; kf[5] = kb.y; kf[6] = kb.z; kf[7] = kb.w;
-        } else {
-            unpack8(*reinterpret_cast<const uint4 *>(krow + 8 * u), kf);
-        }
+        unpack8(*reinterpret_cast<const uint4 *>(krow + 8 * u), kf);
 #pragma unroll
         for (int t = 0; t < NQ; ++t) {
             const float4 qa = *reinterpret_cast<const float4 *>(qrow[t] + 8 * u);
@@ -141,21 +130,13 @@ __device__ __forceinline__ void attn_chunk_pass(const AttnParams &p, const uint1
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
             // keys past cn have weight 0 and are given value 0
-            if (F32KV) {
-                const float4 raw = (cb + cc < cn)
-                                       ? *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(Vs) +
-                                                                           (cb + cc) * 128 + 4 * lane)
-                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                v[cc][0] = raw.x; v[cc][1] = raw.y; v[cc][2] = raw.z; v[cc][3] = raw.w;
-            } else {
-                const uint2 raw = (cb + cc < cn)
-                                      ? *reinterpret_cast<const uint2 *>(Vs + (cb + cc) * 128 + 4 * lane)
-                                      : make_uint2(0u, 0u);
-                v[cc][0] = __uint_as_float(raw.x << 16);
-                v[cc][1] = __uint_as_float(raw.x & 0xffff0000u);
-                v[cc][2] = __uint_as_float(raw.y << 16);
-                v[cc][3] = __uint_as_float(raw.y & 0xffff0000u);
-            }
+            const uint2 raw = (cb + cc < cn)
+                                  ? *reinterpret_cast<const uint2 *>(Vs + (cb + cc) * 128 + 4 * lane)
+                                  : make_uint2(0u, 0u);
+            v[cc][0] = __uint_as_float(raw.x << 16);
+            v[cc][1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[cc][2] = __uint_as_float(raw.y << 16);
+            v[cc][3] = __uint_as_float(raw.y & 0xffff0000u);
         }
 #pragma unroll
         for (int t = 0; t < NQ; ++t) {
@@ -227,8 +208,13 @@ struct AttnRopeParams {
 
 constexpr int kRopeBatch = 4;        // head vectors a warp rotates per batch (loads issued together)
 
-template <int NQ>
-__global__ void __launch_bounds__(kAttnThreads) attn_chunk_rope_kernel(const AttnRopeParams P) {
+// MINB: CTAs per SM the register budget is cut for.  3 (<= 85 registers) makes a chunk's pass ~20 % slower
+// but lets half as many CTAs again run at once: worth it when the history is long enough for several waves of
+// CTAs (measured at width 16: 1245 -> 1286 us per replay at cache_len 300, where 176 CTAs are one wave either
+// way; 1406 -> 1336 us at cache_len 700, where 368 CTAs need two waves at two per SM).  The host picks it
+// from the segment size.
+template <int NQ, int MINB>
+__global__ void __launch_bounds__(kAttnThreads, MINB) attn_chunk_rope_kernel(const AttnRopeParams P) {
     extern __shared__ __align__(16) unsigned char dyn[];
     const AttnParams &p = P.a;
     pdl_launch_dependents();
@@ -244,24 +230,23 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_rope_kernel(const Att
     const bool fresh = j == p.NC - 1;
 
     const int G = p.H / p.Hkv, QV = G * p.M, heads = p.H + 2 * p.Hkv;
-    // the chunk's K and V rows are kept as fp32: widened once here instead of by every warp in its pass
-    float *Kf = reinterpret_cast<float *>(dyn);                           // [32][132]
-    float *Vf = Kf + 32 * kKeyStrideF;                                    // [32][128]
-    float *Qs = Vf + 32 * 128;                                            // [QV][128]
+    uint16_t *Ks = reinterpret_cast<uint16_t *>(dyn);                    // [32][136]
+    uint16_t *Vs = Ks + 32 * kKeyStride;                                  // [32][128]
+    float *Qs = reinterpret_cast<float *>(Vs + 32 * 128);                 // [QV][128]
     float *Ps = Qs + (size_t)QV * 128;                                    // [QV][32]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x, nwarps = nthr >> 5;
     const int per = (QV + (int)gridDim.z - 1) / (int)gridDim.z;
     const int q_lo = (int)blockIdx.z * per, q_hi = min(QV, q_lo + per);
 
     // Nothing below depends on the previous kernel until the wait: history rows, positions, tables.
-    uint4 kreg[4], vreg[4];                                               // up to 512 pieces over >= 128 threads
+    // The chunk's history rows go straight to shared memory (asynchronous 16-byte copies, no registers
+    // held across the rotation below).
     if (!fresh) {
         const uint4 *kg = reinterpret_cast<const uint4 *>(p.k_base + ((size_t)hk * p.kv_rows + c0) * 128);
         const uint4 *vg = reinterpret_cast<const uint4 *>(p.v_base + ((size_t)hk * p.kv_rows + c0) * 128);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int i = tid + k * nthr;
-            if (i < cn * 16) { kreg[k] = kg[i]; vreg[k] = vg[i]; }
+        for (int i = tid; i < cn * 16; i += nthr) {
+            cp_async16(Ks + (i >> 4) * kKeyStride + 8 * (i & 15), kg + i);
+            cp_async16(Vs + 8 * i, vg + i);
         }
     }
     const uint2 qw = *reinterpret_cast<const uint2 *>(P.q_w + 4 * lane);
@@ -291,11 +276,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_rope_kernel(const Att
                 const uint2 kbits = make_uint2(
                     (uint32_t)bm_f32_to_bf16(o[0]) | ((uint32_t)bm_f32_to_bf16(o[1]) << 16),
                     (uint32_t)bm_f32_to_bf16(o[2]) | ((uint32_t)bm_f32_to_bf16(o[3]) << 16));
-                *reinterpret_cast<float4 *>(Kf + m * kKeyStrideF + 4 * lane) =
-                    make_float4(bm_bf16_rn(o[0]), bm_bf16_rn(o[1]), bm_bf16_rn(o[2]), bm_bf16_rn(o[3]));
-                *reinterpret_cast<float4 *>(Vf + m * 128 + 4 * lane) =
-                    make_float4(__uint_as_float(vraw[k].x << 16), __uint_as_float(vraw[k].x & 0xffff0000u),
-                                __uint_as_float(vraw[k].y << 16), __uint_as_float(vraw[k].y & 0xffff0000u));
+                *reinterpret_cast<uint2 *>(Ks + m * kKeyStride + 4 * lane) = kbits;
+                *reinterpret_cast<uint2 *>(Vs + m * 128 + 4 * lane) = vraw[k];
                 if (blockIdx.z == 0) {
                     const size_t row = ((size_t)hk * p.kv_rows + p.sigma + m) * 128 + 4 * lane;
                     *reinterpret_cast<uint2 *>(P.k_out + row) = kbits;
@@ -327,26 +309,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_rope_kernel(const Att
                 make_float4(bm_bf16_rn(o[0]), bm_bf16_rn(o[1]), bm_bf16_rn(o[2]), bm_bf16_rn(o[3]));
         }
     }
-    if (!fresh) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int i = tid + k * nthr;
-            if (i < cn * 16) {
-                float kf[8], vf[8];
-                unpack8(kreg[k], kf);
-                unpack8(vreg[k], vf);
-                float *kd = Kf + (i >> 4) * kKeyStrideF + 8 * (i & 15), *vd = Vf + 8 * i;
-                *reinterpret_cast<float4 *>(kd) = make_float4(kf[0], kf[1], kf[2], kf[3]);
-                *reinterpret_cast<float4 *>(kd + 4) = make_float4(kf[4], kf[5], kf[6], kf[7]);
-                *reinterpret_cast<float4 *>(vd) = make_float4(vf[0], vf[1], vf[2], vf[3]);
-                *reinterpret_cast<float4 *>(vd + 4) = make_float4(vf[4], vf[5], vf[6], vf[7]);
-            }
-        }
-    }
+    cp_async_wait_all();
     __syncthreads();
     for (int q0 = q_lo + warp * NQ; q0 < q_hi; q0 += nwarps * NQ)
-        attn_chunk_pass<NQ, true>(p, reinterpret_cast<const uint16_t *>(Kf), reinterpret_cast<const uint16_t *>(Vf), Qs, Ps,
-                                  q0, q_hi, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P_);
+        attn_chunk_pass<NQ>(p, Ks, Vs, Qs, Ps, q0, q_hi, G, hk, j, c0, cn, lane, role, cache_len, n_pend, P_);
 }
 
 template <int NQ>

@@ -127,6 +127,8 @@ ATTN_CASES = [
     (5, 2, 1, 64, 20, 1, 4, "draft"),
     (16, 16, 8, 256, 0, 0, 8, "ar"),
     (17, 16, 8, 256, 40, 9, 8, "draft"),
+    (16, 16, 8, 4096, 2500, 8, 8, "draft"),    # long segment: the three-CTAs-per-SM build of the chunk kernel
+    (9, 32, 8, 4096, 3000, 0, 8, "verify"),
 ]
 
 
