@@ -885,6 +885,37 @@ int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void
     return cuda_status(cudaGetLastError());
 }
 
+long long bm_logit_scratch_bytes(void) { return (long long)sizeof(bm::LogitScratch); }
+
+int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out, void *scratch,
+                         void *stream) {
+    if (!logits || !idx || !scratch || rows < 1 || rows > bm::kLogitMaxRows || vocab < 1 || ld < vocab ||
+        !aligned16(scratch))
+        return BM_EINVAL;
+    count_launch();
+    bm::argmax_split_kernel<<<dim3(bm::logit_splits(rows), rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float *>(logits), vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_out),
+        static_cast<bm::LogitScratch *>(scratch));
+    return cuda_status(cudaGetLastError());
+}
+
+int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf, void *conf,
+                         void *n_out, void *scratch, void *stream) {
+    if (!logits || !idx || !max_buf || !conf || !n_out || !scratch || D < 1 || D > bm::kLogitMaxRows || vocab < 1 ||
+        ld < vocab || vocab > bm::kConfMaxChunks * 256 || !aligned16(scratch))
+        return BM_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bm::LogitScratch *sc = static_cast<bm::LogitScratch *>(scratch);
+    count_launch();
+    bm::argmax_split_kernel<<<dim3(bm::logit_splits(D), D), 256, 0, st>>>(
+        static_cast<const float *>(logits), vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_buf), sc);
+    count_launch();
+    bm::confidence_split_kernel<<<dim3(bm::logit_splits(D), D), 256, 0, st>>>(
+        static_cast<const float *>(logits), vocab, ld, static_cast<const float *>(max_buf), static_cast<float *>(conf), D,
+        tau, static_cast<int *>(n_out), sc);
+    return cuda_status(cudaGetLastError());
+}
+
 int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, void *stream) {
     if (!draft || !verify || !n_out || D < 1) return BM_EINVAL;
     count_launch();

@@ -506,6 +506,145 @@ __global__ void chain_length_kernel(const float *conf, int D, float tau, int *ou
     *out = n;
 }
 
+// ---- the same reductions spread over many CTAs ------------------------------------------------
+// One CTA per logit row leaves 140 of 148 SMs idle on rows of 151936 values (measured: 129 us for the
+// confidence chain of 8 rows, 37 us for an argmax).  Here a row is cut into S ranges of whole 256-element
+// chunks, one CTA each (S = logit_splits(rows): more ranges when there are few rows); the last CTA of a row to finish (a
+// ticket counter in the caller's scratch) combines the row, and for the confidence chain the last row
+// to finish computes the chain length.  Results are identical to the one-CTA kernels: the argmax
+// comparison does not depend on order, the chunk sums are the same chunk sums and are added in ascending
+// chunk order by one thread.  Scratch (LogitScratch, zero before first use; the kernels leave the
+// counters zero again).
+constexpr int kLogitMaxRows = 32;
+constexpr int kLogitMaxParts = 512;      // rows * S
+
+__host__ __device__ inline int logit_splits(int rows) {
+    int s = kLogitMaxParts / rows;       // 16 at 32 rows
+    return s > 128 ? 128 : (s > 32 && rows > 2 ? 32 : s);
+}
+
+struct LogitScratch {
+    unsigned int arg_tickets[kLogitMaxRows];
+    unsigned int conf_tickets[kLogitMaxRows];
+    unsigned int rows_done;
+    unsigned int pad[63];
+    float part_max[kLogitMaxParts];
+    int part_idx[kLogitMaxParts];
+    float chunk_sum[kLogitMaxRows * kConfMaxChunks];
+};
+
+__device__ __forceinline__ void logit_split_range(int vocab, int split, int S, int &v_lo, int &v_hi) {
+    const int nchunks = (vocab + 255) / 256;
+    const int per = (nchunks + S - 1) / S;
+    v_lo = min(vocab, split * per * 256);
+    v_hi = min(vocab, (split + 1) * per * 256);
+}
+
+// grid (S, rows), 256 threads
+__global__ void __launch_bounds__(256) argmax_split_kernel(const float *__restrict__ logits, int vocab, int ld,
+                                                          int64_t *__restrict__ idx, float *__restrict__ max_out,
+                                                          LogitScratch *sc) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ unsigned int ticket;
+    const int split = blockIdx.x, S = gridDim.x, r = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *x = logits + (size_t)r * ld;
+    int v_lo, v_hi;
+    logit_split_range(vocab, split, S, v_lo, v_hi);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int v = v_lo + threadIdx.x; v < v_hi; v += 256) {
+        const float f = x[v];
+        if (f > best || (f == best && v < bi)) { best = f; bi = v; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        sc->part_max[r * S + split] = best;
+        sc->part_idx[r * S + split] = bi;
+        __threadfence();
+        ticket = atomicAdd(&sc->arg_tickets[r], 1u);
+    }
+    __syncthreads();
+    if (ticket != (unsigned int)(S - 1) || threadIdx.x != 0) return;
+    // last CTA of the row: every partial is visible
+    __threadfence();
+    best = -INFINITY;
+    bi = 0x7fffffff;
+    for (int s = 0; s < S; ++s) {
+        const float f = __ldcg(&sc->part_max[r * S + s]);
+        const int i = __ldcg(&sc->part_idx[r * S + s]);
+        if (f > best || (f == best && i < bi)) { best = f; bi = i; }
+    }
+    idx[r] = bi;
+    if (max_out) max_out[r] = best;
+    sc->arg_tickets[r] = 0u;
+}
+
+// grid (S, D), 256 threads.  row_max[r] must be final (argmax_split_kernel of the same rows has
+// completed: stream order).  The last row to finish writes the chain length.
+__global__ void __launch_bounds__(256) confidence_split_kernel(const float *__restrict__ logits, int vocab, int ld,
+                                                              const float *__restrict__ row_max,
+                                                              float *__restrict__ conf, int D, float tau,
+                                                              int *__restrict__ n_out, LogitScratch *sc) {
+    __shared__ unsigned int ticket;
+    const int split = blockIdx.x, S = gridDim.x, r = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *x = logits + (size_t)r * ld;
+    const float mx = row_max[r];
+    const int nchunks = (vocab + 255) / 256;
+    const int per = (nchunks + S - 1) / S;
+    const int c_lo = min(nchunks, split * per), c_hi = min(nchunks, (split + 1) * per);
+    float *sums = sc->chunk_sum + (size_t)r * kConfMaxChunks;
+    const bool vec = (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+    for (int c = c_lo + warp; c < c_hi; c += 8) {
+        const int v0 = c * 256 + lane * 8;
+        float acc = 0.0f;
+        if (vec && v0 + 8 <= vocab) {
+            const float4 a = *reinterpret_cast<const float4 *>(x + v0), b = *reinterpret_cast<const float4 *>(x + v0 + 4);
+            acc += bm_expf(a.x - mx); acc += bm_expf(a.y - mx); acc += bm_expf(a.z - mx); acc += bm_expf(a.w - mx);
+            acc += bm_expf(b.x - mx); acc += bm_expf(b.y - mx); acc += bm_expf(b.z - mx); acc += bm_expf(b.w - mx);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (v0 + e < vocab) acc += bm_expf(x[v0 + e] - mx);
+        }
+        acc = warp_sum_butterfly(acc);
+        if (lane == 0) sums[c] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ticket = atomicAdd(&sc->conf_tickets[r], 1u);
+    }
+    __syncthreads();
+    if (ticket != (unsigned int)(S - 1) || threadIdx.x != 0) return;
+    // last CTA of the row: add the chunk sums in ascending order
+    __threadfence();
+    float total = 0.0f;
+    for (int c = 0; c < nchunks; ++c) total += __ldcg(&sums[c]);
+    const float lse = mx + bm_logf(total);
+    conf[r] = bm_expf(mx - lse);
+    sc->conf_tickets[r] = 0u;
+    __threadfence();
+    if (atomicAdd(&sc->rows_done, 1u) != (unsigned int)(D - 1)) return;
+    // last row: the chain length over all confidences
+    __threadfence();
+    int n = 1;
+    for (int q = 1; q < D; ++q) {
+        if (__ldcg(&conf[q]) > tau) ++n; else break;
+    }
+    *n_out = n;
+    sc->rows_done = 0u;
+}
+
 __global__ void verify_accept_kernel(const int64_t *draft, const int64_t *verify, int D, int *out) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     int n = 0;

@@ -46,8 +46,11 @@ def _decode_hits_stop(tokenizer, token_ids: Sequence[int], stop_strings) -> bool
     return _first_stop_index(text, stop_strings) < len(text)
 
 
-def _argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Row argmax, lowest index on ties (native kernel); written into `out` when given."""
+def _argmax_rows(logits: torch.Tensor, out=None) -> torch.Tensor:
+    """Row argmax, lowest index on ties (native kernel); written into `out` when given.  `out` may be
+    (tensor, scratch): with the scratch of ops.logit_scratch every row is reduced by 16-128 CTAs."""
+    if isinstance(out, tuple):
+        return ops.argmax_rows(logits, out=out[0], scratch=out[1])
     return ops.argmax_rows(logits, out=out)
 
 
@@ -56,8 +59,12 @@ def _fused_draft_chain(logits: torch.Tensor, threshold: float,
     """(draft ids [D], iter_accept) with iter_accept = 1 + the number of leading rows
     r >= 1 whose confidence exp(max - logsumexp) exceeds the threshold
     (fast_generate.py:111-130).  Row 0 is always committed.  `out` = (ids, max work area,
-    confidences, count) places the results in the caller's buffers."""
-    idx, n, _ = ops.draft_chain(logits, threshold, bufs=out)
+    confidences, count[, scratch]) places the results in the caller's buffers; with the scratch of
+    ops.logit_scratch the reductions run on 16-128 CTAs per row."""
+    if out is not None and len(out) > 4:
+        idx, n, _ = ops.draft_chain(logits, threshold, bufs=tuple(out[:4]), scratch=out[4])
+    else:
+        idx, n, _ = ops.draft_chain(logits, threshold, bufs=out)
     return idx, n
 
 
@@ -131,8 +138,14 @@ class _DecodeBufs:
     chain_work: torch.Tensor    # fp32 [2, D]: row maxima and confidences of the chain kernel
     verify_rec: torch.Tensor    # int64 [2D + 2]: verifier ids (D + 1) | accepted count | draft ids (D)
 
+    logit_scratch: Optional[torch.Tensor] = None   # ops.logit_scratch: partials of the many-CTA logit reductions
+
     def chain_out(self, D: int):
-        return self.chain_rec[:D], self.chain_work[0], self.chain_work[1], self.chain_rec[D:D + 1]
+        out = (self.chain_rec[:D], self.chain_work[0], self.chain_work[1], self.chain_rec[D:D + 1])
+        return out + (self.logit_scratch,) if self.logit_scratch is not None else out
+
+    def argmax_out(self, view: torch.Tensor):
+        return (view, self.logit_scratch) if self.logit_scratch is not None else view
 
 
 def _alloc_decode_bufs(atlas, max_gen_len: int, eos_ids, prompt_len: int = 0) -> _DecodeBufs:
@@ -143,6 +156,7 @@ def _alloc_decode_bufs(atlas, max_gen_len: int, eos_ids, prompt_len: int = 0) ->
         chain_rec=torch.zeros(D + 1, dtype=torch.long, device=dev),
         chain_work=torch.zeros((2, D), dtype=torch.float32, device=dev),
         verify_rec=torch.zeros(2 * D + 2, dtype=torch.long, device=dev),
+        logit_scratch=ops.logit_scratch(dev) if torch.device(dev).type == "cuda" else None,
         gen_buf=torch.zeros(max_gen_len + m_max + 1, dtype=torch.long, device=dev),
         pending_buf=torch.zeros(m_max + 1, dtype=torch.long, device=dev),
         commit_buf=torch.zeros(m_max + 1, dtype=torch.long, device=dev),
@@ -293,7 +307,7 @@ class _Session:
         atlas, bufs, D = self.atlas, self.bufs, self.D
         gv.cuda_graph.replay()
         rec = bufs.verify_rec
-        verify_tokens = _argmax_rows(gv.logits_out, rec[:D + 1])
+        verify_tokens = _argmax_rows(gv.logits_out, bufs.argmax_out(rec[:D + 1]))
         acc_t = _fused_verify_accept(draft_tokens, verify_tokens, D, rec[D + 1:D + 2])
         if draft_host is None:
             verify_host, acc_host, draft_host = _read_record(rec, verify_tokens, acc_t, draft_tokens)
@@ -362,10 +376,12 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
         ses.ensure_room()
         g = ses.ar_step(tok_dev, ses.cache_len)
         ses.cache_len += 1
-        tok_dev = _argmax_rows(g.logits_out)[-1:]
-        # queued before the host read below, so it does not sit in the GPU-idle window; an EOS token
+        # the argmax lands in the output buffer itself (queued before the host read below); an EOS token
         # written here lies past gen_count and is never returned
-        bufs.gen_buf[gen_count:gen_count + 1].copy_(tok_dev)
+        slot = bufs.gen_buf[gen_count:gen_count + 1]
+        tok_dev = _argmax_rows(g.logits_out, bufs.argmax_out(slot))[-1:]
+        if tok_dev.data_ptr() != slot.data_ptr():
+            slot.copy_(tok_dev)
         next_tok = int(tok_dev.item())
         if bufs.has_eos and next_tok in eos_ids:
             break
@@ -416,7 +432,7 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
     accepted_draft_total = verifier_bonus_total = 0
 
     chain_out = bufs.chain_out(D)
-    spec_draft_out = bufs.verify_rec[D + 2:2 * D + 2]
+    spec_draft_out = bufs.argmax_out(bufs.verify_rec[D + 2:2 * D + 2])
     t1 = time.time()
     while gen_count < max_gen_len and not eos_found:
         n_iters += 1

@@ -132,6 +132,9 @@ def _declare_optional(L) -> None:
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],
         "bm_verify_accept": [vp, vp, ci, vp, vp],
+        "bm_argmax_rows_split": [vp, ci, ci, ci, vp, vp, vp, vp],
+        "bm_draft_chain_split": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp, vp],
+        "bm_logit_scratch_bytes": [],
     }
     for name, args in protos.items():
         fn = getattr(L, name)

@@ -209,22 +209,38 @@ def verify_attention(q, k_layer, v_layer, sigma, state, scratch, *, pdl: bool = 
     return out
 
 
-def argmax_rows(logits: torch.Tensor, *, out=None) -> torch.Tensor:
+def logit_scratch(device) -> torch.Tensor:
+    """Zeroed scratch for the many-CTA logit reductions (bm_logit_scratch_bytes); one per stream of calls."""
+    return torch.zeros(int(native.lib().bm_logit_scratch_bytes()), dtype=torch.uint8, device=device)
+
+
+def argmax_rows(logits: torch.Tensor, *, out=None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row argmax, lowest index on ties.  With `scratch` (logit_scratch) each row is spread over 16-128 CTAs."""
     rows, vocab = logits.shape
     idx = out if out is not None else torch.empty(rows, dtype=torch.int64, device=logits.device)
+    if scratch is not None and rows <= 32:
+        check(native.lib().bm_argmax_rows_split(_ptr(logits), rows, vocab, logits.stride(0), _ptr(idx), None,
+                                                _ptr(scratch), _stream(logits.device)), "bm_argmax_rows_split")
+        return idx
     check(native.lib().bm_argmax_rows(_ptr(logits), rows, vocab, logits.stride(0), _ptr(idx), None,
                                       _stream(logits.device)), "bm_argmax_rows")
     return idx
 
 
-def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None):
-    """Returns (idx int64 [D], iter_accept int32 [1] (device), conf fp32 [D])."""
+def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None, scratch: Optional[torch.Tensor] = None):
+    """Returns (idx int64 [D], iter_accept int32 [1] (device), conf fp32 [D]).  With `scratch`
+    (logit_scratch) the two reductions run on 16-128 CTAs per row."""
     D, vocab = logits.shape
     dev = logits.device
     if bufs is None:
         bufs = (torch.empty(D, dtype=torch.int64, device=dev), torch.empty(D, device=dev),
                 torch.empty(D, device=dev), torch.empty(1, dtype=torch.int32, device=dev))
     idx, mx, conf, n = bufs
+    if scratch is not None and D <= 32:
+        check(native.lib().bm_draft_chain_split(_ptr(logits), D, vocab, logits.stride(0), float(tau), _ptr(idx),
+                                                _ptr(mx), _ptr(conf), _ptr(n), _ptr(scratch), _stream(dev)),
+              "bm_draft_chain_split")
+        return idx, n, conf
     check(native.lib().bm_draft_chain(_ptr(logits), D, vocab, logits.stride(0), float(tau), _ptr(idx),
                                       _ptr(mx), _ptr(conf), _ptr(n), _stream(dev)), "bm_draft_chain")
     return idx, n, conf

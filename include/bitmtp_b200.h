@@ -329,6 +329,16 @@ int bm_argmax_rows(const void *logits, int rows, int vocab, int ld, void *idx, v
 int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void *idx,
                    void *max_buf, void *conf, void *n_out, void *stream);
 
+/* The two reductions above spread over 16 to 128 CTAs per logit row (more when there are few rows) (one CTA per row leaves most of the GPU idle on
+ * rows of 151936 values); same results bit for bit.  `scratch`: bm_logit_scratch_bytes() bytes of device
+ * memory, 16-byte aligned, zero before its first use (the kernels leave its counters zero), not shared by
+ * calls that may run at the same time.  rows, D <= 32. */
+long long bm_logit_scratch_bytes(void);
+int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out, void *scratch,
+                         void *stream);
+int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf,
+                         void *conf, void *n_out, void *scratch, void *stream);
+
 /* *n_out (device int32) = length of the longest common prefix of draft[0:D] and
  * verify[0:D] (int64).  Replaces _fused_verify_accept
  * (src/bonsai_sft/gpu/fast_generate.py:133-146). */

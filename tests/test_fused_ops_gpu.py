@@ -435,3 +435,35 @@ def test_width1_row_fused_register_kernel_equals_staged_kernel(src_mode, N, K, s
         assert torch.equal(u.view(torch.int16) if u.dtype == torch.bfloat16 else u,
                            v.view(torch.int16) if v.dtype == torch.bfloat16 else v), name
     assert float(a[0].float().abs().sum()) > 0
+
+
+@pytest.mark.parametrize("rows,vocab,ld", [(8, 151936, 151936), (9, 151669, 151936), (1, 1000, 1000), (17, 4099, 4100),
+                                           (32, 300, 333)])
+def test_split_logit_reductions_equal_the_single_cta_kernels(rows, vocab, ld):
+    """bm_argmax_rows_split / bm_draft_chain_split (16-128 CTAs per row, last-arriver combine) against
+    bm_argmax_rows / bm_draft_chain: indices, confidences (bit for bit) and chain lengths, with ties in
+    the rows, ragged vocabulary sizes and unaligned leading dimensions; three calls in a row on one scratch
+    show that the ticket counters are left clean."""
+    gen = torch.Generator().manual_seed(rows * 7 + vocab)
+    base = torch.randn(rows, ld, generator=gen) * 3.0
+    base[:, vocab:] = 1e9                                     # padding columns must never win
+    if vocab > 600:
+        base[0, 17] = base[0, 512] = base[0].max() + 1.0        # a tie across two ranges: lowest index wins
+    lg = base.to(DEV)[:, :vocab]
+    scratch = ops.logit_scratch(DEV)
+    want_idx = ops.argmax_rows(lg)
+    for _ in range(3):
+        got_idx = ops.argmax_rows(lg, scratch=scratch)
+        assert torch.equal(got_idx, want_idx)
+    if vocab > 600:
+        assert int(want_idx[0]) == 17
+    for tau in (0.0, 1e-6, 0.5):
+        idx0, n0, conf0 = ops.draft_chain(lg, tau)
+        for _ in range(2):
+            idx1, n1, conf1 = ops.draft_chain(lg, tau, scratch=scratch)
+            assert torch.equal(idx1, idx0)
+            assert torch.equal(conf1.view(torch.int32), conf0.view(torch.int32))
+            assert int(n1) == int(n0)
+    torch.cuda.synchronize()
+    assert native.lib().bm_device_error() == 0
+    assert int(scratch[: 4 * 65].view(torch.int32).abs().sum()) == 0
