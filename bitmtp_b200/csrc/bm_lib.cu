@@ -588,6 +588,22 @@ int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n
     return cuda_status(cudaGetLastError());
 }
 
+int bm_commit_stage_draft(const void *src, int n_commit, int verified, void *gen_dst, void *pending, int stage,
+                          int cache_len, int M, int D, long long mask_id, int role, int P, void *tok, void *pos,
+                          void *state, void *stream) {
+    if (!src || !gen_dst || !pending || n_commit < 1 || n_commit > 32) return BM_EINVAL;
+    if (stage) {
+        const int n_pend = verified ? 1 : n_commit;
+        if (!tok || !pos || !state || M < 1 || M > BM_MAX_W || P + D != M || n_pend > P) return BM_EINVAL;
+    }
+    count_launch();
+    bm::commit_stage_draft_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const int64_t *>(src), n_commit, verified, static_cast<int64_t *>(gen_dst),
+        static_cast<int64_t *>(pending), stage, cache_len, M, D, (int64_t)mask_id, role, P, static_cast<int64_t *>(tok),
+        static_cast<int64_t *>(pos), static_cast<bm::StepState *>(state));
+    return cuda_status(cudaGetLastError());
+}
+
 int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const void *res, const void *norm_w, float eps,
                          void *h_out, const void *amax_in, void *amax_zero, const void *B, const void *ws, int N, int K,
                          void *C, int ldc, int out_kind, int silu, void *amax_out, int pdl, void *stream) {

@@ -409,6 +409,40 @@ __global__ void stage_replay_inputs_kernel(int kind, const int64_t *__restrict__
     }
 }
 
+// The end of one decode step and the start of the next in one launch: the committed ids go to the output
+// buffer and become the pending rows (all of them after a confidence commit, the last one = the verifier's
+// token after a verified step: fast_generate.py:1121-1140), then the draft inputs are staged from them as
+// stage_replay_inputs_kernel kind 0 does.  One warp; n_commit <= 32.  stage == 0: commit only.
+__global__ void commit_stage_draft_kernel(const int64_t *__restrict__ src, int n_commit, int verified,
+                                          int64_t *__restrict__ gen_dst, int64_t *__restrict__ pending, int stage,
+                                          int cache_len, int M, int D, int64_t mask_id, int role, int P,
+                                          int64_t *__restrict__ tok, int64_t *__restrict__ pos, StepState *st) {
+    const int i = threadIdx.x;
+    if (i < n_commit) {
+        const int64_t t = src[i];
+        gen_dst[i] = t;
+        if (!verified) pending[i] = t;
+        else if (i == n_commit - 1) pending[0] = t;
+    }
+    if (!stage) return;
+    __syncwarp();
+    const int n_pend = verified ? 1 : n_commit;
+    if (i == 0) {
+        st->cache_len = cache_len;
+        st->n_pend = n_pend > P ? P : n_pend;
+        st->role = role;
+        st->P = P;
+    }
+    if (i >= M) return;
+    int64_t t, q;
+    if (i > P) { t = mask_id; q = cache_len + n_pend - 1 + (i - P); }
+    else if (i == P) { t = pending[n_pend - 1]; q = cache_len + n_pend - 1; }
+    else if (i < n_pend) { t = pending[i]; q = cache_len + i; }
+    else { t = 0; q = 0; }
+    tok[i] = t;
+    pos[i] = q;
+}
+
 // Copies rows [src_row, src_row + n) to [dst_row, dst_row + n) in every
 // (k|v, layer, kv head) plane of the shared buffer [planes, kv_rows, 128] bf16.
 // Replaces GraphAtlas.commit_kv / commit_kv_from_verify

@@ -198,6 +198,7 @@ class _Session:
         self.bufs = _alloc_decode_bufs(atlas, max_gen_len, eos_ids, prompt_len=self.seq_len)
         self.cache_len = 0
         self.sigma = atlas.segment_ladder[0]
+        self._deferred = None        # (ids, count, verified, output offset) of a commit not yet written
 
     # -- prefill, first token, segment choice (fast_generate.py:203-222, 951-969)
     def start(self) -> Tuple[float, int, float]:
@@ -220,7 +221,9 @@ class _Session:
                 shared[0, i, :, :, : self.seq_len, :].copy_(ck[0])
                 shared[1, i, :, :, : self.seq_len, :].copy_(cv[0])
             del cache
-        bufs.gen_buf[0:1].copy_(_argmax_rows(logits[-1:].contiguous()))
+        first = _argmax_rows(logits[-1:].contiguous(), bufs.argmax_out(bufs.gen_buf[0:1]))
+        if first.data_ptr() != bufs.gen_buf.data_ptr():
+            bufs.gen_buf[0:1].copy_(first)
         self.cache_len = self.seq_len
         torch.cuda.synchronize()
         prefill_time = time.time() - t0
@@ -256,6 +259,31 @@ class _Session:
         atlas.commit_kv(g, position, n_accept=1)
         return g
 
+    # -- commit of a step: ids -> output buffer and pending rows (fast_generate.py:1121-1140).  Deferred so
+    #    that the next draft replay's staging kernel can do it in the same launch.
+    @staticmethod
+    def _device_ids(t: torch.Tensor) -> bool:
+        return t.is_cuda and t.dtype == torch.int64 and t.is_contiguous()
+
+    def defer_commit(self, src: torch.Tensor, n_commit: int, verified: bool, gen_off: int) -> None:
+        self.flush_commit()
+        self._deferred = (src, int(n_commit), bool(verified), int(gen_off))
+
+    def flush_commit(self) -> None:
+        d, self._deferred = self._deferred, None
+        if d is None:
+            return
+        src, n, verified, off = d
+        bufs = self.bufs
+        if self._device_ids(src):
+            ops.commit_stage_draft(src, n, verified, bufs.gen_buf[off:], bufs.pending_buf)
+            return
+        bufs.gen_buf[off:off + n].copy_(src[:n])
+        if verified:
+            bufs.pending_buf[0:1].copy_(src[n - 1:n])
+        else:
+            bufs.pending_buf[:n].copy_(src[:n])
+
     # -- draft replay: materialises the pending rows, proposes D tokens
     def draft_step(self, n_pend: int, role: str) -> CapturedGraph:
         atlas, bufs, D = self.atlas, self.bufs, self.D
@@ -263,6 +291,18 @@ class _Session:
         P = M - D
         self.ensure_room()
         g = atlas.get_graph(M, self.sigma, role)
+        d = self._deferred
+        if (d is not None and g.tokens_buf.is_cuda and self._device_ids(d[0]) and 1 <= n_pend <= P
+                and n_pend == (1 if d[2] else d[1])):
+            # the previous step's commit and this replay's inputs in one launch
+            self._deferred = None
+            atlas.stage_draft_after_commit(g, d[0], d[1], d[2], bufs.gen_buf[d[3]:], bufs.pending_buf,
+                                           self.cache_len, D, self.MASK)
+            g.cuda_graph.replay()
+            atlas.commit_kv(g, self.cache_len, n_pend)
+            self.cache_len += n_pend
+            return g
+        self.flush_commit()
         if g.tokens_buf.is_cuda and 1 <= n_pend <= P:
             atlas.stage_draft(g, bufs.pending_buf, n_pend, self.cache_len, D, self.MASK)
             g.cuda_graph.replay()
@@ -496,24 +536,20 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
         verifier_bonus_total += bonus_emitted
 
         if n_commit > 0:
-            bufs.gen_buf[gen_count:gen_count + n_commit].copy_(commit_src[:n_commit])
+            # ids -> output buffer; pending rows := the bonus token after a verified step (its rows were
+            # promoted), or the whole committed block after a confidence commit (recomputed as pending next
+            # time).  Written by the next draft replay's staging launch, or by the flush below.
+            ses.defer_commit(commit_src, n_commit, use_verify, gen_count)
             gen_count += n_commit
         elif policy != "spec":
             eos_found = True
         if eos_found or gen_count >= max_gen_len or n_commit <= 0:
             break
-
-        if use_verify:
-            # verified rows were promoted; only the bonus token is pending
-            bufs.pending_buf[0:1].copy_(commit_src[n_commit - 1:n_commit])
-            n_pend = 1
-        else:
-            # confidence commit: the committed block is recomputed as pending next time
-            bufs.pending_buf[:n_commit].copy_(commit_src[:n_commit])
-            n_pend = n_commit
+        n_pend = 1 if use_verify else n_commit
         if ses.out_of_room(n_pend):
             break
 
+    ses.flush_commit()
     torch.cuda.synchronize()
     decode_time = max(time.time() - t1, 1e-9)
     out = bufs.gen_buf[:gen_count].clone()

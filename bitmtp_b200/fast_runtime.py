@@ -221,6 +221,15 @@ class GraphAtlas:
         ops.stage_replay_inputs(0, pending, None, n_pend, cache_len, graph.M, D, mask_id, _ROLE_ID[graph.role],
                                 graph.P, graph.tokens_buf, graph.positions_buf, graph.attn_mask)
 
+    def stage_draft_after_commit(self, graph: CapturedGraph, src: torch.Tensor, n_commit: int, verified: bool,
+                                 gen_dst: torch.Tensor, pending: torch.Tensor, cache_len: int, D: int,
+                                 mask_id: int) -> None:
+        """The previous step's commit (ids -> output buffer and pending rows) and this draft replay's inputs in
+        one launch."""
+        ops.commit_stage_draft(src, n_commit, verified, gen_dst, pending,
+                               stage=(cache_len, graph.M, D, mask_id, _ROLE_ID[graph.role], graph.P,
+                                      graph.tokens_buf, graph.positions_buf, graph.attn_mask))
+
     def stage_verify(self, graph: CapturedGraph, pending: torch.Tensor, n_pend: int, draft_tokens: torch.Tensor,
                      cache_len: int, D: int) -> None:
         if cache_len <= 0:

@@ -135,6 +135,7 @@ def _declare_optional(L) -> None:
         "bm_argmax_rows_split": [vp, ci, ci, ci, vp, vp, vp, vp],
         "bm_draft_chain_split": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp, vp],
         "bm_logit_scratch_bytes": [],
+        "bm_commit_stage_draft": [vp, ci, ci, vp, vp, ci, ci, ci, ci, ctypes.c_longlong, ci, ci, vp, vp, vp, vp],
     }
     for name, args in protos.items():
         fn = getattr(L, name)

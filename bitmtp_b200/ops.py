@@ -331,6 +331,21 @@ def stage_replay_inputs(kind: int, src_a: torch.Tensor, src_b: Optional[torch.Te
     check(rc, "bm_stage_replay_inputs")
 
 
+def commit_stage_draft(src: torch.Tensor, n_commit: int, verified: bool, gen_dst: torch.Tensor, pending: torch.Tensor,
+                       *, stage=None) -> None:
+    """Committed ids -> output buffer and pending rows, and (with `stage` = (cache_len, M, D, mask_id, role, P,
+    tok, pos, state)) the next draft replay's inputs, in one launch (bm_commit_stage_draft)."""
+    if stage is None:
+        rc = native.lib().bm_commit_stage_draft(_ptr(src), int(n_commit), int(verified), _ptr(gen_dst), _ptr(pending),
+                                                0, 0, 1, 0, 0, 0, 1, None, None, None, _stream(src.device))
+    else:
+        cache_len, M, D, mask_id, role, P, tok, pos, state = stage
+        rc = native.lib().bm_commit_stage_draft(_ptr(src), int(n_commit), int(verified), _ptr(gen_dst), _ptr(pending),
+                                                1, int(cache_len), int(M), int(D), int(mask_id), int(role), int(P),
+                                                _ptr(tok), _ptr(pos), _ptr(state), _stream(src.device))
+    check(rc, "bm_commit_stage_draft")
+
+
 def gemv_row_fused(src_mode: int, x: torch.Tensor, w: torch.Tensor, ws: torch.Tensor, *, out: torch.Tensor,
                    gather: Optional[torch.Tensor] = None, res: Optional[torch.Tensor] = None,
                    norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, h_out: Optional[torch.Tensor] = None,

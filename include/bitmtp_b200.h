@@ -221,6 +221,15 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
 int bm_stage_replay_inputs(int kind, const void *src_a, const void *src_b, int n_pend, int cache_len, int M, int D,
                            long long mask_id, int role, int P, void *tok, void *pos, void *state, void *stream);
 
+/* End of one decode step and start of the next in one launch: gen_dst[0..n_commit) = src[0..n_commit) (the
+ * committed ids into the output buffer); pending[0..n_commit) = the same ids after a confidence commit
+ * (verified == 0), pending[0] = src[n_commit-1] after a verified step; then, if stage != 0, the draft inputs of
+ * width M = P + D are staged from the pending ids as bm_stage_replay_inputs kind 0 does (n_pend = n_commit or 1).
+ * Replaces the copies of src/bonsai_sft/gpu/fast_generate.py:1121-1140 and the fills of :1015-1037. */
+int bm_commit_stage_draft(const void *src, int n_commit, int verified, void *gen_dst, void *pending, int stage,
+                          int cache_len, int M, int D, long long mask_id, int role, int P, void *tok, void *pos,
+                          void *state, void *stream);
+
 /* Width-1 GEMV that makes its own INT8 activations from a bf16 row, for the AR replay (one launch per
  * projection instead of two): every CTA quantises the row itself.
  *   src_mode 1: x bf16 [K] with the bits of its absmax in amax_in[0] (as left by

@@ -467,3 +467,39 @@ def test_split_logit_reductions_equal_the_single_cta_kernels(rows, vocab, ld):
     torch.cuda.synchronize()
     assert native.lib().bm_device_error() == 0
     assert int(scratch[: 4 * 65].view(torch.int32).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M,D,n_commit,verified,cache_len", [(16, 8, 8, False, 300), (9, 8, 5, True, 41), (12, 8, 3, False, 7),
+                                                              (9, 8, 1, False, 64), (5, 4, 1, True, 20), (17, 8, 9, False, 100)])
+def test_commit_and_stage_draft_in_one_launch(M, D, n_commit, verified, cache_len):
+    """bm_commit_stage_draft against the copies of a step's commit followed by bm_stage_replay_inputs kind 0."""
+    MASK, P = 151654, M - D
+    gen = torch.Generator().manual_seed(M * 13 + n_commit)
+    src = torch.randint(0, 150000, (17,), generator=gen, dtype=torch.int64).to(DEV)
+    n_pend = 1 if verified else n_commit
+    # the plain sequence
+    gen_a = torch.full((40,), -1, dtype=torch.int64, device=DEV)
+    pend_a = torch.full((18,), -2, dtype=torch.int64, device=DEV)
+    gen_a[5:5 + n_commit] = src[:n_commit]
+    if verified:
+        pend_a[0:1] = src[n_commit - 1:n_commit]
+    else:
+        pend_a[:n_commit] = src[:n_commit]
+    tok_a, pos_a = torch.full((M,), -1, dtype=torch.int64, device=DEV), torch.full((M,), -1, dtype=torch.int64, device=DEV)
+    st_a = ops.new_step_state(DEV)
+    ops.stage_replay_inputs(0, pend_a, None, n_pend, cache_len, M, D, MASK, native.ROLE_DRAFT, P, tok_a, pos_a, st_a)
+    # one launch
+    gen_b = torch.full((40,), -1, dtype=torch.int64, device=DEV)
+    pend_b = torch.full((18,), -2, dtype=torch.int64, device=DEV)
+    tok_b, pos_b = torch.full((M,), -1, dtype=torch.int64, device=DEV), torch.full((M,), -1, dtype=torch.int64, device=DEV)
+    st_b = ops.new_step_state(DEV)
+    ops.commit_stage_draft(src, n_commit, verified, gen_b[5:], pend_b,
+                           stage=(cache_len, M, D, MASK, native.ROLE_DRAFT, P, tok_b, pos_b, st_b))
+    for name, a, b in (("output ids", gen_a, gen_b), ("pending ids", pend_a, pend_b), ("tokens", tok_a, tok_b),
+                       ("positions", pos_a, pos_b), ("step record", st_a, st_b)):
+        assert torch.equal(a, b), name
+    # commit only
+    gen_c = torch.full((40,), -1, dtype=torch.int64, device=DEV)
+    pend_c = torch.full((18,), -2, dtype=torch.int64, device=DEV)
+    ops.commit_stage_draft(src, n_commit, verified, gen_c[5:], pend_c)
+    assert torch.equal(gen_c, gen_a) and torch.equal(pend_c, pend_a)
