@@ -19,14 +19,17 @@ D8_WIDTHS = (1, 8, 9, 10, 12, 16, 17)
 
 def acceptance_hooks(FG, policy):
     """Replacements for the loops' confidence-chain and prefix-accept reductions that apply
-    a synthetic.AcceptancePolicy.  The kernels still run; their counts are overwritten in
-    place, so they stay part of the record the loop reads in one copy."""
+    a synthetic.AcceptancePolicy.  The kernels still run.  A replaced chain length is handed to the
+    loop as a host value; a replaced accepted-prefix length is written over the kernel's count in
+    place, so that it stays part of the record the loop reads in one copy."""
     chain, accept = FG._fused_draft_chain, FG._fused_verify_accept
 
     def hooked_chain(logits, threshold, out=None):
         idx, n = chain(logits, threshold, out)
         a = policy.chain_count()
-        return idx, (n if a is None else n.fill_(a))
+        # the replacement count is a host value: the loop then reads only the ids from the device (still one
+        # copy), and no extra kernel of the harness runs inside the timed region
+        return idx, (n if a is None else torch.tensor([a], dtype=torch.int64))
 
     def hooked_accept(draft, verify, Dd, out=None):
         n = accept(draft, verify, Dd, out)
