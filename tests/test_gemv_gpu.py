@@ -243,3 +243,20 @@ def test_prepared_activations_on_the_head_shape(oracle):
                              out_kind=native.OUT_F32)
         assert np.array_equal(out.cpu().numpy().view(np.uint32), y32.view(np.uint32))
     assert native.lib().bm_device_error() == 0
+
+
+def test_launch_counter_counts_this_librarys_launches():
+    """bm_launch_count: +1 per GEMV call, +2 for the many-CTA confidence chain (argmax + confidence)."""
+    dev = torch.device("cuda:0")
+    lib = native.lib()
+    case = synthetic.gemv_case(1, 64, 256, seed=3)
+    A, B, ws, s = (case[k].to(dev) for k in ("A", "B", "ws", "s"))
+    before = lib.bm_launch_count()
+    ops.t2_gemv(A, B, s, ws)
+    assert lib.bm_launch_count() - before == 1
+    logits = torch.randn(8, 1000, device=dev)
+    scratch = ops.logit_scratch(dev)
+    before = lib.bm_launch_count()
+    ops.draft_chain(logits, 0.5, scratch=scratch)
+    assert lib.bm_launch_count() - before == 2
+    torch.cuda.synchronize()
