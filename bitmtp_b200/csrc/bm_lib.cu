@@ -204,13 +204,20 @@ bool make_mma_plan(int N, int K, bool half, int sms, int force_rb, MmaPlan *out)
     }
     if (best_rb == 0) {
         // Nothing fits twice per SM (very long K): one CTA per SM with the whole budget.
-        const int tiles = N / 8;
-        const int grid = tiles < sms ? tiles : sms;
-        for (int stages = 2; stages >= 1; --stages) {
-            const bm::MmaSmem L = bm::mma_smem_layout(K, 1, stages, half);
-            if (L.total <= kMaxSmemPerCta) {
-                out->rb = 1; out->stages = stages; out->grid = grid; out->smem = L.total;
-                return true;
+        // 16-row tiles when they give every CTA one tile where 8-row tiles would give some CTAs two
+        // (2048 rows: 128 tiles on 128 SMs instead of 256 on 148).
+        for (int rb = 2; rb >= 1; --rb) {
+            if (force_rb && rb != force_rb && force_rb <= 2) continue;
+            if ((N % (8 * rb)) != 0) continue;
+            const int tiles = N / (8 * rb);
+            if (rb == 2 && !force_rb && !(tiles <= sms && 2 * tiles > sms)) continue;
+            const int grid = tiles < sms ? tiles : sms;
+            for (int stages = 2; stages >= 1; --stages) {
+                const bm::MmaSmem L = bm::mma_smem_layout(K, rb, stages, half);
+                if (L.total <= kMaxSmemPerCta) {
+                    out->rb = rb; out->stages = stages; out->grid = grid; out->smem = L.total;
+                    return true;
+                }
             }
         }
         return false;
