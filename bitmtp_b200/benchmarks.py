@@ -149,7 +149,7 @@ def run_decode(args, world, rank, local, dist):
     D = cfg["block_size"]
     policy = synthetic.AcceptancePolicy(args.accept, D, seed=rank)
     FG._fused_draft_chain, FG._fused_verify_accept = acceptance_hooks(FG, policy)
-    counted = list(atlas.graphs.values()) + list(atlas.prefill_graphs.values())
+    counted = list(atlas.graphs.values()) + list(atlas.prefill_graphs.values()) + list(atlas.dense_graphs.values())
     for g in counted:
         g.cuda_graph = _ReplayCounter(g.cuda_graph)
     fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
@@ -200,6 +200,9 @@ def run_decode(args, world, rank, local, dist):
     replays = {f"{r}:M{M}": g.cuda_graph.replays for (M, _, r), g in sorted(atlas.graphs.items())
                if g.cuda_graph.replays}
     replays["prompt-slab:M16"] = sum(g.cuda_graph.replays for g in atlas.prefill_graphs.values())
+    for (M, _, r), g in sorted(atlas.dense_graphs.items()):
+        if g.cuda_graph.replays:
+            replays[f"{r}:M{M}:3-per-SM attention"] = g.cuda_graph.replays
     roof_m = 16 if args.mode in ("hybrid", "conf") else (1 if args.mode == "ar" else 9)
     rf = _gemv_roofline(model, roof_m, device)
     peak, peak_kind = bench.peaks()

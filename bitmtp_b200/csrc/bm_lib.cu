@@ -833,7 +833,7 @@ int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_b
         rp.v_out = const_cast<uint16_t *>(p.v_base);
         rp.eps = rope->eps;
         // long segments: several waves of chunk CTAs, so trade a slower pass for three CTAs per SM
-        const bool dense = (long long)NC * Hkv * qsplit > 4LL * current_device().sm_count;
+        const bool dense = (pdl & BM_ATTN_DENSE) != 0 || (long long)NC * Hkv * qsplit > 4LL * current_device().sm_count;
 #define BM_ROPE_CASE(NQ_) \
         rc = dense ? launch_ex(bm::attn_chunk_rope_kernel<NQ_, 3>, grid, dim3(threads), smem, st, pdl, rp) \
                    : launch_ex(bm::attn_chunk_rope_kernel<NQ_, 2>, grid, dim3(threads), smem, st, pdl, rp)

@@ -290,7 +290,7 @@ class _Session:
         M = _select_M_for_pending(atlas, n_pend)
         P = M - D
         self.ensure_room()
-        g = atlas.get_graph(M, self.sigma, role)
+        g = atlas.get_graph(M, self.sigma, role, self.cache_len)
         d = self._deferred
         if (d is not None and g.tokens_buf.is_cuda and self._device_ids(d[0]) and 1 <= n_pend <= P
                 and n_pend == (1 if d[2] else d[1])):
@@ -328,7 +328,7 @@ class _Session:
     # -- width-(D+1) verifier inputs and replay
     def stage_verify(self, n_pend: int, draft_tokens: torch.Tensor, role: str) -> CapturedGraph:
         atlas, bufs, D = self.atlas, self.bufs, self.D
-        gv = atlas.get_graph(D + 1, self.sigma, role)
+        gv = atlas.get_graph(D + 1, self.sigma, role, self.cache_len)
         if gv.tokens_buf.is_cuda and draft_tokens.dtype == torch.int64 and draft_tokens.is_contiguous():
             atlas.stage_verify(gv, bufs.pending_buf, n_pend, draft_tokens, self.cache_len, D)
             return gv

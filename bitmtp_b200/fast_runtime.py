@@ -18,6 +18,7 @@ What differs from the reference, by design:
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -138,6 +139,7 @@ class GraphAtlas:
                 for role in self.roles:
                     if role != "ar":
                         self.graphs[(M, sigma, role)] = self._capture_one(M, sigma, role)
+        self._capture_dense_twins()
         # Prompt slabs: one AR-causal graph of PREFILL_CHUNK rows per segment, layers only (the one
         # logit row a prompt needs is taken afterwards).  Kept apart from `graphs`, whose key set
         # mirrors the reference's.  Needs workspace rows for a whole slab.
@@ -200,8 +202,44 @@ class GraphAtlas:
                 return sigma
         return self.segment_ladder[-1]
 
-    def get_graph(self, M: int, sigma: int, role: str) -> CapturedGraph:
+    def get_graph(self, M: int, sigma: int, role: str, cache_len: Optional[int] = None) -> CapturedGraph:
+        """The graph of (M, sigma, role).  With `cache_len`, the twin captured with the attention chunk kernel
+        built for three CTAs per SM where that history length makes it the faster one (same results)."""
+        if cache_len is not None:
+            twin = getattr(self, "dense_graphs", {}).get((M, sigma, role))
+            if twin is not None and self._prefer_dense(M, cache_len):
+                return twin
         return self.graphs[(M, sigma, role)]
+
+    def _chunk_ctas(self, M: int, rows: int) -> int:
+        """CTAs of the attention chunk kernel that have work with `rows` history rows."""
+        qv = (self.args.n_heads // self.n_kv) * M
+        return ((rows + 31) // 32 + 1) * self.n_kv * (2 if qv >= 16 else 1)
+
+    def _prefer_dense(self, M: int, cache_len: int) -> bool:
+        """A chunk's pass is ~1.2x slower in the three-per-SM build; it wins when it saves a wave of CTAs
+        (measured at width 16: 1406 -> 1336 us per replay with 368 CTAs, 1245 -> 1286 us with 176)."""
+        items, sms = self._chunk_ctas(M, cache_len), self._sm_count
+        waves2, waves3 = -(-items // (2 * sms)), -(-items // (3 * sms))
+        return waves2 > 1.2 * waves3
+
+    def _capture_dense_twins(self) -> None:
+        """Twins of the wide graphs for history lengths between the one-wave regime and the segment sizes for
+        which the kernel picks the three-per-SM build by itself."""
+        self.dense_graphs: Dict[Tuple[int, int, str], CapturedGraph] = {}
+        self._sm_count = int(native.lib().bm_sm_count())
+        if os.environ.get("BM_DENSE_TWINS", "1") == "0":
+            return
+        for (M, sigma, role) in list(self.graphs):
+            if M == 1 or self._chunk_ctas(M, sigma) > 4 * self._sm_count:      # already dense by itself
+                continue
+            if not any(self._prefer_dense(M, c) for c in range(32, sigma + 1, 32)):
+                continue
+            self.model.attn_dense = True
+            try:
+                self.dense_graphs[(M, sigma, role)] = self._capture_one(M, sigma, role)
+            finally:
+                self.model.attn_dense = False
 
     # ------------------------------------------------------------------ per-step API
     def prepare_step(self, graph: CapturedGraph, cache_len: int, n_pend: int,

@@ -358,6 +358,9 @@ class Transformer(nn.Module):
         # slower on B200 (one 8-warp CTA per SM hides less latency than several resident CTAs of
         # the stand-alone kernels), so it is opt-in: BM_SWEEP=1.
         self.use_sweep = os.environ.get("BM_SWEEP", "0") == "1"
+        # attention chunk kernel built for three CTAs per SM; the atlas sets it while it captures the graphs it
+        # replays at cache lengths whose chunk grid needs more than one wave of the two-per-SM build
+        self.attn_dense = False
         # SiLU(gate) * up inside the gate|up GEMV + a flat quantisation kernel instead of GEMV + one SiLU
         # CTA per row (BM_FUSED_FFN=0 restores the latter)
         self.fused_ffn = os.environ.get("BM_FUSED_FFN", "1") != "0"
@@ -608,6 +611,8 @@ class Transformer(nn.Module):
         W = self.workspace(M)
         pdl = self.use_pdl
         attn_pdl = (native.PDL_OVERLAP | native.PDL_STABLE_STATE) if (pdl and stable_state) else int(pdl)
+        if self.attn_dense:
+            attn_pdl |= native.ATTN_DENSE
         k0 = kv_full[0][0]
         kv_rows = k0.stride(-3) // a.head_dim
         sigma = k0.shape[-2] - M

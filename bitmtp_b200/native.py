@@ -34,7 +34,7 @@ STATIC_ATTN_SCRATCH_BYTES = 8 << 20     # BM_STATIC_ATTN_SCRATCH_BYTES of the he
 OUT_BF16, OUT_F32, OUT_F32_OF_BF16 = 0, 1, 2
 PATH_AUTO, PATH_DP4A, PATH_MMA, PATH_ROWWARP, PATH_DIRECT = 0, 1, 2, 3, 4
 ROLE_DRAFT, ROLE_VERIFY, ROLE_AR = 0, 1, 2
-PDL_OVERLAP, PDL_STABLE_STATE, PDL_STAGED = 1, 2, 4
+PDL_OVERLAP, PDL_STABLE_STATE, PDL_STAGED, ATTN_DENSE = 1, 2, 4, 16
 
 _lib = None
 

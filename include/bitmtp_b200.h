@@ -39,6 +39,8 @@ extern "C" {
 #define BM_PDL_OVERLAP 1
 #define BM_PDL_STABLE_STATE 2
 #define BM_PDL_STAGED 4        /* bm_t2_gemv_row_fused only: use the shared-memory-staged kernel at every size */
+#define BM_ATTN_DENSE 16       /* bm_rope_verify_attention(_rows) only: the chunk kernel built for three CTAs per SM
+                                  (slower per chunk, more chunks at once); chosen by itself for long segments */
 
 #define BM_PATH_AUTO 0
 #define BM_PATH_DP4A 1
