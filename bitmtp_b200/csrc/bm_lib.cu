@@ -16,7 +16,6 @@
 #include "verify_attn.cuh"
 #include "t2_gemv_rowwarp.cuh"
 #include "t2_gemv_direct.cuh"
-#include "decode_sweep.cuh"
 
 #include <cudaTypedefs.h>
 #include <map>
@@ -316,25 +315,22 @@ int weight_tensor_map(const void *B, int N, int K, CUtensorMap *out) {
     return BM_OK;
 }
 
-// Warps per CTA and panels per stage of the row-per-warp kernel.  `force` (tuning aid) packs
-// warps in bits 0..4 and log2(panels per stage) + 1 in bits 5..6; 0 = defaults.
+// Warps per CTA and panels per stage of the row-per-warp kernel.
 struct RowWarpCfg { int warps, pb; };
 
-inline RowWarpCfg rowwarp_cfg(int W, int K, int force) {
+inline RowWarpCfg rowwarp_cfg(int W, int K) {
     RowWarpCfg c;
-    const int pcode = (force >> 5) & 3;
-    c.pb = pcode == 1 ? 1 : (pcode == 2 ? 2 : (pcode == 3 ? 4 : 2));
-    int warps = force & 31;
-    if (warps < 1 || warps > bm::kRwMaxWarps) warps = bm::kRwMaxWarps;
+    c.pb = 2;
+    int warps = bm::kRwMaxWarps;
     // keep at least two stages per warp
     while (warps > 4 && bm::rowwarp_smem_layout(W, K, warps, c.pb).stages < 2) --warps;
     c.warps = warps;
     return c;
 }
 
-bool rowwarp_fits(int W, int N, int K, int force = 0) {
+bool rowwarp_fits(int W, int N, int K) {
     if (W > 8 || (K % 512) != 0 || (N % bm::kRwRows) != 0) return false;
-    const RowWarpCfg c = rowwarp_cfg(W, K, force);
+    const RowWarpCfg c = rowwarp_cfg(W, K);
     return bm::rowwarp_smem_layout(W, K, c.warps, c.pb).stages >= 2;
 }
 
@@ -350,22 +346,16 @@ int launch_rowwarp(const bm::RowWarpParams &P, int warps, int sms, int pdl, cuda
     return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, false>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
 }
 
-int gemv_launch_rowwarp(const bm::GemvParams &p0, int sms, int pdl, int force, cudaStream_t stream) {
-    if (!rowwarp_fits(p0.W, p0.N, p0.K, force)) return BM_EINVAL;
+int gemv_launch_rowwarp(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
+    if (!rowwarp_fits(p0.W, p0.N, p0.K)) return BM_EINVAL;
     bm::RowWarpParams P;
     const int rc = weight_tensor_map(p0.B, p0.N, p0.K, &P.tmap);
     if (rc != BM_OK) return rc;
     P.g = p0;
     P.g.pdl = pdl;
-    const RowWarpCfg c = rowwarp_cfg(p0.W, p0.K, force);
-    if (p0.W == 1) {
-        if (c.pb == 1) return launch_rowwarp<1, 1>(P, c.warps, sms, pdl, stream);
-        if (c.pb == 2) return launch_rowwarp<1, 2>(P, c.warps, sms, pdl, stream);
-        return launch_rowwarp<1, 4>(P, c.warps, sms, pdl, stream);
-    }
-    if (c.pb == 1) return launch_rowwarp<2, 1>(P, c.warps, sms, pdl, stream);
-    if (c.pb == 2) return launch_rowwarp<2, 2>(P, c.warps, sms, pdl, stream);
-    return launch_rowwarp<2, 4>(P, c.warps, sms, pdl, stream);
+    const RowWarpCfg c = rowwarp_cfg(p0.W, p0.K);
+    if (p0.W == 1) return launch_rowwarp<1, 2>(P, c.warps, sms, pdl, stream);
+    return launch_rowwarp<2, 2>(P, c.warps, sms, pdl, stream);
 }
 
 }  // namespace
@@ -400,7 +390,8 @@ struct PeerArgs {
     void *const *peer_C0;      // first output buffer of every rank
     void *const *peer_C1;      // second output buffer of every rank
     void *const *peer_flags;
-    void *done;                // uint32 [2]
+    void *done;                // uint32 [4]
+    unsigned int poll_limit;   // 0: default
 };
 
 static int gemv_common(const void *A, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
@@ -445,6 +436,7 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     p.src_mode = 0;
     p.xb = p.res = p.norm_w = nullptr;
     p.gather = nullptr;
+    p.gather_rows = 0;
     p.h_out = nullptr;
     p.eps = 0.0f;
     p.amax_in = nullptr;
@@ -452,6 +444,7 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
+    p.poll_limit = 0;
     for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
     if (peer != nullptr && peer->world > 1) {
         if (peer->world > 8 || peer->rank < 0 || peer->rank >= peer->world || out_kind != BM_OUT_BF16 || G_out != nullptr ||
@@ -460,6 +453,7 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
         p.world = peer->world;
         p.rank = peer->rank;
         p.done = static_cast<unsigned int *>(peer->done);
+        p.poll_limit = peer->poll_limit ? peer->poll_limit : (1u << 22);
         for (int i = 0; i < peer->world; ++i) {
             if (!peer->peer_C0[i] || !peer->peer_C1[i] || !peer->peer_flags[i]) return BM_EINVAL;
             p.peer_C[0][i] = static_cast<uint16_t *>(peer->peer_C0[i]);
@@ -471,8 +465,8 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The MMA consumer needs an even number of groups (K % 256 == 0); every model shape
     // has it.  Odd group counts go to the lanes-across-K consumer.
-    const int force_rb = (path >> 8) & 0xff;          // tuning aid: BM_PATH_MMA | (rows_per_tile/8 << 8)
-    path &= 0xff;
+    if (path < BM_PATH_AUTO || path > BM_PATH_DIRECT) return BM_EINVAL;
+    const int force_rb = 0;                           // tile height chosen by make_mma_plan
     if (path == BM_PATH_AUTO) {
         // Many rows and at most 8 tokens: every warp streams its own rows.  With fewer than about
         // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner
@@ -487,7 +481,7 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
         else path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     }
     if (path == BM_PATH_DIRECT) return gemv_launch_direct(p, pdl, st);
-    if (path == BM_PATH_ROWWARP) return gemv_launch_rowwarp(p, sms, pdl, force_rb, st);
+    if (path == BM_PATH_ROWWARP) return gemv_launch_rowwarp(p, sms, pdl, st);
     if (path == BM_PATH_DP4A) return gemv_launch_dp4a(p, sms, pdl, st);
     if (path == BM_PATH_MMA) return (K % 256) == 0 ? gemv_launch_mma(p, sms, pdl, force_rb, st) : BM_EINVAL;
     return BM_EINVAL;
@@ -509,16 +503,18 @@ int bm_quant_rows(const void *x, int M, int K, void *q, void *q_prep, void *asum
                      static_cast<const uint16_t *>(x), K, sink, static_cast<float *>(s), pdl);
 }
 
-int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps, int M,
-                     int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s, void *n_out,
+int bm_rmsnorm_fused(const void *x, const void *gather, int gather_rows, const void *res, const void *w, float eps,
+                     int M, int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s, void *n_out,
                      int pdl, void *stream) {
     if (!x || !w || M < 1 || dim < 256 || (dim % 256) != 0 || dim > 8192) return BM_EINVAL;
+    if (gather && gather_rows < 1) return BM_EINVAL;
     if (((q != nullptr) || (q_prep != nullptr)) != (s != nullptr)) return BM_EINVAL;
     if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
     if (!aligned16(x) || !aligned16(w) || (res && !aligned16(res))) return BM_EINVAL;
     bm::NormParams p;
     p.x = static_cast<const uint16_t *>(x);
     p.gather = static_cast<const int64_t *>(gather);
+    p.gather_rows = gather_rows;
     p.res = static_cast<const uint16_t *>(res);
     p.w = static_cast<const uint16_t *>(w);
     p.h_out = static_cast<uint16_t *>(h_out);
@@ -556,6 +552,7 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
     p.src_mode = 0;
     p.xb = p.res = p.norm_w = nullptr;
     p.gather = nullptr;
+    p.gather_rows = 0;
     p.h_out = nullptr;
     p.eps = 0.0f;
     p.amax_in = nullptr;
@@ -563,6 +560,7 @@ int bm_t2_gemv_gate_up_silu(const void *A_prep, const void *a_sums, const void *
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
+    p.poll_limit = 0;
     for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
     const int sms = current_device().sm_count;
     const bool half = W <= 8, one = K == 2048;
@@ -613,7 +611,8 @@ int bm_commit_stage_draft(const void *src, int n_commit, int verified, void *gen
     return cuda_status(cudaGetLastError());
 }
 
-int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const void *res, const void *norm_w, float eps,
+int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, int gather_rows, const void *res,
+                         const void *norm_w, float eps,
                          void *h_out, const void *amax_in, void *amax_zero, const void *B, const void *ws, int N, int K,
                          void *C, int ldc, int out_kind, int silu, void *amax_out, int pdl, void *stream) {
     if ((src_mode != 1 && src_mode != 2) || !x || !B || !ws || !C || N < 8 || (N % 8) != 0 || (K % 256) != 0 || K < 256)
@@ -621,6 +620,7 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
     const bool staged = (pdl & BM_PDL_STAGED) != 0;     // testing aid: keep to the shared-memory-staged kernel
     pdl &= BM_PDL_OVERLAP;
     if (src_mode == 1 && !amax_in) return BM_EINVAL;
+    if (gather && gather_rows < 1) return BM_EINVAL;
     if (src_mode == 2 && (!norm_w || K != 8 * bm::kGemvThreads)) return BM_EINVAL;
     if (silu && (!amax_out || out_kind != BM_OUT_BF16 || (N % 16) != 0)) return BM_EINVAL;
     if (ldc < N || (ldc % 4) != 0 || out_kind < 0 || out_kind > 2) return BM_EINVAL;
@@ -648,6 +648,7 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
     p.res = static_cast<const uint16_t *>(res);
     p.norm_w = static_cast<const uint16_t *>(norm_w);
     p.gather = static_cast<const int64_t *>(gather);
+    p.gather_rows = gather_rows;
     p.h_out = static_cast<uint16_t *>(h_out);
     p.eps = eps;
     p.amax_in = static_cast<const unsigned int *>(amax_in);
@@ -655,6 +656,7 @@ int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const 
     p.world = 0;
     p.rank = 0;
     p.done = nullptr;
+    p.poll_limit = 0;
     for (int i = 0; i < 8; ++i) { p.peer_C[0][i] = p.peer_C[1][i] = nullptr; p.peer_flags[i] = nullptr; }
     const int sms = current_device().sm_count;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -952,7 +954,8 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
 // ---------------------------------------------------------------------------- N-split GEMV
 int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *ws, int W, int N_shard, int K, int ldc,
                       int col0, int world, int rank, void *const *peer_C0, void *const *peer_C1,
-                      void *const *peer_flags, void *state, int pdl, void *stream) {
+                      void *const *peer_flags, void *state, int poll_limit, int pdl, void *stream) {
+    if (poll_limit < 0) return BM_EINVAL;
     if (world < 2 || world > 8 || rank < 0 || rank >= world || col0 < 0 || (col0 % 8) != 0 || col0 + N_shard > ldc ||
         !peer_C0 || !peer_C1 || !peer_flags || !state)
         return BM_EINVAL;
@@ -963,82 +966,9 @@ int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *w
         s0[i] = static_cast<uint16_t *>(peer_C0[i]) + col0;
         s1[i] = static_cast<uint16_t *>(peer_C1[i]) + col0;
     }
-    PeerArgs peer{world, rank, s0, s1, peer_flags, state};
+    PeerArgs peer{world, rank, s0, s1, peer_flags, state, (unsigned int)poll_limit};
     return gemv_common(A, nullptr, B, s0[rank], s, ws, W, N_shard, K, ldc, BM_OUT_BF16, BM_PATH_AUTO, nullptr, pdl,
                        stream, &peer);
-}
-
-// ---------------------------------------------------------------------------- layer sweep
-int bm_decode_sweep(const bm_sweep_args *a, void *stream) {
-    if (!a || !a->layers || !a->tokens || !a->positions || !a->embed || !a->cos_t || !a->sin_t || !a->state ||
-        !a->attn_scratch || !a->h || !a->xq || !a->xsum || !a->xs || !a->xqkv || !a->attq || !a->attsum ||
-        !a->atts || !a->attn_out || !a->inner || !a->inner_amax || !a->iq || !a->isum || !a->is_ ||
-        !a->ffn_out || !a->barrier)
-        return BM_EINVAL;
-    if (a->n_layers < 1 || a->M < 1 || a->M > 16 || a->dim != 2048 || a->H * 128 != 2048 || a->ffn != 6144 ||
-        a->Hkv < 1 || (a->H % a->Hkv) != 0 || a->sigma < 0 || a->kv_rows < a->sigma + a->M)
-        return BM_EINVAL;
-    bm::SweepParams p;
-    p.layers = static_cast<const bm::SweepLayer *>(a->layers);
-    p.n_layers = a->n_layers; p.M = a->M; p.dim = a->dim; p.H = a->H; p.Hkv = a->Hkv; p.ffn = a->ffn;
-    p.kv_rows = a->kv_rows; p.sigma = a->sigma;
-    p.NC = (a->sigma + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK + 1;
-    p.eps = a->eps;
-    p.tokens = static_cast<const int64_t *>(a->tokens);
-    p.positions = static_cast<const int64_t *>(a->positions);
-    p.embed = static_cast<const uint16_t *>(a->embed);
-    p.cos_t = static_cast<const uint16_t *>(a->cos_t);
-    p.sin_t = static_cast<const uint16_t *>(a->sin_t);
-    p.state = static_cast<const bm::StepState *>(a->state);
-    p.h = static_cast<uint16_t *>(a->h);
-    p.xq = static_cast<int8_t *>(a->xq);
-    p.xsum = static_cast<int32_t *>(a->xsum);
-    p.xs = static_cast<float *>(a->xs);
-    p.xqkv = static_cast<uint16_t *>(a->xqkv);
-    char *sc = static_cast<char *>(a->attn_scratch);
-    p.pm = reinterpret_cast<float *>(sc + 256);
-    p.pl = p.pm + (size_t)a->M * a->H * p.NC;
-    p.po = p.pl + (size_t)a->M * a->H * p.NC;
-    p.attq = static_cast<int8_t *>(a->attq);
-    p.attsum = static_cast<int32_t *>(a->attsum);
-    p.atts = static_cast<float *>(a->atts);
-    p.attn_out = static_cast<uint16_t *>(a->attn_out);
-    p.inner = static_cast<uint16_t *>(a->inner);
-    p.inner_amax = static_cast<unsigned int *>(a->inner_amax);
-    p.iq = static_cast<int8_t *>(a->iq);
-    p.isum = static_cast<int32_t *>(a->isum);
-    p.is_ = static_cast<float *>(a->is_);
-    p.ffn_out = static_cast<uint16_t *>(a->ffn_out);
-    p.bar = static_cast<unsigned int *>(a->barrier);
-    p.timing = static_cast<unsigned long long *>(a->timing);
-    const int G = a->H / a->Hkv, QV = G * a->M;
-    size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;   // attention
-    const size_t merge = (size_t)a->H * 128 * 2 + (size_t)a->H * p.NC * sizeof(float);
-    const size_t gemv = (size_t)bm::kGemvWarps * 16 * 40 * sizeof(float);
-    if (merge > smem) smem = merge;
-    if (gemv > smem) smem = gemv;
-    if (smem > 200 * 1024) return BM_EINVAL;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e = cudaFuncSetAttribute(bm::decode_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_status(e);
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bm::decode_sweep_kernel, bm::kSweepThreads, smem);
-    if (e != cudaSuccess) return cuda_status(e);
-    if (per_sm < 1) return BM_EINVAL;
-    e = cudaMemsetAsync(a->barrier, 0, 8, st);
-    if (e != cudaSuccess) return cuda_status(e);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(current_device().sm_count);
-    cfg.blockDim = dim3(bm::kSweepThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once: the barrier needs it
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    count_launch();
-    return cuda_status(cudaLaunchKernelEx(&cfg, bm::decode_sweep_kernel, p));
 }
 
 // ---------------------------------------------------------- attention without allocation

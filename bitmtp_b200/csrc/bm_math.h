@@ -150,6 +150,17 @@ BM_HD float bm_silu_bf16(float x) {
     return bm_bf16_rn(x / (1.0f + bm_expf(-x)));
 }
 
+// Row argmax comparison: does candidate (f at index v) beat the current best (best at index bi)?
+// A NaN counts as the largest value and the lowest index wins among equals, which is what
+// torch.argmax returns (fast_generate.py:786, 809, 1079 call it on the logit rows).  With this rule
+// a row always yields an index inside the row, whatever it holds, so an id that stays on the device
+// and feeds the next replay's embedding gather can never point outside the table.
+BM_HD int bm_argmax_better(float f, int v, float best, int bi) {
+    const int fn = f != f, bn = best != best;
+    if (fn != bn) return fn;
+    return f > best || ((fn || f == best) && v < bi);
+}
+
 // Position of element k (0..15 within a 16-element run) after the 4x4 byte
 // transpose the GEMV kernels apply to activations so that one dp4a / MMA
 // register lines up with the codes `(word >> 2i) & 0x03030303` extracts:

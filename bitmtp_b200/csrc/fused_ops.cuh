@@ -187,9 +187,16 @@ __global__ void __launch_bounds__(kQuantAmaxThreads) quant_rows_amax_kernel(
 // elements 8t..8t+7, which is exactly the lane-partial of the oracle's
 // sum-of-squares order; warps are its 256-element chunks.
 // =============================================================================
+// Row of a gathered table, kept inside the table whatever the id is (a corrupt id then reads a valid
+// row instead of memory far outside the allocation).
+__device__ __forceinline__ size_t gather_row(int64_t id, int rows) {
+    return (size_t)(id < 0 ? 0 : (id >= rows ? rows - 1 : id));
+}
+
 struct NormParams {
     const uint16_t *x;
     const int64_t *gather;
+    int gather_rows;   // rows of x when `gather` is given: indices are clamped to [0, gather_rows)
     const uint16_t *res;
     const uint16_t *w;
     uint16_t *h_out;
@@ -210,7 +217,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const NormParams p) {
     // the norm weights do not depend on the previous kernel: requested before the wait, used after the sum
     const uint4 wraw = reinterpret_cast<const uint4 *>(p.w)[t];
     if (p.pdl) pdl_wait();
-    const size_t src_row = p.gather ? (size_t)p.gather[m] : (size_t)(p.row0 + m);
+    const size_t src_row = p.gather ? gather_row(p.gather[m], p.gather_rows) : (size_t)(p.row0 + m);
     float h[8];
     unpack8(reinterpret_cast<const uint4 *>(p.x + src_row * p.dim)[t], h);
     if (p.res) {
@@ -475,19 +482,19 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *__restri
     int bi = 0x7fffffff;
     for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
         const float f = x[v];
-        if (f > best || (f == best && v < bi)) { best = f; bi = v; }
+        if (bm_argmax_better(f, v, best, bi)) { best = f; bi = v; }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, off);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        if (bm_argmax_better(ob, oi, best, bi)) { best = ob; bi = oi; }
     }
     if (lane == 0) { sv[warp] = best; si[warp] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+            if (bm_argmax_better(sv[w], si[w], best, bi)) { best = sv[w]; bi = si[w]; }
         idx[r] = bi;
         if (max_out) max_out[r] = best;
     }
@@ -589,19 +596,19 @@ __global__ void __launch_bounds__(256) argmax_split_kernel(const float *__restri
     int bi = 0x7fffffff;
     for (int v = v_lo + threadIdx.x; v < v_hi; v += 256) {
         const float f = x[v];
-        if (f > best || (f == best && v < bi)) { best = f; bi = v; }
+        if (bm_argmax_better(f, v, best, bi)) { best = f; bi = v; }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, off);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        if (bm_argmax_better(ob, oi, best, bi)) { best = ob; bi = oi; }
     }
     if (lane == 0) { sv[warp] = best; si[warp] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w)
-            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+            if (bm_argmax_better(sv[w], si[w], best, bi)) { best = sv[w]; bi = si[w]; }
         sc->part_max[r * S + split] = best;
         sc->part_idx[r * S + split] = bi;
         __threadfence();
@@ -616,7 +623,7 @@ __global__ void __launch_bounds__(256) argmax_split_kernel(const float *__restri
     for (int s = 0; s < S; ++s) {
         const float f = __ldcg(&sc->part_max[r * S + s]);
         const int i = __ldcg(&sc->part_idx[r * S + s]);
-        if (f > best || (f == best && i < bi)) { best = f; bi = i; }
+        if (bm_argmax_better(f, i, best, bi)) { best = f; bi = i; }
     }
     idx[r] = bi;
     if (max_out) max_out[r] = best;

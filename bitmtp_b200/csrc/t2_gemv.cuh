@@ -78,6 +78,7 @@ struct GemvParams {
     int src_mode;
     const uint16_t *xb, *res, *norm_w;
     const int64_t *gather;
+    int gather_rows;        // rows of xb when `gather` is given (the id is clamped into the table)
     uint16_t *h_out;
     float eps;
     const unsigned int *amax_in;
@@ -90,7 +91,9 @@ struct GemvParams {
     unsigned int *peer_flags[8];    // flag arrays [world] of the ranks; [rank] = the local one
     unsigned int *done;             // local: [0] counter of finished CTAs (zero between launches),
                                     //        [1] number of completed calls (the epoch; device-resident so
-                                    //        that a captured graph can be replayed)
+                                    //        that a captured graph can be replayed),
+                                    //        [2] epoch of the last call whose wait for a peer ran out (0: none)
+    unsigned int poll_limit;        // polls of one peer's flag before the wait is given up
 };
 
 struct GemvSmem {
@@ -229,7 +232,13 @@ __device__ __forceinline__ void gemv_peer_finish(const GemvParams &p) {
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
             if ((int)(v - epoch) >= 0) break;
-            if (++spins > (1u << 22)) { report_error(kErrPeerWaitTimeout); break; }
+            if (++spins > p.poll_limit) {
+                // give up: the caller finds the call number in done[2] (the output then holds stale
+                // columns of that peer) and the device error word says why
+                report_error(kErrPeerWaitTimeout);
+                p.done[2] = epoch;
+                break;
+            }
             __nanosleep(100);
         }
     }
@@ -397,7 +406,7 @@ __device__ __forceinline__ void gemv_stage_row_from_bf16(const GemvParams &p, un
     float s;
     if (p.src_mode == 2) {
         const uint4 wraw = reinterpret_cast<const uint4 *>(p.norm_w)[t];
-        const size_t src_row = p.gather ? (size_t)p.gather[0] : 0;
+        const size_t src_row = p.gather ? gather_row(p.gather[0], p.gather_rows) : 0;
         float h[8];
         unpack8(reinterpret_cast<const uint4 *>(p.xb + src_row * p.K)[t], h);
         if (p.res) {

@@ -291,7 +291,6 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                 }
                 // IL groups in lock-step: their four-MMA chains are independent of each other,
                 // so consecutive MMAs never wait for the previous one's result.
-#ifndef BM_EXP_NO_COMPUTE
 #pragma unroll
                 for (int j0 = 0; j0 < 4; j0 += IL) {
                     uint2 x[IL], y[IL];
@@ -353,9 +352,6 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                         }
                     }
                 }
-#else
-                if (pp == 0 && lane == 0) acc[0][0] += (float)stage[woff[0]];
-#endif
                 arow += 4 * BM_GROUP;
                 nbp += 4 * 64;
                 G += 4;

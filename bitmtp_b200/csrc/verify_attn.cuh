@@ -56,6 +56,13 @@ __host__ __device__ inline size_t attn_scratch_bytes(int M, int H, int sigma) {
     return 256 + (size_t)M * H * NC * 4 * 2 + (size_t)M * H * NC * 128 * 4;
 }
 
+// History length of this replay.  The record is written by other launches (or by the caller through
+// the C ABI), so it is clamped to [0, sigma] before anything is indexed with it: the scratch, the
+// shared-memory arrays and the K/V planes are all sized from sigma.  Identity for every valid record.
+__device__ __forceinline__ int attn_cache_len(const AttnParams &p) {
+    return min(max(p.state->cache_len, 0), p.sigma);
+}
+
 // ---- kernel 1: one (chunk, kv head); a warp serves NQ query vectors at a time --------
 // lane = key in the score phase (NQ independent fma chains, one per query vector, each in
 // ascending d), lane = 4 output dims in the numerator phase (4*NQ independent chains, each
@@ -221,7 +228,7 @@ __global__ void __launch_bounds__(kAttnThreads, MINB) attn_chunk_rope_kernel(con
     const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
     if (p.pdl && !early) pdl_wait();
     const int j = blockIdx.x, hk = blockIdx.y;
-    const int cache_len = p.state->cache_len, n_pend = p.state->n_pend, role = p.state->role, P_ = p.state->P;
+    const int cache_len = attn_cache_len(p), n_pend = p.state->n_pend, role = p.state->role, P_ = p.state->P;
     const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
     int c0, cn;
     if (j == p.NC - 1) { c0 = p.sigma; cn = p.M; }
@@ -325,7 +332,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnPara
     const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
     if (p.pdl && !early) pdl_wait();
     const int j = blockIdx.x, hk = blockIdx.y;
-    const int cache_len = p.state->cache_len, n_pend = p.state->n_pend, role = p.state->role,
+    const int cache_len = attn_cache_len(p), n_pend = p.state->n_pend, role = p.state->role,
               P = p.state->P;
     const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
     int c0, cn;
@@ -498,7 +505,7 @@ __global__ void __launch_bounds__(256) attn_merge_part_kernel(const AttnParams p
     pdl_launch_dependents();
     const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
     if (p.pdl && !early) pdl_wait();
-    const int cache_len = p.state->cache_len;
+    const int cache_len = attn_cache_len(p);
     if (early) pdl_wait();
     const int m = blockIdx.x, h0 = blockIdx.y * hpc;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x, nwarps = nthr >> 5;
@@ -574,7 +581,7 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const AttnPar
     pdl_launch_dependents();
     const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
     if (p.pdl && !early) pdl_wait();
-    const int cache_len = p.state->cache_len;
+    const int cache_len = attn_cache_len(p);
     if (early) pdl_wait();
     attn_merge_row(p, blockIdx.x, cache_len, dyn, l_s, red);
 }

@@ -328,12 +328,10 @@ class StepWorkspace:
         self.att_sum = buf((M, q_dim // 128), i32)
         self.i_sum = buf((M, args.ffn_dim // 128), i32)
         self.h_sum = buf((M, args.dim // 128), i32)
-        # extra buffers of the persistent layer kernel
         self.inner = buf((M, args.ffn_dim), bf)
         self.inner_amax = torch.zeros((2, M), dtype=i32, device=device)   # row absmax bits, two slots used in turn
         self.att_amax = torch.zeros((2, M), dtype=i32, device=device)
         self.h2 = buf((M, args.dim), bf)            # second residual buffer of the width-1 fused path
-        self.sweep_barrier = torch.zeros((2,), dtype=i32, device=device)
         self.n_pad = n_pad
 
 
@@ -353,11 +351,6 @@ class Transformer(nn.Module):
         # successor start early (GEMVs then request their weight tiles while the predecessor
         # is still running) and waits for its predecessor before touching activations.
         self.use_pdl = os.environ.get("BM_PDL", "1") != "0"
-        # One persistent kernel for the whole layer stack of a replay (bm_decode_sweep), where the
-        # geometry allows it.  Bit-identical to the operator-by-operator launches but measured
-        # slower on B200 (one 8-warp CTA per SM hides less latency than several resident CTAs of
-        # the stand-alone kernels), so it is opt-in: BM_SWEEP=1.
-        self.use_sweep = os.environ.get("BM_SWEEP", "0") == "1"
         # attention chunk kernel built for three CTAs per SM; the atlas sets it while it captures the graphs it
         # replays at cache lengths whose chunk grid needs more than one wave of the two-per-SM build
         self.attn_dense = False
@@ -371,7 +364,6 @@ class Transformer(nn.Module):
         # width-1 replays: RMSNorm / quantisation inside the consuming GEMV, 6 launches per layer instead
         # of 10 (BM_FUSED_AR=0: the general sequence)
         self.fused_ar = os.environ.get("BM_FUSED_AR", "1") != "0"
-        self._sweep_tables = {}
 
     def tie_weights(self) -> None:
         # plain attribute, not a registered parameter: the state dict keeps the reference's keys
@@ -525,44 +517,6 @@ class Transformer(nn.Module):
             ops.t2_gemv_prepared(W.iq, W.i_sum, ff.down_proj.weight.data, W.is_,
                                  ff.down_proj.weight_scale, out=W.ffn_out, ldc=a.dim, pdl=pdl)
 
-    def _sweep_layer_table(self, kv_full, kv_rows: int) -> torch.Tensor:
-        """Device table of the 14 pointers per layer bm_decode_sweep reads, for one KV buffer.
-        Built on first use (outside graph capture: the atlas runs one eager pass first)."""
-        key = (kv_full[0][0].data_ptr(), kv_full[0][1].data_ptr(), kv_rows, len(kv_full))
-        tab = self._sweep_tables.get(key)
-        if tab is not None:
-            return tab
-        rows = []
-        for layer, (k_l, v_l) in zip(self.layers, kv_full):
-            at, ff = layer.attention, layer.feed_forward
-            tensors = (at.wqkv_weight, at.o_proj.weight.data, ff.w_gu, ff.down_proj.weight.data,
-                       at.wqkv_scale, at.o_proj.weight_scale, ff.w_gu_scale, ff.down_proj.weight_scale,
-                       layer.input_layernorm.weight.data, layer.post_attention_layernorm.weight.data,
-                       at.q_norm.weight.data, at.k_norm.weight.data, k_l, v_l)
-            rows.append([t.data_ptr() for t in tensors])
-        if len(self._sweep_tables) > 64:
-            self._sweep_tables.clear()
-        tab = torch.tensor(rows, dtype=torch.int64).to(self.embed_tokens.weight.device)
-        self._sweep_tables[key] = tab
-        return tab
-
-    def _sweep_layers(self, W: "StepWorkspace", token_values, positions, kv_full, kv_rows: int, sigma: int,
-                      attn_mask, attn_scratch) -> None:
-        a = self.args
-        L0 = self.layers[0].attention
-        sa = native.SweepArgs()
-        sa.layers = self._sweep_layer_table(kv_full, kv_rows).data_ptr()
-        sa.n_layers, sa.M, sa.dim, sa.H, sa.Hkv, sa.ffn = a.n_layers, W.M, a.dim, a.n_heads, a.n_kv_heads, a.ffn_dim
-        sa.kv_rows, sa.sigma, sa.eps = kv_rows, sigma, a.norm_eps
-        for name, t in (("tokens", token_values), ("positions", positions), ("embed", self.embed_tokens.weight.data),
-                        ("cos_t", L0.rope_cos), ("sin_t", L0.rope_sin), ("state", attn_mask),
-                        ("attn_scratch", attn_scratch), ("h", W.h), ("xq", W.q), ("xsum", W.q_sum), ("xs", W.s),
-                        ("xqkv", W.xqkv), ("attq", W.att_q), ("attsum", W.att_sum), ("atts", W.att_s),
-                        ("attn_out", W.attn_out), ("inner", W.inner), ("inner_amax", W.inner_amax[0]), ("iq", W.iq),
-                        ("isum", W.i_sum), ("is_", W.is_), ("ffn_out", W.ffn_out), ("barrier", W.sweep_barrier)):
-            setattr(sa, name, t.data_ptr())
-        ops.decode_sweep(sa, token_values.device)
-
     def workspace(self, M: int) -> StepWorkspace:
         ws = self._workspaces.get(M)
         if ws is None:
@@ -622,10 +576,7 @@ class Transformer(nn.Module):
         if logits_buf is None:
             logits_buf = torch.empty((rows, W.n_pad), dtype=torch.float32, device=dev)
         eps = a.norm_eps
-        if self.use_sweep and ops.sweep_supported(a.dim, a.n_heads, a.head_dim, a.ffn_dim, M) \
-                and token_values.is_contiguous() and positions.is_contiguous():
-            self._sweep_layers(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch)
-        elif self._ar_fused_supported(M) and token_values.is_contiguous() and positions.is_contiguous():
+        if self._ar_fused_supported(M) and token_values.is_contiguous() and positions.is_contiguous():
             self._layers_ar_fused(W, token_values, positions, kv_full, kv_rows, sigma, attn_mask, attn_scratch,
                                   pdl, attn_pdl)
         else:

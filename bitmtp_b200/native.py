@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 SO_PATH = os.path.join(HERE, "libbitmtp_b200.so")
 SOURCES = ["bm_lib.cu"]
 HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh",
-           "t2_gemv_direct.cuh", "decode_sweep.cuh"]
+           "t2_gemv_direct.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -63,17 +63,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return SO_PATH
 
 
-class SweepArgs(ctypes.Structure):
-    """bm_sweep_args of include/bitmtp_b200.h."""
-    _fields_ = ([("layers", ctypes.c_void_p)]
-                + [(n, ctypes.c_int) for n in ("n_layers", "M", "dim", "H", "Hkv", "ffn", "kv_rows", "sigma")]
-                + [("eps", ctypes.c_float), ("reserved", ctypes.c_int)]
-                + [(n, ctypes.c_void_p) for n in (
-                    "tokens", "positions", "embed", "cos_t", "sin_t", "state", "attn_scratch", "h", "xq", "xsum",
-                    "xs", "xqkv", "attq", "attsum", "atts", "attn_out", "inner", "inner_amax", "iq", "isum", "is_",
-                    "ffn_out", "barrier", "timing")])
-
-
 class NativeError(RuntimeError):
     pass
 
@@ -109,7 +98,7 @@ def _declare_optional(L) -> None:
     vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     protos = {
         "bm_quant_rows": [vp, ci, ci, vp, vp, vp, vp, ci, vp],
-        "bm_rmsnorm_fused": [vp, vp, vp, vp, cf, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
+        "bm_rmsnorm_fused": [vp, vp, ci, vp, vp, cf, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_silu_mul_quant": [vp, ci, ci, vp, vp, vp, vp, vp, ci, vp],
         "bm_qknorm_rope_kvappend": [vp, vp, vp, cf, vp, vp, vp, ci, ci, ci, vp, vp, ci, ci, vp, ci, vp],
         "bm_set_step_state": [vp, ci, ci, ci, ci, vp],
@@ -117,9 +106,8 @@ def _declare_optional(L) -> None:
         "bm_verify_attention_scratch_bytes": [ci, ci, ci],
         "bm_verify_attention": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, vp],
         "bm_verify_attention_static": [vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp],
-        "bm_decode_sweep": [ctypes.POINTER(SweepArgs), vp],
         "bm_zero_words": [vp, ci, vp],
-        "bm_t2_gemv_row_fused": [ci, vp, vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, vp, ci, ci, ci, vp, ci, vp],
+        "bm_t2_gemv_row_fused": [ci, vp, vp, ci, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, vp, ci, ci, ci, vp, ci, vp],
         "bm_stage_replay_inputs": [ci, vp, vp, ci, ci, ci, ci, ctypes.c_longlong, ci, ci, vp, vp, vp, vp],
         "bm_rope_verify_attention_rows": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, ci, vp],
         "bm_rope_verify_attention": [vp, vp, vp, cf, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp,
@@ -127,7 +115,7 @@ def _declare_optional(L) -> None:
         "bm_t2_gemv_gate_up_silu": [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, ci, vp],
         "bm_quant_rows_amax": [vp, vp, vp, ci, ci, vp, vp, vp, vp, ci, vp],
         "bm_t2_gemv_nsplit": [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp),
-                              ctypes.POINTER(vp), vp, ci, vp],
+                              ctypes.POINTER(vp), vp, ci, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],

@@ -64,7 +64,9 @@ class FusedNSplitLinear:
     flag per peer says "my slice is there".  No collective library call on the data path.
 
     The output buffers and flag arrays live in torch symmetric memory (peer-mapped allocations).
-    All ranks must call `forward` the same number of times with the same W."""
+    All ranks must call `forward` the same number of times with the same W.  A peer that never
+    publishes (a rank that died or is far behind) ends the kernel's bounded wait: `failed_call()`
+    then names the call whose output is invalid."""
 
     def __init__(self, weight: torch.Tensor, scale: torch.Tensor, *, n_full: int, max_w: int = 16,
                  group: Optional[dist.ProcessGroup] = None):
@@ -98,7 +100,9 @@ class FusedNSplitLinear:
         pad = [vp(0)] * (8 - len(ptrs))
         self._peer_c = [(vp * 8)(*[vp(p + b * self.half_bytes) for p in ptrs] + pad) for b in range(2)]
         self._peer_flags = (vp * 8)(*[vp(p + flag_off) for p in ptrs] + pad)
-        self.state = torch.zeros(2, dtype=torch.int32, device=dev)   # CTA counter, completed calls
+        # CTA counter, completed calls, number of the last call whose peer wait ran out (0: none), unused
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.poll_limit = 0                     # polls of a peer's flag before the wait is given up (0: default)
         self.calls = 0
         self.out = [self.buf[b * self.half_bytes: b * self.half_bytes + max_w * n_full * 2]
                     .view(torch.bfloat16).view(max_w, n_full) for b in range(2)]
@@ -120,6 +124,13 @@ class FusedNSplitLinear:
         rc = native.lib().bm_t2_gemv_nsplit(
             a_int8.data_ptr(), self.weight.data_ptr(), s.data_ptr(), self.scale.data_ptr(), W, self.rows, K, self.n,
             self.col0, self.world, self.rank, cast(self._peer_c[0]), cast(self._peer_c[1]), cast(self._peer_flags),
-            self.state.data_ptr(), int(pdl), stream)
+            self.state.data_ptr(), int(self.poll_limit), int(pdl), stream)
         native.check(rc, "bm_t2_gemv_nsplit")
         return self.out[b][:W]
+
+    def failed_call(self) -> int:
+        """Number of the last `forward` call (1, 2, ...) whose wait for a peer ran out, 0 if none did.
+        The output of that call holds stale columns for the silent peer and must not be used.  One
+        4-byte device-to-host copy; callers that already read a result every step can read
+        `self.state[2]` with it instead."""
+        return int(self.state[2].item())

@@ -123,7 +123,7 @@ def rmsnorm_fused(x: torch.Tensor, w: torch.Tensor, eps: float, *, M: Optional[i
         out["s"] = torch.empty((M, 1), dtype=torch.float32, device=dev)
     if want_n and "n" not in out:
         out["n"] = torch.empty((M, dim), dtype=torch.bfloat16, device=dev)
-    rc = native.lib().bm_rmsnorm_fused(_ptr(x), _ptr(gather), _ptr(res), _ptr(w), float(eps), M, dim,
+    rc = native.lib().bm_rmsnorm_fused(_ptr(x), _ptr(gather), int(x.shape[0]) if gather is not None else 0, _ptr(res), _ptr(w), float(eps), M, dim,
                                        row0, _ptr(out.get("h")), _ptr(out.get("q")), _ptr(out.get("qp")),
                                        _ptr(out.get("asum")), _ptr(out.get("s")), _ptr(out.get("n")),
                                        int(pdl), _stream(dev))
@@ -253,20 +253,6 @@ def verify_accept(draft: torch.Tensor, verify: torch.Tensor, D: int, *, out=None
     return n
 
 
-# --------------------------------------------------------------------------- layer sweep
-SWEEP_LAYER_FIELDS = 14
-
-
-def sweep_supported(dim: int, n_heads: int, head_dim: int, ffn_dim: int, M: int) -> bool:
-    """Geometry the persistent layer kernel serves (bm_decode_sweep)."""
-    return dim == 2048 and head_dim == 128 and n_heads * head_dim == 2048 and ffn_dim == 6144 and 1 <= M <= 16
-
-
-def decode_sweep(args: "native.SweepArgs", device) -> None:
-    """All layers of one replay in one launch; `args` is a filled native.SweepArgs."""
-    check(native.lib().bm_decode_sweep(ctypes.byref(args), _stream(device)), "bm_decode_sweep")
-
-
 # --------------------------------------------------------------------------- fused SwiGLU
 def gate_up_silu(a_prep: torch.Tensor, a_sums: torch.Tensor, w_gu: torch.Tensor, s: torch.Tensor,
                  w_gu_scale: torch.Tensor, *, inner: torch.Tensor, amax: torch.Tensor, pdl: bool = False) -> None:
@@ -356,7 +342,7 @@ def gemv_row_fused(src_mode: int, x: torch.Tensor, w: torch.Tensor, ws: torch.Te
     K = w.shape[1] * 4
     N = w.shape[0] // 2 if silu else w.shape[0]
     rc = native.lib().bm_t2_gemv_row_fused(
-        int(src_mode), _ptr(x), _ptr(gather), _ptr(res), _ptr(norm_w), float(eps), _ptr(h_out), _ptr(amax_in),
+        int(src_mode), _ptr(x), _ptr(gather), int(x.shape[0]) if gather is not None else 0, _ptr(res), _ptr(norm_w), float(eps), _ptr(h_out), _ptr(amax_in),
         _ptr(amax_zero), _ptr(w), _ptr(ws), N, K, _ptr(out), out.shape[-1], int(out_kind), int(silu), _ptr(amax_out),
         int(pdl), _stream(x.device))
     check(rc, f"bm_t2_gemv_row_fused(mode={src_mode}, N={N}, K={K})")

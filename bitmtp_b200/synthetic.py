@@ -175,6 +175,28 @@ class AcceptancePolicy:
         return a - 1
 
 
+def acceptance_hooks(FG, policy: "AcceptancePolicy"):
+    """Replacements for the decode loops' confidence-chain and prefix-accept reductions
+    (`FG._fused_draft_chain`, `FG._fused_verify_accept`; FG = bitmtp_b200.fast_generate) that apply
+    an AcceptancePolicy.  The kernels still run.  A replaced chain length is handed to the loop as a
+    host value, so the loop still reads only the ids from the device (one copy) and no extra kernel
+    runs inside a timed region; a replaced accepted-prefix length is written over the kernel's count
+    in place, so that it stays part of the record the loop reads in one copy."""
+    chain, accept = FG._fused_draft_chain, FG._fused_verify_accept
+
+    def hooked_chain(logits, threshold, out=None):
+        idx, n = chain(logits, threshold, out)
+        a = policy.chain_count()
+        return idx, (n if a is None else torch.tensor([a], dtype=torch.int64))
+
+    def hooked_accept(draft, verify, Dd, out=None):
+        n = accept(draft, verify, Dd, out)
+        a = policy.accept_count()
+        return n if a is None else n.fill_(a)
+
+    return hooked_chain, hooked_accept
+
+
 def random_prompt(length: int, vocab: int, seed: int = 0) -> torch.Tensor:
     gen = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (1, length), generator=gen, dtype=torch.int64)

@@ -81,8 +81,7 @@ void t2g128_int8xint2_linear(int8_t *A, int8_t *B, void *C, float *s, void *ws, 
  *   out_kind  BM_OUT_*
  *   path      BM_PATH_*  (AUTO: the MMA consumer whenever K % 256 == 0, which
  *             covers every model shape; the lanes-across-K dp4a consumer otherwise.
- *             BM_PATH_MMA with K % 256 != 0 is BM_EINVAL).  Tuning aid: BM_PATH_MMA |
- *             (rb << 8) with rb in {1, 2, 4} forces tiles of 8*rb output rows)
+ *             BM_PATH_MMA with K % 256 != 0 is BM_EINVAL; any other value is BM_EINVAL)
  *   C         16-byte aligned, ldc a multiple of 4
  *   G_out     int32 [W, N, K/128] exact group sums, or NULL
  *   pdl       1 = launch with programmatic stream serialisation: the kernel
@@ -125,7 +124,8 @@ int bm_quant_rows(const void *x, int M, int K, void *q, void *q_prep, void *asum
 
 /* (gather | residual add) + RMSNorm + (INT8 quantisation | bf16 store), one row per CTA.
  *   x       bf16 [*, dim]; row m is x[gather[m]] when gather (int64 [M]) is given,
- *           else x[row0 + m]
+ *           else x[row0 + m].  gather_rows = rows of x: an id outside [0, gather_rows)
+ *           reads the nearest valid row instead of memory outside the table
  *   res     optional bf16 [*, dim], read at row0 + m: h = bf16(x + res)
  *   w       bf16 [dim] norm weight;  dim a multiple of 256, <= 8192
  *   h_out   optional bf16 [M, dim]: the row before the norm
@@ -134,8 +134,8 @@ int bm_quant_rows(const void *x, int M, int K, void *q, void *q_prep, void *asum
  * Replaces _fused_norm_quant, _fused_add_norm_quant, RMSNorm.forward on the logit
  * rows and the embedding gather (src/bonsai_sft/gpu/model.py:307-336, 290-295,
  * 1386, 1401-1402). */
-int bm_rmsnorm_fused(const void *x, const void *gather, const void *res, const void *w, float eps,
-                     int M, int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s,
+int bm_rmsnorm_fused(const void *x, const void *gather, int gather_rows, const void *res, const void *w,
+                     float eps, int M, int dim, int row0, void *h_out, void *q, void *q_prep, void *asum, void *s,
                      void *n_out, int pdl, void *stream);
 
 /* inner = bf16(bf16(silu(gate)) * up), then the quantisation of bm_quant_rows.
@@ -237,14 +237,15 @@ int bm_commit_stage_draft(const void *src, int n_commit, int verified, void *gen
  *   src_mode 1: x bf16 [K] with the bits of its absmax in amax_in[0] (as left by
  *               bm_rope_verify_attention_rows or bm_t2_gemv_gate_up_silu); amax_zero[0] (optional, another
  *               word) is cleared.  Equals bm_quant_rows_amax + bm_t2_gemv_prepared.
- *   src_mode 2: h = bf16(x_row + res) (x_row = x[gather[0]] when gather is given, res optional), stored to
+ *   src_mode 2: h = bf16(x_row + res) (x_row = x[gather[0]] when gather is given, the id clamped to
+ *               [0, gather_rows); res optional), stored to
  *               h_out [K] (must not alias x or res), then RMSNorm with norm_w and eps and the codes.
  *               K == 2048.  Equals bm_rmsnorm_fused + bm_t2_gemv_prepared.
  *   silu != 0: B holds 2N rows (gate, then up), C bf16 [N] = bf16(silu(g) * u), amax_out[0] gathers its
  *               absmax (zero on entry), as bm_t2_gemv_gate_up_silu.
  * Other arguments as bm_t2_gemv.  Bit-identical to the chains named above. */
-int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, const void *res, const void *norm_w,
-                         float eps, void *h_out, const void *amax_in, void *amax_zero, const void *B,
+int bm_t2_gemv_row_fused(int src_mode, const void *x, const void *gather, int gather_rows, const void *res,
+                         const void *norm_w, float eps, void *h_out, const void *amax_in, void *amax_zero, const void *B,
                          const void *ws, int N, int K, void *C, int ldc, int out_kind, int silu, void *amax_out,
                          int pdl, void *stream);
 
@@ -264,48 +265,21 @@ int bm_quant_rows_amax(const void *x, const void *amax_in, void *amax_zero, int 
  * peer's consumers still read).  The last CTA to finish publishes the call number in slot [rank] of
  * every peer's flag array (peer_flags[i]: uint32 [world] of rank i) and waits, with a limit, until all
  * peers have published the same number in the local array: when the kernel ends the full [W, ldc]
- * block is in this GPU's buffer, bit-identical to the single-GPU product.  state: local uint32 [2],
- * zero before the first call ([0] CTA counter, [1] completed calls; device-resident, so a captured
- * graph can be replayed).  The result of call k (k = 1, 2, ...) is in buffer k & 1.  All ranks make
- * the same sequence of calls.  The reference has no multi-GPU inference path; this is the exchange
- * step of the wide-layer configuration.  bm_device_error() = 4 when a peer did not answer in time. */
+ * block is in this GPU's buffer, bit-identical to the single-GPU product.  state: local uint32 [4],
+ * zero before the first call ([0] CTA counter, [1] completed calls, [2] status, [3] unused;
+ * device-resident, so a captured graph can be replayed).  The result of call k (k = 1, 2, ...) is in
+ * buffer k & 1.  All ranks make the same sequence of calls.
+ * A peer that does not publish within poll_limit polls of its flag (0 = the default, 2^22 polls of
+ * >= 100 ns each) ends the wait: the kernel returns, state[2] = k names the call, and
+ * bm_device_error() = 4.  The output of call k is then INVALID for that peer's columns (they still
+ * hold the values of call k - 2); the local shard's columns are correct.  Read state[2] with the
+ * step's own device-to-host copy to learn of it without synchronising the device.
+ * The reference has no multi-GPU inference path; this is the exchange step of the wide-layer
+ * configuration. */
 int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *ws, int W, int N_shard,
                       int K, int ldc, int col0, int world, int rank, void *const *peer_C0,
-                      void *const *peer_C1, void *const *peer_flags, void *state, int pdl, void *stream);
-
-/* All transformer layers of one decode replay in ONE persistent kernel launch: per layer
- * (residual add +) RMSNorm + quant, qkv GEMV, q/k norm + RoPE + KV append + block-verify attention,
- * o GEMV, residual add + RMSNorm + quant, gate|up GEMV + SiLU*up + quant, down GEMV — the body of
- * the layer loop of Transformer.forward_sdlm_decode_graph_kernel
- * (src/bonsai_sft/gpu/model.py:1386-1399 with 1119-1137, 958-1009, 1053-1064).  Results are
- * bit-identical to calling the operators above one by one.
- *   layers   device array, 14 pointers per layer: packed codes of wqkv [(H+2Hkv)*128, dim/4],
- *            wo [dim, H*128/4], gate|up [2*ffn, dim/4], down [dim, ffn/4]; their bf16 scales in
- *            the same order; input_layernorm, post_attention_layernorm, q_norm, k_norm weights
- *            (bf16); the layer's K and V planes [Hkv, kv_rows, 128] (bf16)
- *   tokens, positions int64 [M]; embed bf16 [vocab, dim]; cos_t / sin_t bf16 [max_pos, 128];
- *   state: bm_set_step_state record; attn_scratch: bm_verify_attention_scratch_bytes(M, H, sigma)
- *   workspace (caller-allocated, contents irrelevant on entry): h, attn_out, ffn_out bf16 [M, dim];
- *   xq int8 [M, dim] + xsum int32 [M, dim/128] + xs fp32 [M]; xqkv bf16 [M, (H+2Hkv)*128];
- *   attq int8 [M, H*128] + attsum + atts; inner bf16 [M, ffn]; inner_amax uint32 [M];
- *   iq int8 [M, ffn] + isum + is; barrier: 8 bytes (zeroed by the call).
- * On return (stream order) h and ffn_out hold the residual stream and the last down projection,
- * i.e. the inputs of the final norm, and the K/V rows [sigma, sigma+M) of every layer are written.
- * Serves dim == 2048, H*128 == 2048, ffn == 6144, head_dim 128, M <= 16; anything else is
- * BM_EINVAL and the caller uses the operators.  One CTA per SM, launched cooperatively; the
- * stages are separated by a bounded software grid barrier (bm_device_error() = 3 on expiry). */
-typedef struct bm_sweep_args {
-    const void *layers;
-    int n_layers, M, dim, H, Hkv, ffn, kv_rows, sigma;
-    float eps;
-    int reserved;
-    const void *tokens, *positions, *embed, *cos_t, *sin_t, *state;
-    void *attn_scratch;
-    void *h, *xq, *xsum, *xs, *xqkv, *attq, *attsum, *atts, *attn_out, *inner, *inner_amax, *iq, *isum,
-        *is_, *ffn_out, *barrier;
-    void *timing; /* optional uint64 [19]: %globaltimer (ns) of CTA 0 in layer 1: [2k] stage k starts, [2k+1] its work is done, [18] end */
-} bm_sweep_args;
-int bm_decode_sweep(const bm_sweep_args *args, void *stream);
+                      void *const *peer_C1, void *const *peer_flags, void *state, int poll_limit, int pdl,
+                      void *stream);
 
 /* bm_qknorm_rope_kvappend + bm_verify_attention in two launches instead of three: the attention's chunk
  * kernel reads the qkv projection output (xqkv bf16 [M, (H + 2 Hkv) * 128]) and does the q/k head norm, the

@@ -418,8 +418,8 @@ BMO_API void bmo_argmax_rows(const float *logits, int rows, int vocab, int64_t *
         const float *x = logits + (size_t)r * vocab;
         float best = x[0];
         int64_t bi = 0;
-        for (int v = 1; v < vocab; ++v)
-            if (x[v] > best) { best = x[v]; bi = v; }
+        for (int v = 1; v < vocab; ++v)   // NaN counts as the maximum, lowest index wins (bm_argmax_better)
+            if (bm_argmax_better(x[v], v, best, (int)bi)) { best = x[v]; bi = v; }
         idx[r] = bi;
     }
 }

@@ -74,6 +74,40 @@ def build_reference_kernel(reference_root: str, force: bool = False, verbose: bo
     return REF_OUT
 
 
+REF_SITE = os.path.join(HERE, "..", "baseline", "_ref")
+
+
+def install_reference_python(reference_root: str, force: bool = False) -> str:
+    """Install the reference's Python package, unmodified, into the git-ignored baseline/_ref with pip
+    (offline, no dependency resolution: its pins name older torch / transformers than this image has)
+    and place the reference kernel built above where its ctypes loader looks for it
+    (src/bonsai_sft/gpu/model.py:206-219).  Only the benchmark's reference arm imports from there
+    (oracle/reference_decode.py, bench.py's reference_cpu_linear_path).  The source tree is read-only,
+    so pip builds from a temporary copy.  Returns the site directory, or "" when nothing was installed."""
+    import shutil
+    import tempfile
+    site = os.path.abspath(REF_SITE)
+    pkg = os.path.join(site, "bonsai_sft")
+    if not os.path.isdir(os.path.join(reference_root, "src", "bonsai_sft")):
+        return site if os.path.isdir(pkg) else ""
+    if force or not os.path.isdir(pkg):
+        tmp = tempfile.mkdtemp(prefix="bitmtp_ref_")
+        try:
+            src = os.path.join(tmp, "reference")
+            shutil.copytree(reference_root, src, symlinks=True)
+            os.makedirs(site, exist_ok=True)
+            subprocess.run([sys.executable, "-m", "pip", "install", "--quiet", "--no-index", "--no-build-isolation",
+                            "--no-deps", "--upgrade", "--find-links", "/opt/wheelhouse", "--target", site, src],
+                           check=True)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+    if os.path.exists(REF_OUT) and os.path.isdir(pkg):
+        dst = os.path.join(pkg, "gpu", "t2g128_kernels", "libbonsai_t2.so")
+        if not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(REF_OUT):
+            shutil.copyfile(REF_OUT, dst)
+    return site if os.path.isdir(pkg) else ""
+
+
 def reference_kernel_path() -> str:
     """Path of the built reference kernel library, "" if it has not been built."""
     return REF_OUT if os.path.exists(REF_OUT) else ""
@@ -84,3 +118,4 @@ if __name__ == "__main__":
     root = os.environ.get("BITMTP_REFERENCE", "")
     if root:
         print(build_reference_kernel(root, force="--force" in sys.argv, verbose=True) or "reference checkout not found")
+        print(install_reference_python(root, force="--force" in sys.argv) or "reference package not installed")

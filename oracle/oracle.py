@@ -275,7 +275,10 @@ class OracleModel:
     src/bonsai_sft/gpu/model.py:931-956, 1042-1051, 1223-1243.
     """
 
-    def __init__(self, cfg: dict, state: dict, max_positions: int):
+    def __init__(self, cfg: dict, state: dict, max_positions: int, head=None):
+        """`head`: optional (packed codes int8/uint8 [vocab, dim/4], scales bf16 [vocab, dim/128]) of the
+        tied head when the caller already holds it on the T2 grid (vocab a multiple of 8); otherwise the
+        embedding is packed here."""
         import torch
         self.cfg = dict(cfg)
         self.dim, self.L = cfg["dim"], cfg["n_layers"]
@@ -309,7 +312,11 @@ class OracleModel:
                                       u16(f + "up_proj.weight_scale")], 0),
                 wdown=u8(f + "down_proj.weight"), wdown_s=u16(f + "down_proj.weight_scale"),
             ))
-        self.head_w, self.head_s = self._pack_head(state["embed_tokens.weight"])
+        if head is not None and head[0].shape[0] % 8 == 0:
+            self.head_w = np.ascontiguousarray(head[0].cpu().numpy().view(np.uint8))
+            self.head_s = torch_to_u16(head[1].to(torch.bfloat16))
+        else:
+            self.head_w, self.head_s = self._pack_head(state["embed_tokens.weight"])
         self.cos, self.sin = rope_tables(cfg, max_positions)
 
     @staticmethod

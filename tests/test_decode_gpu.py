@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from bitmtp_b200 import fast_generate as FG, generate, native, ops, synthetic
-from bitmtp_b200.benchmarks import acceptance_hooks
+from bitmtp_b200.synthetic import acceptance_hooks
 from bitmtp_b200.fast_runtime import GraphAtlas
 from bitmtp_b200.model import make_sdlm_cache
 
@@ -91,52 +91,6 @@ def test_token_streams_match_reference_loops(rec, monkeypatch):
     sig = atlas.segment_ladder[0]
     ptrs = {g.kv_full[0][0].data_ptr() for (M, s, r), g in atlas.graphs.items() if s == sig}
     assert ptrs == {atlas.kv_buffers[sig].data_ptr()}
-
-
-SWEEP_CASES = [("ar", 1, 20, 0), ("ar", 16, 0, 0), ("verify", 9, 130, 0), ("draft", 9, 30, 1),
-               ("draft", 12, 65, 3), ("draft", 16, 200, 8), ("draft", 8, 31, 0), ("ar", 5, 97, 0)]
-
-
-@pytest.mark.parametrize("role,M,cache_len,n_pend", SWEEP_CASES)
-def test_layer_sweep_kernel_equals_operator_path(oracle, role, M, cache_len, n_pend):
-    """The persistent layer kernel (bm_decode_sweep) against the operator-by-operator launches on
-    the 1.7B layer geometry (3 layers, small vocabulary): logits and every KV row bit for bit;
-    one case is also checked against the CPU oracle forward."""
-    geometry = dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096)
-    cfg = synthetic.make_config(geometry, block_size=8)
-    sigma, m_max = 256, 17
-    model, state = _model(cfg, 5, sigma + m_max)
-    assert ops.sweep_supported(cfg["dim"], cfg["n_heads"], cfg["head_dim"], cfg["ffn_dim"], M)
-    D, L, Hkv = 8, cfg["n_layers"], cfg["n_kv_heads"]
-    gen = torch.Generator().manual_seed(M * 100 + cache_len)
-    kv = (torch.randn(2, L, 1, Hkv, sigma + m_max, 128, generator=gen) * 0.5).to(torch.bfloat16)
-    tokens = torch.randint(0, cfg["vocab_size"], (M,), generator=gen).to(DEV)
-    positions = torch.arange(max(cache_len - 1, 0), max(cache_len - 1, 0) + M).to(DEV)
-    rid = oracle.ROLE_IDS[role]
-    ls, le = {"ar": (0, M), "verify": (0, min(D + 1, M)), "draft": (M - D, M)}[role]
-    state_t = ops.new_step_state(DEV)
-    ops.set_step_state(state_t, cache_len, min(n_pend, max(M - D, 0)), rid, M - D)
-    outs = {}
-    for sweep in (False, True):
-        kvd = kv.to(DEV)
-        kv_full = [(kvd[0, i][:, :, : sigma + M, :], kvd[1, i][:, :, : sigma + M, :]) for i in range(L)]
-        model.use_sweep = sweep
-        try:
-            for rep in range(2):                       # second call: barrier words and buffers are reused
-                logits = model.forward_sdlm_decode_graph_kernel(tokens, positions, kv_full, M, state_t, ls, le, "t2")
-        finally:
-            model.use_sweep = False
-        torch.cuda.synchronize()
-        assert native.lib().bm_device_error() == 0
-        outs[sweep] = (logits.clone(), kvd.clone())
-    assert torch.equal(outs[True][0].view(torch.int32), outs[False][0].view(torch.int32)), "logits differ"
-    assert torch.equal(outs[True][1].view(torch.int16), outs[False][1].view(torch.int16)), "KV rows differ"
-    if (role, M) == ("draft", 9):
-        om = oracle.OracleModel(cfg, state, max_positions=sigma + m_max)
-        kv_np = oracle.torch_to_u16(kv).copy()
-        want = om.forward(tokens.cpu().numpy(), positions.cpu().numpy(), kv_np, sigma, rid, cache_len, n_pend, ls, le)
-        assert np.array_equal(outs[True][0].cpu().numpy().view(np.uint32), want.view(np.uint32))
-        assert np.array_equal(oracle.torch_to_u16(outs[True][1].cpu()), kv_np)
 
 
 @pytest.mark.parametrize("cache_len", [0, 37, 200])

@@ -129,6 +129,8 @@ ATTN_CASES = [
     (17, 16, 8, 256, 40, 9, 8, "draft"),
     (16, 16, 8, 4096, 2500, 8, 8, "draft"),    # long segment: the three-CTAs-per-SM build of the chunk kernel
     (9, 32, 8, 4096, 3000, 0, 8, "verify"),
+    (16, 16, 8, 256, 256, 8, 8, "draft"),      # the history fills the whole segment (cache_len == sigma)
+    (9, 16, 8, 64, 64, 0, 8, "verify"),
 ]
 
 
@@ -154,6 +156,52 @@ def test_verify_attention(oracle, M, H, Hkv, sigma, cache_len, n_pend, D, role):
         assert np.array_equal(qq.cpu().numpy(), qo)
         assert np.array_equal(s.cpu().numpy().reshape(-1).view(np.uint32), so.view(np.uint32))
     assert int(scratch[:256].sum().item()) == 0
+
+
+def test_attention_clamps_a_record_beyond_the_segment(oracle):
+    """A step record that claims more history than the segment holds (a stale record, a wrong segment
+    passed through the C ABI) must not index past the scratch or the K/V planes: the kernels clamp the
+    length to sigma, so the call equals the one with cache_len == sigma."""
+    M, H, Hkv, sigma, D = 9, 16, 8, 64, 8
+    gen = torch.Generator().manual_seed(5)
+    q = _bf16(gen, M, H, 128, scale=1.5).to(DEV)
+    k = _bf16(gen, Hkv, sigma + 17, 128, scale=1.5).to(DEV)
+    v = _bf16(gen, Hkv, sigma + 17, 128).to(DEV)
+    scratch = ops.attention_scratch(M, H, sigma, DEV)
+    outs = []
+    for claimed in (sigma, sigma + 1000):
+        state = ops.new_step_state(DEV)
+        ops.set_step_state(state, claimed, 1, native.ROLE_DRAFT, M - D)
+        att, qq, s = ops.verify_attention(q, k, v, sigma, state, scratch)
+        torch.cuda.synchronize()
+        outs.append((att.clone(), qq.clone(), s.clone()))
+    assert native.lib().bm_device_error() == 0
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+
+
+def test_argmax_of_nan_rows_stays_inside_the_row(oracle):
+    """A row of NaNs (a corrupt scale upstream) must still give an index inside the row: the id stays on
+    the device and feeds the next replay's embedding gather.  NaN counts as the maximum and the lowest
+    index wins, as torch.argmax does; the gather itself clamps ids it is given."""
+    vocab = 5000
+    lg = torch.randn(4, vocab)
+    lg[0] = float("nan")
+    lg[1, 1234] = float("nan")
+    lg[1, 4000] = float("nan")
+    lg[2] = float("-inf")
+    want = torch.argmax(lg, dim=-1)
+    assert want.tolist()[:3] == [0, 1234, 0]
+    assert np.array_equal(oracle.argmax_rows(lg.numpy()), want.numpy())
+    d = lg.to(DEV)
+    assert torch.equal(ops.argmax_rows(d).cpu(), want)
+    assert torch.equal(ops.argmax_rows(d, scratch=ops.logit_scratch(DEV)).cpu(), want)
+    # out-of-table ids are clamped by the gathering RMSNorm
+    table = _bf16(torch.Generator().manual_seed(1), 10, 256).to(DEV)
+    w = torch.ones(256, dtype=torch.bfloat16, device=DEV)
+    ids = torch.tensor([2 ** 31 - 1, -5, 3], dtype=torch.int64, device=DEV)
+    got = ops.rmsnorm_fused(table, w, 1e-6, gather=ids, want_q=False, want_h=True)["h"]
+    assert torch.equal(got.view(torch.int16), table[[9, 0, 3]].view(torch.int16))
 
 
 def test_kv_copy_rows():

@@ -154,9 +154,17 @@ def test_whole_forward_against_reference_forward():
                         ls, le)
         want = F[f"c{ci}_logits"]
         scale = np.abs(want).max()
-        # two layers of bf16 intermediates: a few bf16 steps on the logits
-        assert np.abs(lg - want).max() <= 4e-2 * scale, ci
-        assert (lg.argmax(-1) == want.argmax(-1)).mean() >= 0.8
+        # Measured against the unmodified reference forward, in bf16 steps at the scale of the logits
+        # (2^(floor(log2 scale) - 7)), per case (role/width): ar/1 3.6 max, 0.56 mean; verify/9 5.0, 0.67;
+        # draft/9 4.2, 0.60; draft/12 4.8, 0.69; draft/16 2.1, 0.32 -- two layers of bf16 intermediates whose
+        # fp32 sums run in another order.  Bound: 6 steps at most, 1 step on average; the greedy token
+        # agrees on every row but one of the 34 (draft/12: 7 of 8).
+        step = 2.0 ** (np.floor(np.log2(scale)) - 7)
+        d = np.abs(lg - want)
+        assert d.max() <= 6 * step, (ci, d.max() / step)
+        assert d.mean() <= 1.0 * step, (ci, d.mean() / step)
+        agree = lg.argmax(-1) == want.argmax(-1)
+        assert agree.sum() >= len(agree) - 1, ci
         got_rows, want_rows = f32(kv[:, :, 0, :, sigma:sigma + M, :]), f32(F[f"c{ci}_kv_rows"])
         assert np.abs(got_rows - want_rows).max() <= 4e-2 * np.abs(want_rows).max()
         # layer 0 sees identical inputs on both sides: its appended rows agree to one bf16 step
