@@ -686,7 +686,7 @@ def timed_generations(args, device, local, dist, model, atlas, cfg, steps, warmu
     policy = synthetic.AcceptancePolicy(args.accept, D, seed=rank)
     saved = FG._fused_draft_chain, FG._fused_verify_accept
     FG._fused_draft_chain, FG._fused_verify_accept = synthetic.acceptance_hooks(FG, policy)
-    counted = list(atlas.graphs.values()) + list(atlas.prefill_graphs.values()) + list(atlas.dense_graphs.values())
+    counted = list(atlas.graphs.values()) + list(atlas.prefill_graphs.values())
     for g in counted:
         if not isinstance(g.cuda_graph, _ReplayCounter):
             g.cuda_graph = _ReplayCounter(g.cuda_graph)
@@ -738,9 +738,6 @@ def timed_generations(args, device, local, dist, model, atlas, cfg, steps, warmu
     replays = {f"{r}:M{M}": g.cuda_graph.replays for (M, _, r), g in sorted(atlas.graphs.items())
                if g.cuda_graph.replays}
     replays["prompt-slab:M16"] = sum(g.cuda_graph.replays for g in atlas.prefill_graphs.values())
-    for (M, _, r), g in sorted(atlas.dense_graphs.items()):
-        if g.cuda_graph.replays:
-            replays[f"{r}:M{M}:3-per-SM attention"] = g.cuda_graph.replays
     return {"ms": ms, "clocks": clocks, "tok": tok, "dec_t": dec_t, "tot_t": tot_t, "iters": iters, "ttft": ttft,
             "launches": launches, "replays": replays,
             "dec_t_max": max_over_ranks(dist, dec_t, device), "tok_all": sum_over_ranks(dist, tok, device),

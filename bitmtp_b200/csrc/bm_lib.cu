@@ -16,6 +16,7 @@
 #include "verify_attn.cuh"
 #include "t2_gemv_rowwarp.cuh"
 #include "t2_gemv_direct.cuh"
+#include "dense_head.cuh"
 
 #include <cudaTypedefs.h>
 #include <map>
@@ -757,104 +758,104 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma) {
 }  // extern "C"
 
 namespace {
-// Inputs of the chunk kernel with the q/k norm, RoPE and KV append folded in (null: rotated queries in `q`).
+// Inputs of the attention kernel with the q/k norm, RoPE and KV append folded in (null: rotated queries in `q`).
 struct RopeInputs {
     const void *xqkv, *q_w, *k_w, *cos_t, *sin_t, *positions;
     float eps;
 };
 
+template <bool ROPE>
+int launch_attention(int nq, dim3 grid, size_t smem, cudaStream_t st, int pdl, const bm::AttnParams &p) {
+    const dim3 block(bm::kAttnThreads);
+    switch (nq) {
+        case 1: return launch_ex(bm::attn_fused_kernel<1, ROPE>, grid, block, smem, st, pdl, p);
+        case 2: return launch_ex(bm::attn_fused_kernel<2, ROPE>, grid, block, smem, st, pdl, p);
+        case 3: return launch_ex(bm::attn_fused_kernel<3, ROPE>, grid, block, smem, st, pdl, p);
+        default: return launch_ex(bm::attn_fused_kernel<4, ROPE>, grid, block, smem, st, pdl, p);
+    }
+}
+
+// One attention launch (scores, softmax, numerators, merge: bf16 rows + row absmax bits), followed by the
+// flat quantisation launch unless the caller asked for rows only (`amax_rows` != null).
 int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_base, const void *v_base, int M, int H,
                           int Hkv, int kv_rows, int sigma, const void *state, void *scratch, void *att_out,
                           void *q_out, void *q_prep, void *asum, void *s_out, int pdl, void *stream,
                           void *amax_rows = nullptr) {
-    // amax_rows != null: rows only (bf16 att_out + absmax bits per row), quantisation left to the caller
-    int dummy_s = 0;
     if (amax_rows != nullptr) {
-        if (!att_out || (H % 4) != 0) return BM_EINVAL;
-        q_prep = nullptr;
-        asum = nullptr;
-        q_out = att_out;                              // satisfies the "some sink" check; not written
-        s_out = &dummy_s;
+        if (!att_out) return BM_EINVAL;
+    } else {
+        if ((!q_out && !q_prep) || !s_out || (q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
     }
     if (rope != nullptr) {
         if (!rope->xqkv || !rope->q_w || !rope->k_w || !rope->cos_t || !rope->sin_t || !rope->positions) return BM_EINVAL;
         if ((reinterpret_cast<uintptr_t>(rope->xqkv) & 7u) || (reinterpret_cast<uintptr_t>(rope->cos_t) & 7u) ||
-            (reinterpret_cast<uintptr_t>(rope->sin_t) & 7u))
+            (reinterpret_cast<uintptr_t>(rope->sin_t) & 7u) || (reinterpret_cast<uintptr_t>(rope->q_w) & 7u) ||
+            (reinterpret_cast<uintptr_t>(rope->k_w) & 7u))
             return BM_EINVAL;
         q = rope->xqkv;                               // only for the null / alignment checks below
     }
-    if (!q || !k_base || !v_base || !state || !scratch || (!q_out && !q_prep) || !s_out) return BM_EINVAL;
-    if ((q_prep == nullptr) != (asum == nullptr)) return BM_EINVAL;
-    if (M < 1 || M > BM_MAX_W || H < 1 || H > bm::kMergeMaxHeads || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
+    if (!q || !k_base || !v_base || !state || !scratch) return BM_EINVAL;
+    if (M < 1 || M > BM_MAX_W || H < 1 || Hkv < 1 || (H % Hkv) != 0) return BM_EINVAL;
     if (sigma < 0 || sigma + M > kv_rows || !aligned16(q) || !aligned16(k_base) || !aligned16(v_base) ||
         !aligned16(scratch) || (att_out && !aligned16(att_out)))
         return BM_EINVAL;
-    const int NC = (sigma + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK + 1;
-    if (NC > 160) return BM_EINVAL;
+    const int NJ = (sigma + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER + 1;
+    if (NJ > bm::kAttnMaxNJ) return BM_EINVAL;
     const int G = H / Hkv, QV = G * M;
-    bm::AttnParams p;
+    int nq = 1, Z = 1;
+    bm::attn_query_split(QV, &nq, &Z);
+    if (Hkv * Z > bm::kAttnTickets) return BM_EINVAL;
+    if ((H * 128) % 256 != 0 && amax_rows == nullptr) return BM_EINVAL;   // the flat quantisation wants K % 256 == 0
+    bm::AttnParams p = {};
     p.q = static_cast<const uint16_t *>(q);
     p.k_base = static_cast<const uint16_t *>(k_base);
     p.v_base = static_cast<const uint16_t *>(v_base);
     p.state = static_cast<const bm::StepState *>(state);
-    p.M = M; p.H = H; p.Hkv = Hkv; p.kv_rows = kv_rows; p.sigma = sigma; p.NC = NC;
+    p.M = M; p.H = H; p.Hkv = Hkv; p.kv_rows = kv_rows; p.sigma = sigma; p.NJ = NJ;
     char *sc = static_cast<char *>(scratch);
-    p.ctr = reinterpret_cast<int *>(sc);
-    p.amax = reinterpret_cast<unsigned int *>(sc + 128);
-    p.pm = reinterpret_cast<float *>(sc + 256);
-    p.pl = p.pm + (size_t)M * H * NC;
-    p.po = p.pl + (size_t)M * H * NC;
-    p.att = static_cast<uint16_t *>(att_out);
-    p.q_out = bm::QuantSink{static_cast<int8_t *>(q_out), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
-    p.s_out = static_cast<float *>(s_out);
-    p.pdl = pdl;
+    p.tickets = reinterpret_cast<unsigned int *>(sc);
+    unsigned int *own_amax = reinterpret_cast<unsigned int *>(sc) + bm::kAttnTickets;
+    p.pm = reinterpret_cast<float *>(sc + bm::kAttnHeaderBytes);
+    p.pl = p.pm + (size_t)M * H * NJ;
+    p.po = p.pl + (size_t)M * H * NJ;
+    uint16_t *own_rows = reinterpret_cast<uint16_t *>(p.po + (size_t)M * H * NJ * 128);
+    p.att = att_out ? static_cast<uint16_t *>(att_out) : own_rows;
+    p.amax = amax_rows ? static_cast<unsigned int *>(amax_rows) : own_amax;
+    p.pdl = pdl & (BM_PDL_OVERLAP | BM_PDL_STABLE_STATE);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)32 * bm::kKeyStride * 2 + 32 * 128 * 2 + (size_t)QV * 128 * 4 + (size_t)QV * 32 * 4;
-    // Many query vectors: two CTAs per (chunk, kv head), each with half of them, so that more
-    // warps are resident per chunk (the per-warp instruction stream is what bounds this kernel).
-    const int qsplit = QV >= 16 ? 2 : 1;
-    const int qv_cta = (QV + qsplit - 1) / qsplit;
-    const int nq = bm::attn_nq(qv_cta);
-    int warps = (qv_cta + nq - 1) / nq;
-    if (warps > bm::kAttnThreads / 32) warps = bm::kAttnThreads / 32;
-    const int threads = 32 * warps < bm::kAttnMinThreads ? bm::kAttnMinThreads : 32 * warps;
-    const size_t msmem = (size_t)H * 128 * 2 + (size_t)H * NC * sizeof(float);
-    if (smem > 200 * 1024 || msmem > 200 * 1024) return BM_EINVAL;
-    int rc;
-    const dim3 grid(NC, Hkv, qsplit);
-    if (rope != nullptr) {
-        bm::AttnRopeParams rp;
-        rp.a = p;
-        rp.xqkv = static_cast<const uint16_t *>(rope->xqkv);
-        rp.q_w = static_cast<const uint16_t *>(rope->q_w);
-        rp.k_w = static_cast<const uint16_t *>(rope->k_w);
-        rp.cos_t = static_cast<const uint16_t *>(rope->cos_t);
-        rp.sin_t = static_cast<const uint16_t *>(rope->sin_t);
-        rp.positions = static_cast<const int64_t *>(rope->positions);
-        rp.k_out = const_cast<uint16_t *>(p.k_base);
-        rp.v_out = const_cast<uint16_t *>(p.v_base);
-        rp.eps = rope->eps;
-        // long segments: several waves of chunk CTAs, so trade a slower pass for three CTAs per SM
-        const bool dense = (pdl & BM_ATTN_DENSE) != 0 || (long long)NC * Hkv * qsplit > 4LL * current_device().sm_count;
-#define BM_ROPE_CASE(NQ_) \
-        rc = dense ? launch_ex(bm::attn_chunk_rope_kernel<NQ_, 3>, grid, dim3(threads), smem, st, pdl, rp) \
-                   : launch_ex(bm::attn_chunk_rope_kernel<NQ_, 2>, grid, dim3(threads), smem, st, pdl, rp)
-        if (nq == 2) BM_ROPE_CASE(2);
-        else if (nq == 4) BM_ROPE_CASE(4);
-        else BM_ROPE_CASE(8);
-#undef BM_ROPE_CASE
-    } else if (nq == 2) rc = launch_ex(bm::attn_chunk_kernel<2>, grid, dim3(threads), smem, st, pdl, p);
-    else if (nq == 4) rc = launch_ex(bm::attn_chunk_kernel<4>, grid, dim3(threads), smem, st, pdl, p);
-    else rc = launch_ex(bm::attn_chunk_kernel<8>, grid, dim3(threads), smem, st, pdl, p);
-    if (rc != BM_OK) return rc;
-    if (amax_rows != nullptr) {
-        const int hpc = 4;
-        return launch_ex(bm::attn_merge_part_kernel, dim3(M, H / hpc), dim3(hpc * 64), (size_t)hpc * NC * sizeof(float),
-                         st, pdl, p, static_cast<unsigned int *>(amax_rows), hpc);
+    if (amax_rows == nullptr) {
+        // this call gathers the row absmax in the scratch header: clear it first (stream-ordered)
+        const cudaError_t e = cudaMemsetAsync(own_amax, 0, BM_MAX_W * sizeof(unsigned int), st);
+        if (e != cudaSuccess) return cuda_status(e);
     }
-    int mthreads = H * 64 < bm::kMergeThreads ? H * 64 : bm::kMergeThreads;
-    mthreads = (mthreads + 31) / 32 * 32;
-    return launch_ex(bm::attn_merge_kernel, dim3(M), dim3(mthreads), msmem, st, pdl, p);
+    const size_t smem = bm::attn_smem_bytes(nq);
+    const dim3 grid(NJ, Hkv, Z);
+    // after a memset node the launch cannot overlap its predecessor programmatically
+    const int attn_pdl = amax_rows ? (pdl & BM_PDL_OVERLAP) : 0;
+    if (amax_rows == nullptr) p.pdl = 0;
+    int rc;
+    if (rope != nullptr) {
+        p.xqkv = static_cast<const uint16_t *>(rope->xqkv);
+        p.q_w = static_cast<const uint16_t *>(rope->q_w);
+        p.k_w = static_cast<const uint16_t *>(rope->k_w);
+        p.cos_t = static_cast<const uint16_t *>(rope->cos_t);
+        p.sin_t = static_cast<const uint16_t *>(rope->sin_t);
+        p.positions = static_cast<const int64_t *>(rope->positions);
+        p.k_out = const_cast<uint16_t *>(p.k_base);
+        p.v_out = const_cast<uint16_t *>(p.v_base);
+        p.eps = rope->eps;
+        rc = launch_attention<true>(nq, grid, smem, st, attn_pdl, p);
+    } else {
+        rc = launch_attention<false>(nq, grid, smem, st, attn_pdl, p);
+    }
+    if (rc != BM_OK || amax_rows != nullptr) return rc;
+    // INT8 codes of the rows from the flat grid, with the absmax the merge gathered
+    bm::QuantSink sink{static_cast<int8_t *>(q_out), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
+    const int K = H * 128, units = M * (K / 8);
+    const int qgrid = (units + bm::kQuantAmaxThreads - 1) / bm::kQuantAmaxThreads;
+    return launch_ex(bm::quant_rows_amax_kernel, dim3(qgrid), dim3(bm::kQuantAmaxThreads), 0, st, pdl & BM_PDL_OVERLAP,
+                     static_cast<const uint16_t *>(p.att), static_cast<const unsigned int *>(own_amax),
+                     static_cast<unsigned int *>(nullptr), M, K, sink, static_cast<float *>(s_out), pdl & BM_PDL_OVERLAP);
 }
 }  // namespace
 
@@ -951,6 +952,36 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     return cuda_status(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------- dense draft heads
+int bm_dense_head(const void *h, const void *W, int fp8, const void *w_scale, int R, int N, int K, void *out, int ldc,
+                  void *h_scale_out, int pdl, void *stream) {
+    if (!h || !W || !out || R < 1 || R > bm::kDenseMaxRows || N < 16 || (N % 16) != 0 || K < 256 || (K % 256) != 0)
+        return BM_EINVAL;
+    if (ldc < N || (fp8 && !w_scale) || !aligned16(h) || !aligned16(W)) return BM_EINVAL;
+    bm::DenseHeadParams p;
+    p.W = W;
+    p.h = static_cast<const uint16_t *>(h);
+    p.w_scale = static_cast<const float *>(w_scale);
+    p.out = static_cast<float *>(out);
+    p.h_scale_out = static_cast<float *>(h_scale_out);
+    p.R = R; p.N = N; p.K = K; p.ldc = ldc; p.pdl = pdl & BM_PDL_OVERLAP;
+    const size_t smem = bm::dense_head_smem(R, K, fp8 != 0);
+    if (smem > (size_t)kMaxSmemPerCta) return BM_EINVAL;
+    const int sms = current_device().sm_count;
+    const int blocks = N / 16;
+    int grid = (smem <= (size_t)(kMaxSmemPerCta - 2048) / 2 ? 2 : 1) * sms;   // two CTAs per SM when the rows fit twice
+    if (grid * (bm::kDenseThreads / 32) > blocks) grid = (blocks + bm::kDenseThreads / 32 - 1) / (bm::kDenseThreads / 32);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 g(grid), b(bm::kDenseThreads);
+    const int nb = (R + 7) / 8;
+#define BM_DENSE_CASE(NB_) \
+    if (nb == NB_) return fp8 ? launch_ex(bm::dense_head_kernel<NB_, true>, g, b, smem, st, p.pdl, p) \
+                             : launch_ex(bm::dense_head_kernel<NB_, false>, g, b, smem, st, p.pdl, p);
+    BM_DENSE_CASE(1) BM_DENSE_CASE(2) BM_DENSE_CASE(3)
+#undef BM_DENSE_CASE
+    return BM_EINVAL;
+}
+
 // ---------------------------------------------------------------------------- N-split GEMV
 int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *ws, int W, int N_shard, int K, int ldc,
                       int col0, int world, int rank, void *const *peer_C0, void *const *peer_C1,
@@ -981,7 +1012,8 @@ int bm_t2_gemv_nsplit(const void *A, const void *B, const void *s, const void *w
 //
 // The array is shared by every call on a device: two calls whose execution can overlap
 // (different streams, or different host threads) race on it and must be serialised by the
-// caller.  No word of it has to be initialised; each call writes what it later reads.
+// caller.  It starts as zeros when the module is loaded, which is what the counters in its
+// first KiB need; every call leaves them zero again and writes every other word it reads.
 constexpr size_t kStaticAttnScratchBytes = BM_STATIC_ATTN_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
 
@@ -990,14 +1022,21 @@ static void *g_static_attn_ptr[kMaxDevices];      // device address of the array
 static std::mutex g_static_attn_mutex;
 
 // Looks the array's address up on the current device, once per device.  The look-up is a
-// runtime call, so the first call on a device should be made outside stream capture.
-static int static_attn_scratch(void **out) {
+// runtime call, so it is refused while `stream` is capturing: the first call on a device has to be
+// made outside stream capture.
+static int static_attn_scratch(void **out, cudaStream_t stream) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_status(e);
     if (dev < 0 || dev >= kMaxDevices) return BM_EINVAL;
     std::lock_guard<std::mutex> lock(g_static_attn_mutex);
     if (g_static_attn_ptr[dev] == nullptr) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            fprintf(stderr, "bm_verify_attention_static: first call on device %d while its stream is capturing; "
+                            "call it once outside capture\n", dev);
+            return BM_ECAPTURE;
+        }
         void *ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
         if (e != cudaSuccess) return cuda_status(e);
@@ -1021,7 +1060,7 @@ int bm_verify_attention_static(const void *q, const void *k_base, const void *v_
         return BM_ETOOBIG;
     }
     void *scratch = nullptr;
-    const int rc = static_attn_scratch(&scratch);
+    const int rc = static_attn_scratch(&scratch, static_cast<cudaStream_t>(stream));
     if (rc != BM_OK) return rc;
     return bm_verify_attention(q, k_base, v_base, M, H, Hkv, kv_rows, sigma, state, scratch, att_out, q_out,
                                q_prep, asum, s_out, pdl, stream);

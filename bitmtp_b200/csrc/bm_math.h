@@ -27,7 +27,8 @@
 
 #define BM_GROUP 128          /* K elements that share one weight scale      */
 #define BM_SLOTS 16           /* partial sums per output before the tree     */
-#define BM_ATTN_CHUNK 32      /* keys per attention partial                  */
+#define BM_ATTN_CHUNK 32      /* keys per attention sub-chunk (one warp pass) */
+#define BM_ATTN_SUPER 128     /* keys per attention super-chunk (one partial) */
 #define BM_MAX_W 32           /* widest token block accepted by any kernel   */
 
 BM_HD uint32_t bm_f32_bits(float f) {

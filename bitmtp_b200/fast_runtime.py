@@ -18,7 +18,6 @@ What differs from the reference, by design:
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -31,6 +30,10 @@ from .model import PREFILL_CHUNK, ModelArgs, SDLMLayerCache, Transformer, make_s
 DEFAULT_SEGMENT_LADDER = (256, 1024, 4096)
 DEFAULT_M_SET = (1, 8, 9, 10, 12, 16, 17)
 ROLES = ("draft", "verify", "ar")
+
+# head of each role (fast_runtime.py:179-205): native packed T2 everywhere, the dense e4m3 / bf16 tied
+# table for the acceptance-tolerant draft variants
+ROLE_HEAD_PRECISION = {"ar": "t2", "draft": "t2", "verify": "t2", "draft_fp8": "fp8", "draft_bf16": "bf16_raw"}
 
 _ROLE_ID = {"draft": native.ROLE_DRAFT, "draft_fp8": native.ROLE_DRAFT,
             "draft_bf16": native.ROLE_DRAFT, "verify": native.ROLE_VERIFY, "ar": native.ROLE_AR}
@@ -84,11 +87,6 @@ class GraphAtlas:
         self.m_set = tuple(sorted(set(m_set)))
         self.roles = tuple(roles)
         validate_graph_roles(self.roles)
-        for role in self.roles:
-            if role in ("draft_fp8", "draft_bf16"):
-                raise NotImplementedError(
-                    f"role {role!r}: the dense fp8/bf16 draft head is not built; the packed T2 head "
-                    "('draft') reads a quarter of the bytes and is exact")
         self.D = args.block_size
         self.M_max = max(self.m_set)
         self.vocab_size = args.vocab_size
@@ -100,6 +98,10 @@ class GraphAtlas:
             print(f"[GraphAtlas] D={self.D}, segments={self.segment_ladder}, M_set={self.m_set}, "
                   f"roles={self.roles}, kernels={native.lib().bm_version().decode()}")
         self.model.prepare_t2_lm_head()
+        if "draft_fp8" in self.roles:                  # fast_runtime.py:112-114
+            self.model.prepare_fp8_lm_head()
+        if "draft_bf16" in self.roles:
+            self.model.prepare_bf16_lm_head()
         self._allocate_shared_kv()
         self._allocate_input_bufs()
         self._capture_all()
@@ -139,7 +141,6 @@ class GraphAtlas:
                 for role in self.roles:
                     if role != "ar":
                         self.graphs[(M, sigma, role)] = self._capture_one(M, sigma, role)
-        self._capture_dense_twins()
         # Prompt slabs: one AR-causal graph of PREFILL_CHUNK rows per segment, layers only (the one
         # logit row a prompt needs is taken afterwards).  Kept apart from `graphs`, whose key set
         # mirrors the reference's.  Needs workspace rows for a whole slab.
@@ -159,6 +160,7 @@ class GraphAtlas:
         D = self.D
         P = M - D
         ls, le = logit_rows if logit_rows is not None else role_logit_rows(role, M, D)
+        precision = ROLE_HEAD_PRECISION[role]
         shared = self.kv_buffers[sigma]
         slot = shared[:, :, :, :, : sigma + M, :]
         kv_full = [(slot[0, i], slot[1, i]) for i in range(self.n_layers)]
@@ -172,7 +174,7 @@ class GraphAtlas:
         def body():
             return self.model.forward_sdlm_decode_graph_kernel(
                 token_values=tokens_buf, positions=positions_buf, kv_full=kv_full, block_size=M,
-                attn_mask=state, logits_start=ls, logits_end=le, lm_head_precision="t2",
+                attn_mask=state, logits_start=ls, logits_end=le, lm_head_precision=precision,
                 attn_scratch=scratch, logits_buf=logits_buf, stable_state=True)
 
         # One eager pass on a side stream (sets kernel attributes, proves the launch
@@ -190,7 +192,7 @@ class GraphAtlas:
         n_kernels = int(native.lib().bm_launch_count() - launches_before)
         return CapturedGraph(cuda_graph=graph, tokens_buf=tokens_buf, positions_buf=positions_buf,
                              attn_mask=state, logits_out=logits, kv_full=kv_full, M=M, sigma=sigma,
-                             role=role, P=P, logits_start=ls, logits_end=le, lm_head_precision="t2",
+                             role=role, P=P, logits_start=ls, logits_end=le, lm_head_precision=precision,
                              n_kernels=n_kernels)
 
     # ------------------------------------------------------------------ selection
@@ -203,43 +205,9 @@ class GraphAtlas:
         return self.segment_ladder[-1]
 
     def get_graph(self, M: int, sigma: int, role: str, cache_len: Optional[int] = None) -> CapturedGraph:
-        """The graph of (M, sigma, role).  With `cache_len`, the twin captured with the attention chunk kernel
-        built for three CTAs per SM where that history length makes it the faster one (same results)."""
-        if cache_len is not None:
-            twin = getattr(self, "dense_graphs", {}).get((M, sigma, role))
-            if twin is not None and self._prefer_dense(M, cache_len):
-                return twin
+        """The graph of (M, sigma, role).  `cache_len` is accepted for callers that know the history length;
+        one graph serves every length."""
         return self.graphs[(M, sigma, role)]
-
-    def _chunk_ctas(self, M: int, rows: int) -> int:
-        """CTAs of the attention chunk kernel that have work with `rows` history rows."""
-        qv = (self.args.n_heads // self.n_kv) * M
-        return ((rows + 31) // 32 + 1) * self.n_kv * (2 if qv >= 16 else 1)
-
-    def _prefer_dense(self, M: int, cache_len: int) -> bool:
-        """A chunk's pass is ~1.2x slower in the three-per-SM build; it wins when it saves a wave of CTAs
-        (measured at width 16: 1406 -> 1336 us per replay with 368 CTAs, 1245 -> 1286 us with 176)."""
-        items, sms = self._chunk_ctas(M, cache_len), self._sm_count
-        waves2, waves3 = -(-items // (2 * sms)), -(-items // (3 * sms))
-        return waves2 > 1.2 * waves3
-
-    def _capture_dense_twins(self) -> None:
-        """Twins of the wide graphs for history lengths between the one-wave regime and the segment sizes for
-        which the kernel picks the three-per-SM build by itself."""
-        self.dense_graphs: Dict[Tuple[int, int, str], CapturedGraph] = {}
-        self._sm_count = int(native.lib().bm_sm_count())
-        if os.environ.get("BM_DENSE_TWINS", "1") == "0":
-            return
-        for (M, sigma, role) in list(self.graphs):
-            if M == 1 or self._chunk_ctas(M, sigma) > 4 * self._sm_count:      # already dense by itself
-                continue
-            if not any(self._prefer_dense(M, c) for c in range(32, sigma + 1, 32)):
-                continue
-            self.model.attn_dense = True
-            try:
-                self.dense_graphs[(M, sigma, role)] = self._capture_one(M, sigma, role)
-            finally:
-                self.model.attn_dense = False
 
     # ------------------------------------------------------------------ per-step API
     def prepare_step(self, graph: CapturedGraph, cache_len: int, n_pend: int,

@@ -322,6 +322,7 @@ class StepWorkspace:
         self.ffn_out = buf((M, args.dim), bf)
         self.hq = buf((M, args.dim), i8)
         self.hs = buf((M, 1), f32)
+        self.hn = buf((M, args.dim), bf)            # normed logit rows of the dense draft heads
         # per-128-group sums that travel with the GEMV-ready codes in q / att_q / iq / hq
         i32 = torch.int32
         self.q_sum = buf((M, args.dim // 128), i32)
@@ -351,16 +352,11 @@ class Transformer(nn.Module):
         # successor start early (GEMVs then request their weight tiles while the predecessor
         # is still running) and waits for its predecessor before touching activations.
         self.use_pdl = os.environ.get("BM_PDL", "1") != "0"
-        # attention chunk kernel built for three CTAs per SM; the atlas sets it while it captures the graphs it
-        # replays at cache lengths whose chunk grid needs more than one wave of the two-per-SM build
-        self.attn_dense = False
         # SiLU(gate) * up inside the gate|up GEMV + a flat quantisation kernel instead of GEMV + one SiLU
         # CTA per row (BM_FUSED_FFN=0 restores the latter)
         self.fused_ffn = os.environ.get("BM_FUSED_FFN", "1") != "0"
-        # q/k norm + RoPE + KV append folded into the attention's chunk kernel (BM_FUSED_ROPE=0: own launch)
+        # q/k norm + RoPE + KV append folded into the attention kernel (BM_FUSED_ROPE=0: own launch)
         self.fused_rope = os.environ.get("BM_FUSED_ROPE", "1") != "0"
-        # attention merge over (row, 4 heads) CTAs + flat quantisation (BM_SPLIT_MERGE=0: one merge CTA per row)
-        self.split_merge = os.environ.get("BM_SPLIT_MERGE", "1") != "0"
         # width-1 replays: RMSNorm / quantisation inside the consuming GEMV, 6 launches per layer instead
         # of 10 (BM_FUSED_AR=0: the general sequence)
         self.fused_ar = os.environ.get("BM_FUSED_AR", "1") != "0"
@@ -400,6 +396,46 @@ class Transformer(nn.Module):
         self._lm_head_t2_scale = scale.to(dev)
         self._lm_head_t2_vocab = vocab
         self._lm_head_n_pad = n_pad
+
+    @torch.no_grad()
+    def prepare_fp8_lm_head(self) -> None:
+        """Per-tensor e4m3 copy of the tied head for the `draft_fp8` role (model.py:1169-1194): rows padded
+        to a multiple of 16, w_scale = bf16(amax|W| / 448) kept as an fp32 device scalar, table =
+        (W / w_scale) cast to e4m3.  A one-time conversion at load; the per-step work is bm_dense_head."""
+        if getattr(self, "_lm_head_fp8_w", None) is not None:
+            return
+        fp8_max = torch.finfo(torch.float8_e4m3fn).max
+        W = self._lm_head_weight().data
+        vocab, dim = W.shape
+        vocab_pad = (vocab + 15) // 16 * 16
+        Wp = W
+        if vocab_pad != vocab:
+            Wp = torch.zeros(vocab_pad, dim, dtype=W.dtype, device=W.device)
+            Wp[:vocab].copy_(W)
+        w_scale = (Wp.abs().amax() / fp8_max).clamp_min(1e-12).to(torch.float32)
+        out = torch.empty(vocab_pad, dim, dtype=torch.float8_e4m3fn, device=W.device)
+        for r0 in range(0, vocab_pad, 16384):          # in slabs: no second full-size temporary
+            out[r0:r0 + 16384] = (Wp[r0:r0 + 16384] / w_scale).to(torch.float8_e4m3fn)
+        self._lm_head_fp8_w = out
+        self._lm_head_w_scale = w_scale.reshape(1).contiguous()
+        self._lm_head_fp8_max = fp8_max
+        self._lm_head_vocab = vocab
+
+    @torch.no_grad()
+    def prepare_bf16_lm_head(self) -> None:
+        """Table of the `draft_bf16` role (model.py:1276-1282): the tied bf16 embedding itself; a zero-padded
+        copy only when the vocabulary is not a multiple of 16 rows."""
+        if getattr(self, "_lm_head_bf16_w", None) is not None:
+            return
+        W = self._lm_head_weight().data
+        vocab, dim = W.shape
+        if vocab % 16 == 0 and W.is_contiguous():
+            self._lm_head_bf16_w = W
+        else:
+            Wp = torch.zeros((vocab + 15) // 16 * 16, dim, dtype=W.dtype, device=W.device)
+            Wp[:vocab].copy_(W)
+            self._lm_head_bf16_w = Wp
+        self._lm_head_vocab = vocab
 
     def prepare_merged_weights(self, max_positions: int = 256) -> None:
         """model.py:1444-1447; the RoPE tables are built once and shared by all layers."""
@@ -459,10 +495,9 @@ class Transformer(nn.Module):
         # (16-runs transposed 4x4, plus per-group sums), so no GEMV CTA permutes or sums them.
         qsink = {"h": W.h, "qp": W.q, "asum": W.q_sum, "s": W.s}
         fused_ffn = self.fused_ffn and M <= 16 and a.ffn_dim % 16 == 0 and a.dim % 256 == 0
-        split_merge = self.split_merge and a.n_heads % 4 == 0 and (a.n_heads * a.head_dim) % 256 == 0
         if fused_ffn:
             ops.zero_words(W.inner_amax[0])           # slot of layer 0; every layer clears the next one's
-        if self.fused_rope and split_merge:
+        if self.fused_rope:
             ops.zero_words(W.att_amax[0])
         ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=M,
                           gather=token_values, pdl=pdl, out=qsink)
@@ -474,22 +509,16 @@ class Transformer(nn.Module):
             ops.t2_gemv_prepared(W.q, W.q_sum, at.wqkv_weight, W.s, at.wqkv_scale, out=W.xqkv,
                                  ldc=W.xqkv.shape[1], pdl=pdl)
             k_l, v_l = kv_full[i]
-            if self.fused_rope and split_merge:
-                # chunk kernel with the RoPE folded in, merge spread over (row, 4 heads) CTAs with the row
-                # absmax by atomic max, INT8 codes from the flat quantisation kernel
+            if self.fused_rope:
+                # one attention launch (q/k norm, RoPE and KV append folded in; the last CTA of a query group
+                # merges the split-KV partials and gathers the row absmax by atomic max), then the INT8 codes
+                # from the flat quantisation kernel
                 ops.rope_verify_attention_rows(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
                                                at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
                                                _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma, attn_mask,
                                                attn_scratch, att=W.att, amax=W.att_amax[i & 1], pdl=attn_pdl)
                 ops.quant_rows_amax(W.att, W.att_amax[i & 1], prep=(W.att_q, W.att_sum), s=W.att_s,
                                     amax_zero=W.att_amax[(i + 1) & 1], pdl=pdl)
-            elif self.fused_rope:
-                # q/k norm + RoPE + KV append inside the attention's chunk kernel: one launch less
-                ops.rope_verify_attention(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps, at.rope_cos,
-                                          at.rope_sin, positions, a.n_heads, a.n_kv_heads,
-                                          _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows), sigma, attn_mask,
-                                          attn_scratch, out=(None, None, W.att_s), prep=(W.att_q, W.att_sum),
-                                          pdl=attn_pdl)
             else:
                 ops.qknorm_rope_kvappend(W.xqkv, at.q_norm.weight.data, at.k_norm.weight.data, eps,
                                          at.rope_cos, at.rope_sin, positions, a.n_heads, a.n_kv_heads,
@@ -555,7 +584,7 @@ class Transformer(nn.Module):
         written by launches that finished before this forward's first launch (a captured
         replay); the attention then reads them without waiting for the preceding kernel.
         """
-        if lm_head_precision not in ("t2",):
+        if lm_head_precision not in ("t2", "fp8", "bf16_raw"):
             raise RuntimeError(f"unsupported lm_head precision: {lm_head_precision!r}")
         a = self.args
         M = int(block_size)
@@ -565,8 +594,6 @@ class Transformer(nn.Module):
         W = self.workspace(M)
         pdl = self.use_pdl
         attn_pdl = (native.PDL_OVERLAP | native.PDL_STABLE_STATE) if (pdl and stable_state) else int(pdl)
-        if self.attn_dense:
-            attn_pdl |= native.ATTN_DENSE
         k0 = kv_full[0][0]
         kv_rows = k0.stride(-3) // a.head_dim
         sigma = k0.shape[-2] - M
@@ -585,14 +612,28 @@ class Transformer(nn.Module):
         if rows == 0:
             # layers only: the caller takes the logit rows it wants with head_from_workspace
             return logits_buf[:, : self._lm_head_t2_vocab]
-        return self.head_from_workspace(M, logits_start, rows, logits_buf)
+        return self.head_from_workspace(M, logits_start, rows, logits_buf, lm_head_precision)
 
-    def head_from_workspace(self, M: int, row0: int, rows: int, logits_buf: torch.Tensor) -> torch.Tensor:
-        """Final norm and packed head over rows [row0, row0 + rows) of the width-M workspace as the
-        layer loop left it: h + ffn_out, RMSNorm, INT8 quantisation, T2 head
-        (reference: model.py:1402-1404, 1245-1296).  Returns fp32 logits [rows, vocab]."""
+    def head_from_workspace(self, M: int, row0: int, rows: int, logits_buf: torch.Tensor,
+                            precision: str = "t2") -> torch.Tensor:
+        """Final norm and head over rows [row0, row0 + rows) of the width-M workspace as the layer loop
+        left it: h + ffn_out, RMSNorm, then by `precision` (reference: model.py:1402-1404, 1245-1296)
+          t2        INT8 quantisation + the packed T2 head
+          fp8       the e4m3 copy of the tied table with per-tensor scales (prepare_fp8_lm_head)
+          bf16_raw  the bf16 tied table itself
+        Returns fp32 logits [rows, vocab]."""
         W = self.workspace(M)
         pdl = self.use_pdl
+        if precision in ("fp8", "bf16_raw"):
+            ops.rmsnorm_fused(W.h, self.norm.weight.data, self.args.norm_eps, M=rows, res=W.ffn_out, row0=row0,
+                              pdl=pdl, want_q=False, out={"n": W.hn})
+            if precision == "fp8":
+                self.prepare_fp8_lm_head()
+                ops.dense_head(W.hn[:rows], self._lm_head_fp8_w, out=logits_buf, w_scale=self._lm_head_w_scale, pdl=pdl)
+            else:
+                self.prepare_bf16_lm_head()
+                ops.dense_head(W.hn[:rows], self._lm_head_bf16_w, out=logits_buf, pdl=pdl)
+            return logits_buf[:, : self._lm_head_vocab]
         ops.rmsnorm_fused(W.h, self.norm.weight.data, self.args.norm_eps, M=rows, res=W.ffn_out, row0=row0,
                           pdl=pdl, out={"qp": W.hq, "asum": W.h_sum, "s": W.hs})
         ops.t2_gemv_prepared(W.hq[:rows], W.h_sum[:rows], self._lm_head_t2_w, W.hs[:rows],

@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 SO_PATH = os.path.join(HERE, "libbitmtp_b200.so")
 SOURCES = ["bm_lib.cu"]
 HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh",
-           "t2_gemv_direct.cuh"]
+           "t2_gemv_direct.cuh", "dense_head.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -30,11 +30,12 @@ NVCC_FLAGS = [
 BM_OK = 0
 BM_EINVAL = 22
 BM_ETOOBIG = 27
+BM_ECAPTURE = 16
 STATIC_ATTN_SCRATCH_BYTES = 8 << 20     # BM_STATIC_ATTN_SCRATCH_BYTES of the header
 OUT_BF16, OUT_F32, OUT_F32_OF_BF16 = 0, 1, 2
 PATH_AUTO, PATH_DP4A, PATH_MMA, PATH_ROWWARP, PATH_DIRECT = 0, 1, 2, 3, 4
 ROLE_DRAFT, ROLE_VERIFY, ROLE_AR = 0, 1, 2
-PDL_OVERLAP, PDL_STABLE_STATE, PDL_STAGED, ATTN_DENSE = 1, 2, 4, 16
+PDL_OVERLAP, PDL_STABLE_STATE, PDL_STAGED = 1, 2, 4
 
 _lib = None
 
@@ -117,6 +118,7 @@ def _declare_optional(L) -> None:
         "bm_t2_gemv_nsplit": [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp),
                               ctypes.POINTER(vp), vp, ci, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
+        "bm_dense_head": [vp, vp, ci, vp, ci, ci, ci, vp, ci, vp, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],
         "bm_verify_accept": [vp, vp, ci, vp, vp],

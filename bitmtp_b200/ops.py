@@ -246,6 +246,24 @@ def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None, scratch: Optiona
     return idx, n, conf
 
 
+def dense_head(h: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor, w_scale: Optional[torch.Tensor] = None,
+               h_scale_out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+    """Dense draft head: bf16 rows h [R, K] against the bf16 table w [N, K], or against its e4m3 copy
+    (w.dtype float8_e4m3fn, `w_scale` the per-tensor fp32 scale).  `out` fp32 [R, >= N] receives the
+    bf16-rounded logits."""
+    R, K = h.shape
+    N = w.shape[0]
+    fp8 = w.dtype == torch.float8_e4m3fn
+    if not fp8 and w.dtype != torch.bfloat16:
+        raise RuntimeError("dense_head: the table must be bf16 or float8_e4m3fn")
+    if fp8 and (w_scale is None or w_scale.dtype != torch.float32):
+        raise RuntimeError("dense_head: an e4m3 table needs its fp32 per-tensor scale")
+    rc = native.lib().bm_dense_head(_ptr(h), _ptr(w), int(fp8), _ptr(w_scale), R, N, K, _ptr(out), out.stride(0),
+                                    _ptr(h_scale_out), int(pdl), _stream(h.device))
+    check(rc, f"bm_dense_head(R={R}, N={N}, K={K}, fp8={fp8})")
+    return out
+
+
 def verify_accept(draft: torch.Tensor, verify: torch.Tensor, D: int, *, out=None) -> torch.Tensor:
     n = out if out is not None else torch.empty(1, dtype=torch.int32, device=draft.device)
     check(native.lib().bm_verify_accept(_ptr(draft), _ptr(verify), D, _ptr(n), _stream(draft.device)),

@@ -47,7 +47,7 @@ def make_parser() -> argparse.ArgumentParser:
     p.add_argument("--exact-m1-verify", action="store_true",
                    help="Use the same width-1 graph as AR; requires margin 0.")
     p.add_argument("--draft-precision", choices=("native", "fp8", "bf16"), default="native",
-                   help="Only the native packed T2 head is built; fp8 / bf16 are rejected at capture.")
+                   help="Head of the draft role: native packed T2, or the dense tied table as e4m3 / bf16.")
     p.add_argument("--verify-precision", choices=("native",), default="native")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--no-flex-attention", action="store_true",

@@ -22,6 +22,7 @@ extern "C" {
 #define BM_OK 0
 #define BM_EINVAL 22
 #define BM_ETOOBIG 27          /* the request exceeds a built-in limit               */
+#define BM_ECAPTURE 16         /* set-up that cannot run while the stream is capturing */
 #define BM_ECUDA_BASE 1000
 
 /* out_kind for bm_t2_gemv */
@@ -39,8 +40,6 @@ extern "C" {
 #define BM_PDL_OVERLAP 1
 #define BM_PDL_STABLE_STATE 2
 #define BM_PDL_STAGED 4        /* bm_t2_gemv_row_fused only: use the shared-memory-staged kernel at every size */
-#define BM_ATTN_DENSE 16       /* bm_rope_verify_attention(_rows) only: the chunk kernel built for three CTAs per SM
-                                  (slower per chunk, more chunks at once); chosen by itself for long segments */
 
 #define BM_PATH_AUTO 0
 #define BM_PATH_DP4A 1
@@ -166,17 +165,22 @@ int bm_set_step_state(void *state, int cache_len, int n_pend, int role, int P, v
 int bm_kv_copy_rows(void *kv, int planes, int kv_rows, int src_row, int dst_row, int n,
                     void *stream);
 
-/* Scratch bytes bm_verify_attention needs for (M, H, sigma). Host-only arithmetic. */
+/* Scratch bytes bm_verify_attention needs for (M, H, sigma): a 1 KiB header of counters, the
+ * split-KV partials (one per 128 keys, query row and head) and one bf16 copy of the output rows.
+ * Host-only arithmetic. */
 int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma);
 
 /* Block-verify attention of one layer + INT8 quantisation of its output rows.
  *   q bf16 [M, H, 128]; k_base, v_base bf16 [Hkv, kv_rows, 128]; history rows are
  *   [0, cache_len), the M rows of this replay sit at [sigma, sigma + M);
  *   state: the record written by bm_set_step_state;
- *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned, contents
- *   irrelevant on entry (every word read by a call is written by that call);
+ *   scratch: bm_verify_attention_scratch_bytes bytes, 16-byte aligned, ZERO before its
+ *   first use (its first KiB holds counters that every call leaves zero again); not
+ *   shared by calls that may execute at the same time;
  *   att_out bf16 [M, H*128] or NULL; q_out / q_prep / asum: the quantised rows (see
- *   bm_quant_rows); s_out fp32 [M].
+ *   bm_quant_rows); s_out fp32 [M].  H*128 a multiple of 256; sigma <= 8064.
+ * Two launches: the attention itself (scores, softmax, numerators and the merge of the
+ * split-KV partials by the last CTA to finish) and the flat quantisation of its rows.
  * Visibility follows the reference's draft / verify / ar masks.  Replaces the
  * attention and o-projection input quantisation of
  * Attention.forward_sdlm_graph_kernel (src/bonsai_sft/gpu/model.py:989-1005) and the
@@ -187,14 +191,16 @@ int bm_verify_attention(const void *q, const void *k_base, const void *v_base, i
                         void *stream);
 
 /* bm_verify_attention for callers that cannot provide scratch memory; it has no
- * counterpart in the reference.  Same arguments without `scratch`: the chunk partials go to
+ * counterpart in the reference.  Same arguments without `scratch`: the split-KV partials go to
  * an array built into the library (BM_STATIC_ATTN_SCRATCH_BYTES per device), so the call
  * allocates and frees nothing.  Requests whose
  * bm_verify_attention_scratch_bytes(M, H, sigma) exceeds that size return BM_ETOOBIG
- * (16 rows x 16 heads fit up to sigma = 1984; 1 row x 16 heads up to sigma = 32224).
- * The first call on a device looks the array's address up and should therefore be made
- * before any stream capture on that device.  All calls on a device share the one array:
- * calls that may execute at the same time must be serialised by the caller. */
+ * (16 rows x 16 heads fit up to sigma = 7808, 32 rows x 32 heads up to sigma = 1792); every
+ * shape is also bound by bm_verify_attention's own sigma <= 8064 (BM_EINVAL beyond it).
+ * The first call on a device looks the array's address up, which is a runtime call: make it
+ * before any stream capture on that device.  A first call on a capturing stream returns
+ * BM_ECAPTURE and enqueues nothing.  All calls on a device share the one array: calls that
+ * may execute at the same time must be serialised by the caller. */
 #define BM_STATIC_ATTN_SCRATCH_BYTES (8u << 20)
 int bm_verify_attention_static(const void *q, const void *k_base, const void *v_base, int M, int H,
                                int Hkv, int kv_rows, int sigma, const void *state, void *att_out,
@@ -323,6 +329,20 @@ int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *
                          void *stream);
 int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf,
                          void *conf, void *n_out, void *scratch, void *stream);
+
+/* Dense tied head for the draft role: out fp32 [R, ldc] = bf16-rounded logits of the R bf16 rows
+ * h [R, K] against the dense table W [N, K].
+ *   fp8 == 0: W is bf16 (the tied embedding itself), out = bf16(h . W^T): the `bf16_raw` branch of
+ *             Transformer._lm_head (src/bonsai_sft/gpu/model.py:1276-1282, F.linear);
+ *   fp8 != 0: W is e4m3 (prepare_fp8_lm_head, model.py:1169-1194: W / w_scale with w_scale =
+ *             bf16(amax|W| / 448) in *w_scale, a device fp32); the rows are scaled per tensor by
+ *             h_scale = bf16(amax|h| / 448), cast to e4m3 and the product is multiplied by
+ *             h_scale * w_scale: the `fp8` branch (model.py:1266-1275, torch._scaled_mm).
+ *             h_scale_out (optional device fp32) receives h_scale.
+ * fp32 accumulation on the tensor cores (mma.sync, fixed k order); R <= 24, N % 16 == 0,
+ * K % 256 == 0.  Streams the whole table once: 2 (1) bytes per weight. */
+int bm_dense_head(const void *h, const void *W, int fp8, const void *w_scale, int R, int N, int K, void *out,
+                  int ldc, void *h_scale_out, int pdl, void *stream);
 
 /* *n_out (device int32) = length of the longest common prefix of draft[0:D] and
  * verify[0:D] (int64).  Replaces _fused_verify_accept

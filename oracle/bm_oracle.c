@@ -324,24 +324,29 @@ BMO_API void bmo_qknorm_rope_kvappend(const uint16_t *xqkv, const uint16_t *q_w,
 // q bf16 [M, H, 128]; k_base, v_base bf16 [Hkv, kv_rows, 128]; the M rows this
 // replay appended sit at [sigma, sigma+M).  out bf16 [M, H*128].
 //
-// Keys are visited in fixed chunks of BM_ATTN_CHUNK rows: history chunks
-// [32j, 32j+32) clipped to cache_len, then one chunk holding the M appended
-// rows.  Per chunk and query vector:
-//   score   dot over the 128 dims with fma in ascending d, times 1/sqrt(128)
-//   m_j     max of the visible scores
-//   p       bm_expf(score - m_j), 0 for hidden keys
-//   l_j     sum of p over the chunk's 32 positions in butterfly order
-//   o_j[d]  fma(bf16(p_c), v[c][d], o_j[d]) over visible c ascending
-// Chunks are merged in ascending order with weights bm_expf(m_j - m), m the
-// global max: l = fma(l_j, w, l), o[d] = fma(o_j[d], w, o[d]); chunks with no
-// visible key are skipped.  out = bf16(o / l).
+// Keys are visited in super-chunks of BM_ATTN_SUPER (128) rows, each cut into sub-chunks of
+// BM_ATTN_CHUNK (32): history super-chunks [128J, 128J+128) clipped to cache_len, then one
+// super-chunk holding the M appended rows.  Three levels, every one in a fixed order:
+//   level 0, per sub-chunk and query vector:
+//     score   dot over the 128 dims with fma in ascending d, times 1/sqrt(128)
+//     m_c     max of the visible scores (-inf when none is visible)
+//     p       bm_expf(score - m_c), 0 for hidden keys
+//     l_c     sum of p over the sub-chunk's 32 positions in butterfly order
+//     o_c[d]  fma(bf16(p_k), v[k][d], o_c[d]) over visible k ascending
+//   level 1, per super-chunk: M_J = max_c m_c; w_c = bm_expf(m_c - M_J) (0 when m_c = -inf);
+//     L_J = fma(l_c, w_c, L_J) and O_J[d] = fma(o_c[d], w_c, O_J[d]) over its four sub-chunks
+//     ascending (a sub-chunk without rows contributes l = 0, o = 0, w = 0)
+//   level 2: m = max_J M_J; W_J = bm_expf(M_J - m) (0 when M_J = -inf); l = fma(L_J, W_J, l),
+//     o[d] = fma(O_J[d], W_J, o[d]) over the super-chunks ascending, the appended rows last.
+// out = bf16(o / l).
 BMO_API void bmo_attention(const uint16_t *q, const uint16_t *k_base, const uint16_t *v_base,
                            int M, int H, int Hkv, int kv_rows, int sigma, int cache_len,
                            int n_pend, int P, int role, uint16_t *out) {
     const int G = H / Hkv;
     const float scale = 0.08838834764831845f;   // 1/sqrt(128)
-    const int n_hist = (cache_len + BM_ATTN_CHUNK - 1) / BM_ATTN_CHUNK;
-    const int n_chunks = n_hist + 1;
+    const int SUB = BM_ATTN_SUPER / BM_ATTN_CHUNK;
+    const int n_hs = (cache_len + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER;
+    const int n_super = n_hs + 1;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int m = 0; m < M; ++m) {
         for (int h = 0; h < H; ++h) {
@@ -350,55 +355,69 @@ BMO_API void bmo_attention(const uint16_t *q, const uint16_t *k_base, const uint
             const uint16_t *vb = v_base + (size_t)hk * kv_rows * 128;
             float qf[128];
             for (int d = 0; d < 128; ++d) qf[d] = bm_bf16_to_f32(q[((size_t)m * H + h) * 128 + d]);
-            float *cm = (float *)malloc(sizeof(float) * n_chunks * 130);
-            float *cl = cm + n_chunks;
-            float *co = cl + n_chunks;
+            float *SM = (float *)malloc(sizeof(float) * n_super * 130);   // M_J, L_J, O_J[128]
+            float *SL = SM + n_super;
+            float *SO = SL + n_super;
             float gmax = -INFINITY;
-            for (int j = 0; j < n_chunks; ++j) {
-                const int c0 = j < n_hist ? j * BM_ATTN_CHUNK : sigma;
-                const int cn = j < n_hist
-                                   ? (cache_len - c0 < BM_ATTN_CHUNK ? cache_len - c0 : BM_ATTN_CHUNK)
-                                   : M;
-                float sc[BM_ATTN_CHUNK];
-                int vis[BM_ATTN_CHUNK];
-                float mj = -INFINITY;
-                for (int c = 0; c < cn; ++c) {
-                    vis[c] = bm_visible(role, m, c0 + c, sigma, cache_len, n_pend, P);
-                    if (!vis[c]) continue;
-                    const uint16_t *kr = kb + (size_t)(c0 + c) * 128;
-                    float acc = 0.0f;
-                    for (int d = 0; d < 128; ++d) acc = fmaf(qf[d], bm_bf16_to_f32(kr[d]), acc);
-                    sc[c] = acc * scale;
-                    mj = sc[c] > mj ? sc[c] : mj;
+            for (int J = 0; J < n_super; ++J) {
+                const int key0 = J < n_hs ? J * BM_ATTN_SUPER : sigma;
+                const int nkeys = J < n_hs ? (cache_len - key0 < BM_ATTN_SUPER ? cache_len - key0 : BM_ATTN_SUPER) : M;
+                float cm[8], cl[8], co[8][128];
+                for (int c = 0; c < SUB; ++c) {
+                    const int c0 = key0 + c * BM_ATTN_CHUNK;
+                    int cn = nkeys - c * BM_ATTN_CHUNK;
+                    cn = cn > BM_ATTN_CHUNK ? BM_ATTN_CHUNK : cn;
+                    float sc[BM_ATTN_CHUNK];
+                    int vis[BM_ATTN_CHUNK];
+                    float mc = -INFINITY;
+                    for (int k = 0; k < cn; ++k) {
+                        vis[k] = bm_visible(role, m, c0 + k, sigma, cache_len, n_pend, P);
+                        if (!vis[k]) continue;
+                        const uint16_t *kr = kb + (size_t)(c0 + k) * 128;
+                        float acc = 0.0f;
+                        for (int d = 0; d < 128; ++d) acc = fmaf(qf[d], bm_bf16_to_f32(kr[d]), acc);
+                        sc[k] = acc * scale;
+                        mc = sc[k] > mc ? sc[k] : mc;
+                    }
+                    cm[c] = mc;
+                    for (int d = 0; d < 128; ++d) co[c][d] = 0.0f;
+                    float lane[32];
+                    for (int k = 0; k < 32; ++k) lane[k] = 0.0f;
+                    for (int k = 0; k < cn; ++k) {
+                        if (!vis[k]) continue;
+                        const float p = bm_expf(sc[k] - mc);
+                        lane[k] = p;
+                        const float pb = bm_bf16_rn(p);
+                        const uint16_t *vr = vb + (size_t)(c0 + k) * 128;
+                        for (int d = 0; d < 128; ++d) co[c][d] = fmaf(pb, bm_bf16_to_f32(vr[d]), co[c][d]);
+                    }
+                    cl[c] = bmo_butterfly32(lane);
                 }
-                cm[j] = mj;
-                float *oj = co + (size_t)j * 128;
-                for (int d = 0; d < 128; ++d) oj[d] = 0.0f;
-                float lane[32];
-                for (int c = 0; c < 32; ++c) lane[c] = 0.0f;
-                for (int c = 0; c < cn; ++c) {
-                    if (!vis[c]) continue;
-                    const float p = bm_expf(sc[c] - mj);
-                    lane[c] = p;
-                    const float pb = bm_bf16_rn(p);
-                    const uint16_t *vr = vb + (size_t)(c0 + c) * 128;
-                    for (int d = 0; d < 128; ++d) oj[d] = fmaf(pb, bm_bf16_to_f32(vr[d]), oj[d]);
+                float MJ = -INFINITY;
+                for (int c = 0; c < SUB; ++c) MJ = cm[c] > MJ ? cm[c] : MJ;
+                float LJ = 0.0f;
+                float *OJ = SO + (size_t)J * 128;
+                for (int d = 0; d < 128; ++d) OJ[d] = 0.0f;
+                for (int c = 0; c < SUB; ++c) {
+                    const float w = cm[c] > -INFINITY ? bm_expf(cm[c] - MJ) : 0.0f;
+                    LJ = fmaf(cl[c], w, LJ);
+                    for (int d = 0; d < 128; ++d) OJ[d] = fmaf(co[c][d], w, OJ[d]);
                 }
-                cl[j] = bmo_butterfly32(lane);
-                gmax = mj > gmax ? mj : gmax;
+                SM[J] = MJ;
+                SL[J] = LJ;
+                gmax = MJ > gmax ? MJ : gmax;
             }
             float l = 0.0f, o[128];
             for (int d = 0; d < 128; ++d) o[d] = 0.0f;
-            for (int j = 0; j < n_chunks; ++j) {
-                if (!(cm[j] > -INFINITY)) continue;
-                const float w = bm_expf(cm[j] - gmax);
-                l = fmaf(cl[j], w, l);
-                const float *oj = co + (size_t)j * 128;
-                for (int d = 0; d < 128; ++d) o[d] = fmaf(oj[d], w, o[d]);
+            for (int J = 0; J < n_super; ++J) {
+                const float w = SM[J] > -INFINITY ? bm_expf(SM[J] - gmax) : 0.0f;
+                l = fmaf(SL[J], w, l);
+                const float *OJ = SO + (size_t)J * 128;
+                for (int d = 0; d < 128; ++d) o[d] = fmaf(OJ[d], w, o[d]);
             }
             for (int d = 0; d < 128; ++d)
                 out[(size_t)m * H * 128 + h * 128 + d] = bm_f32_to_bf16(o[d] / l);
-            free(cm);
+            free(SM);
         }
     }
 }

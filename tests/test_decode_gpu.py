@@ -189,36 +189,3 @@ def test_captured_prompt_slabs_equal_operator_prefill(geometry, seq):
         assert torch.equal(shared[0, i, 0, :, :seq, :].view(torch.int16), ck[0].view(torch.int16)), f"K layer {i}"
         assert torch.equal(shared[1, i, 0, :, :seq, :].view(torch.int16), cv[0].view(torch.int16)), f"V layer {i}"
         assert not shared[:, i, 0, :, seq:sigma, :].any(), "rows past the prompt were written"
-
-
-def test_three_per_sm_attention_twins_give_the_same_stream(monkeypatch):
-    """For history lengths whose chunk grid needs a second wave of CTAs the atlas replays twins of the wide
-    graphs captured with the attention chunk kernel built for three CTAs per SM.  On the 1.7B layer geometry
-    with a 1024-row segment the twins exist, are chosen past ~560 history rows, and a generation that crosses
-    that length produces the same tokens as an atlas without twins."""
-    geometry = dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096)
-    cfg = synthetic.make_config(geometry, block_size=8)
-    ladder, m_set, roles = (1024,), (1, 9, 16), ("ar", "draft", "verify")
-    model, _ = _model(cfg, 5, 1024 + 17)
-    prompt = synthetic.random_prompt(520, cfg["vocab_size"], seed=9)
-    streams = []
-    for twins in ("1", "0"):
-        monkeypatch.setenv("BM_DENSE_TWINS", twins)
-        atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=ladder, m_set=m_set, roles=roles,
-                           capture_verbose=False)
-        if twins == "1":
-            assert {(9, 1024, "draft"), (16, 1024, "draft"), (9, 1024, "verify")} <= set(atlas.dense_graphs)
-            assert not atlas._prefer_dense(16, 300) and atlas._prefer_dense(16, 700)
-            assert atlas.get_graph(16, 1024, "draft", 700) is atlas.dense_graphs[(16, 1024, "draft")]
-            assert atlas.get_graph(16, 1024, "draft", 300) is atlas.graphs[(16, 1024, "draft")]
-        else:
-            assert not atlas.dense_graphs
-        policy = synthetic.AcceptancePolicy("categorical", 8, seed=3)
-        fc, fa = acceptance_hooks(FG, policy)
-        monkeypatch.setattr(FG, "_fused_draft_chain", fc)
-        monkeypatch.setattr(FG, "_fused_verify_accept", fa)
-        out, _ = FG.fast_hybrid_generate(model, atlas, prompt, max_gen_len=120, eos_ids=())
-        monkeypatch.undo()
-        streams.append(out.cpu().tolist())
-        assert native.lib().bm_device_error() == 0
-    assert streams[0] == streams[1] and len(streams[0]) == 120
