@@ -17,6 +17,7 @@
 #include "t2_gemv_rowwarp.cuh"
 #include "t2_gemv_direct.cuh"
 #include "dense_head.cuh"
+#include "t2_gemm_wide.cuh"
 
 #include <cudaTypedefs.h>
 #include <map>
@@ -686,7 +687,7 @@ int bm_zero_words(void *p, int n, void *stream) {
 
 int bm_quant_rows_amax(const void *x, const void *amax_in, void *amax_zero, int M, int K, void *q, void *q_prep,
                        void *asum, void *s, int pdl, void *stream) {
-    if (!x || !amax_in || !s || (!q && !q_prep) || M < 1 || M > 32 || K < 256 || (K % 256) != 0 || !aligned16(x))
+    if (!x || !amax_in || !s || (!q && !q_prep) || M < 1 || M > 65535 || K < 256 || (K % 256) != 0 || !aligned16(x))
         return BM_EINVAL;
     if ((q_prep == nullptr) != (asum == nullptr) || amax_zero == amax_in) return BM_EINVAL;
     bm::QuantSink sink{static_cast<int8_t *>(q), static_cast<int8_t *>(q_prep), static_cast<int32_t *>(asum)};
@@ -714,7 +715,7 @@ int bm_qknorm_rope_kvappend(const void *xqkv, const void *q_w, const void *k_w, 
                             const void *sin_t, const void *positions, int M, int H, int Hkv, void *k_base,
                             void *v_base, int kv_rows, int sigma, void *q_out, int pdl, void *stream) {
     if (!xqkv || !q_w || !k_w || !cos_t || !sin_t || !positions || !k_base || !v_base || !q_out) return BM_EINVAL;
-    if (M < 1 || M > BM_MAX_W || H < 1 || Hkv < 1 || (H % Hkv) != 0 || sigma < 0 || sigma + M > kv_rows) return BM_EINVAL;
+    if (M < 1 || M > 65535 || H < 1 || Hkv < 1 || (H % Hkv) != 0 || sigma < 0 || sigma + M > kv_rows) return BM_EINVAL;
     bm::RopeParams p;
     p.xqkv = static_cast<const uint16_t *>(xqkv);
     p.q_w = static_cast<const uint16_t *>(q_w);
@@ -950,6 +951,85 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     bm::verify_accept_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int64_t *>(draft), static_cast<const int64_t *>(verify), D, static_cast<int *>(n_out));
     return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------- prompt (many-row) path
+int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s, const void *ws, int T,
+                    int N, int K, int ldc, int pdl, void *stream) {
+    if (!A_prep || !a_sums || !B || !C || !s || !ws || T < 1 || N < bm::kWideRows || (N % bm::kWideRows) != 0 ||
+        K < BM_GROUP || (K % BM_GROUP) != 0 || ldc < N)
+        return BM_EINVAL;
+    if (!aligned16(A_prep) || !aligned16(B)) return BM_EINVAL;
+    const int ng = K / BM_GROUP, SB = bm::wide_slots_per_stage(ng);
+    size_t smem = 0;
+    for (int s0 = 0; s0 < BM_SLOTS; s0 += SB) {
+        int ngs = 0;
+        for (int i = 0; i < SB; ++i) {
+            const int t = (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS;
+            ngs += t > 0 ? t : 0;
+        }
+        const size_t need = (size_t)bm::wide_smem_layout(ngs > 0 ? ngs : 1).total;
+        smem = need > smem ? need : smem;
+    }
+    if (smem > (size_t)kMaxSmemPerCta) return BM_EINVAL;
+    bm::WideParams p;
+    p.A = static_cast<const int8_t *>(A_prep);
+    p.asum = static_cast<const int32_t *>(a_sums);
+    p.s = static_cast<const float *>(s);
+    p.B = static_cast<const uint8_t *>(B);
+    p.ws = static_cast<const uint16_t *>(ws);
+    p.C = static_cast<uint16_t *>(C);
+    p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.pdl = pdl & BM_PDL_OVERLAP;
+    const dim3 grid(N / bm::kWideRows, (T + bm::kWideTokens - 1) / bm::kWideTokens);
+    if (grid.y > 65535) return BM_EINVAL;
+    return launch_ex(bm::t2_gemm_wide_kernel, grid, dim3(bm::kWideThreads), smem, static_cast<cudaStream_t>(stream), p.pdl, p);
+}
+
+namespace {
+// Slabs, grid.x and scratch layout of the prompt-mode attention.
+struct PromptAttnPlan { int n_slabs, units, NJ, nq, Z; size_t ticket_bytes, total; };
+bool prompt_attn_plan(int T, int hist0, int slab_rows, int H, int Hkv, PromptAttnPlan *pl) {
+    if (T < 1 || hist0 < 0 || slab_rows < 1 || slab_rows > BM_MAX_W || H < 1 || Hkv < 1 || (H % Hkv) != 0) return false;
+    pl->n_slabs = (T + slab_rows - 1) / slab_rows;
+    pl->units = 0;
+    for (int s = 0; s < pl->n_slabs; ++s) pl->units += (hist0 + s * slab_rows + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER + 1;
+    pl->NJ = (hist0 + T + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER + 1;
+    bm::attn_query_split((H / Hkv) * slab_rows, &pl->nq, &pl->Z);
+    pl->ticket_bytes = ((size_t)pl->n_slabs * Hkv * pl->Z * 4 + 1023) / 1024 * 1024;
+    pl->total = pl->ticket_bytes + (size_t)T * H * pl->NJ * 4 * 2 + (size_t)T * H * pl->NJ * 128 * 4;
+    return pl->NJ <= bm::kAttnMaxNJ;
+}
+}  // namespace
+
+long long bm_prompt_attention_scratch_bytes(int T, int hist0, int slab_rows, int H, int Hkv) {
+    PromptAttnPlan pl;
+    return prompt_attn_plan(T, hist0, slab_rows, H, Hkv, &pl) ? (long long)pl.total : -1;
+}
+
+int bm_prompt_attention(const void *q, const void *k_base, const void *v_base, int T, int hist0, int slab_rows, int H,
+                        int Hkv, int kv_rows, void *scratch, void *att_out, void *amax_out, int pdl, void *stream) {
+    PromptAttnPlan pl;
+    if (!q || !k_base || !v_base || !scratch || !att_out || !amax_out) return BM_EINVAL;
+    if (!prompt_attn_plan(T, hist0, slab_rows, H, Hkv, &pl) || hist0 + T > kv_rows) return BM_EINVAL;
+    if (!aligned16(q) || !aligned16(k_base) || !aligned16(v_base) || !aligned16(scratch) || !aligned16(att_out)) return BM_EINVAL;
+    bm::AttnParams p = {};
+    p.q = static_cast<const uint16_t *>(q);
+    p.k_base = static_cast<const uint16_t *>(k_base);
+    p.v_base = static_cast<const uint16_t *>(v_base);
+    p.state = nullptr;
+    p.M = T; p.H = H; p.Hkv = Hkv; p.kv_rows = kv_rows; p.sigma = hist0; p.NJ = pl.NJ;
+    char *sc = static_cast<char *>(scratch);
+    p.tickets = reinterpret_cast<unsigned int *>(sc);
+    p.pm = reinterpret_cast<float *>(sc + pl.ticket_bytes);
+    p.pl = p.pm + (size_t)T * H * pl.NJ;
+    p.po = p.pl + (size_t)T * H * pl.NJ;
+    p.att = static_cast<uint16_t *>(att_out);
+    p.amax = static_cast<unsigned int *>(amax_out);
+    p.pdl = pdl & BM_PDL_OVERLAP;
+    p.slab_rows = slab_rows;
+    p.slab_hist0 = hist0;
+    const dim3 grid(pl.units, Hkv, pl.Z);
+    return launch_attention<false>(pl.nq, grid, bm::attn_smem_bytes(pl.nq), static_cast<cudaStream_t>(stream), p.pdl, p);
 }
 
 // ---------------------------------------------------------------------------- dense draft heads

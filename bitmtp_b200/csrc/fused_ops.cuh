@@ -170,7 +170,8 @@ __global__ void __launch_bounds__(kQuantAmaxThreads) quant_rows_amax_kernel(
         if (i == 0) s_out[m] = s;
     }
     emit_codes(sink, (size_t)m * K, K, i, quant8(v, s), active, lane);
-    if (amax_zero != nullptr && blockIdx.x == 0 && threadIdx.x < M) amax_zero[threadIdx.x] = 0u;
+    if (amax_zero != nullptr && blockIdx.x == 0)
+        for (int r = threadIdx.x; r < M; r += kQuantAmaxThreads) amax_zero[r] = 0u;
 }
 
 // =============================================================================

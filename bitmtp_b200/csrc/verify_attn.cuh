@@ -61,6 +61,12 @@ struct AttnParams {
     const int64_t *positions;        // [M]
     uint16_t *k_out, *v_out;         // the layer's planes (same memory as k_base / v_base)
     float eps;
+    // Prompt mode (plain build only; slab_rows > 0): M prompt rows whose K / V already sit at rows
+    // [slab_hist0, slab_hist0 + M) of the planes are served as AR-causal slabs of slab_rows rows: slab s
+    // sees history [0, slab_hist0 + s * slab_rows) and its own rows.  blockIdx.x runs over the
+    // (slab, super-chunk) pairs in slab order; `state` is not read; q, att, amax and the partials are
+    // indexed by prompt row; tickets [slabs][Hkv][gridDim.z].
+    int slab_rows, slab_hist0;
 };
 
 __host__ __device__ inline size_t attn_scratch_bytes(int M, int H, int sigma) {
@@ -216,14 +222,35 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     // while the predecessor is still running.
     const bool early = (p.pdl & BM_PDL_STABLE_STATE) != 0;
     if (p.pdl && !early) pdl_wait();
-    const int J = blockIdx.x, hk = blockIdx.y, z = blockIdx.z;
-    const int cache_len = attn_cache_len(p), n_pend = p.state->n_pend, role = p.state->role, P_ = p.state->P;
+    const int hk = blockIdx.y, z = blockIdx.z;
+    int J = blockIdx.x, M_ = p.M, sigma_ = p.sigma, r0 = 0, cache_len, n_pend, role, P_;
+    unsigned int *ticket = p.tickets + hk * gridDim.z + z;
+    if (!ROPE && p.slab_rows > 0) {
+        // prompt mode: find this CTA's slab; a slab with history h has ceil(h / 128) + 1 super-chunks
+        int s = 0, rem = J, h = p.slab_hist0;
+        for (;;) {
+            const int units = (h + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER + 1;
+            if (rem < units) break;
+            rem -= units;
+            ++s;
+            h += p.slab_rows;
+        }
+        r0 = s * p.slab_rows;
+        M_ = min(p.slab_rows, p.M - r0);
+        cache_len = sigma_ = h;
+        n_pend = 0; role = BM_ROLE_AR; P_ = 0;
+        J = rem < (h + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER ? rem : p.NJ - 1;
+        ticket += (size_t)s * p.Hkv * gridDim.z;
+        if (M_ <= 0) return;
+    } else {
+        cache_len = attn_cache_len(p); n_pend = p.state->n_pend; role = p.state->role; P_ = p.state->P;
+    }
     const int n_hs = (cache_len + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER;     // history super-chunks with rows
     const bool fresh = J == p.NJ - 1;
     if (!fresh && J >= n_hs) return;
-    const int key0 = fresh ? p.sigma : J * BM_ATTN_SUPER;
-    const int nkeys = fresh ? p.M : min(BM_ATTN_SUPER, cache_len - key0);
-    const int G = p.H / p.Hkv, QV = G * p.M, heads = p.H + 2 * p.Hkv;
+    const int key0 = fresh ? sigma_ : J * BM_ATTN_SUPER;
+    const int nkeys = fresh ? M_ : min(BM_ATTN_SUPER, cache_len - key0);
+    const int G = p.H / p.Hkv, QV = G * M_, heads = p.H + 2 * p.Hkv;
     const int q_lo = z * QC;
     if (q_lo >= QV) return;
 
@@ -250,7 +277,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     // share of those rows (m = warp, warp + 8, ...: at most kFreshPerWarp)
     const int qi = warp, qv = q_lo + qi;
     const bool q_live = qi < QC && qv < QV;
-    const int qg_ = q_live ? qv / p.M : 0, qm = q_live ? qv - qg_ * p.M : 0;
+    const int qg_ = q_live ? qv / M_ : 0, qm = q_live ? qv - qg_ * M_ : 0;
     constexpr int kFreshPerWarp = BM_MAX_W / (kAttnThreads / 32);
     uint2 qw = make_uint2(0u, 0u), kw = qw, qcos = qw, qsin = qw;
     uint2 kcos[kFreshPerWarp], ksin[kFreshPerWarp];
@@ -268,7 +295,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 #pragma unroll
                 for (int k = 0; k < kFreshPerWarp; ++k) {
                     const int m = warp + k * (kAttnThreads / 32);
-                    if (m < p.M) {
+                    if (m < M_) {
                         const size_t pos = (size_t)p.positions[m];
                         kcos[k] = *reinterpret_cast<const uint2 *>(p.cos_t + pos * 128 + 4 * lane);
                         ksin[k] = *reinterpret_cast<const uint2 *>(p.sin_t + pos * 128 + 4 * lane);
@@ -288,7 +315,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 #pragma unroll
             for (int k = 0; k < kFreshPerWarp; ++k) {
                 const int m = warp + k * (kAttnThreads / 32);
-                if (m < p.M) {
+                if (m < M_) {
                     kraw[k] = *reinterpret_cast<const uint2 *>(p.xqkv + ((size_t)m * heads + p.H + hk) * 128 + 4 * lane);
                     vraw[k] = *reinterpret_cast<const uint2 *>(p.xqkv + ((size_t)m * heads + p.H + p.Hkv + hk) * 128 + 4 * lane);
                 }
@@ -304,7 +331,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 #pragma unroll
                 for (int k = 0; k < kFreshPerWarp; ++k) {
                     const int m = warp + k * (kAttnThreads / 32);
-                    if (m < p.M) {
+                    if (m < M_) {
                         const size_t pos = (size_t)p.positions[m];
                         kcos[k] = *reinterpret_cast<const uint2 *>(p.cos_t + pos * 128 + 4 * lane);
                         ksin[k] = *reinterpret_cast<const uint2 *>(p.sin_t + pos * 128 + 4 * lane);
@@ -326,7 +353,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 #pragma unroll
             for (int k = 0; k < kFreshPerWarp; ++k) {
                 const int m = warp + k * (kAttnThreads / 32);
-                if (m >= p.M) break;                                       // warp-uniform
+                if (m >= M_) break;                                       // warp-uniform
                 float o[4];
                 rope_head_vector(kraw[k], kw, kcos[k], ksin[k], p.eps, lane, o);
                 const uint2 kbits = make_uint2((uint32_t)bm_f32_to_bf16(o[0]) | ((uint32_t)bm_f32_to_bf16(o[1]) << 16),
@@ -334,7 +361,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
                 *reinterpret_cast<uint2 *>(Ks + m * kKeyStride + 4 * lane) = kbits;
                 *reinterpret_cast<uint2 *>(Vs + m * 128 + 4 * lane) = vraw[k];
                 if (z == 0) {
-                    const size_t row = ((size_t)hk * p.kv_rows + p.sigma + m) * 128 + 4 * lane;
+                    const size_t row = ((size_t)hk * p.kv_rows + sigma_ + m) * 128 + 4 * lane;
                     *reinterpret_cast<uint2 *>(p.k_out + row) = kbits;
                     *reinterpret_cast<uint2 *>(p.v_out + row) = vraw[k];
                 }
@@ -352,7 +379,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
         if (qi < QC) {
             float4 qf = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (q_live) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(p.q + ((size_t)qm * p.H + hk * G + qg_) * 128 + 4 * lane);
+                const uint2 raw = *reinterpret_cast<const uint2 *>(p.q + ((size_t)(r0 + qm) * p.H + hk * G + qg_) * 128 + 4 * lane);
                 qf = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
                                  __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
             }
@@ -370,14 +397,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 #pragma unroll
         for (int t = 0; t < NQ; ++t) {
             const int v = min(q_lo + sg * NQ + t, QV - 1);        // vectors past QV repeat the last one; dropped below
-            rows[t] = v - (v / p.M) * p.M;
+            rows[t] = v - (v / M_) * M_;
         }
         float *mcw = mc + c * QC + sg * NQ, *lcw = lc + c * QC + sg * NQ;
         float *ocw = oc + ((size_t)c * QC + sg * NQ) * 128;
         if (cn > 0) {
             attn_sub_pass<NQ>(Ks + c * BM_ATTN_CHUNK * kKeyStride, Vs + c * BM_ATTN_CHUNK * 128, Qs + sg * NQ * 128,
                               Ps + sg * NQ * BM_ATTN_SUPER, c * BM_ATTN_CHUNK, rows, key0 + c * BM_ATTN_CHUNK, cn, lane,
-                              p.sigma, role, cache_len, n_pend, P_, mcw, lcw, ocw);
+                              sigma_, role, cache_len, n_pend, P_, mcw, lcw, ocw);
         } else {
 #pragma unroll
             for (int t = 0; t < NQ; ++t) {
@@ -404,14 +431,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
             O[2] = fmaf(o.z, w, O[2]);
             O[3] = fmaf(o.w, w, O[3]);
         }
-        const size_t pb = ((size_t)qm * p.H + hk * G + qg_) * p.NJ + J;
+        const size_t pb = ((size_t)(r0 + qm) * p.H + hk * G + qg_) * p.NJ + J;
         *reinterpret_cast<float4 *>(p.po + pb * 128 + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
         if (lane == 0) { p.pm[pb] = MJ; p.pl[pb] = L; }
     }
     // ticket: the last CTA of this (kv head, query group) to get here merges the super-chunks
     __threadfence();
     __syncthreads();
-    unsigned int *ticket = p.tickets + hk * gridDim.z + z;
     if (tid == 0) sh_ticket = atomicAdd(ticket, 1u);
     __syncthreads();
     if (sh_ticket != (unsigned int)n_hs) return;                  // n_hs + 1 CTAs take part
@@ -421,7 +447,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
 
     // level 2: super-chunk partials of query vector qi in ascending order (history, then the replay's rows)
     const int nv = n_hs + 1;
-    const size_t pb = ((size_t)qm * p.H + hk * G + qg_) * p.NJ;
+    const size_t pb = ((size_t)(r0 + qm) * p.H + hk * G + qg_) * p.NJ;
     constexpr int kBatch = 8;
     float4 part[kBatch];
     // the first batch of numerators is requested together with the maxima and sums: one round trip
@@ -475,9 +501,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     for (int e = 0; e < 4; ++e) v[e] = bm_bf16_rn(o[e] / l);
     const uint2 bits = make_uint2((uint32_t)bm_f32_to_bf16(v[0]) | ((uint32_t)bm_f32_to_bf16(v[1]) << 16),
                                   (uint32_t)bm_f32_to_bf16(v[2]) | ((uint32_t)bm_f32_to_bf16(v[3]) << 16));
-    *reinterpret_cast<uint2 *>(p.att + (size_t)qm * p.H * 128 + (hk * G + qg_) * 128 + 4 * lane) = bits;
+    *reinterpret_cast<uint2 *>(p.att + (size_t)(r0 + qm) * p.H * 128 + (hk * G + qg_) * 128 + 4 * lane) = bits;
     const float amax = warp_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
-    if (lane == 0 && amax != 0.0f) atomicMax(&p.amax[qm], __float_as_uint(amax));
+    if (lane == 0 && amax != 0.0f) atomicMax(&p.amax[r0 + qm], __float_as_uint(amax));
 }
 
 }  // namespace bm

@@ -271,10 +271,17 @@ class GraphAtlas:
         Transformer.forward_sdlm_prefill, which launches every operator of every slab from the host
         and computes all rows' logits; the decode loops need only the last row (reference:
         fast_generate.py:203-222 take `logits[-1]`).  Returns fp32 logits [1, vocab]."""
-        g = self.prefill_graphs[sigma]
         seq = int(prompt_ids.shape[0])
         if seq < 1 or seq > sigma:
             raise ValueError(f"prompt of {seq} tokens does not fit segment {sigma}")
+        if self.model.wide_prefill_supported() and seq > PREFILL_CHUNK:
+            # the many-row kernels: every projection reads its weights once per 32 prompt rows, one
+            # attention launch per layer; K / V rows land in place.  Bit-identical to the slab replays below.
+            shared = self.kv_buffers[sigma]
+            planes = [(shared[0, i], shared[1, i]) for i in range(self.n_layers)]
+            return self.model.prefill_wide(prompt_ids, planes, sigma + self.M_max, self.prefill_logits
+                                           if getattr(self, "prefill_logits", None) is not None else None)
+        g = self.prefill_graphs[sigma]
         ids = prompt_ids.to(torch.int64).contiguous()
         n = 0
         for c0 in range(0, seq, PREFILL_CHUNK):

@@ -641,6 +641,92 @@ class Transformer(nn.Module):
                              ldc=W.n_pad, pdl=pdl)
         return logits_buf[:, : self._lm_head_t2_vocab]
 
+    def wide_prefill_supported(self) -> bool:
+        """The many-row prompt path needs every projection's row count to be a multiple of 128 and the
+        flat quantisation's K % 256 == 0; every released geometry and the test geometries have both."""
+        a = self.args
+        q_dim, kv_dim = a.n_heads * a.head_dim, a.n_kv_heads * a.head_dim
+        return (all(n % 128 == 0 for n in (q_dim + 2 * kv_dim, a.dim, 2 * a.ffn_dim)) and q_dim % 256 == 0
+                and a.dim % 256 == 0 and a.ffn_dim % 128 == 0 and os.environ.get("BM_WIDE_PREFILL", "1") != "0")
+
+    @torch.no_grad()
+    def prefill_rows_wide(self, token_values: torch.Tensor, kv_planes: List[SDLMLayerCache], kv_rows: int,
+                          hist0: int, ws: "PromptWorkspace", scratch: torch.Tensor) -> None:
+        """One wave of the prompt forward on the many-row kernels: T = len(token_values) rows at positions
+        hist0 .. hist0 + T - 1, whose K / V rows are written in place at rows [hist0, hist0 + T) of every
+        layer's planes (`kv_planes[i]` = (k, v) [1, n_kv, kv_rows, hd]); rows [0, hist0) are history.
+        Same arithmetic, row for row, as the slab-by-slab prefill (forward_sdlm_prefill), so K / V rows and
+        the residual stream equal it bit for bit: every projection is bm_t2_gemm_wide (tensor cores, each
+        weight byte read once per 32 rows), the attention one launch over AR-causal slabs of PREFILL_CHUNK
+        rows.  Leaves the residual stream in ws.h / ws.ffn_out (reference: model.py:1306-1340)."""
+        a = self.args
+        T = int(token_values.shape[0])
+        eps, pdl = a.norm_eps, self.use_pdl
+        torch.add(torch.arange(T, device=token_values.device, dtype=torch.int64), hist0, out=ws.positions[:T])
+        pos = ws.positions[:T]
+        L0 = self.layers[0]
+        h, q, q_sum, s = ws.h[:T], ws.q[:T], ws.q_sum[:T], ws.s[:T]
+        qsink = {"h": h, "qp": q, "asum": q_sum, "s": s}
+        ops.zero_words(ws.att_amax[0])
+        ops.rmsnorm_fused(self.embed_tokens.weight.data, L0.input_layernorm.weight.data, eps, M=T,
+                          gather=token_values, pdl=pdl, out=qsink)
+        for i, layer in enumerate(self.layers):
+            at, ff = layer.attention, layer.feed_forward
+            if i > 0:
+                ops.rmsnorm_fused(ws.ffn_out[:T], layer.input_layernorm.weight.data, eps, M=T, res=h, pdl=pdl, out=qsink)
+            ops.t2_gemm_wide(q, q_sum, at.wqkv_weight, s, at.wqkv_scale, out=ws.xqkv[:T], pdl=pdl)
+            k_l, v_l = kv_planes[i]
+            kl, vl = _LayerView(k_l, kv_rows), _LayerView(v_l, kv_rows)
+            ops.qknorm_rope_kvappend(ws.xqkv[:T], at.q_norm.weight.data, at.k_norm.weight.data, eps, at.rope_cos,
+                                     at.rope_sin, pos, a.n_heads, a.n_kv_heads, kl, vl, hist0, pdl=pdl, q_out=ws.qrot[:T])
+            ops.prompt_attention(ws.qrot[:T], kl, vl, hist0, PREFILL_CHUNK, scratch, att=ws.att[:T],
+                                 amax=ws.att_amax[i & 1][:T], pdl=pdl)
+            ops.quant_rows_amax(ws.att[:T], ws.att_amax[i & 1][:T], prep=(ws.att_q[:T], ws.att_sum[:T]), s=ws.att_s[:T],
+                                amax_zero=ws.att_amax[(i + 1) & 1][:T], pdl=pdl)
+            ops.t2_gemm_wide(ws.att_q[:T], ws.att_sum[:T], at.o_proj.weight.data, ws.att_s[:T], at.o_proj.weight_scale,
+                             out=ws.attn_out[:T], pdl=pdl)
+            ops.rmsnorm_fused(h, layer.post_attention_layernorm.weight.data, eps, M=T, res=ws.attn_out[:T], pdl=pdl,
+                              out=qsink)
+            ops.t2_gemm_wide(q, q_sum, ff.w_gu, s, ff.w_gu_scale, out=ws.gu[:T], pdl=pdl)
+            ops.silu_mul_quant(ws.gu[:T], pdl=pdl, out=(None, ws.is_[:T]), prep=(ws.iq[:T], ws.i_sum[:T]))
+            ops.t2_gemm_wide(ws.iq[:T], ws.i_sum[:T], ff.down_proj.weight.data, ws.is_[:T], ff.down_proj.weight_scale,
+                             out=ws.ffn_out[:T], pdl=pdl)
+
+    @torch.no_grad()
+    def prefill_wide(self, token_values: torch.Tensor, kv_planes: List[SDLMLayerCache], kv_rows: int,
+                     logits_buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The whole prompt through prefill_rows_wide in waves of PREFILL_WAVE rows, then the packed head on
+        the last row (the only logit row a decode loop uses).  Returns fp32 logits [1, vocab]."""
+        seq = int(token_values.shape[0])
+        dev = token_values.device
+        a = self.args
+        self.prepare_t2_lm_head()
+        wave = min(PREFILL_WAVE, (seq + PREFILL_CHUNK - 1) // PREFILL_CHUNK * PREFILL_CHUNK)
+        ws = getattr(self, "_prompt_ws", None)
+        if ws is None or ws.T < wave:
+            ws = self._prompt_ws = PromptWorkspace(a, max(wave, PREFILL_WAVE if seq > PREFILL_WAVE else wave), dev)
+        ids = token_values.to(torch.int64).contiguous()
+        n = 0
+        for c0 in range(0, seq, wave):
+            n = min(wave, seq - c0)
+            key = (n, c0)
+            cache = self.__dict__.setdefault("_prompt_scratch", {})
+            scratch = cache.get(key)
+            if scratch is None:
+                if len(cache) > 16:
+                    cache.clear()
+                scratch = cache[key] = ops.prompt_attention_scratch(n, c0, PREFILL_CHUNK, a.n_heads, a.n_kv_heads, dev)
+            self.prefill_rows_wide(ids[c0:c0 + n], kv_planes, kv_rows, c0, ws, scratch)
+        if logits_buf is None:
+            logits_buf = torch.empty((1, self._lm_head_n_pad), dtype=torch.float32, device=dev)
+        # final norm + packed head on the last row of the last wave
+        W1 = self.workspace(1)
+        ops.rmsnorm_fused(ws.h, self.norm.weight.data, a.norm_eps, M=1, res=ws.ffn_out, row0=n - 1, pdl=self.use_pdl,
+                          out={"qp": W1.hq, "asum": W1.h_sum, "s": W1.hs})
+        ops.t2_gemv_prepared(W1.hq[:1], W1.h_sum[:1], self._lm_head_t2_w, W1.hs[:1], self._lm_head_t2_scale,
+                             out_kind=native.OUT_F32_OF_BF16, out=logits_buf, ldc=self._lm_head_n_pad, pdl=self.use_pdl)
+        return logits_buf[:, : self._lm_head_t2_vocab]
+
     @torch.no_grad()
     def forward_sdlm_prefill(self, token_values: torch.Tensor, cache: List[SDLMLayerCache],
                              positions: Optional[torch.Tensor] = None, block_size: int = 1,
@@ -681,6 +767,33 @@ class Transformer(nn.Module):
 
 
 PREFILL_CHUNK = 16
+PREFILL_WAVE = 256          # prompt rows one pass of the many-row path takes
+
+
+class PromptWorkspace:
+    """Intermediates of one wave of the many-row prompt path (Transformer.prefill_rows_wide)."""
+
+    def __init__(self, args: ModelArgs, T: int, device):
+        bf, i8, f32, i32 = torch.bfloat16, torch.int8, torch.float32, torch.int32
+        q_dim = args.n_heads * args.head_dim
+        qkv = q_dim + 2 * args.n_kv_heads * args.head_dim
+
+        def buf(shape, dtype):
+            return torch.empty(shape, dtype=dtype, device=device)
+
+        self.T = T
+        self.h = buf((T, args.dim), bf)
+        self.q, self.q_sum, self.s = buf((T, args.dim), i8), buf((T, args.dim // 128), i32), buf((T, 1), f32)
+        self.xqkv = buf((T, qkv), bf)
+        self.qrot = buf((T, args.n_heads, args.head_dim), bf)
+        self.att = buf((T, q_dim), bf)
+        self.att_amax = torch.zeros((2, T), dtype=i32, device=device)
+        self.att_q, self.att_sum, self.att_s = buf((T, q_dim), i8), buf((T, q_dim // 128), i32), buf((T, 1), f32)
+        self.attn_out = buf((T, args.dim), bf)
+        self.gu = buf((T, 2 * args.ffn_dim), bf)
+        self.iq, self.i_sum, self.is_ = buf((T, args.ffn_dim), i8), buf((T, args.ffn_dim // 128), i32), buf((T, 1), f32)
+        self.ffn_out = buf((T, args.dim), bf)
+        self.positions = torch.zeros(T, dtype=torch.int64, device=device)
 
 
 class _LayerView:

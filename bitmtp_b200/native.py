@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 SO_PATH = os.path.join(HERE, "libbitmtp_b200.so")
 SOURCES = ["bm_lib.cu"]
 HEADERS = ["bm_math.h", "bm_common.cuh", "t2_gemv.cuh", "fused_ops.cuh", "verify_attn.cuh", "t2_gemv_rowwarp.cuh",
-           "t2_gemv_direct.cuh", "dense_head.cuh"]
+           "t2_gemv_direct.cuh", "dense_head.cuh", "t2_gemm_wide.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -119,6 +119,9 @@ def _declare_optional(L) -> None:
                               ctypes.POINTER(vp), vp, ci, ci, vp],
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_dense_head": [vp, vp, ci, vp, ci, ci, ci, vp, ci, vp, ci, vp],
+        "bm_t2_gemm_wide": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
+        "bm_prompt_attention_scratch_bytes": [ci, ci, ci, ci, ci],
+        "bm_prompt_attention": [vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],
         "bm_draft_chain": [vp, ci, ci, ci, cf, vp, vp, vp, vp, vp],
         "bm_verify_accept": [vp, vp, ci, vp, vp],

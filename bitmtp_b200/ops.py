@@ -246,6 +246,35 @@ def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None, scratch: Optiona
     return idx, n, conf
 
 
+def t2_gemm_wide(a_prep: torch.Tensor, a_sums: torch.Tensor, b_packed: torch.Tensor, s: torch.Tensor, ws: torch.Tensor,
+                 *, out: torch.Tensor, pdl: bool = False) -> torch.Tensor:
+    """The packed product for many rows (a prompt): out bf16 [T, N], each row what t2_gemv_prepared gives it."""
+    T, K = a_prep.shape
+    N = b_packed.shape[0]
+    rc = native.lib().bm_t2_gemm_wide(_ptr(a_prep), _ptr(a_sums), _ptr(b_packed), _ptr(out), _ptr(s), _ptr(ws), T, N, K,
+                                      out.stride(0), int(pdl), _stream(a_prep.device))
+    check(rc, f"bm_t2_gemm_wide(T={T}, N={N}, K={K})")
+    return out
+
+
+def prompt_attention_scratch(T: int, hist0: int, slab_rows: int, H: int, Hkv: int, device) -> torch.Tensor:
+    n = int(native.lib().bm_prompt_attention_scratch_bytes(T, hist0, slab_rows, H, Hkv))
+    if n < 0:
+        raise RuntimeError(f"prompt attention does not take T={T}, hist0={hist0}, slab_rows={slab_rows}")
+    return torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=device)
+
+
+def prompt_attention(q: torch.Tensor, k_layer, v_layer, hist0: int, slab_rows: int, scratch: torch.Tensor, *,
+                     att: torch.Tensor, amax: torch.Tensor, pdl: bool = False) -> None:
+    """Causal attention of T prompt rows whose K / V rows already sit at [hist0, hist0 + T) of the layer's
+    planes; q bf16 [T, H, 128] rotated queries.  att bf16 [T, H*128], amax uint32 [T] (zero on entry)."""
+    T, H, _ = q.shape
+    Hkv, kv_rows = k_layer.shape[-3], k_layer.shape[-2]
+    rc = native.lib().bm_prompt_attention(_ptr(q), _ptr(k_layer), _ptr(v_layer), T, int(hist0), int(slab_rows), H, Hkv,
+                                          kv_rows, _ptr(scratch), _ptr(att), _ptr(amax), int(pdl), _stream(q.device))
+    check(rc, f"bm_prompt_attention(T={T}, hist0={hist0})")
+
+
 def dense_head(h: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor, w_scale: Optional[torch.Tensor] = None,
                h_scale_out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
     """Dense draft head: bf16 rows h [R, K] against the bf16 table w [N, K], or against its e4m3 copy

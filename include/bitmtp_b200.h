@@ -330,6 +330,29 @@ int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *
 int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf,
                          void *conf, void *n_out, void *scratch, void *stream);
 
+/* The packed product for MANY rows at once (a prompt): C bf16 [T, ldc] = the value bm_t2_gemv_prepared
+ * gives every row alone, bit for bit, with each weight byte read once per 32 rows instead of once per
+ * GEMV launch.  A_prep / a_sums / s: GEMV-ready INT8 rows, their group sums and multipliers for T rows;
+ * N % 128 == 0, K % 128 == 0.  Tensor-core kernel (mma.sync int8, exact int32 group sums, the GEMV's
+ * fp32 order).  Replaces the dense bf16 fallback of T2LinearKernel.forward behind forward_sdlm_prefill
+ * (src/bonsai_sft/gpu/model.py:650-656, 1306-1340). */
+int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s, const void *ws,
+                    int T, int N, int K, int ldc, int pdl, void *stream);
+
+/* Causal attention of a whole prompt in one launch.  The K / V rows of the T prompt rows already sit at
+ * rows [hist0, hist0 + T) of the planes (bm_qknorm_rope_kvappend with sigma = hist0); q bf16 [T, H, 128]
+ * are the rotated queries.  The rows are served as AR-causal slabs of slab_rows rows (slab s sees rows
+ * [0, hist0 + s * slab_rows) as history and its own rows causally), which is exactly what
+ * bm_verify_attention computes when called once per slab with sigma = cache_len = the slab's start, so
+ * the results equal that slab-by-slab prefill bit for bit.  att_out bf16 [T, H*128]; amax_out uint32 [T]
+ * (zero on entry) gathers the row absmax bits for bm_quant_rows_amax.  scratch:
+ * bm_prompt_attention_scratch_bytes(...) bytes, zero before first use.  slab_rows <= 32,
+ * hist0 + T <= 8064.  Replaces the SDPA call of the prompt forward (model.py:797-800). */
+long long bm_prompt_attention_scratch_bytes(int T, int hist0, int slab_rows, int H, int Hkv);
+int bm_prompt_attention(const void *q, const void *k_base, const void *v_base, int T, int hist0, int slab_rows,
+                        int H, int Hkv, int kv_rows, void *scratch, void *att_out, void *amax_out, int pdl,
+                        void *stream);
+
 /* Dense tied head for the draft role: out fp32 [R, ldc] = bf16-rounded logits of the R bf16 rows
  * h [R, K] against the dense table W [N, K].
  *   fp8 == 0: W is bf16 (the tied embedding itself), out = bf16(h . W^T): the `bf16_raw` branch of

@@ -21,7 +21,7 @@ _MODELS = {}
 
 
 def _model(cfg, seed, max_positions):
-    key = (json.dumps(cfg, sort_keys=True), seed)
+    key = (json.dumps(cfg, sort_keys=True), seed, max_positions)
     if key not in _MODELS:
         state = synthetic.make_state(cfg, seed=seed)
         m = generate.model_from_state(generate.args_from_config(cfg), state, DEV)
@@ -162,15 +162,20 @@ def test_confidence_stream_with_categorical_acceptance_equals_cpu_loop(oracle):
         assert stats[key] == want_stats[key], key
 
 
-@pytest.mark.parametrize("geometry,seq", [("tiny", 37), ("tiny", 16), ("tiny", 5), ("layers3", 70)])
-def test_captured_prompt_slabs_equal_operator_prefill(geometry, seq):
-    """GraphAtlas.prefill (captured 16-row slab graphs writing into the segment, head for the last
-    row only) against Transformer.forward_sdlm_prefill (every operator launched from the host,
-    rows written in place): the prompt's K/V rows in every layer and the last row's logits, bit
-    for bit, for ragged, exact and shorter-than-a-slab prompts."""
-    geo = synthetic.TINY if geometry == "tiny" else dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096)
+@pytest.mark.parametrize("geometry,seq", [("tiny", 37), ("tiny", 16), ("tiny", 5), ("layers3", 70), ("layers3", 300),
+                                          ("cut4b", 200), ("tiny", 129)])
+def test_atlas_prefill_equals_operator_prefill(geometry, seq, monkeypatch):
+    """GraphAtlas.prefill against Transformer.forward_sdlm_prefill (the slab-by-slab prompt forward,
+    every operator launched from the host, rows written in place): the prompt's K/V rows in every layer
+    and the last row's logits, bit for bit.  Prompts longer than a slab go through the many-row kernels
+    (bm_t2_gemm_wide, bm_prompt_attention; 300 rows = two waves), shorter ones through the captured slab
+    graph; with BM_WIDE_PREFILL=0 every length goes through the slab graphs."""
+    geo = {"tiny": synthetic.TINY, "layers3": dict(synthetic.BONSAI_1P7B, n_layers=3, vocab_size=4096),
+           "cut4b": dict(synthetic.BONSAI_4B, n_layers=2, vocab_size=4096)}[geometry]
+    if geometry == "tiny" and seq == 129:
+        monkeypatch.setenv("BM_WIDE_PREFILL", "0")
     cfg = synthetic.make_config(geo, block_size=8)
-    sigma, m_set = 128, (1, 9, 16)
+    sigma, m_set = 128 if seq <= 128 else 512, (1, 9, 16)
     model, _ = _model(cfg, 5, sigma + max(m_set))
     atlas = GraphAtlas(model, model.args, torch.device(DEV), segment_ladder=(sigma,), m_set=m_set,
                        roles=("ar", "draft", "verify"), capture_verbose=False)
