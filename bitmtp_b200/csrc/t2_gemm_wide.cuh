@@ -158,34 +158,64 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
         for (int i = 0; i < SB; ++i) ngs += (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS > 0 ? (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS : 0;
         const WideSmem L = wide_smem_layout(ngs > 0 ? ngs : 1);
         if (s0 > 0) __syncthreads();                          // everyone is done with the previous stage
-        // weights first: they do not depend on the previous kernel in the stream
+        // local index -> group, slot-major (every thread keeps the short table in registers)
+        int grp_of[kWideMaxStageGroups];
         {
             int li = 0;
             for (int i = 0; i < SB; ++i)
-                for (int grp = s0 + i; grp < ng; grp += BM_SLOTS, ++li) {
-                    for (int j = tid; j < kWideRows * 2; j += kWideThreads) {
-                        const int r = j >> 1, h = j & 1;
-                        cp_async16(wsm + L.w_off + (size_t)r * L.w_stride + li * 32 + 16 * h,
-                                   p.B + (size_t)(n0 + r) * (p.K / 4) + grp * 32 + 16 * h);
-                    }
-                    for (int r = tid; r < kWideRows; r += kWideThreads)
-                        reinterpret_cast<uint16_t *>(wsm + L.sc_off)[r * ngs + li] = p.ws[(size_t)(n0 + r) * ng + grp];
-                }
+                for (int grp = s0 + i; grp < ng && li < kWideMaxStageGroups; grp += BM_SLOTS) grp_of[li++] = grp;
+        }
+        // weights first: they do not depend on the previous kernel in the stream.  Codes by 16-byte
+        // asynchronous copies; the scales (2 bytes per row and group) are fetched into registers together
+        // and stored afterwards, so that the stage costs one memory round trip, not one per group.
+        for (int e = tid; e < ngs * kWideRows * 2; e += kWideThreads) {
+            const int li = e / (kWideRows * 2), j2 = e - li * (kWideRows * 2), r = j2 >> 1, h = j2 & 1;
+            cp_async16(wsm + L.w_off + (size_t)r * L.w_stride + li * 32 + 16 * h,
+                       p.B + (size_t)(n0 + r) * (p.K / 4) + grp_of[li] * 32 + 16 * h);
+        }
+        constexpr int kScPer = (kWideMaxStageGroups * kWideRows + kWideThreads - 1) / kWideThreads;   // 6
+        uint16_t scv[kScPer];
+#pragma unroll
+        for (int k = 0; k < kScPer; ++k) {
+            const int e = tid + k * kWideThreads;
+            if (e < ngs * kWideRows) {
+                const int li = e / kWideRows, r = e - li * kWideRows;
+                scv[k] = p.ws[(size_t)(n0 + r) * ng + grp_of[li]];
+            }
         }
         if (!waited) { pdl_wait(); waited = true; }
-        {
-            int li = 0;
-            for (int i = 0; i < SB; ++i)
-                for (int grp = s0 + i; grp < ng; grp += BM_SLOTS, ++li) {
-                    for (int j = tid; j < kWideTokens * 8; j += kWideThreads) {
-                        const int r = j >> 3, h = j & 7;
-                        unsigned char *dst = wsm + L.act_off + (size_t)r * L.act_stride + li * 128 + 16 * h;
-                        if (t0 + r < p.T) cp_async16(dst, p.A + (size_t)(t0 + r) * p.K + grp * 128 + 16 * h);
-                        else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    for (int r = tid; r < kWideTokens; r += kWideThreads)
-                        reinterpret_cast<int *>(wsm + L.asum_off)[r * ngs + li] = t0 + r < p.T ? p.asum[(size_t)(t0 + r) * ng + grp] : 0;
-                }
+        for (int e = tid; e < ngs * kWideTokens * 8; e += kWideThreads) {
+            const int li = e / (kWideTokens * 8), j2 = e - li * (kWideTokens * 8), r = j2 >> 3, h = j2 & 7;
+            unsigned char *dst = wsm + L.act_off + (size_t)r * L.act_stride + li * 128 + 16 * h;
+            if (t0 + r < p.T) cp_async16(dst, p.A + (size_t)(t0 + r) * p.K + grp_of[li] * 128 + 16 * h);
+            else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        constexpr int kAsPer = (kWideMaxStageGroups * kWideTokens + kWideThreads - 1) / kWideThreads;  // 2
+        int asv[kAsPer];
+#pragma unroll
+        for (int k = 0; k < kAsPer; ++k) {
+            const int e = tid + k * kWideThreads;
+            asv[k] = 0;
+            if (e < ngs * kWideTokens) {
+                const int li = e / kWideTokens, r = e - li * kWideTokens;
+                if (t0 + r < p.T) asv[k] = p.asum[(size_t)(t0 + r) * ng + grp_of[li]];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kScPer; ++k) {
+            const int e = tid + k * kWideThreads;
+            if (e < ngs * kWideRows) {
+                const int li = e / kWideRows, r = e - li * kWideRows;
+                reinterpret_cast<uint16_t *>(wsm + L.sc_off)[r * ngs + li] = scv[k];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kAsPer; ++k) {
+            const int e = tid + k * kWideThreads;
+            if (e < ngs * kWideTokens) {
+                const int li = e / kWideTokens, r = e - li * kWideTokens;
+                reinterpret_cast<int *>(wsm + L.asum_off)[r * ngs + li] = asv[k];
+            }
         }
         cp_async_wait_all();
         __syncthreads();

@@ -347,6 +347,8 @@ class Transformer(nn.Module):
             raise NotImplementedError("only tied-embedding T2 checkpoints are in scope")
         self._lm_head_weight_ref = None
         self._lm_head_t2_w = None
+        # prompt waves of a shape seen before are replayed as CUDA graphs (BM_PROMPT_GRAPHS=0: always eager)
+        self.use_prompt_graphs = os.environ.get("BM_PROMPT_GRAPHS", "1") != "0"
         self._workspaces = {}
         # Programmatic dependent launch between the kernels of a replay: every kernel lets its
         # successor start early (GEMVs then request their weight tiles while the predecessor
@@ -650,8 +652,8 @@ class Transformer(nn.Module):
                 and a.dim % 256 == 0 and a.ffn_dim % 128 == 0 and os.environ.get("BM_WIDE_PREFILL", "1") != "0")
 
     @torch.no_grad()
-    def prefill_rows_wide(self, token_values: torch.Tensor, kv_planes: List[SDLMLayerCache], kv_rows: int,
-                          hist0: int, ws: "PromptWorkspace", scratch: torch.Tensor) -> None:
+    def prefill_rows_wide(self, token_values: torch.Tensor, positions: torch.Tensor, kv_planes: List[SDLMLayerCache],
+                          kv_rows: int, hist0: int, ws: "PromptWorkspace", scratch: torch.Tensor) -> None:
         """One wave of the prompt forward on the many-row kernels: T = len(token_values) rows at positions
         hist0 .. hist0 + T - 1, whose K / V rows are written in place at rows [hist0, hist0 + T) of every
         layer's planes (`kv_planes[i]` = (k, v) [1, n_kv, kv_rows, hd]); rows [0, hist0) are history.
@@ -662,8 +664,7 @@ class Transformer(nn.Module):
         a = self.args
         T = int(token_values.shape[0])
         eps, pdl = a.norm_eps, self.use_pdl
-        torch.add(torch.arange(T, device=token_values.device, dtype=torch.int64), hist0, out=ws.positions[:T])
-        pos = ws.positions[:T]
+        pos = positions
         L0 = self.layers[0]
         h, q, q_sum, s = ws.h[:T], ws.q[:T], ws.q_sum[:T], ws.s[:T]
         qsink = {"h": h, "qp": q, "asum": q_sum, "s": s}
@@ -707,16 +708,34 @@ class Transformer(nn.Module):
             ws = self._prompt_ws = PromptWorkspace(a, max(wave, PREFILL_WAVE if seq > PREFILL_WAVE else wave), dev)
         ids = token_values.to(torch.int64).contiguous()
         n = 0
+        cache = self.__dict__.setdefault("_prompt_waves", {})
         for c0 in range(0, seq, wave):
             n = min(wave, seq - c0)
-            key = (n, c0)
-            cache = self.__dict__.setdefault("_prompt_scratch", {})
-            scratch = cache.get(key)
-            if scratch is None:
-                if len(cache) > 16:
+            # Per (rows, first position, KV buffer): the attention scratch, the position ids and, from the
+            # second prompt of that shape on, a CUDA graph of the wave (about 280 launches whose host cost
+            # would otherwise exceed their device time).  The graph reads its ids from ws.tokens.
+            key = (n, c0, kv_planes[0][0].data_ptr(), kv_rows)
+            rec = cache.get(key)
+            if rec is None:
+                if len(cache) > 32:
                     cache.clear()
-                scratch = cache[key] = ops.prompt_attention_scratch(n, c0, PREFILL_CHUNK, a.n_heads, a.n_kv_heads, dev)
-            self.prefill_rows_wide(ids[c0:c0 + n], kv_planes, kv_rows, c0, ws, scratch)
+                rec = cache[key] = {"scratch": ops.prompt_attention_scratch(n, c0, PREFILL_CHUNK, a.n_heads,
+                                                                            a.n_kv_heads, dev),
+                                    "pos": torch.arange(c0, c0 + n, device=dev, dtype=torch.int64), "uses": 0,
+                                    "graph": None}
+            rec["uses"] += 1
+            ws.tokens[:n].copy_(ids[c0:c0 + n])
+            if rec["graph"] is None and rec["uses"] >= 2 and self.use_prompt_graphs \
+                    and not torch.cuda.is_current_stream_capturing():
+                torch.cuda.synchronize(dev)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.prefill_rows_wide(ws.tokens[:n], rec["pos"], kv_planes, kv_rows, c0, ws, rec["scratch"])
+                rec["graph"] = g
+            if rec["graph"] is not None:
+                rec["graph"].replay()
+            else:
+                self.prefill_rows_wide(ws.tokens[:n], rec["pos"], kv_planes, kv_rows, c0, ws, rec["scratch"])
         if logits_buf is None:
             logits_buf = torch.empty((1, self._lm_head_n_pad), dtype=torch.float32, device=dev)
         # final norm + packed head on the last row of the last wave
@@ -793,7 +812,7 @@ class PromptWorkspace:
         self.gu = buf((T, 2 * args.ffn_dim), bf)
         self.iq, self.i_sum, self.is_ = buf((T, args.ffn_dim), i8), buf((T, args.ffn_dim // 128), i32), buf((T, 1), f32)
         self.ffn_out = buf((T, args.dim), bf)
-        self.positions = torch.zeros(T, dtype=torch.int64, device=device)
+        self.tokens = torch.zeros(T, dtype=torch.int64, device=device)
 
 
 class _LayerView:
