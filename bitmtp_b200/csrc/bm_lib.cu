@@ -317,12 +317,20 @@ int weight_tensor_map(const void *B, int N, int K, CUtensorMap *out) {
     return BM_OK;
 }
 
-// Warps per CTA and panels per stage of the row-per-warp kernel.
-struct RowWarpCfg { int warps, pb; };
+// Warps per CTA, panels per stage and K split of the row-per-warp kernel.  The split (2 or 4 warps per
+// 16-row block) is taken when the matrix has too few blocks to give every warp of every SM one.
+struct RowWarpCfg { int warps, pb, ks; };
 
-inline RowWarpCfg rowwarp_cfg(int W, int K) {
+inline int rowwarp_ksplit(int N, int K, int sms) {
+    const int blocks = N / bm::kRwRows;
+    if ((K % 2048) != 0 || blocks >= 8 * sms) return 1;
+    return 2 * blocks >= 8 * sms ? 2 : 4;
+}
+
+inline RowWarpCfg rowwarp_cfg(int W, int K, int ks = 1) {
     RowWarpCfg c;
-    c.pb = 2;
+    c.ks = ks;
+    c.pb = ks == 4 ? 1 : 2;
     int warps = bm::kRwMaxWarps;
     // keep at least two stages per warp
     while (warps > 4 && bm::rowwarp_smem_layout(W, K, warps, c.pb).stages < 2) --warps;
@@ -336,28 +344,36 @@ bool rowwarp_fits(int W, int N, int K) {
     return bm::rowwarp_smem_layout(W, K, c.warps, c.pb).stages >= 2;
 }
 
-template <int NTOK, int PB>
+template <int NTOK, int PB, int KS>
 int launch_rowwarp(const bm::RowWarpParams &P, int warps, int sms, int pdl, cudaStream_t stream) {
     const bm::RowWarpSmem L = bm::rowwarp_smem_layout(P.g.W, P.g.K, warps, PB);
-    const int blocks = P.g.N / bm::kRwRows;
-    int grid = (blocks + warps - 1) / warps;
+    const int blocks = P.g.N / bm::kRwRows, teams = warps / KS;
+    int grid = (blocks + teams - 1) / teams;
     if (grid > sms) grid = sms;
     const size_t smem = (size_t)L.total + 1024;
     if (P.g.G != nullptr)
-        return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, true>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
-    return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, false>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
+        return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, true, KS>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
+    return launch_ex(bm::t2_gemv_rowwarp_kernel<NTOK, PB, false, KS>, dim3(grid), dim3(warps * 32), smem, stream, pdl, P);
 }
 
 int gemv_launch_rowwarp(const bm::GemvParams &p0, int sms, int pdl, cudaStream_t stream) {
     if (!rowwarp_fits(p0.W, p0.N, p0.K)) return BM_EINVAL;
+    const int ks = rowwarp_ksplit(p0.N, p0.K, sms);
     bm::RowWarpParams P;
     const int rc = weight_tensor_map(p0.B, p0.N, p0.K, &P.tmap);
     if (rc != BM_OK) return rc;
     P.g = p0;
     P.g.pdl = pdl;
-    const RowWarpCfg c = rowwarp_cfg(p0.W, p0.K);
-    if (p0.W == 1) return launch_rowwarp<1, 2>(P, c.warps, sms, pdl, stream);
-    return launch_rowwarp<2, 2>(P, c.warps, sms, pdl, stream);
+    const RowWarpCfg c = rowwarp_cfg(p0.W, p0.K, ks);
+    if (c.warps % ks) return BM_EINVAL;
+    if (p0.W == 1) {
+        if (ks == 1) return launch_rowwarp<1, 2, 1>(P, c.warps, sms, pdl, stream);
+        if (ks == 2) return launch_rowwarp<1, 2, 2>(P, c.warps, sms, pdl, stream);
+        return launch_rowwarp<1, 1, 4>(P, c.warps, sms, pdl, stream);
+    }
+    if (ks == 1) return launch_rowwarp<2, 2, 1>(P, c.warps, sms, pdl, stream);
+    if (ks == 2) return launch_rowwarp<2, 2, 2>(P, c.warps, sms, pdl, stream);
+    return launch_rowwarp<2, 1, 4>(P, c.warps, sms, pdl, stream);
 }
 
 }  // namespace
@@ -470,16 +486,20 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
     if (path < BM_PATH_AUTO || path > BM_PATH_DIRECT) return BM_EINVAL;
     const int force_rb = 0;                           // tile height chosen by make_mma_plan
     if (path == BM_PATH_AUTO) {
-        // Many rows and at most 8 tokens: every warp streams its own rows.  With fewer than about
-        // eight 16-row blocks per SM the warps of the cooperative tiles, which split K, finish sooner
-        // (measured on 14336 x 8192, 12288 x 2048 and smaller).
-        // One token over a few MB of weights (two over at most 2 MB): the launch is latency-bound and
-        // the kernel with a single memory round trip wins (2.6-5.6 us against 4.4-7.2 us of the staged
-        // kernels, measured); from four tokens on its dp4a work costs more than it saves.
-        if (rowwarp_fits(W, N, K) && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
-        else if (p.world <= 1 && bm::direct_fits(W, N, K) &&
-                 (size_t)N * K / 4 <= (W == 1 ? kDirectMaxBytes : (W == 2 ? kDirectMaxBytes / 4 : 0)))
-            path = BM_PATH_DIRECT;
+        // Measured on B200 (one call after the other over weights that rotate through more than L2):
+        //  * many rows and at most 8 tokens: every warp streams its own 16-row blocks (row-per-warp kernel);
+        //  * one token over up to 4 MB of weights (two over up to 2 MB): the launch is latency-bound and the
+        //    kernel with a single memory round trip wins (3.3-5.3 us against 5.2-8.4 us);
+        //  * otherwise, up to 8 tokens and K a multiple of 2048: the row-per-warp kernel with two or four warps
+        //    sharing a block (2048 x 6144 at W = 8: 9.7 against 11.2 us; a 14336 x 8192 shard: 14.7 against 28.8 us);
+        //  * everything else (more than 8 tokens, odd K): the cooperative tiles.
+        const bool rw = rowwarp_fits(W, N, K);
+        const size_t wbytes = (size_t)N * K / 4;
+        const bool direct_ok = p.world <= 1 && bm::direct_fits(W, N, K) &&
+                               wbytes <= (W == 1 ? (size_t)4 << 20 : (W == 2 ? (size_t)2 << 20 : 0));
+        if (rw && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
+        else if (direct_ok) path = BM_PATH_DIRECT;
+        else if (rw && (K % 2048) == 0) path = BM_PATH_ROWWARP;
         else path = (K % 256) == 0 ? BM_PATH_MMA : BM_PATH_DP4A;
     }
     if (path == BM_PATH_DIRECT) return gemv_launch_direct(p, pdl, st);

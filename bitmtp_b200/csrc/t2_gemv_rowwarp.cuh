@@ -19,7 +19,13 @@
 //   * the 16 scale slots of the canonical order live in registers (64 accumulators per
 //     lane), the tree over them is evaluated in registers, and the scales come straight
 //     from global memory one panel ahead.
-// Requires W <= 8, K % 512 == 0, N % 16 == 0.  One CTA of 16 (W == 1: 24) warps per SM.
+// K split (KS = 2 or 4, for matrices with too few rows to give every warp a block, e.g. the shard of a
+// layer split over GPUs): a team of KS warps shares a block of 16 rows.  The canonical order survives
+// the split because the panels are dealt by SLOT, not by range: panel p feeds slots 4(p % 4) .. +3, so
+// warp ks of a pair takes the panels with (p % 4) / 2 == ks (slots 0-7 or 8-15), warp ks of a quad those
+// with p % 4 == ks (four slots); every slot's chain stays with one warp, each warp sums its slots with
+// its part of the butterfly tree, and warp 0 of the team adds the KS partial sums in tree order.
+// Requires W <= 8, K % 512 == 0 (K % 2048 == 0 when split), N % 16 == 0.  One CTA of 16 warps per SM.
 #pragma once
 
 #include <cuda.h>
@@ -44,7 +50,7 @@ struct RowWarpParams {
 };
 
 struct RowWarpSmem {
-    int invs_off, nb_off, act_off, act_stride, asum_off, stage_off, stages, total;
+    int invs_off, nb_off, act_off, act_stride, asum_off, xch_off, stage_off, stages, total;
 };
 
 // `pb` panels (1, 2 or 4) make one stage: they are requested back to back and complete on one
@@ -62,6 +68,9 @@ __host__ __device__ inline RowWarpSmem rowwarp_smem_layout(int W, int K, int war
     L.act_stride = K + kActPad;
     L.act_off = off;
     off += (W + 1) * L.act_stride;                    // row W is all zero (lanes without a token)
+    off = (off + 15) & ~15;
+    L.xch_off = off;                                  // K split: partial sums of the team's other warps, two buffers,
+    off += 2 * kRwMaxWarps * 32 * 4 * 4 + 64;         // then one give-up flag per team
     off = (off + 1023) & ~1023;                       // the swizzle pattern is address based
     L.stage_off = off;
     int stages = (kRwSmemBudget - off) / (warps * pb * kRwStageBytes);
@@ -97,8 +106,9 @@ __device__ __forceinline__ uint4 transpose_run16(uint4 x) {
                       __byte_perm(hi01, hi23, 0x5410), __byte_perm(hi01, hi23, 0x7632));
 }
 
-template <int NTOK, int PB, bool EMIT_G>
+template <int NTOK, int PB, bool EMIT_G, int KS = 1>
 __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(const __grid_constant__ RowWarpParams P) {
+    static_assert(KS == 1 || (KS == 2 && PB == 2) || (KS == 4 && PB == 1), "panels per stage follow the split");
     extern __shared__ __align__(1024) unsigned char rw_smem[];
     unsigned char *const smem = rw_smem;
     const int THREADS = (int)blockDim.x, WARPS = THREADS >> 5;
@@ -119,10 +129,11 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
     ring0 += (1024u - (smem_u32(ring0) & 1023u)) & 1023u;
     unsigned char *ring = ring0 + warp * S * kStage;
 
-    // blocks of this warp: b = first + t * stride
+    // blocks of this warp's team: b = first + t * stride
     const int n_blocks = p.N / kRwRows;
-    const int first = warp * (int)gridDim.x + (int)blockIdx.x;
-    const int stride = WARPS * (int)gridDim.x;
+    const int team = warp / KS, ks = warp % KS, TEAMS = WARPS / KS;
+    const int first = team * (int)gridDim.x + (int)blockIdx.x;
+    const int stride = TEAMS * (int)gridDim.x;
     const int my_blocks = first < n_blocks ? (n_blocks - first + stride - 1) / stride : 0;
 
     if (lane == 0) {
@@ -131,8 +142,10 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
     }
     __syncwarp();
     // Producer state (lane 0): next stage to fill, next panel / row of the matrix, stages left.
-    const int pgroups = (panels + PB - 1) / PB;       // stages per block of rows
-    int ist = 0, iss_pan = 0, iss_y = first * kRwRows, to_issue = my_blocks * pgroups;
+    // this warp's panels: all of them (KS == 1), the pairs (4i + 2ks, 4i + 2ks + 1), or the singles 4i + ks
+    const int pan0 = KS == 1 ? 0 : (KS == 2 ? 2 * ks : ks), pan_step = KS == 1 ? PB : 4;
+    const int pgroups = KS == 1 ? (panels + PB - 1) / PB : panels / 4;       // stages per block of rows
+    int ist = 0, iss_pan = pan0, iss_y = first * kRwRows, to_issue = my_blocks * pgroups;
     const int y_step = stride * kRwRows;
     auto issue_next = [&]() {
         const int np = panels - iss_pan < PB ? panels - iss_pan : PB;
@@ -144,8 +157,8 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                               &bars[ist]);
         --to_issue;
         if (++ist == S) ist = 0;
-        iss_pan += PB;
-        if (iss_pan >= panels) { iss_pan = 0; iss_y += y_step; }
+        iss_pan += pan_step;
+        if (iss_pan >= panels) { iss_pan = pan0; iss_y += y_step; }
     };
     // Weights do not depend on the previous kernel in the stream: request them first.
     if (lane == 0)
@@ -190,6 +203,8 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
             for (int i = threadIdx.x; i < 8 * ng; i += THREADS) asum_s[i] = 0;
         for (int i = threadIdx.x; i < L.act_stride / 16; i += THREADS)
             *reinterpret_cast<uint4 *>(smem + L.act_off + p.W * L.act_stride + 16 * i) = make_uint4(0u, 0u, 0u, 0u);
+        if (KS > 1 && threadIdx.x < kRwMaxWarps)
+            reinterpret_cast<int *>(smem + L.xch_off + 2 * kRwMaxWarps * 32 * 4 * 4)[threadIdx.x] = 0;
         __syncthreads();
         if (threadIdx.x < 8) invs_w[threadIdx.x] = threadIdx.x < p.W ? 1.0f / sval : 0.0f;
         if (prepared)
@@ -270,24 +285,27 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
         for (int s = 0; s < BM_SLOTS; ++s)
 #pragma unroll
             for (int e = 0; e < NA; ++e) acc[s][e] = 0.0f;
-        uint2 nsc0 = *reinterpret_cast<const uint2 *>(sc0), nsc8 = *reinterpret_cast<const uint2 *>(sc8);
-        const unsigned char *arow = arow0, *nbp = nb_base;
-        int G = 0;
+        uint2 nsc0 = *reinterpret_cast<const uint2 *>(sc0 + 4 * pan0), nsc8 = *reinterpret_cast<const uint2 *>(sc8 + 4 * pan0);
 
         for (int p4 = 0; p4 < panels && ok; p4 += 4) {
 #pragma unroll
             for (int pp = 0; pp < 4; ++pp) {
                 const int pan = p4 + pp;
                 if (pan >= panels) break;                              // warp-uniform
+                if (KS == 2 && (pp >> 1) != ks) continue;              // another warp of the team owns these slots
+                if (KS == 4 && pp != ks) continue;
+                const unsigned char *arow = arow0 + (size_t)pan * 4 * BM_GROUP, *nbp = nb_base + (size_t)pan * 4 * 64;
+                const int G = 4 * pan;
                 if (pp % PB == 0) {
                     ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[cst], cpar));
                     if (!ok) break;
                 }
                 const unsigned char *stage = ring + cst * kStage + (pp % PB) * kRwStageBytes;
                 const uint2 csc0 = nsc0, csc8 = nsc8;
-                if (pan + 1 < panels) {
-                    nsc0 = *reinterpret_cast<const uint2 *>(sc0 + 4 * (pan + 1));
-                    nsc8 = *reinterpret_cast<const uint2 *>(sc8 + 4 * (pan + 1));
+                const int nxt = KS == 1 ? pan + 1 : (KS == 2 ? ((pp & 1) ? pan + 3 : pan + 1) : pan + 4);   // next panel of this warp
+                if (nxt < panels) {
+                    nsc0 = *reinterpret_cast<const uint2 *>(sc0 + 4 * nxt);
+                    nsc8 = *reinterpret_cast<const uint2 *>(sc8 + 4 * nxt);
                 }
                 // IL groups in lock-step: their four-MMA chains are independent of each other,
                 // so consecutive MMAs never wait for the previous one's result.
@@ -352,9 +370,6 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                         }
                     }
                 }
-                arow += 4 * BM_GROUP;
-                nbp += 4 * 64;
-                G += 4;
                 if (pp % PB == PB - 1 || pan == panels - 1) {
                     ++waited;
                     if (++cst == S) { cst = 0; cpar ^= 1u; }
@@ -363,7 +378,7 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                 }
             }
         }
-        if (!ok) break;
+        if (KS == 1 && !ok) break;
         // Tree over the 16 slots (offsets 1, 2, 4, 8), reciprocal multiply, store.
         float yv[NA];
 #pragma unroll
@@ -372,7 +387,29 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
             const float s45 = acc[4][e] + acc[5][e], s67 = acc[6][e] + acc[7][e];
             const float s89 = acc[8][e] + acc[9][e], sab = acc[10][e] + acc[11][e];
             const float scd = acc[12][e] + acc[13][e], sef = acc[14][e] + acc[15][e];
-            yv[e] = ((s01 + s23) + (s45 + s67)) + ((s89 + sab) + (scd + sef));
+            if (KS == 1) yv[e] = ((s01 + s23) + (s45 + s67)) + ((s89 + sab) + (scd + sef));
+            else if (KS == 2) yv[e] = ks == 0 ? (s01 + s23) + (s45 + s67) : (s89 + sab) + (scd + sef);
+            else yv[e] = ks == 0 ? s01 + s23 : (ks == 1 ? s45 + s67 : (ks == 2 ? s89 + sab : scd + sef));
+        }
+        if (KS > 1) {
+            // the team's other warps hand their partial sums to warp 0, which adds them in tree order; two
+            // buffers used in turn, so that one named barrier per block of rows is enough
+            float *xch = reinterpret_cast<float *>(smem + L.xch_off) + (size_t)((t & 1) * kRwMaxWarps + team * KS) * 32 * 4;
+            volatile int *tfail = reinterpret_cast<volatile int *>(smem + L.xch_off + 2 * kRwMaxWarps * 32 * 4 * 4) + team;
+            if (!ok && lane == 0) *tfail = 1;          // a wait of this warp ran out: the whole team leaves after the barrier
+            if (ks != 0) {
+#pragma unroll
+                for (int e = 0; e < NA; ++e) xch[((ks - 1) * 32 + lane) * 4 + e] = yv[e];
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(KS * 32) : "memory");
+            if (*tfail) { ok = false; break; }
+            if (ks != 0) continue;
+#pragma unroll
+            for (int e = 0; e < NA; ++e) {
+                const float p1 = xch[(0 * 32 + lane) * 4 + e];
+                if (KS == 2) yv[e] = yv[e] + p1;
+                else yv[e] = (yv[e] + p1) + (xch[(1 * 32 + lane) * 4 + e] + xch[(2 * 32 + lane) * 4 + e]);
+            }
         }
         if (NTOK == 2) {
             const int t0 = 2 * q, t1 = 2 * q + 1;
@@ -397,7 +434,7 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
         // land in this warp's ring before the CTA's shared memory is released.
         if (lane == 0) {
             report_error(kErrRowWarpWaitTimeout);
-            const int in_flight = my_blocks * pgroups - to_issue - waited;
+            const int in_flight = my_blocks * pgroups - to_issue - waited;   // stages requested and not consumed
             for (int c = 0; c < in_flight; ++c) {
                 for (int it = 0; it < (1 << 12); ++it)
                     if (mbar_try_wait(&bars[cst], cpar)) break;

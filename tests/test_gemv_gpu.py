@@ -166,7 +166,9 @@ def test_linearity_property_full_size():
 
 
 ROWWARP = [(1, 16, 512), (2, 64, 512), (3, 48, 1024), (8, 2048, 2048), (5, 2048, 6144), (4, 6144, 2560),
-           (8, 2560, 9728), (7, 12288, 2048), (1, 151936, 2048), (8, 28672, 8192), (6, 4096, 4096)]
+           (8, 2560, 9728), (7, 12288, 2048), (1, 151936, 2048), (8, 28672, 8192), (6, 4096, 4096),
+           # shards of the 8192 -> 28672 layer split over 2, 4 and 8 GPUs: two and four warps share a 16-row block
+           (1, 14336, 8192), (8, 7168, 8192), (1, 3584, 8192), (8, 3584, 8192)]
 
 
 @pytest.mark.parametrize("W,N,K", ROWWARP)
