@@ -13,8 +13,12 @@ Writes the same directory the reference's converter writes
                              byte, value+2) and `.weight_scale` bf16 [out, in/128]
     model_state_fp16.pt      optional: the same tensors unpacked (frozen bf16 grid)
 
-Offline CPU code; nothing here touches CUDA.  Same command line:
+Same command line:
     python -m bitmtp_b200.convert_bonsai_mtp_to_gpu --src HF_DIR --out OUT_DIR [--no-kernel] [--no-fp16]
+With the defaults this is offline CPU code and touches no CUDA.  Two additions of this build:
+    --device cuda:0   freeze and pack each tensor with the device kernel (bm_pack_t2_g128); same bytes
+    --safetensors     also write model_state_t2g128.safetensors (same tensors, same names), which
+                      `generate.build_model` memory-maps straight to the device when it is present
 """
 from __future__ import annotations
 
@@ -92,8 +96,22 @@ def gpu_config(hf: dict) -> dict:
 
 
 @torch.no_grad()
+def freeze_and_pack(t: torch.Tensor, device: str = "cpu"):
+    """(frozen bf16 [N, K], packed int8 [N, K/4], scale bf16 [N, K/128]) of one bf16 weight, all on the CPU.
+    `device` "cpu" runs the torch expressions above; a CUDA device runs the packing kernel instead
+    (identical bytes; tests/test_pack_gpu.py compares the two)."""
+    if torch.device(device).type == "cpu":
+        frozen = freeze_ternary_g128(t)
+        return (frozen,) + tuple(pack_t2_g128(frozen))
+    from . import ops
+    packed, scale, frozen = ops.pack_t2_g128(t.to(device).contiguous(), want_frozen=True)
+    return frozen.cpu(), packed.cpu(), scale.cpu()
+
+
+@torch.no_grad()
 def convert(src_ckpt_dir: str, out_dir: str, pack_kernel: bool = True, pack_fp16: bool = True,
-            quant: str = "ternary", quantize_embedding: bool = True) -> None:
+            quant: str = "ternary", quantize_embedding: bool = True, *, device: str = "cpu",
+            safetensors_copy: bool = False) -> None:
     """Freeze the HF weights on the ternary g128 grid and write the packed checkpoint.
     Nothing is written unless every tensor converted; an existing output is never touched."""
     if quant != "ternary":
@@ -119,12 +137,12 @@ def convert(src_ckpt_dir: str, out_dir: str, pack_kernel: bool = True, pack_fp16
                 if not is_ternary_tensor(key) or t.dim() != 2 or t.shape[1] % GROUP != 0:
                     packed[key] = dense[key] = t          # norms stay bf16
                     continue
-                frozen = freeze_ternary_g128(t)
+                frozen, codes, scale = freeze_and_pack(t, device)
                 dense[key] = frozen
                 if key == _EMBED:
                     packed[key] = frozen                  # gathered, not multiplied: stays bf16
                 else:
-                    packed[key], packed[key.replace(".weight", ".weight_scale")] = pack_t2_g128(frozen)
+                    packed[key], packed[key.replace(".weight", ".weight_scale")] = codes, scale
     expect = 2 + cfg["n_layers"] * (4 + 2 * len(_PROJECTIONS))
     if len(packed) != expect:
         raise ValueError(f"checkpoint has {len(packed)} converted tensors, expected {expect}")
@@ -133,12 +151,16 @@ def convert(src_ckpt_dir: str, out_dir: str, pack_kernel: bool = True, pack_fp16
         torch.save(dense, os.path.join(out_dir, "model_state_fp16.pt"))
     if pack_kernel:
         torch.save(packed, os.path.join(out_dir, "model_state_t2g128.pt"))
+        if safetensors_copy:
+            from safetensors.torch import save_file
+            save_file({k: v.contiguous() for k, v in packed.items()},
+                      os.path.join(out_dir, "model_state_t2g128.safetensors"))
     with open(os.path.join(out_dir, "bonsai_gpu_config.json"), "w") as f:
         json.dump(cfg, f, indent=2)
     print(f"[convert] wrote {out_dir}: {len(packed)} tensors, kernel_kind=t2g128")
 
 
-def main(argv=None):
+def make_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(description="Convert public Bonsai T2 checkpoints: 1.7B D4/D8 or 4B D8.")
     ap.add_argument("--src", required=True, help="HF safetensors directory of SFT or MTP checkpoint")
     ap.add_argument("--out", required=True, help="output directory")
@@ -147,6 +169,14 @@ def main(argv=None):
     ap.add_argument("--quant", choices=("ternary",), default="ternary")
     ap.add_argument("--keep-embedding-fp", action="store_true",
                     help="legacy compatibility flag; rejected by the T2-only release")
+    ap.add_argument("--device", default="cpu", help="cpu (default), or a CUDA device to pack with the device kernel")
+    ap.add_argument("--safetensors", action="store_true",
+                    help="also write model_state_t2g128.safetensors for memory-mapped loading")
+    return ap
+
+
+def main(argv=None):
+    ap = make_parser()
     args = ap.parse_args(argv)
     try:
         with open(os.path.join(args.src, "config.json")) as f:
@@ -155,7 +185,8 @@ def main(argv=None):
     except (OSError, ValueError, TypeError) as error:
         ap.error(str(error))
     convert(args.src, args.out, pack_kernel=not args.no_kernel, pack_fp16=not args.no_fp16,
-            quant=args.quant, quantize_embedding=not args.keep_embedding_fp)
+            quant=args.quant, quantize_embedding=not args.keep_embedding_fp, device=args.device,
+            safetensors_copy=args.safetensors)
 
 
 if __name__ == "__main__":

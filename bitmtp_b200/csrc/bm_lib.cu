@@ -973,6 +973,20 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
     return cuda_status(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------- converter
+int bm_pack_t2_g128(const void *w, int N, int K, void *packed, void *scale, void *frozen, void *stream) {
+    if (!w || !packed || !scale || N < 1 || K < BM_GROUP || (K % BM_GROUP) != 0) return BM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(w) & 7u) || (frozen && (reinterpret_cast<uintptr_t>(frozen) & 7u))) return BM_EINVAL;
+    const long long units = (long long)N * (K / BM_GROUP);
+    const long long blocks = (units + 7) / 8;
+    if (blocks > 0x7fffffffLL) return BM_EINVAL;
+    count_launch();
+    bm::pack_t2_g128_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t *>(w), N, K, static_cast<uint8_t *>(packed), static_cast<uint16_t *>(scale),
+        static_cast<uint16_t *>(frozen));
+    return cuda_status(cudaGetLastError());
+}
+
 // ---------------------------------------------------------------------------- prompt (many-row) path
 int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void *C, const void *s, const void *ws, int T,
                     int N, int K, int ldc, int pdl, void *stream) {

@@ -66,7 +66,16 @@ def model_from_state(args: ModelArgs, state: dict, device) -> Transformer:
 
 def build_model(ckpt_dir: str, use_kernel: bool, device) -> Transformer:
     """generate.py:48-68: read the config, build the module tree in bf16, load
-    `model_state_t2g128.pt`, tie the head to the embedding."""
+    `model_state_t2g128.pt`, tie the head to the embedding.  When the converter also wrote
+    `model_state_t2g128.safetensors`, that file is memory-mapped and each tensor copied straight to
+    the device, with no unpickling and no host copy of the whole state."""
     args = load_args_from_ckpt(ckpt_dir, use_kernel=use_kernel)
-    sd = torch.load(os.path.join(ckpt_dir, "model_state_t2g128.pt"), map_location=device)
-    return model_from_state(args, sd, device)
+    return model_from_state(args, load_packed_state(ckpt_dir, device), device)
+
+
+def load_packed_state(ckpt_dir: str, device) -> dict:
+    st = os.path.join(ckpt_dir, "model_state_t2g128.safetensors")
+    if os.path.isfile(st):
+        from safetensors.torch import load_file
+        return load_file(st, device=str(device))
+    return torch.load(os.path.join(ckpt_dir, "model_state_t2g128.pt"), map_location=device)

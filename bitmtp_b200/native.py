@@ -120,6 +120,7 @@ def _declare_optional(L) -> None:
         "bm_t2_gemv_prepared": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp],
         "bm_dense_head": [vp, vp, ci, vp, ci, ci, ci, vp, ci, vp, ci, vp],
         "bm_t2_gemm_wide": [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
+        "bm_pack_t2_g128": [vp, ci, ci, vp, vp, vp, vp],
         "bm_prompt_attention_scratch_bytes": [ci, ci, ci, ci, ci],
         "bm_prompt_attention": [vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, vp],
         "bm_argmax_rows": [vp, ci, ci, ci, vp, vp, vp],

@@ -246,6 +246,21 @@ def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None, scratch: Optiona
     return idx, n, conf
 
 
+def pack_t2_g128(w: torch.Tensor, *, want_frozen: bool = False):
+    """Freeze + pack bf16 weights [N, K] on the device: (packed int8 [N, K/4], scale bf16 [N, K/128]) and, with
+    `want_frozen`, the bf16 weights on the ternary grid.  Same bytes as the converter's CPU packer."""
+    _require_cuda(w)
+    if w.dtype != torch.bfloat16 or w.dim() != 2 or w.shape[1] % 128:
+        raise RuntimeError("pack_t2_g128 takes a bf16 [N, K] tensor with K a multiple of 128")
+    N, K = w.shape
+    packed = torch.empty((N, K // 4), dtype=torch.int8, device=w.device)
+    scale = torch.empty((N, K // 128), dtype=torch.bfloat16, device=w.device)
+    frozen = torch.empty_like(w) if want_frozen else None
+    check(native.lib().bm_pack_t2_g128(_ptr(w), N, K, _ptr(packed), _ptr(scale), _ptr(frozen), _stream(w.device)),
+          f"bm_pack_t2_g128(N={N}, K={K})")
+    return (packed, scale, frozen) if want_frozen else (packed, scale)
+
+
 def t2_gemm_wide(a_prep: torch.Tensor, a_sums: torch.Tensor, b_packed: torch.Tensor, s: torch.Tensor, ws: torch.Tensor,
                  *, out: torch.Tensor, pdl: bool = False) -> torch.Tensor:
     """The packed product for many rows (a prompt): out bf16 [T, N], each row what t2_gemv_prepared gives it."""

@@ -102,7 +102,7 @@ def validate_artifacts(args, widths) -> dict:
     if kind != "t2g128":
         raise ValueError(f"unsupported kernel_kind: {kind!r} (this build serves t2g128 checkpoints)")
     state = args.ckpt / "model_state_t2g128.pt"
-    if not state.is_file():
+    if not state.is_file() and not (args.ckpt / "model_state_t2g128.safetensors").is_file():
         raise ValueError(f"missing packed checkpoint: {state}")
     tok = args.hf_ckpt
     if not (tok / "tokenizer_config.json").is_file():

@@ -330,6 +330,14 @@ int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *
 int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau, void *idx, void *max_buf,
                          void *conf, void *n_out, void *scratch, void *stream);
 
+/* Freeze + pack on the device: w bf16 [N, K] (latent or already frozen) -> packed uint8 [N, K/4] (four
+ * natural-order codes per byte, value + 2), scale bf16 [N, K/128] and, when frozen != NULL, the bf16
+ * weights on the {-s, 0, +s} grid.  The arithmetic of freeze_quantize_to_ternary_g128
+ * (src/bonsai_sft/ternary_modules.py:86-93) followed by _pack_t2_g128
+ * (src/bonsai_sft/gpu/convert_bonsai_mtp_to_gpu.py:127-144), which the reference's converter runs on the
+ * CPU; same bytes.  K % 128 == 0; w and frozen 8-byte aligned. */
+int bm_pack_t2_g128(const void *w, int N, int K, void *packed, void *scale, void *frozen, void *stream);
+
 /* The packed product for MANY rows at once (a prompt): C bf16 [T, ldc] = the value bm_t2_gemv_prepared
  * gives every row alone, bit for bit, with each weight byte read once per 32 rows instead of once per
  * GEMV launch.  A_prep / a_sums / s: GEMV-ready INT8 rows, their group sums and multipliers for T rows;

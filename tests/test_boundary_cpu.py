@@ -114,12 +114,9 @@ def test_cli_rejects_bad_options(tmp_path):
             RG.main(base + extra)
 
 
-def test_converter_layout(tmp_path):
-    """A tiny HF-style checkpoint through convert(): key names, dtypes and shapes of the
-    reference's packed layout (tests/test_bonsai_converter.py:184-196), and a state dict the
-    loader accepts."""
+def tiny_hf_checkpoint(tmp_path):
+    """A tiny HF-style (Qwen3 naming) bf16 safetensors checkpoint of the TINY geometry; returns its directory."""
     from safetensors.torch import save_file
-    from bitmtp_b200 import convert_bonsai_mtp_to_gpu as CV, generate
     g = synthetic.TINY
     hf = {"hidden_size": g["dim"], "num_hidden_layers": g["n_layers"], "num_attention_heads": g["n_heads"],
           "num_key_value_heads": g["n_kv_heads"], "head_dim": 128, "intermediate_size": g["ffn_dim"],
@@ -145,6 +142,17 @@ def test_converter_layout(tmp_path):
                           "mlp.down_proj": (dim, ffn)}.items():
             t[p + n + ".weight"] = torch.randn(o, k, generator=gen) * 0.02
     save_file({k: v.to(torch.bfloat16) for k, v in t.items()}, str(src / "model.safetensors"))
+    return src
+
+
+def test_converter_layout(tmp_path):
+    """A tiny HF-style checkpoint through convert(): key names, dtypes and shapes of the
+    reference's packed layout (tests/test_bonsai_converter.py:184-196), and a state dict the
+    loader accepts."""
+    from bitmtp_b200 import convert_bonsai_mtp_to_gpu as CV, generate
+    g = synthetic.TINY
+    dim, ffn, qd = g["dim"], g["ffn_dim"], g["n_heads"] * 128
+    src = tiny_hf_checkpoint(tmp_path)
     out = tmp_path / "out"
     CV.convert(str(src), str(out))
     with pytest.raises(ValueError, match="already exists"):
@@ -166,3 +174,26 @@ def test_converter_layout(tmp_path):
     cfg["mask_token_id"] = 5
     m = generate.model_from_state(generate.args_from_config(cfg), sd, "cpu")
     assert m.layers[1].feed_forward.down_proj.weight.shape == (dim, ffn // 4)
+
+
+def test_safetensors_copy_loads_to_the_same_state(tmp_path):
+    """--safetensors writes the packed state a second time under the same names; build_model prefers it and
+    gets the tensors torch.load gives."""
+    from bitmtp_b200 import convert_bonsai_mtp_to_gpu as CV, generate
+    src = tiny_hf_checkpoint(tmp_path)
+    out = tmp_path / "out"
+    CV.convert(str(src), str(out), pack_fp16=False, safetensors_copy=True)   # what `--no-fp16 --safetensors` passes
+    ns = CV.make_parser().parse_args(["--src", "a", "--out", "b", "--safetensors", "--device", "cuda:0"])
+    assert ns.safetensors and ns.device == "cuda:0"
+    assert CV.make_parser().parse_args(["--src", "a", "--out", "b"]).device == "cpu"
+    assert (out / "model_state_t2g128.safetensors").is_file() and not (out / "model_state_fp16.pt").exists()
+    pt = torch.load(out / "model_state_t2g128.pt")
+    st = generate.load_packed_state(str(out), "cpu")
+    assert sorted(pt) == sorted(st)
+    for k in pt:
+        assert st[k].dtype == pt[k].dtype and torch.equal(st[k], pt[k]), k
+    m = generate.build_model(str(out), use_kernel=True, device="cpu")
+    assert torch.equal(m.layers[0].attention.q_proj.weight.data, pt["layers.0.attention.q_proj.weight"])
+    (out / "model_state_t2g128.safetensors").unlink()
+    again = generate.load_packed_state(str(out), "cpu")
+    assert torch.equal(again["norm.weight"], pt["norm.weight"])
