@@ -401,7 +401,13 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
                      max_gen_len: int = 512, eos_ids=_BONSAI_EOS_IDS,
                      stop_strings: Optional[Sequence[str]] = None, tokenizer=None) -> Tuple[torch.Tensor, dict]:
     """Greedy AR decode with the captured width-1 graph (fast_generate.py:178-292): one
-    replay and one host read per token."""
+    replay and one host read per token.
+
+    The next token stays on the device (the argmax writes it into the output buffer and the next
+    replay's staging kernel gathers it from there), so the replay of token j + 1 is queued BEFORE the
+    host reads token j: the read (an asynchronous copy to pinned memory plus an event) only decides
+    when to stop.  A replay queued behind a token that turns out to be EOS, or to end a stop string,
+    writes a staging row and an output slot past `gen_count`; neither is ever returned."""
     if 1 not in atlas.m_set:
         raise ValueError("atlas does not include M=1 for AR path")
     ses = _Session(model, atlas, input_ids, max_gen_len, eos_ids)
@@ -409,27 +415,42 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
     prefill_time, next_tok, t0 = ses.start()
     if bufs.has_eos and next_tok in eos_ids:
         return bufs.gen_buf[:0].clone(), _empty_stats(prefill_time, ses.seq_len, with_draft=False)
-    gen_count = 1
+    gen_count = 1                                  # tokens the host has seen
+    launched = 1                                   # tokens whose replay has been queued (token 0: the prefill's)
     t1 = time.time()
-    tok_dev = bufs.gen_buf[0:1]                    # the token of the next replay, kept on the device
+    pipelined = bufs.gen_buf.is_cuda
+    depth = 2 if pipelined else 1
+    if pipelined:
+        host_tok = torch.empty(depth, dtype=torch.int64).pin_memory()
+        seen = [torch.cuda.Event() for _ in range(depth)]
+    last_dev = None
+    top = atlas.segment_ladder[-1]
     while gen_count < max_gen_len:
-        ses.ensure_room()
-        g = ses.ar_step(tok_dev, ses.cache_len)
-        ses.cache_len += 1
-        # the argmax lands in the output buffer itself (queued before the host read below); an EOS token
-        # written here lies past gen_count and is never returned
-        slot = bufs.gen_buf[gen_count:gen_count + 1]
-        tok_dev = _argmax_rows(g.logits_out, bufs.argmax_out(slot))[-1:]
-        if tok_dev.data_ptr() != slot.data_ptr():
-            slot.copy_(tok_dev)
-        next_tok = int(tok_dev.item())
+        while (launched < max_gen_len and launched - gen_count < depth
+               and (launched == 1 or ses.cache_len + 1 <= top)):
+            ses.ensure_room()
+            g = ses.ar_step(bufs.gen_buf[launched - 1:launched], ses.cache_len)
+            ses.cache_len += 1
+            slot = bufs.gen_buf[launched:launched + 1]
+            last_dev = _argmax_rows(g.logits_out, bufs.argmax_out(slot))[-1:]
+            if last_dev.data_ptr() != slot.data_ptr():
+                slot.copy_(last_dev)
+            if pipelined:
+                host_tok[launched % depth:launched % depth + 1].copy_(slot, non_blocking=True)
+                seen[launched % depth].record()
+            launched += 1
+        if launched == gen_count:
+            break                                  # the largest segment is full
+        if pipelined:
+            seen[gen_count % depth].synchronize()
+            next_tok = int(host_tok[gen_count % depth])
+        else:
+            next_tok = int(last_dev.item())
         if bufs.has_eos and next_tok in eos_ids:
             break
         gen_count += 1
         if (stop_strings and tokenizer is not None
                 and _decode_hits_stop(tokenizer, bufs.gen_buf[:gen_count].tolist(), stop_strings)):
-            break
-        if ses.cache_len + 1 > atlas.segment_ladder[-1]:
             break
     torch.cuda.synchronize()
     decode_time = max(time.time() - t1, 1e-9)
