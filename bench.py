@@ -59,9 +59,12 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv-one", "gemv-nsplit"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemv-one", "gemv-nsplit", "attention", "prompt-gemm"])
     ap.add_argument("--shape", default="151936x2048", help="gemv-one: NxK")
-    ap.add_argument("--w", type=int, default=1, help="gemv-one: width")
+    ap.add_argument("--w", type=int, default=1, help="gemv-one, attention: width")
+    ap.add_argument("--cache-len", type=int, default=700, help="attention: history rows")
+    ap.add_argument("--layers", type=int, default=28, help="attention: dependent launches per graph, one K/V plane each")
+    ap.add_argument("--rows", type=int, default=256, help="prompt-gemm: prompt rows")
     ap.add_argument("--path", default="auto", choices=["auto", "dp4a", "mma", "rowwarp", "direct"])
     ap.add_argument("--calls", type=int, default=0, help="gemv-one: launches per step")
     ap.add_argument("--pdl", action="store_true",
@@ -1167,6 +1170,87 @@ def run_reference_decode(args) -> dict:
     return line
 
 
+# ----------------------------------------------------------------------------- single-kernel workloads
+def run_kernel(args, world, rank, local, dist):
+    """`attention`: the replay's attention launch (q/k norm, RoPE, KV append, split-KV, merge) on the 1.7B head
+    geometry, `--layers` dependent launches per graph over distinct K/V planes.  `prompt-gemm`: the many-row
+    T2 x int8 GEMM of the prompt forward over weight copies that exceed L2.  One JSON line each; these are the
+    commands the ncu summaries under profiles/ were captured from."""
+    import torch
+    from bitmtp_b200 import native, ops, synthetic
+    from bitmtp_b200.model import _LayerView
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    steps = args.steps or 20
+    warmup = args.warmup if args.warmup is not None else 5
+    peak, peak_kind = peaks()
+    gen = torch.Generator(device=device).manual_seed(0)
+    if args.workload == "attention":
+        H, Hkv, sigma, M, L, cl = 16, 8, 1024, args.w, args.layers, args.cache_len
+        kv_rows = sigma + 17
+        kvb = (torch.randn(2, L, 1, Hkv, kv_rows, 128, device=device, generator=gen) * 0.5).to(torch.bfloat16)
+        cos = torch.rand(kv_rows, 128, device=device, generator=gen).to(torch.bfloat16)
+        sin = torch.rand(kv_rows, 128, device=device, generator=gen).to(torch.bfloat16)
+        qw = torch.ones(128, dtype=torch.bfloat16, device=device)
+        xqkv = torch.randn(M, (H + 2 * Hkv) * 128, device=device, generator=gen).to(torch.bfloat16)
+        att = torch.empty(M, H * 128, dtype=torch.bfloat16, device=device)
+        amax = torch.zeros(2, M, dtype=torch.int32, device=device)
+        scratch = ops.attention_scratch(17, H, sigma, device)
+        pos = torch.arange(cl, cl + M, device=device)
+        state = ops.new_step_state(device)
+        role = native.ROLE_AR if M == 1 else native.ROLE_DRAFT
+        ops.set_step_state(state, cl, min(8, max(M - 8, 0)), role, max(M - 8, 0))
+        pdl = native.PDL_OVERLAP | native.PDL_STABLE_STATE
+
+        def chain():
+            for i in range(L):
+                ops.rope_verify_attention_rows(xqkv, qw, qw, 1e-6, cos, sin, pos, H, Hkv, _LayerView(kvb[0, i], kv_rows),
+                                               _LayerView(kvb[1, i], kv_rows), sigma, state, scratch, att=att,
+                                               amax=amax[i & 1], pdl=pdl)
+        calls = L
+        alg = 2 * Hkv * (cl + M) * 256 + M * (H + 2 * Hkv) * 256 + M * H * 256      # live K/V rows + qkv in + rows out
+        label = f"attention launch, 16/8 heads, width {M}, cache_len {cl}, segment {sigma}, {L} dependent launches per graph"
+        bound, unit, scale, pk = "hbm", "GB/s", 1e9, peak
+    else:
+        n, k = (int(x) for x in args.shape.lower().split("x"))
+        T = args.rows
+        copies = max(2, (160 << 20) // (n * k // 4) + 1)
+        Bs = [synthetic.device_ternary(n, k, gen, device) for _ in range(copies)]
+        A = torch.randint(-127, 128, (T, k), device=device, dtype=torch.int8, generator=gen)
+        asum = A.view(T, k // 128, 128).sum(dim=2, dtype=torch.int32)
+        sc = torch.rand(T, device=device, generator=gen) * 40 + 20
+        C = torch.empty(T, n, dtype=torch.bfloat16, device=device)
+
+        def chain():
+            for B, ws in Bs:
+                ops.t2_gemm_wide(A, asum, B, sc, ws, out=C)
+        calls = copies
+        alg = 2 * T * n * k                                                             # integer multiply-adds x 2
+        label = f"prompt GEMM {n}x{k}, {T} rows, {copies} weight copies (> L2) per graph"
+        bound, unit, scale = "tensor", "TOP/s", 1e12
+        try:
+            pk = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        except Exception:
+            pk, peak_kind = 1590.0, "fallback"
+    graph = capture(chain, device)
+    sampler = ClockSampler(local)
+    ms, clocks = time_replays(graph, steps, warmup, dist, device, sampler)
+    err = native.lib().bm_device_error()
+    if err:
+        raise RuntimeError(f"device error word = {err}")
+    us = ms * 1e3 / (steps * calls)
+    achieved = alg / (us * 1e-6) / scale
+    return {"metric": f"{args.workload} us per launch", "value": round(us, 3), "unit": "us", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 -> fp32" if args.workload == "attention" else "s8 x ternary -> s32",
+            "data": "synthetic", "config": {"workload": label, "timing": "CUDA events around graph replays"},
+            "gpu_launches": steps * calls, "clocks": clocks,
+            "roofline": {"bound": bound, "achieved": round(achieved, 3), "peak": pk, "unit": unit,
+                         "frac": round(achieved / pk, 5), "traffic": None, "peak_kind": peak_kind,
+                         "note": "peak = measured bf16 cuBLAS rate; the int8 tensor path is nominally 2x that"
+                         if bound == "tensor" else "algorithmic bytes = live K/V rows + the replay's qkv rows in and attention rows out"}}
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1181,6 +1265,8 @@ def main():
         out = run_decode(args, world, rank, local, dist)
     elif args.workload == "gemv-nsplit":
         out = run_nsplit(args, world, rank, local, dist)
+    elif args.workload in ("attention", "prompt-gemm"):
+        out = run_kernel(args, world, rank, local, dist)
     else:
         out = run_gemv(args, world, rank, local, dist)
     if rank == 0:

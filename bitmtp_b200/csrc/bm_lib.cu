@@ -825,9 +825,12 @@ int verify_attention_impl(const void *q, const RopeInputs *rope, const void *k_b
     const int G = H / Hkv, QV = G * M;
     int nq = 1, Z = 1;
     bm::attn_query_split(QV, &nq, &Z);
+    // more z-slices than the coarse split needs: every CTA picks the split for the history length it reads
+    Z = bm::attn_zmax(QV, nq);
     if (Hkv * Z > bm::kAttnTickets) return BM_EINVAL;
     if ((H * 128) % 256 != 0 && amax_rows == nullptr) return BM_EINVAL;   // the flat quantisation wants K % 256 == 0
     bm::AttnParams p = {};
+    p.slots = 2 * current_device().sm_count;                     // two CTAs of this kernel per SM (shared memory)
     p.q = static_cast<const uint16_t *>(q);
     p.k_base = static_cast<const uint16_t *>(k_base);
     p.v_base = static_cast<const uint16_t *>(v_base);

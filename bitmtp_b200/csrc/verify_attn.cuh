@@ -67,6 +67,7 @@ struct AttnParams {
     // (slab, super-chunk) pairs in slab order; `state` is not read; q, att, amax and the partials are
     // indexed by prompt row; tickets [slabs][Hkv][gridDim.z].
     int slab_rows, slab_hist0;
+    int slots;       // CTAs the device holds at once (0: keep the coarse query split)
 };
 
 __host__ __device__ inline size_t attn_scratch_bytes(int M, int H, int sigma) {
@@ -79,6 +80,24 @@ __host__ __device__ inline void attn_query_split(int QV, int *nq, int *z) {
     const int zz = (QV + kAttnMaxQ - 1) / kAttnMaxQ;
     *z = zz;
     *nq = (QV + 2 * zz - 1) / (2 * zz);
+}
+
+// The split above is the coarsest one (fewest CTAs).  A replay's launch carries more z-slices than that
+// and every CTA picks, from the history length it reads on the device, the FINEST split whose working
+// CTAs still fit the machine in one wave: query vectors per CTA between kAttnMinQ and 2 * nq.  With few
+// history chunks that spreads the queries over more SMs (4 instead of 8 vectors per CTA is a quarter
+// faster at width 16); with many it falls back to the coarse split, because a second wave costs more
+// than the finer split saves.  Which CTA computes a query vector changes nothing in the arithmetic.
+constexpr int kAttnMinQ = 4;
+__host__ __device__ inline int attn_zmax(int QV, int nq) {
+    const int qc_min = 2 * nq < kAttnMinQ ? 2 * nq : kAttnMinQ;
+    return (QV + qc_min - 1) / qc_min;
+}
+__host__ __device__ inline int attn_pick_qc(int QV, int nq, int alive_chunks_x_heads, int slots) {
+    const int QC = 2 * nq;
+    for (int qc = (QC < kAttnMinQ ? QC : kAttnMinQ); qc < QC; ++qc)
+        if (alive_chunks_x_heads * ((QV + qc - 1) / qc) <= slots) return qc;
+    return QC;
 }
 
 __host__ __device__ inline size_t attn_smem_bytes(int nq) {
@@ -251,7 +270,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     const int key0 = fresh ? sigma_ : J * BM_ATTN_SUPER;
     const int nkeys = fresh ? M_ : min(BM_ATTN_SUPER, cache_len - key0);
     const int G = p.H / p.Hkv, QV = G * M_, heads = p.H + 2 * p.Hkv;
-    const int q_lo = z * QC;
+    // query vectors per CTA for this history length (see attn_pick_qc); sub-group 0 takes the larger half
+    const int qc = (p.slots > 0 && p.slab_rows == 0) ? attn_pick_qc(QV, NQ, (n_hs + 1) * p.Hkv, p.slots) : QC;
+    const int nq0 = (qc + 1) >> 1;
+    const int q_lo = z * qc;
     if (q_lo >= QV) return;
 
     uint16_t *Ks = reinterpret_cast<uint16_t *>(dyn);                              // [128][136]
@@ -276,7 +298,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     // this warp's query vector (one per warp: QC <= 8) and, in the CTA of the replay's own rows, its
     // share of those rows (m = warp, warp + 8, ...: at most kFreshPerWarp)
     const int qi = warp, qv = q_lo + qi;
-    const bool q_live = qi < QC && qv < QV;
+    const bool q_live = qi < qc && qv < QV;
     const int qg_ = q_live ? qv / M_ : 0, qm = q_live ? qv - qg_ * M_ : 0;
     constexpr int kFreshPerWarp = BM_MAX_W / (kAttnThreads / 32);
     uint2 qw = make_uint2(0u, 0u), kw = qw, qcos = qw, qsin = qw;
@@ -393,21 +415,32 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     {
         const int c = warp & (kAttnSub - 1), sg = warp >> 2;
         const int cn = min(BM_ATTN_CHUNK, nkeys - c * BM_ATTN_CHUNK);
-        int rows[NQ];
-#pragma unroll
-        for (int t = 0; t < NQ; ++t) {
-            const int v = min(q_lo + sg * NQ + t, QV - 1);        // vectors past QV repeat the last one; dropped below
-            rows[t] = v - (v / M_) * M_;
-        }
-        float *mcw = mc + c * QC + sg * NQ, *lcw = lc + c * QC + sg * NQ;
-        float *ocw = oc + ((size_t)c * QC + sg * NQ) * 128;
+        const int qoff = sg ? nq0 : 0, nqs = sg ? qc - nq0 : nq0;     // this warp's vectors: [qoff, qoff + nqs)
+        float *mcw = mc + c * QC + qoff, *lcw = lc + c * QC + qoff;
+        float *ocw = oc + ((size_t)c * QC + qoff) * 128;
         if (cn > 0) {
-            attn_sub_pass<NQ>(Ks + c * BM_ATTN_CHUNK * kKeyStride, Vs + c * BM_ATTN_CHUNK * 128, Qs + sg * NQ * 128,
-                              Ps + sg * NQ * BM_ATTN_SUPER, c * BM_ATTN_CHUNK, rows, key0 + c * BM_ATTN_CHUNK, cn, lane,
-                              sigma_, role, cache_len, n_pend, P_, mcw, lcw, ocw);
+            const uint16_t *Kc = Ks + c * BM_ATTN_CHUNK * kKeyStride, *Vc = Vs + c * BM_ATTN_CHUNK * 128;
+            const float *Qw = Qs + qoff * 128;
+            float *Pw = Ps + qoff * BM_ATTN_SUPER;
+            const int k0 = key0 + c * BM_ATTN_CHUNK, pc = c * BM_ATTN_CHUNK, qb = q_lo + qoff;
+            // vectors past QV repeat the last one; their results are dropped by q_live below
+#define BM_ATTN_PASS(N_)                                                                                          \
+    {                                                                                                             \
+        int rows[N_];                                                                                             \
+        _Pragma("unroll") for (int t = 0; t < N_; ++t) {                                                          \
+            const int v = min(qb + t, QV - 1);                                                                    \
+            rows[t] = v - (v / M_) * M_;                                                                          \
+        }                                                                                                         \
+        attn_sub_pass<N_>(Kc, Vc, Qw, Pw, pc, rows, k0, cn, lane, sigma_, role, cache_len, n_pend, P_, mcw, lcw,  \
+                          ocw);                                                                                   \
+    }
+            if (NQ >= 4 && nqs == 4) BM_ATTN_PASS(4)
+            else if (NQ >= 3 && nqs == 3) BM_ATTN_PASS(3)
+            else if (NQ >= 2 && nqs == 2) BM_ATTN_PASS(2)
+            else if (nqs == 1) BM_ATTN_PASS(1)
+#undef BM_ATTN_PASS
         } else {
-#pragma unroll
-            for (int t = 0; t < NQ; ++t) {
+            for (int t = 0; t < nqs; ++t) {
                 if (lane == 0) { mcw[t] = -INFINITY; lcw[t] = 0.0f; }
                 *reinterpret_cast<float4 *>(ocw + t * 128 + 4 * lane) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
