@@ -262,3 +262,30 @@ def test_launch_counter_counts_this_librarys_launches():
     ops.draft_chain(logits, 0.5, scratch=scratch)
     assert lib.bm_launch_count() - before == 2
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("T", [1, 31, 32, 33, 100, 256])
+@pytest.mark.parametrize("N,K", [(128, 256), (256, 512), (4096, 2048), (2048, 6144), (6144, 2560), (2560, 9728),
+                                 (2048, 4096)])
+def test_many_row_product_equals_the_gemv_row_for_row(T, N, K):
+    """bm_t2_gemm_wide against the decode GEMV on the same GEMV-ready rows, 16 rows at a time: every bf16
+    output bit for bit.  The GEMV itself is compared with the oracle above, so this pins the prompt GEMM to the
+    oracle at every prompt length incl. ragged last tiles, K with 2 to 76 groups (slots with zero, one and
+    several groups) and the 4B shapes."""
+    if N * K > 2048 * 6144 and T not in (33, 256):
+        pytest.skip("large shapes at two prompt lengths")
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(N + K + T)
+    B, ws = synthetic.device_ternary(N, K, gen, dev)
+    x = (torch.randn(T, K, device=dev, generator=gen) * 1.3).to(torch.bfloat16)
+    qp, asum, s = ops.quant_rows(x, prepared=True)
+    want = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    for r0 in range(0, T, 16):
+        r1 = min(T, r0 + 16)
+        ops.t2_gemv_prepared(qp[r0:r1], asum[r0:r1], B, s[r0:r1], ws, out=want[r0:r1])
+    got = torch.full((T + 1, N + 128), 7.0, dtype=torch.bfloat16, device=dev)           # guard row and columns
+    ops.t2_gemm_wide(qp, asum, B, s, ws, out=got[:T, :N])
+    torch.cuda.synchronize()
+    assert native.lib().bm_device_error() == 0
+    assert torch.equal(got[:T, :N].view(torch.int16), want.view(torch.int16))
+    assert bool((got[T] == 7.0).all()) and bool((got[:, N:] == 7.0).all()), "wrote outside the output"
