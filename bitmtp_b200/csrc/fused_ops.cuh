@@ -721,11 +721,16 @@ __global__ void __launch_bounds__(256) confidence_split_kernel(const float *__re
         ticket = atomicAdd(&sc->conf_tickets[r], 1u);
     }
     __syncthreads();
-    if (ticket != (unsigned int)(S - 1) || threadIdx.x != 0) return;
-    // last CTA of the row: add the chunk sums in ascending order
+    if (ticket != (unsigned int)(S - 1)) return;
+    // last CTA of the row: add the chunk sums in ascending order.  All threads fetch them into shared memory
+    // first (one round trip instead of one per addend); thread 0 then adds them in the same order as before.
     __threadfence();
+    __shared__ float staged[kConfMaxChunks];
+    for (int c = threadIdx.x; c < nchunks; c += blockDim.x) staged[c] = __ldcg(&sums[c]);
+    __syncthreads();
+    if (threadIdx.x != 0) return;
     float total = 0.0f;
-    for (int c = 0; c < nchunks; ++c) total += __ldcg(&sums[c]);
+    for (int c = 0; c < nchunks; ++c) total += staged[c];
     const float lse = mx + bm_logf(total);
     conf[r] = bm_expf(mx - lse);
     sc->conf_tickets[r] = 0u;

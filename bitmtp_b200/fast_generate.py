@@ -95,6 +95,44 @@ def _read_record(rec: torch.Tensor, *parts: torch.Tensor) -> List[List[int]]:
     return out
 
 
+_PINNED: dict = {}          # host staging buffers for _begin_read, by element count (pinned once, reused)
+
+
+def _begin_read(rec: torch.Tensor, *parts: torch.Tensor):
+    """Start the device-to-host copy of `parts` (see _read_record) without waiting for it: the copy goes to a
+    pinned buffer behind an event, so launches queued after this call overlap the host's wait.  Returns a
+    handle for _finish_read.  CPU tensors, or parts that do not tile the record, are read at once."""
+    addr, total = rec.data_ptr(), 0
+    tiled = rec.is_contiguous() and rec.is_cuda
+    for p in parts:
+        tiled = (tiled and p.dtype == rec.dtype and p.is_contiguous()
+                 and p.data_ptr() == addr + total * rec.element_size())
+        total += p.numel()
+    if not tiled or total > rec.numel():
+        return (None, None, _read_record(rec, *parts))
+    key = (rec.dtype, total)
+    slot = _PINNED.get(key)
+    if slot is None:
+        slot = _PINNED[key] = (torch.empty(total, dtype=rec.dtype).pin_memory(), torch.cuda.Event())
+    host, event = slot
+    host.copy_(rec[:total], non_blocking=True)
+    event.record()
+    return (host, event, [p.numel() for p in parts])
+
+
+def _finish_read(handle) -> List[List[int]]:
+    host, event, sizes = handle
+    if host is None:
+        return sizes
+    event.synchronize()
+    flat = host.tolist()
+    out, at = [], 0
+    for n in sizes:
+        out.append(flat[at:at + n])
+        at += n
+    return out
+
+
 def _select_M_for_pending(atlas, n_pend: int) -> int:
     """Smallest captured width with room for n_pend pending rows ahead of the D block rows
     (fast_generate.py:574-583).  D=8, widths {9,10,12,16,17}: 1->9, 2->10, 3-4->12,
@@ -510,12 +548,14 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
             gv = None if exact_m1_verify else ses.stage_verify(n_pend, draft_tokens, verify_role)
         else:
             draft_tokens, iter_accept_t = _fused_draft_chain(gd.logits_out, threshold, chain_out)
-            # Verifier inputs are queued before the host reads the chain length, so the
-            # read overlaps their preparation (fast_generate.py:1040-1055).
+            # The record's copy to the host is queued first, the verifier's inputs behind it, so that
+            # their preparation overlaps the host's wait (fast_generate.py:1040-1055 queue them before a
+            # blocking read).
             gv = None
+            pending_read = _begin_read(bufs.chain_rec, draft_tokens, iter_accept_t)
             if policy == "hybrid" and not exact_m1_verify:
                 gv = ses.stage_verify(n_pend, draft_tokens, verify_role)
-            draft_host, n_host = _read_record(bufs.chain_rec, draft_tokens, iter_accept_t)
+            draft_host, n_host = _finish_read(pending_read)
             iter_accept = int(n_host[0])
             use_verify = policy == "hybrid" and iter_accept < hybrid_m
 
