@@ -979,9 +979,9 @@ int bm_verify_accept(const void *draft, const void *verify, int D, void *n_out, 
 // ---------------------------------------------------------------------------- converter
 int bm_pack_t2_g128(const void *w, int N, int K, void *packed, void *scale, void *frozen, void *stream) {
     if (!w || !packed || !scale || N < 1 || K < BM_GROUP || (K % BM_GROUP) != 0) return BM_EINVAL;
-    if ((reinterpret_cast<uintptr_t>(w) & 7u) || (frozen && (reinterpret_cast<uintptr_t>(frozen) & 7u))) return BM_EINVAL;
+    if (!aligned16(w) || (frozen && !aligned16(frozen)) || (reinterpret_cast<uintptr_t>(packed) & 1u)) return BM_EINVAL;
     const long long units = (long long)N * (K / BM_GROUP);
-    const long long blocks = (units + 7) / 8;
+    const long long blocks = (units + 15) / 16;                     // two (row, group) units per warp
     if (blocks > 0x7fffffffLL) return BM_EINVAL;
     count_launch();
     bm::pack_t2_g128_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(

@@ -473,50 +473,51 @@ __global__ void kv_copy_rows_kernel(uint16_t *kv, int planes, int kv_rows, int s
 //   s = max(absmax of the group, 1e-8) (fp32); q = clamp(round_half_even(w / s), -1, 1);
 //   frozen = bf16(q * s); scale = bf16(absmax of frozen) (= bf16(s) unless the group is all zero);
 //   code = q + 2, element j of a row in bits 2 (j % 4) of byte j / 4.
-// One warp per (row, group): lane l owns elements 4l .. 4l+3, i.e. one packed byte.
+// Half a warp per (row, group): lane l owns elements 8l .. 8l+7, i.e. two packed bytes.
 // =============================================================================
 __global__ void __launch_bounds__(256) pack_t2_g128_kernel(const uint16_t *__restrict__ w, int N, int K,
                                                            uint8_t *__restrict__ packed, uint16_t *__restrict__ scale,
                                                            uint16_t *__restrict__ frozen) {
-    const int lane = threadIdx.x & 31, ng = K / BM_GROUP;
-    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (unit >= (long long)N * ng) return;                // warp-uniform
-    const int n = (int)(unit / ng), g = (int)(unit - (long long)n * ng);
-    const size_t base = (size_t)n * K + (size_t)g * BM_GROUP + 4 * lane;
-    const uint2 raw = *reinterpret_cast<const uint2 *>(w + base);
-    const float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
-    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-    amax = warp_max(amax);
-    const float s = fmaxf(amax, 1e-8f);
-    float fr[4], famax = 0.0f;
-    int q[4];
+    // half a warp per (row, group): lane l of the half owns elements 8l .. 8l+7 (one 16-byte load, two packed bytes)
+    const int lane = threadIdx.x & 31, sub = lane & 15, ng = K / BM_GROUP;
+    const long long unit = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+    const bool live = unit < (long long)N * ng;            // K % 128 == 0: a row's groups never straddle rows
+    const long long u = live ? unit : 0;
+    const int n = (int)(u / ng), g = (int)(u - (long long)n * ng);
+    const size_t base = (size_t)n * K + (size_t)g * BM_GROUP + 8 * sub;
+    const uint4 raw = *reinterpret_cast<const uint4 *>(w + base);
+    float x[8];
+    unpack8(raw, x);
+    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float s = fmaxf(amax, 1e-8f);
+    float fr[8], famax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
         float r = rintf(x[i] / s);
         r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
-        q[i] = (int)r;
         fr[i] = bm_bf16_rn(r * s);
         famax = fmaxf(famax, fabsf(fr[i]));
     }
-    famax = warp_max(famax);
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) famax = fmaxf(famax, __shfl_xor_sync(0xffffffffu, famax, off));
     const uint16_t sc = bm_f32_to_bf16(famax);
     // the packer rounds the frozen value against the bf16 scale once more (identity on the grid)
     const float sden = fmaxf(bm_bf16_to_f32(sc), 1e-30f);
-    uint32_t byte = 0;
+    uint32_t two = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
         float r = rintf(fr[i] / sden);
         r = r < -1.0f ? -1.0f : (r > 1.0f ? 1.0f : r);
-        byte |= (uint32_t)((int)r + 2) << (2 * i);
+        two |= (uint32_t)((int)r + 2) << (2 * i);
     }
-    (void)q;
-    packed[(size_t)n * (K / 4) + (size_t)g * 32 + lane] = (uint8_t)byte;
-    if (lane == 0) scale[(size_t)n * ng + g] = sc;
-    if (frozen != nullptr)
-        *reinterpret_cast<uint2 *>(frozen + base) =
-            make_uint2((uint32_t)bm_f32_to_bf16(fr[0]) | ((uint32_t)bm_f32_to_bf16(fr[1]) << 16),
-                       (uint32_t)bm_f32_to_bf16(fr[2]) | ((uint32_t)bm_f32_to_bf16(fr[3]) << 16));
+    if (!live) return;
+    *reinterpret_cast<uint16_t *>(packed + (size_t)n * (K / 4) + (size_t)g * 32 + 2 * sub) = (uint16_t)two;
+    if (sub == 0) scale[(size_t)n * ng + g] = sc;
+    if (frozen != nullptr) *reinterpret_cast<uint4 *>(frozen + base) = pack8(fr);
 }
 
 // =============================================================================

@@ -335,7 +335,7 @@ int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau
  * weights on the {-s, 0, +s} grid.  The arithmetic of freeze_quantize_to_ternary_g128
  * (src/bonsai_sft/ternary_modules.py:86-93) followed by _pack_t2_g128
  * (src/bonsai_sft/gpu/convert_bonsai_mtp_to_gpu.py:127-144), which the reference's converter runs on the
- * CPU; same bytes.  K % 128 == 0; w and frozen 8-byte aligned. */
+ * CPU; same bytes.  K % 128 == 0; w and frozen 16-byte aligned. */
 int bm_pack_t2_g128(const void *w, int N, int K, void *packed, void *scale, void *frozen, void *stream);
 
 /* The packed product for MANY rows at once (a prompt): C bf16 [T, ldc] = the value bm_t2_gemv_prepared
