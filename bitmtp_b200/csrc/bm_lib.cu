@@ -489,14 +489,15 @@ static int gemv_common(const void *A, const void *a_sums, const void *B, void *C
         // Measured on B200 (one call after the other over weights that rotate through more than L2):
         //  * many rows and at most 8 tokens: every warp streams its own 16-row blocks (row-per-warp kernel);
         //  * one token over up to 4 MB of weights (two over up to 2 MB): the launch is latency-bound and the
-        //    kernel with a single memory round trip wins (3.3-5.3 us against 5.2-8.4 us);
+        //    kernel with a single memory round trip wins (3.3-5.3 us against 5.2-8.4 us); for three or four
+        //    tokens it still does up to 1 MB (2048 x 2048: 5.2 against 5.6 us, 1024 x 2048: 4.4 against 5.6 us);
         //  * otherwise, up to 8 tokens and K a multiple of 2048: the row-per-warp kernel with two or four warps
         //    sharing a block (2048 x 6144 at W = 8: 9.7 against 11.2 us; a 14336 x 8192 shard: 14.7 against 28.8 us);
         //  * everything else (more than 8 tokens, odd K): the cooperative tiles.
         const bool rw = rowwarp_fits(W, N, K);
         const size_t wbytes = (size_t)N * K / 4;
         const bool direct_ok = p.world <= 1 && bm::direct_fits(W, N, K) &&
-                               wbytes <= (W == 1 ? (size_t)4 << 20 : (W == 2 ? (size_t)2 << 20 : 0));
+                               wbytes <= (W == 1 ? (size_t)4 << 20 : (W == 2 ? (size_t)2 << 20 : (size_t)1 << 20));
         if (rw && N / bm::kRwRows >= 8 * sms) path = BM_PATH_ROWWARP;
         else if (direct_ok) path = BM_PATH_DIRECT;
         else if (rw && (K % 2048) == 0) path = BM_PATH_ROWWARP;
