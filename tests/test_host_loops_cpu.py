@@ -53,3 +53,15 @@ def test_read_record_single_copy_and_fallback():
     assert FG._read_record(rec, rec[1:5], rec[5:6]) == [[8, 9, 10, 11], [3]]
     assert FG._read_record(rec, rec[5:6], rec[:5]) == [[3], [7, 8, 9, 10, 11]]
     assert FG._read_record(rec, torch.tensor([4, 5]), torch.tensor(6)) == [[4, 5], [6]]
+
+
+def test_record_read_handles_on_cpu_tensors():
+    """_begin_read / _finish_read (the split form of _read_record the draft loops use): on host tensors the
+    record is read at once and the handle just carries the lists; parts that do not tile the record fall back to
+    one read per part."""
+    rec = torch.arange(12, dtype=torch.int64)
+    ids, n = rec[:8], rec[8:9]
+    h = FG._begin_read(rec, ids, n)
+    assert FG._finish_read(h) == [list(range(8)), [8]] == FG._read_record(rec, ids, n)
+    other = torch.tensor([5, 6], dtype=torch.int64)
+    assert FG._finish_read(FG._begin_read(rec, ids, other)) == [list(range(8)), [5, 6]]
