@@ -25,10 +25,11 @@ from __future__ import annotations
 import argparse
 import json
 import os
-from typing import Dict, Iterable, Tuple
+from typing import Dict
 
 import torch
 
+from .checkpoint_validation import validate_hf_checkpoint, validate_sdlm_config
 from .contracts import validate_public_model_scope
 from .synthetic import GROUP, pack_t2_g128
 
@@ -58,24 +59,6 @@ def freeze_ternary_g128(w: torch.Tensor) -> torch.Tensor:
     g = w.float().view(n, k // GROUP, GROUP)
     s = g.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
     return (torch.round(g / s).clamp_(-1, 1) * s).view(n, k).to(w.dtype)
-
-
-def _read_hf(src: str) -> Tuple[dict, Iterable[str]]:
-    """config.json + the list of safetensors shards (index file if present)."""
-    with open(os.path.join(src, "config.json")) as f:
-        cfg = json.load(f)
-    index = os.path.join(src, "model.safetensors.index.json")
-    if os.path.isfile(index):
-        with open(index) as f:
-            shards = sorted(set(json.load(f)["weight_map"].values()))
-    else:
-        shards = sorted(f for f in os.listdir(src) if f.endswith(".safetensors"))
-    if not shards:
-        raise ValueError(f"no safetensors shards in {src}")
-    for s in shards:
-        if not os.path.isfile(os.path.join(src, s)):
-            raise ValueError(f"missing shard {s}")
-    return cfg, shards
 
 
 def gpu_config(hf: dict) -> dict:
@@ -113,17 +96,20 @@ def convert(src_ckpt_dir: str, out_dir: str, pack_kernel: bool = True, pack_fp16
             quant: str = "ternary", quantize_embedding: bool = True, *, device: str = "cpu",
             safetensors_copy: bool = False) -> None:
     """Freeze the HF weights on the ternary g128 grid and write the packed checkpoint.
-    Nothing is written unless every tensor converted; an existing output is never touched."""
+    The source is checked first (checkpoint_validation.py); nothing is written unless every tensor
+    converted; an existing output is never touched."""
     if quant != "ternary":
-        raise ValueError("this build converts ternary (T2-g128) checkpoints only")
-    if not quantize_embedding:
-        raise ValueError("ternary requires quantized embedding/head")
+        raise ValueError("quant must be 'ternary' (this build converts T2-g128 checkpoints only)")
     if os.path.lexists(out_dir):
         raise ValueError("conversion output already exists; use a new output directory")
     if not pack_kernel and not pack_fp16:
         raise ValueError("at least one output format must be enabled")
+    if not quantize_embedding:
+        raise ValueError("ternary requires quantized embedding/head; --keep-embedding-fp is Q1-only")
     from safetensors import safe_open
-    hf, shards = _read_hf(src_ckpt_dir)
+    # source config, shard containers and every core tensor's key / shape / dtype, before anything is written
+    hf, shards = validate_hf_checkpoint(src_ckpt_dir)
+    validate_sdlm_config(src_ckpt_dir, hf)
     cfg = gpu_config(hf)
     packed: Dict[str, torch.Tensor] = {}
     dense: Dict[str, torch.Tensor] = {}

@@ -122,7 +122,8 @@ def tiny_hf_checkpoint(tmp_path):
           "num_key_value_heads": g["n_kv_heads"], "head_dim": 128, "intermediate_size": g["ffn_dim"],
           "vocab_size": g["vocab_size"], "rms_norm_eps": 1e-6, "rope_theta": 1e6,
           "rope_scaling": {"original_max_position_embeddings": 8192, "factor": 4.0},
-          "tie_word_embeddings": True, "block_size": 8}
+          "tie_word_embeddings": True, "block_size": 8, "causal_attn": True,
+          "text_mask_token_id": g["vocab_size"] - 1}
     src = tmp_path / "hf"
     src.mkdir()
     (src / "config.json").write_text(json.dumps(hf))
@@ -158,7 +159,7 @@ def test_converter_layout(tmp_path):
     with pytest.raises(ValueError, match="already exists"):
         CV.convert(str(src), str(out))
     cfg = json.loads((out / "bonsai_gpu_config.json").read_text())
-    assert cfg["kernel_kind"] == "t2g128" and cfg["dim"] == dim and cfg["mask_token_id"] == 151654
+    assert cfg["kernel_kind"] == "t2g128" and cfg["dim"] == dim and cfg["mask_token_id"] == g["vocab_size"] - 1
     sd = torch.load(out / "model_state_t2g128.pt")
     w = sd["layers.0.attention.q_proj.weight"]
     ws = sd["layers.0.attention.q_proj.weight_scale"]
