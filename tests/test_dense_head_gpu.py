@@ -118,3 +118,30 @@ def test_cli_accepts_the_dense_draft_precisions():
                                             "--prompt", "hi", "--draft-precision", prec])
         widths, roles, _ = RG.validate_options(args)
         assert role in roles and "verify" in roles
+
+
+@pytest.mark.parametrize("mode,draft", [("ar", None), ("confidence", "draft"), ("hybrid", "draft_fp8"),
+                                        ("speculative", "draft_bf16")])
+def test_atlas_passes_the_checks_of_the_reference_evaluation_adapter(mode, draft):
+    """What the reference's lm-eval / EvalPlus adapter asserts right after it builds its atlas
+    (benchmarks/bonsai_adapter.py:118-157), with its constructor arguments and its role ordering: ladder, width
+    schedule and role tuple come back unchanged, every captured graph reports the head precision of its role, and
+    every graph's per-layer K / V views start at the segment's shared buffer."""
+    cfg = synthetic.make_config(dict(synthetic.TINY, vocab_size=1008), block_size=8)
+    state = synthetic.make_state(cfg, seed=11)
+    model = generate.model_from_state(generate.args_from_config(cfg), state, DEV)
+    model.prepare_merged_weights(max_positions=512 + 17)
+    ladder, widths = (128, 512), ((1,) if mode == "ar" else (1, 8, 9, 10, 12, 16, 17))
+    roles = ("ar",) if mode == "ar" else ((draft, "ar") if mode == "confidence" else (draft, "verify", "ar"))
+    atlas = GraphAtlas(model, model.args, torch.device(DEV), dtype=torch.bfloat16, segment_ladder=ladder, m_set=widths,
+                       roles=roles, capture_verbose=False)
+    assert atlas.segment_ladder == ladder and atlas.m_set == widths and tuple(atlas.roles) == tuple(roles)
+    expected = {"ar": "t2", "verify": "t2", "draft": "t2", "draft_fp8": "fp8", "draft_bf16": "bf16_raw"}
+    assert atlas.graphs, "no graph captured"
+    for (width, sigma, role), graph in atlas.graphs.items():
+        assert role in expected and graph.lm_head_precision == expected[role]
+        shared = atlas.kv_buffers[sigma]
+        for layer, (key_view, value_view) in enumerate(graph.kv_full):
+            assert key_view.data_ptr() == shared[0, layer].data_ptr()
+            assert value_view.data_ptr() == shared[1, layer].data_ptr()
+    assert native.lib().bm_device_error() == 0
