@@ -57,43 +57,66 @@ def make_parser() -> argparse.ArgumentParser:
     return p
 
 
+def _default_min_chain(args) -> int:
+    """3 where a block has four draft positions (D4, and the reference's Orin profiles), otherwise 6."""
+    return 3 if (args.block_size == 4 or is_orin_profile(args.runtime_profile)) else 6
+
+
+def _roles_for(mode: str, draft_precision: str):
+    """Graph roles a mode replays: AR always (first token, exact-M1 verify), a draft role for every MTP mode,
+    the verifier for the two modes that check drafts."""
+    roles = ("ar",)
+    if mode != "ar":
+        roles += (DRAFT_ROLE[draft_precision],)
+    if mode in ("spec", "hybrid"):
+        roles += ("verify",)
+    return roles
+
+
 def validate_options(args):
-    """Option combinations, in the reference's order (run_generation.py:55-81).
-    Returns (widths, roles, min_chain)."""
+    """Option combinations, judged in the reference's order and with its messages
+    (run_generation.py:55-81).  Returns (widths, roles, min_chain)."""
     validate_verification_options(args.margin, args.exact_m1_verify)
     validate_profile_options(args)
-    if not math.isfinite(args.threshold) or not 0 <= args.threshold <= 1:
-        raise ValueError("threshold must be finite and between 0 and 1")
-    if args.max_new_tokens < 1 or args.max_context < 1:
-        raise ValueError("max-new-tokens and max-context must be positive")
-    default_chain = 3 if (is_orin_profile(args.runtime_profile) or args.block_size == 4) else 6
-    min_chain = default_chain if args.min_chain is None else args.min_chain
-    if not 1 <= min_chain <= args.block_size + 1:
-        raise ValueError("min-chain must be in [1, block-size + 1]")
-    if args.min_chain is not None and args.mode != "hybrid":
-        raise ValueError("min-chain is only used by hybrid mode")
-    verifying = args.mode in ("spec", "hybrid")
-    if not verifying and (args.exact_m1_verify or args.margin != 0 or args.verify_precision != "native"):
-        raise ValueError("verification options are only used by spec/hybrid modes")
-    if args.mode == "ar" and args.draft_precision != "native":
-        raise ValueError("AR does not use a draft projection")
-    if args.verify_precision != "native":
-        raise ValueError("strict verification requires the native verifier projection")
-    widths = (1,) if args.mode == "ar" else WIDTHS[args.block_size]
-    roles = ["ar"]
-    if args.mode != "ar":
-        roles.append(DRAFT_ROLE[args.draft_precision])
-    if verifying:
-        roles.append("verify")
-    return widths, tuple(roles), min_chain
+    mode, verifying = args.mode, args.mode in ("spec", "hybrid")
+    min_chain = _default_min_chain(args) if args.min_chain is None else args.min_chain
+    verify_options_set = args.exact_m1_verify or args.margin != 0 or args.verify_precision != "native"
+    # (condition that must hold, message when it does not), first failure wins
+    rules = (
+        (math.isfinite(args.threshold) and 0 <= args.threshold <= 1, "threshold must be finite and between 0 and 1"),
+        (args.max_new_tokens >= 1 and args.max_context >= 1, "max-new-tokens and max-context must be positive"),
+        (1 <= min_chain <= args.block_size + 1, "min-chain must be in [1, block-size + 1]"),
+        (args.min_chain is None or mode == "hybrid", "min-chain is only used by hybrid mode"),
+        (verifying or not verify_options_set, "verification options are only used by spec/hybrid modes"),
+        (mode != "ar" or args.draft_precision == "native", "AR does not use a draft projection"),
+        (args.verify_precision == "native", "strict verification requires the native verifier projection"),
+    )
+    for holds, message in rules:
+        if not holds:
+            raise ValueError(message)
+    widths = (1,) if mode == "ar" else WIDTHS[args.block_size]
+    return widths, _roles_for(mode, args.draft_precision), min_chain
+
+
+def _layer_shapes(config: dict):
+    """(N, K) of the merged projections of a layer and of the padded packed head."""
+    dim, hd = config["dim"], config["head_dim"]
+    q_dim, kv_dim = config["n_heads"] * hd, config["n_kv_heads"] * hd
+    head_rows = (config["vocab_size"] + 31) // 32 * 32
+    return ((q_dim + 2 * kv_dim, dim), (dim, q_dim), (2 * config["ffn_dim"], dim), (dim, config["ffn_dim"]),
+            (head_rows, dim))
+
+
+def _require_file(path: Path, what: str) -> None:
+    if not path.is_file():
+        raise ValueError(f"missing {what}: {path}")
 
 
 def validate_artifacts(args, widths) -> dict:
-    """Local files and kernel shapes (run_generation.py:84-123).  Reads JSON only."""
-    config_path = args.ckpt / "bonsai_gpu_config.json"
-    if not config_path.is_file():
-        raise ValueError(f"missing GPU checkpoint configuration: {config_path}")
-    config = json.loads(config_path.read_text())
+    """Local files and kernel shapes (run_generation.py:84-123).  Reads JSON only; neither torch nor the native
+    library is touched."""
+    _require_file(args.ckpt / "bonsai_gpu_config.json", "GPU checkpoint configuration")
+    config = json.loads((args.ckpt / "bonsai_gpu_config.json").read_text())
     validate_public_model_scope(config)
     validate_profile_model(args.runtime_profile, config)
     if config.get("block_size") != args.block_size:
@@ -101,24 +124,18 @@ def validate_artifacts(args, widths) -> dict:
     kind = config.get("kernel_kind", "q1")
     if kind != "t2g128":
         raise ValueError(f"unsupported kernel_kind: {kind!r} (this build serves t2g128 checkpoints)")
-    state = args.ckpt / "model_state_t2g128.pt"
-    if not state.is_file() and not (args.ckpt / "model_state_t2g128.safetensors").is_file():
-        raise ValueError(f"missing packed checkpoint: {state}")
+    if not any((args.ckpt / name).is_file() for name in ("model_state_t2g128.pt", "model_state_t2g128.safetensors")):
+        raise ValueError(f"missing packed checkpoint: {args.ckpt / 'model_state_t2g128.pt'}")
     tok = args.hf_ckpt
     if not (tok / "tokenizer_config.json").is_file():
         raise ValueError(f"missing tokenizer_config.json in {tok}")
-    if not ((tok / "tokenizer.json").is_file()
-            or all((tok / f).is_file() for f in ("vocab.json", "merges.txt"))):
+    bpe_pair = all((tok / name).is_file() for name in ("vocab.json", "merges.txt"))
+    if not ((tok / "tokenizer.json").is_file() or bpe_pair):
         raise ValueError(f"need tokenizer.json or both vocab.json and merges.txt in {tok}")
-    if args.prompt_file is not None and not args.prompt_file.is_file():
-        raise ValueError(f"missing prompt file: {args.prompt_file}")
-    dim = config["dim"]
-    qw = config["n_heads"] * config["head_dim"]
-    kvw = config["n_kv_heads"] * config["head_dim"]
-    shapes = ((qw + 2 * kvw, dim), (dim, qw), (2 * config["ffn_dim"], dim), (dim, config["ffn_dim"]),
-              ((config["vocab_size"] + 31) // 32 * 32, dim))
-    for m in widths:
-        for n, k in shapes:
+    if args.prompt_file is not None:
+        _require_file(args.prompt_file, "prompt file")
+    for n, k in _layer_shapes(config):
+        for m in widths:
             require_native_shape(m, n, k)
     from .native import SO_PATH                       # path constant only; nothing is loaded
     if not Path(SO_PATH).is_file():
