@@ -13,16 +13,22 @@ from __future__ import annotations
 
 import math
 
-Q1_M = frozenset((1, 4, 5, 6, 7, 8, 9, 10, 12, 16, 17))
-BONSAI_17B_NK = frozenset((
-    (1024, 2048), (2048, 2048), (4096, 2048),
-    (6144, 2048), (12288, 2048), (2048, 6144), (151936, 2048),
-))
-T2_4B_M = frozenset((1, 8, 9, 10, 12, 16, 17))
-T2_4B_NK = frozenset((
-    (1024, 2560), (6144, 2560), (19456, 2560),
-    (2560, 4096), (2560, 9728), (151936, 2560),
-))
+def _projection_shapes(dim, heads, kv_heads, head_dim, ffn, vocab, *, unfused):
+    """(N, K) of every packed projection of one backbone: fused q|k|v and gate|up, o, down, the tied head, the
+    key/value projection on its own, and (where the reference also registers them) the unfused q and gate."""
+    q, kv = heads * head_dim, kv_heads * head_dim
+    shapes = {(kv, dim), (q + 2 * kv, dim), (2 * ffn, dim), (dim, q), (dim, ffn), (vocab, dim)}
+    if unfused:
+        shapes |= {(q, dim), (ffn, dim)}
+    return frozenset(shapes)
+
+
+_PADDED_VOCAB = 151936
+_WIDE = tuple(range(4, 11)) + (12, 16, 17)          # verify widths of D4/D8 blocks plus the prompt-tail widths
+Q1_M = frozenset((1,) + _WIDE)
+BONSAI_17B_NK = _projection_shapes(2048, 16, 8, 128, 6144, _PADDED_VOCAB, unfused=True)
+T2_4B_M = frozenset(m for m in Q1_M if m == 1 or m >= 8)
+T2_4B_NK = _projection_shapes(2560, 32, 8, 128, 9728, _PADDED_VOCAB, unfused=False)
 MAX_WIDTH = 32
 
 
@@ -84,14 +90,22 @@ def validate_public_device_scope(config: dict, capability) -> None:
                          f'device capability {tuple(capability)} is unsupported')
 
 
+_ONE_BIT_KINDS = ("q1", "w1a16")          # the reference's 1-bit kernels: known names, not built here
+_GRAPH_ROLES = frozenset(("ar", "verify", "draft", "draft_fp8", "draft_bf16"))
+
+
+def _registered(m: int, n: int, k: int) -> bool:
+    return any(m in widths and (n, k) in shapes
+               for widths, shapes in ((Q1_M, BONSAI_17B_NK), (T2_4B_M, T2_4B_NK)))
+
+
 def supports_kernel_shape(kind: str, m: int, n: int, k: int) -> bool:
-    """The reference's registered (M, N, K) triples (contracts.py:72-81)."""
+    """Whether (M, N, K) is one of the reference's registered triples (contracts.py:72-81)."""
     if kind == "t2g128":
-        return ((m in Q1_M and (n, k) in BONSAI_17B_NK)
-                or (m in T2_4B_M and (n, k) in T2_4B_NK))
-    if kind in ("q1", "w1a16"):
-        return False          # the 1-bit kernels are outside this build's scope
-    raise ValueError(f"unknown kernel kind: {kind!r}")
+        return _registered(m, n, k)
+    if kind not in _ONE_BIT_KINDS:
+        raise ValueError(f"unknown kernel kind: {kind!r}")
+    return False
 
 
 def supports_native_shape(m: int, n: int, k: int) -> bool:
@@ -99,44 +113,46 @@ def supports_native_shape(m: int, n: int, k: int) -> bool:
     return 1 <= m <= MAX_WIDTH and n >= 8 and n % 8 == 0 and k >= 128 and k % 128 == 0
 
 
+def _refuse_shape(kind: str, m: int, n: int, k: int):
+    raise RuntimeError(f"unsupported {kind} kernel shape: M={m}, N={n}, K={k}")
+
+
 def require_kernel_shape(kind: str, m: int, n: int, k: int) -> None:
-    if not supports_kernel_shape(kind, m, n, k):
-        raise RuntimeError(f"unsupported {kind} kernel shape: M={m}, N={n}, K={k}")
+    supports_kernel_shape(kind, m, n, k) or _refuse_shape(kind, m, n, k)
 
 
 def require_native_shape(m: int, n: int, k: int) -> None:
-    if not supports_native_shape(m, n, k):
-        raise RuntimeError(f"unsupported t2g128 kernel shape: M={m}, N={n}, K={k}")
+    supports_native_shape(m, n, k) or _refuse_shape("t2g128", m, n, k)
 
 
 def supports_layer_kernel_shape(kind: str, m: int, n: int, k: int) -> bool:
-    """contracts.py:89-98."""
-    if kind == "t2g128" and (n, k) in T2_4B_NK:
-        return m == 1
-    return supports_kernel_shape(kind, m, n, k)
+    """The reference's variable-width layer forward uses the 4B kernels at M = 1 only (contracts.py:89-98)."""
+    four_b = kind == "t2g128" and (n, k) in T2_4B_NK
+    return m == 1 if four_b else supports_kernel_shape(kind, m, n, k)
 
 
 def validate_verification_options(rabv_margin: float, exact_m1_verify: bool = False) -> None:
-    """Strict verification accepts a zero margin only (contracts.py:101-108)."""
+    """Strict verification accepts a zero margin only (contracts.py:101-108); a margin that is not a
+    number at all is refused with the same message."""
     try:
-        valid = math.isfinite(rabv_margin) and rabv_margin == 0.0
+        zero = math.isfinite(rabv_margin) and not rabv_margin
     except (TypeError, ValueError):
-        valid = False
-    if not valid:
+        zero = False
+    if not zero:
         raise ValueError("strict verifier requires rabv_margin=0; nonzero margins are unsupported")
 
 
 def validate_native_verifier(use_fp8=False, use_q1=False, use_w1a16=False) -> None:
-    """contracts.py:111-114."""
-    if use_fp8 or use_q1 or use_w1a16:
+    """The verifier projects through the backbone's own packed head (contracts.py:111-114)."""
+    if any((use_fp8, use_q1, use_w1a16)):
         raise ValueError("strict verification requires the native verifier projection")
 
 
 def validate_graph_roles(roles, capability=None) -> None:
-    """contracts.py:117-124."""
-    allowed = {"ar", "draft", "draft_fp8", "draft_bf16", "verify"}
-    unknown = set(roles) - allowed
-    if unknown:
-        raise ValueError(f"unsupported strict graph roles: {sorted(unknown)}")
-    if capability is not None and "draft_fp8" in roles and tuple(capability) < (8, 9):
+    """Role names a session may capture graphs for (contracts.py:117-124)."""
+    strangers = sorted(set(roles) - _GRAPH_ROLES)
+    if strangers:
+        raise ValueError(f"unsupported strict graph roles: {strangers}")
+    fp8_capable = capability is None or tuple(capability) >= (8, 9)
+    if "draft_fp8" in roles and not fp8_capable:
         raise ValueError("FP8 draft projection is unsupported on this GPU; use draft_bf16 or native draft")
