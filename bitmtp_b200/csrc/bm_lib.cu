@@ -786,9 +786,61 @@ struct RopeInputs {
     float eps;
 };
 
+// Launch of the cluster build of the attention kernel: the grid's x extent is one thread-block cluster.
+// Returns -1 (and launches nothing) unless the device holds all of the grid's clusters at once - a
+// cluster that has to wait for a place costs more than the shorter merge saves - so that the caller takes
+// the ticket build; the device is asked once per kernel, cluster size and device.
+template <void (*kernel)(const bm::AttnParams)>
+int launch_attention_cluster(dim3 grid, size_t smem, cudaStream_t st, int pdl, const bm::AttnParams &p) {
+    static std::atomic<int> resident[bm::kAttnMaxCluster + 1][8];    // clusters the device holds, +1 (0: not asked yet)
+    const int dev = current_device().device;
+    if (grid.x > (unsigned)bm::kAttnMaxCluster || dev < 0 || dev >= 8) return -1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(bm::kAttnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = grid.x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    std::atomic<int> &known = resident[grid.x][dev];
+    int held = known.load(std::memory_order_relaxed) - 1;
+    if (held < 0) {
+        int clusters = 0;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && grid.x > 8)
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cfg.numAttrs = 1;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();                     // an unsupported size is an answer, not a failure
+        held = e == cudaSuccess && clusters > 0 ? clusters : 0;
+        known.store(held + 1, std::memory_order_relaxed);
+    }
+    if ((int)(grid.y * grid.z) > held) return -1;
+    cfg.numAttrs = pdl ? 2 : 1;
+    count_launch();
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, p));
+}
+
 template <bool ROPE>
 int launch_attention(int nq, dim3 grid, size_t smem, cudaStream_t st, int pdl, const bm::AttnParams &p) {
     const dim3 block(bm::kAttnThreads);
+    // Cluster build where a (kv head, query group)'s super-chunks fit one cluster.  Same arithmetic, same order.
+    if (p.slab_rows == 0 && p.slots > 0 && grid.x <= (unsigned)bm::kAttnMaxCluster) {
+        int rc;
+        switch (nq) {
+            case 1: rc = launch_attention_cluster<bm::attn_fused_kernel<1, ROPE, true>>(grid, smem, st, pdl, p); break;
+            case 2: rc = launch_attention_cluster<bm::attn_fused_kernel<2, ROPE, true>>(grid, smem, st, pdl, p); break;
+            case 3: rc = launch_attention_cluster<bm::attn_fused_kernel<3, ROPE, true>>(grid, smem, st, pdl, p); break;
+            default: rc = launch_attention_cluster<bm::attn_fused_kernel<4, ROPE, true>>(grid, smem, st, pdl, p); break;
+        }
+        if (rc >= 0) return rc;
+    }
     switch (nq) {
         case 1: return launch_ex(bm::attn_fused_kernel<1, ROPE>, grid, block, smem, st, pdl, p);
         case 2: return launch_ex(bm::attn_fused_kernel<2, ROPE>, grid, block, smem, st, pdl, p);

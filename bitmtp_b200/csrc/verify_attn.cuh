@@ -42,6 +42,7 @@ constexpr int kAttnHeaderBytes = 1024;
 constexpr int kAttnTickets = 224;      // counters in the header; the row absmax words follow
 constexpr int kAttnMaxQ = 8;           // query vectors per CTA (2 sub-groups of up to 4)
 constexpr int kAttnMaxNJ = 64;         // super-chunk partials one merging warp handles (2 per lane)
+constexpr int kAttnMaxCluster = 16;    // super-chunks (CTAs) of one cluster in the cluster build
 
 struct AttnParams {
     const uint16_t *q;        // [M, H, 128] rotated queries (plain build)
@@ -112,6 +113,29 @@ __host__ __device__ inline size_t attn_smem_bytes(int nq) {
 // shared-memory arrays and the K/V planes are all sized from sigma.  Identity for every valid record.
 __device__ __forceinline__ int attn_cache_len(const AttnParams &p) {
     return min(max(p.state->cache_len, 0), p.sigma);
+}
+
+// Thread-block-cluster primitives of the cluster build: one barrier phase = arrive + wait by every
+// thread of every CTA of the cluster that has not exited (a hardware barrier, no polling of memory), and
+// reads of another CTA's shared memory through its cluster-wide address.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_map(const void *own_shared, uint32_t rank) {
+    uint32_t mapped;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(mapped) : "r"((uint32_t)__cvta_generic_to_shared(own_shared)), "r"(rank));
+    return mapped;
+}
+__device__ __forceinline__ float4 cluster_ld4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 cluster_ld2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+    return v;
 }
 
 // q/k head norm + RoPE of one 128-wide head vector by one warp, as qknorm_rope_kvappend_kernel does it:
@@ -230,7 +254,14 @@ __device__ __forceinline__ void attn_sub_pass(const uint16_t *Ks, const uint16_t
 
 // grid (NJ, Hkv, Z), 256 threads.  NQ: query vectors per warp (the CTA serves 2*NQ); ROPE: queries and
 // the replay's own K/V rows are made here from the qkv projection output.
-template <int NQ, bool ROPE>
+// CLUSTER: the NJ CTAs of a (kv head, query group) are one thread-block cluster (launch attribute
+// (NJ, 1, 1), NJ <= kAttnMaxCluster).  The super-chunk partials then stay in the shared memory of the CTA
+// that made them; the CTA of the replay's own rows (cluster rank NJ - 1, always working) reads them
+// through distributed shared memory after one cluster barrier and merges them in the same order as the
+// ticket build, so the fence, the ticket and the read-back from global memory drop out of the chain.  A
+// second barrier keeps the other CTAs' shared memory alive until it has been read.  CTAs of super-chunks
+// without rows take part in both barriers and do nothing else.
+template <int NQ, bool ROPE, bool CLUSTER = false>
 __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ unsigned int sh_ticket;
@@ -266,15 +297,21 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
     }
     const int n_hs = (cache_len + BM_ATTN_SUPER - 1) / BM_ATTN_SUPER;     // history super-chunks with rows
     const bool fresh = J == p.NJ - 1;
-    if (!fresh && J >= n_hs) return;
-    const int key0 = fresh ? sigma_ : J * BM_ATTN_SUPER;
-    const int nkeys = fresh ? M_ : min(BM_ATTN_SUPER, cache_len - key0);
     const int G = p.H / p.Hkv, QV = G * M_, heads = p.H + 2 * p.Hkv;
     // query vectors per CTA for this history length (see attn_pick_qc); sub-group 0 takes the larger half
     const int qc = (p.slots > 0 && p.slab_rows == 0) ? attn_pick_qc(QV, NQ, (n_hs + 1) * p.Hkv, p.slots) : QC;
     const int nq0 = (qc + 1) >> 1;
     const int q_lo = z * qc;
-    if (q_lo >= QV) return;
+    if (q_lo >= QV) return;                // a surplus query group: all its CTAs (a whole cluster) leave here
+    if (!fresh && J >= n_hs) {
+        if (CLUSTER) {                     // a super-chunk without rows: both barrier phases, nothing else
+            cluster_arrive(); cluster_wait();
+            cluster_arrive(); cluster_wait();
+        }
+        return;
+    }
+    const int key0 = fresh ? sigma_ : J * BM_ATTN_SUPER;
+    const int nkeys = fresh ? M_ : min(BM_ATTN_SUPER, cache_len - key0);
 
     uint16_t *Ks = reinterpret_cast<uint16_t *>(dyn);                              // [128][136]
     uint16_t *Vs = Ks + BM_ATTN_SUPER * kKeyStride;                                 // [128][128]
@@ -464,9 +501,75 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fused_kernel(const AttnP
             O[2] = fmaf(o.z, w, O[2]);
             O[3] = fmaf(o.w, w, O[3]);
         }
-        const size_t pb = ((size_t)(r0 + qm) * p.H + hk * G + qg_) * p.NJ + J;
-        *reinterpret_cast<float4 *>(p.po + pb * 128 + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
-        if (lane == 0) { p.pm[pb] = MJ; p.pl[pb] = L; }
+        if (CLUSTER) {
+            // the partial stays in this CTA: numerators over the softmax weights and max / sum over the query
+            // vector, both spent since the CTA barrier after level 0
+            *reinterpret_cast<float4 *>(Ps + qi * BM_ATTN_SUPER + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
+            if (lane == 0) *reinterpret_cast<float2 *>(Qs + qi * 128) = make_float2(MJ, L);
+        } else {
+            const size_t pb = ((size_t)(r0 + qm) * p.H + hk * G + qg_) * p.NJ + J;
+            *reinterpret_cast<float4 *>(p.po + pb * 128 + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
+            if (lane == 0) { p.pm[pb] = MJ; p.pl[pb] = L; }
+        }
+    }
+    if (CLUSTER) {
+        cluster_arrive();
+        cluster_wait();
+        if (fresh && q_live) {
+            // level 2 in the cluster: history super-chunks (cluster ranks 0 .. n_hs-1) in ascending order, then
+            // this CTA's own partial; at most kAttnMaxCluster of them, requested in batches of eight
+            const int nv = n_hs + 1;
+            const float *own_ml = Qs + qi * 128, *own_o = Ps + qi * BM_ATTN_SUPER + 4 * lane;
+            float2 ml = make_float2(-INFINITY, 0.0f);
+            if (lane < n_hs) ml = cluster_ld2(cluster_map(own_ml, (uint32_t)lane));
+            else if (lane == n_hs) ml = *reinterpret_cast<const float2 *>(own_ml);
+            constexpr int kBatch = 8;
+            float4 part[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+                part[i] = i < n_hs    ? cluster_ld4(cluster_map(own_o, (uint32_t)i))
+                          : i == n_hs ? *reinterpret_cast<const float4 *>(own_o)
+                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float gmax = warp_max(ml.x);
+            const float w0 = ml.x > -INFINITY ? bm_expf(ml.x - gmax) : 0.0f;
+            float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int b0 = 0; b0 < nv; b0 += kBatch) {
+                if (b0 > 0) {
+#pragma unroll
+                    for (int i = 0; i < kBatch; ++i) {
+                        const int c = b0 + i;
+                        part[i] = c < n_hs    ? cluster_ld4(cluster_map(own_o, (uint32_t)c))
+                                  : c == n_hs ? *reinterpret_cast<const float4 *>(own_o)
+                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const int c = b0 + i;
+                    if (c < nv) {                                      // warp-uniform
+                        const float w = __shfl_sync(0xffffffffu, w0, c);
+                        const float lj = __shfl_sync(0xffffffffu, ml.y, c);
+                        l = fmaf(lj, w, l);
+                        o[0] = fmaf(part[i].x, w, o[0]);
+                        o[1] = fmaf(part[i].y, w, o[1]);
+                        o[2] = fmaf(part[i].z, w, o[2]);
+                        o[3] = fmaf(part[i].w, w, o[3]);
+                    }
+                }
+            }
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = bm_bf16_rn(o[e] / l);
+            const uint2 bits = make_uint2((uint32_t)bm_f32_to_bf16(v[0]) | ((uint32_t)bm_f32_to_bf16(v[1]) << 16),
+                                          (uint32_t)bm_f32_to_bf16(v[2]) | ((uint32_t)bm_f32_to_bf16(v[3]) << 16));
+            *reinterpret_cast<uint2 *>(p.att + (size_t)(r0 + qm) * p.H * 128 + (hk * G + qg_) * 128 + 4 * lane) = bits;
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+            if (lane == 0 && amax != 0.0f) atomicMax(&p.amax[r0 + qm], __float_as_uint(amax));
+        }
+        // every remote value has been consumed above: the other CTAs of the cluster may leave
+        cluster_arrive();
+        cluster_wait();
+        return;
     }
     // ticket: the last CTA of this (kv head, query group) to get here merges the super-chunks
     __threadfence();

@@ -131,6 +131,12 @@ ATTN_CASES = [
     (9, 32, 8, 4096, 3000, 0, 8, "verify"),
     (16, 16, 8, 256, 256, 8, 8, "draft"),      # the history fills the whole segment (cache_len == sigma)
     (9, 16, 8, 64, 64, 0, 8, "verify"),
+    # grids that are resident at once run as thread-block clusters (merge through distributed shared memory)
+    (1, 16, 8, 1024, 1000, 0, 8, "ar"),        # nine CTAs per cluster, all with rows
+    (1, 32, 8, 1024, 513, 0, 8, "ar"),
+    (8, 16, 8, 1024, 700, 0, 8, "draft"),      # 288 CTAs in 32 clusters, three of nine CTAs without rows
+    (4, 16, 8, 1920, 1901, 0, 4, "draft"),     # the largest cluster (16)
+    (4, 16, 8, 1920, 0, 0, 4, "ar"),           # only the CTA of the replay's own rows works
 ]
 
 
