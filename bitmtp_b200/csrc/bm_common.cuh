@@ -117,6 +117,13 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---- warp reductions in the oracle's butterfly order -------------------------
+// Exact int32 -> fp32 of a group sum without the conversion unit.  A group sum is at most 128 * 127 * 3
+// in magnitude, so kGroupSumBias + G is the bit pattern of the float 1.5 * 2^23 + G; subtracting 1.5 * 2^23
+// (exact: both operands and the result are integers below 2^24) gives (float)G.  The bias is added for free
+// by starting the MMA accumulator at bias - 2 * sum(A) instead of -2 * sum(A).
+constexpr int kGroupSumBias = 0x4B400000;
+__device__ __forceinline__ float group_sum_to_float(int biased) { return __int_as_float(biased) - 12582912.0f; }
+
 __device__ __forceinline__ float warp_sum_butterfly(float v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, off);

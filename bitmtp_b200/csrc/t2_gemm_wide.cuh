@@ -116,16 +116,16 @@ struct WideSlot {
             for (int b = 0; b < 4; ++b) {
                 const unsigned char *ap = act + (size_t)(8 * b + g) * L.act_stride + li * 128 + 32 * q;
                 const uint4 lo = *reinterpret_cast<const uint4 *>(ap), hi = *reinterpret_cast<const uint4 *>(ap + 16);
-                const int c0 = -2 * asum_s[(8 * b + 2 * q) * ngs + li], c1 = -2 * asum_s[(8 * b + 2 * q + 1) * ngs + li];
+                const int c0 = kGroupSumBias - 2 * asum_s[(8 * b + 2 * q) * ngs + li], c1 = kGroupSumBias - 2 * asum_s[(8 * b + 2 * q + 1) * ngs + li];
                 int d[4];
                 mma_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], lo.x, hi.x, c0, c1, c0, c1);
                 mma_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], lo.y, hi.y, d[0], d[1], d[2], d[3]);
                 mma_u8s8(d, a[2][0], a[2][1], a[2][2], a[2][3], lo.z, hi.z, d[0], d[1], d[2], d[3]);
                 mma_u8s8(d, a[3][0], a[3][1], a[3][2], a[3][3], lo.w, hi.w, d[0], d[1], d[2], d[3]);
-                acc[b][0] = fmaf((float)d[0], s0, acc[b][0]);
-                acc[b][1] = fmaf((float)d[1], s0, acc[b][1]);
-                acc[b][2] = fmaf((float)d[2], s8, acc[b][2]);
-                acc[b][3] = fmaf((float)d[3], s8, acc[b][3]);
+                acc[b][0] = fmaf(group_sum_to_float(d[0]), s0, acc[b][0]);
+                acc[b][1] = fmaf(group_sum_to_float(d[1]), s0, acc[b][1]);
+                acc[b][2] = fmaf(group_sum_to_float(d[2]), s8, acc[b][2]);
+                acc[b][3] = fmaf(group_sum_to_float(d[3]), s8, acc[b][3]);
             }
         }
 #pragma unroll

@@ -508,7 +508,7 @@ template <bool HALF>
 struct AFrag {
     uint4 lo0, hi0;   // token r   : the four MMA steps' k-slots 4q.. and 16+4q..
     uint4 lo8, hi8;   // token r+8 (unused when HALF)
-    int nb0, nb8;     // -2 * sum(A) over the group, tokens r and r+8
+    int nb0, nb8;     // kGroupSumBias - 2 * sum(A) over the group, tokens r and r+8
 };
 
 // Fragments of group g for tokens r and r+8 from rows of `stride` bytes (shared-memory
@@ -518,18 +518,18 @@ template <bool HALF>
 __device__ __forceinline__ void load_afrag(AFrag<HALF> &f, const unsigned char *rows, int stride,
                                            const int *asum, int W, int ng, int g, int r, int q) {
     f.lo0 = f.hi0 = f.lo8 = f.hi8 = make_uint4(0u, 0u, 0u, 0u);
-    f.nb0 = f.nb8 = 0;
+    f.nb0 = f.nb8 = kGroupSumBias;
     if (r < W) {
         const uint4 *ap = reinterpret_cast<const uint4 *>(rows + (size_t)r * stride + BM_GROUP * g + 32 * q);
         f.lo0 = ap[0];
         f.hi0 = ap[1];
-        f.nb0 = -2 * asum[r * ng + g];
+        f.nb0 = kGroupSumBias - 2 * asum[r * ng + g];
     }
     if (!HALF && r + 8 < W) {
         const uint4 *ap8 = reinterpret_cast<const uint4 *>(rows + (size_t)(r + 8) * stride + BM_GROUP * g + 32 * q);
         f.lo8 = ap8[0];
         f.hi8 = ap8[1];
-        f.nb8 = -2 * asum[(r + 8) * ng + g];
+        f.nb8 = kGroupSumBias - 2 * asum[(r + 8) * ng + g];
     }
 }
 
@@ -544,15 +544,15 @@ __device__ __forceinline__ void mma_group_step(const AFrag<HALF> &f, uint2 w2, f
     mma_s8u8(d, f.lo0.y, f.lo8.y, f.hi0.y, f.hi8.y, (w2.x >> 2) & M3, (w2.y >> 2) & M3, d[0], d[1], d[2], d[3]);
     mma_s8u8(d, f.lo0.z, f.lo8.z, f.hi0.z, f.hi8.z, (w2.x >> 4) & M3, (w2.y >> 4) & M3, d[0], d[1], d[2], d[3]);
     mma_s8u8(d, f.lo0.w, f.lo8.w, f.hi0.w, f.hi8.w, (w2.x >> 6) & M3, (w2.y >> 6) & M3, d[0], d[1], d[2], d[3]);
-    acc[0] = fmaf((float)d[0], s0, acc[0]);
-    acc[1] = fmaf((float)d[1], s1, acc[1]);
+    acc[0] = fmaf(group_sum_to_float(d[0]), s0, acc[0]);
+    acc[1] = fmaf(group_sum_to_float(d[1]), s1, acc[1]);
     if (!HALF) {
-        acc[2] = fmaf((float)d[2], s0, acc[2]);
-        acc[3] = fmaf((float)d[3], s1, acc[3]);
+        acc[2] = fmaf(group_sum_to_float(d[2]), s0, acc[2]);
+        acc[3] = fmaf(group_sum_to_float(d[3]), s1, acc[3]);
     }
     if (EMIT_G) {
-        if (gdst0) { gdst0[0] = d[0]; gdst0[gstride] = d[1]; }
-        if (!HALF && gdst8) { gdst8[0] = d[2]; gdst8[gstride] = d[3]; }
+        if (gdst0) { gdst0[0] = d[0] - kGroupSumBias; gdst0[gstride] = d[1] - kGroupSumBias; }
+        if (!HALF && gdst8) { gdst8[0] = d[2] - kGroupSumBias; gdst8[gstride] = d[3] - kGroupSumBias; }
     }
 }
 

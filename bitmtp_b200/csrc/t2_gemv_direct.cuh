@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kDirectWarps * 32) t2_gemv_direct_kernel(const
 #pragma unroll
             for (int m = 0; m < WT; ++m) {
                 const int G = direct_group_sum(part[m]) - 2 * asum_g[m][q];
-                acc[m][q] = fmaf((float)G, sc[ps][q], acc[m][q]);
+                acc[m][q] = fmaf(group_sum_to_float(G + kGroupSumBias), sc[ps][q], acc[m][q]);
                 if (p.G != nullptr && g < ng && (lane & 7) == 0 && m < p.W)
                     p.G[((size_t)m * p.N + n) * ng + g] = G;
             }
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const 
             const bool active = g < ng;
             const uint4 a = active ? *reinterpret_cast<const uint4 *>(smem + 2048 * ps + 512 * q + 16 * lane)
                                    : make_uint4(0u, 0u, 0u, 0u);
-            const int asum_g = active ? asum[g] : 0;
+            const int nb = kGroupSumBias - 2 * (active ? asum[g] : 0);
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 const uint32_t w = wv[r][ps][q];
@@ -265,8 +265,7 @@ __global__ void __launch_bounds__(kGemvThreads) t2_gemv_direct_row_kernel(const 
                 part = dp4a_s8_u8(a.y, (w >> 2) & 0x03030303u, part);
                 part = dp4a_s8_u8(a.z, (w >> 4) & 0x03030303u, part);
                 part = dp4a_s8_u8(a.w, (w >> 6) & 0x03030303u, part);
-                const int G = direct_group_sum(part) - 2 * asum_g;
-                acc[r][q] = fmaf((float)G, sc[r][ps][q], acc[r][q]);
+                acc[r][q] = fmaf(group_sum_to_float(direct_group_sum(part) + nb), sc[r][ps][q], acc[r][q]);
             }
         }
     }

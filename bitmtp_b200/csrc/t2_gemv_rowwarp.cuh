@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                     v0 = 2 * qq < p.W ? p.asum[(2 * qq) * ng + gg] : 0;
                     v1 = 2 * qq + 1 < p.W ? p.asum[(2 * qq + 1) * ng + gg] : 0;
                 }
-                nbq[i] = make_int4(-2 * v0, -2 * v1, -2 * v0, -2 * v1);
+                nbq[i] = make_int4(kGroupSumBias - 2 * v0, kGroupSumBias - 2 * v1, kGroupSumBias - 2 * v0, kGroupSumBias - 2 * v1);
             }
         for (int i0 = 0; i0 < total_units; i0 += kMaxUnits * THREADS) {
 #pragma unroll
@@ -255,8 +255,8 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
         if (!prepared) {
             for (int i = threadIdx.x; i < ng * 4; i += THREADS) {
                 const int gg = i >> 2, qq = i & 3, t0 = 2 * qq, t1 = 2 * qq + 1;
-                const int v0 = t0 < p.W ? -2 * asum_s[t0 * ng + gg] : 0;
-                const int v1 = t1 < p.W ? -2 * asum_s[t1 * ng + gg] : 0;
+                const int v0 = kGroupSumBias + (t0 < p.W ? -2 * asum_s[t0 * ng + gg] : 0);
+                const int v1 = kGroupSumBias + (t1 < p.W ? -2 * asum_s[t1 * ng + gg] : 0);
                 nbq[i] = make_int4(v0, v1, v0, v1);
             }
             __syncthreads();
@@ -349,23 +349,23 @@ __global__ void __launch_bounds__(kRwMaxWarps * 32, 1) t2_gemv_rowwarp_kernel(co
                         const float s8 = (j & 1) ? __uint_as_float(w8 & 0xffff0000u) : __uint_as_float(w8 << 16);
                         float(&a)[NA] = acc[4 * pp + j];
                         if (NTOK == 2) {
-                            a[0] = fmaf((float)d[jj][0], s0, a[0]);
-                            a[1] = fmaf((float)d[jj][1], s0, a[1]);
-                            a[2] = fmaf((float)d[jj][2], s8, a[2]);
-                            a[3] = fmaf((float)d[jj][3], s8, a[3]);
+                            a[0] = fmaf(group_sum_to_float(d[jj][0]), s0, a[0]);
+                            a[1] = fmaf(group_sum_to_float(d[jj][1]), s0, a[1]);
+                            a[2] = fmaf(group_sum_to_float(d[jj][2]), s8, a[2]);
+                            a[3] = fmaf(group_sum_to_float(d[jj][3]), s8, a[3]);
                         } else {
-                            a[0] = fmaf((float)d[jj][0], s0, a[0]);
-                            a[1] = fmaf((float)d[jj][2], s8, a[1]);
+                            a[0] = fmaf(group_sum_to_float(d[jj][0]), s0, a[0]);
+                            a[1] = fmaf(group_sum_to_float(d[jj][2]), s8, a[1]);
                         }
                         if (EMIT_G) {
                             const int t0 = 2 * q, t1 = 2 * q + 1;
                             if (t0 < p.W) {
-                                p.G[((size_t)t0 * p.N + n0 + g) * ng + G + j] = d[jj][0];
-                                p.G[((size_t)t0 * p.N + n0 + g + 8) * ng + G + j] = d[jj][2];
+                                p.G[((size_t)t0 * p.N + n0 + g) * ng + G + j] = d[jj][0] - kGroupSumBias;
+                                p.G[((size_t)t0 * p.N + n0 + g + 8) * ng + G + j] = d[jj][2] - kGroupSumBias;
                             }
                             if (t1 < p.W) {
-                                p.G[((size_t)t1 * p.N + n0 + g) * ng + G + j] = d[jj][1];
-                                p.G[((size_t)t1 * p.N + n0 + g + 8) * ng + G + j] = d[jj][3];
+                                p.G[((size_t)t1 * p.N + n0 + g) * ng + G + j] = d[jj][1] - kGroupSumBias;
+                                p.G[((size_t)t1 * p.N + n0 + g + 8) * ng + G + j] = d[jj][3] - kGroupSumBias;
                             }
                         }
                     }
