@@ -115,6 +115,11 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Batches of such copies: commit closes the batch issued so far, wait_batches<N> returns when at most
+// N of this thread's most recent batches are still in flight.
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_batches() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---- warp reductions in the oracle's butterfly order -------------------------
 // Exact int32 -> fp32 of a group sum without the conversion unit.  A group sum is at most 128 * 127 * 3

@@ -1050,17 +1050,7 @@ int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void 
         K < BM_GROUP || (K % BM_GROUP) != 0 || ldc < N)
         return BM_EINVAL;
     if (!aligned16(A_prep) || !aligned16(B)) return BM_EINVAL;
-    const int ng = K / BM_GROUP, SB = bm::wide_slots_per_stage(ng);
-    size_t smem = 0;
-    for (int s0 = 0; s0 < BM_SLOTS; s0 += SB) {
-        int ngs = 0;
-        for (int i = 0; i < SB; ++i) {
-            const int t = (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS;
-            ngs += t > 0 ? t : 0;
-        }
-        const size_t need = (size_t)bm::wide_smem_layout(ngs > 0 ? ngs : 1).total;
-        smem = need > smem ? need : smem;
-    }
+    const size_t smem = bm::wide_smem_bytes(K / BM_GROUP);
     if (smem > (size_t)kMaxSmemPerCta) return BM_EINVAL;
     bm::WideParams p;
     p.A = static_cast<const int8_t *>(A_prep);

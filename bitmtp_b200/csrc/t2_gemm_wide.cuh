@@ -9,19 +9,22 @@
 //
 // This IS a contraction (a weight is reused by every prompt row), so it runs on the tensor cores:
 // mma.sync.m16n8k32 with 16 weight rows as the M dimension (u8 codes as A), 8 prompt rows as the N
-// dimension (s8 activations as B); four MMAs cover a 128-group with -2 * sum(a) as the first C
-// operand, so the int32 fragment is the exact group sum.  The 2-bit -> 8-bit expansion happens in
+// dimension (s8 activations as B); four MMAs cover a 128-group with bias - 2 * sum(a) as the first C
+// operand, so the int32 fragment is the exact group sum plus the bias that turns it into a float.  The 2-bit -> 8-bit expansion happens in
 // registers, once per group and warp, and is reused by the 32 prompt rows of the tile.
 //
 // fp32 order (the GEMV's, see the header of t2_gemv.cuh): group g -> slot g % 16, slot = fma(G,
 // scale, slot) in ascending g, the 16 slots summed as a butterfly tree, times 1/s.  A wide tile cannot
 // hold 16 slot accumulators per output, so the groups are visited SLOT BY SLOT (s, s+16, s+32, ...:
-// one accumulator), and a finished slot is folded into a binary-counter tree (4 registers per output)
-// whose additions are exactly the butterfly's.
+// one accumulator) and combined four slots at a time, (s0 + s1) + (s2 + s3), then the four such values
+// as (q0 + q1) + (q2 + q3): the additions are exactly the butterfly's.
 //
-// CTA = 8 warps = 128 weight rows x 32 prompt rows; the slots are staged through shared memory in
-// batches (activations [32 rows][groups][128 B], codes [128 rows][groups][32 B], scales, group sums),
-// 16-byte asynchronous copies, two CTAs per SM so that one computes while the other loads.
+// CTA = 8 warps = 128 weight rows x 32 prompt rows.  The groups are taken in the slot-major sequence
+// (slot 0's groups, slot 1's, ...) in stages of kWideStageGroups: activations [32 rows][128 B per group]
+// and codes [128 rows][32 B per group] arrive by 16-byte asynchronous copies into a ring of kWideStages
+// buffers, the next stage loading while the current one is multiplied (one CTA barrier per stage); the
+// bf16 scales of the CTA's 128 rows and the C operands (bias - 2 * sum(a)) of its 32 prompt rows are
+// tables loaded once.  Two CTAs per SM.
 #pragma once
 
 #include "bm_common.cuh"
@@ -32,7 +35,16 @@ namespace bm {
 constexpr int kWideThreads = 256;
 constexpr int kWideRows = 128;          // weight rows per CTA (16 per warp)
 constexpr int kWideTokens = 32;         // prompt rows per CTA (4 MMA column blocks)
-constexpr int kWideMaxStageGroups = 12; // groups staged at once (about 100 KB)
+constexpr int kWideStageGroups = 4;     // groups per stage
+constexpr int kWideStages = 2;          // stage buffers
+// Strides chosen so that the fragment reads are free of bank conflicts: activation rows (16-byte reads of
+// 8 rows x 4 quarters) want an odd number of 16-byte units, code rows (8-byte reads of 4 rows x 4
+// quarters) 32 mod 128 bytes, the C-operand table (8-byte reads, stores along the group index) 34 words.
+constexpr int kWideActStride = kWideStageGroups * 128 + 16;
+constexpr int kWideCodeStride = kWideStageGroups * 32 + 32;
+constexpr int kWideStageBytes = kWideTokens * kWideActStride + kWideRows * kWideCodeStride;
+constexpr int kWideNbStride = kWideTokens + 2;
+static_assert((kWideActStride / 16) % 2 == 1 && kWideCodeStride % 128 == 32, "bank-conflict-free strides");
 
 struct WideParams {
     const int8_t *A;        // [T, K] GEMV-ready INT8 rows
@@ -44,212 +56,214 @@ struct WideParams {
     int T, N, K, ldc, pdl;
 };
 
-struct WideSmem {
-    int act_stride, w_stride, act_off, w_off, sc_off, asum_off, total;
-};
+// Scale-table row stride in bf16 elements: ng + 2 makes the 32-bit word stride odd when ng % 4 == 0.
+__host__ __device__ inline int wide_scale_stride(int ng) { return ng + 2; }
 
-// Layout for a stage of `ngs` groups.  Strides are padded so that the fragment reads are free of bank
-// conflicts: activation rows (16-byte reads of 8 rows x 4 quarters) want an odd number of 16-byte units,
-// code rows (8-byte reads of 4 rows x 4 quarters) want 32 mod 128 bytes.
-__host__ __device__ inline WideSmem wide_smem_layout(int ngs) {
-    WideSmem L;
-    L.act_stride = ngs * 128 + 16;
-    int ws = ngs * 32;
-    ws += (32 - (ws % 128) + 128) % 128;
-    L.w_stride = ws;
-    L.act_off = 0;
-    L.w_off = L.act_off + kWideTokens * L.act_stride;
-    L.sc_off = L.w_off + kWideRows * L.w_stride;
-    L.asum_off = L.sc_off + kWideRows * ngs * 2;
-    L.asum_off = (L.asum_off + 15) & ~15;
-    L.total = L.asum_off + kWideTokens * ngs * 4;
-    return L;
+__host__ __device__ inline size_t wide_smem_bytes(int ng) {
+    size_t off = (size_t)kWideStages * kWideStageBytes;
+    off += ((size_t)kWideRows * wide_scale_stride(ng) * 2 + 15) & ~(size_t)15;
+    off += (size_t)ng * kWideNbStride * 4;
+    return off;
 }
 
-// Slots per stage: the largest power of two whose groups (terms per slot = ceil(ng / 16)) fit.
-__host__ __device__ inline int wide_slots_per_stage(int ng) {
-    const int terms = (ng + BM_SLOTS - 1) / BM_SLOTS;
-    int sb = BM_SLOTS;
-    while (sb > 1 && sb * terms > kWideMaxStageGroups) sb >>= 1;
-    return sb;
-}
-
-// Folds slot `s` (compile-time) into the binary-counter tree: level l holds the sum of a finished block
-// of 2^l slots whose partner has not arrived yet; `left + right` with the earlier block on the left,
-// which is the butterfly order ((s0+s1)+(s2+s3))+... of the GEMV.
-template <int S>
-__device__ __forceinline__ void wide_tree_push(float (&tree)[4], float v) {
-    if (S & 1) { v = tree[0] + v; } else { tree[0] = v; return; }
-    if (S & 2) { v = tree[1] + v; } else { tree[1] = v; return; }
-    if (S & 4) { v = tree[2] + v; } else { tree[2] = v; return; }
-    if (S & 8) { v = tree[3] + v; } else { tree[3] = v; return; }
-    tree[3] = v;            // S == 15: the total
-}
-
-template <int S>
-struct WideSlot {
-    // One slot of the canonical order for this warp's 16 rows x 32 prompt rows: its groups are in the staged
-    // batch at local indices li0, li0 + 1, ... (n_terms of them).
-    static __device__ __forceinline__ void run(const unsigned char *act, const unsigned char *wts, const uint16_t *sc,
-                                               const int *asum_s, int ngs, const WideSmem &L, int li0, int n_terms,
-                                               int g, int q, float (&tree)[4][4][4]) {
-        constexpr uint32_t M3 = 0x03030303u;
-        float acc[4][4];
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[b][e] = 0.0f;
-        for (int c = 0; c < n_terms; ++c) {
-            const int li = li0 + c;
-            const uint2 x = *reinterpret_cast<const uint2 *>(wts + (size_t)g * L.w_stride + li * 32 + 8 * q);
-            const uint2 y = *reinterpret_cast<const uint2 *>(wts + (size_t)(g + 8) * L.w_stride + li * 32 + 8 * q);
-            const float s0 = bf16_bits_to_f32(sc[g * ngs + li]), s8 = bf16_bits_to_f32(sc[(g + 8) * ngs + li]);
-            uint32_t a[4][4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                a[t][0] = (x.x >> (2 * t)) & M3;
-                a[t][1] = (y.x >> (2 * t)) & M3;
-                a[t][2] = (x.y >> (2 * t)) & M3;
-                a[t][3] = (y.y >> (2 * t)) & M3;
-            }
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const unsigned char *ap = act + (size_t)(8 * b + g) * L.act_stride + li * 128 + 32 * q;
-                const uint4 lo = *reinterpret_cast<const uint4 *>(ap), hi = *reinterpret_cast<const uint4 *>(ap + 16);
-                const int c0 = kGroupSumBias - 2 * asum_s[(8 * b + 2 * q) * ngs + li], c1 = kGroupSumBias - 2 * asum_s[(8 * b + 2 * q + 1) * ngs + li];
-                int d[4];
-                mma_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], lo.x, hi.x, c0, c1, c0, c1);
-                mma_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], lo.y, hi.y, d[0], d[1], d[2], d[3]);
-                mma_u8s8(d, a[2][0], a[2][1], a[2][2], a[2][3], lo.z, hi.z, d[0], d[1], d[2], d[3]);
-                mma_u8s8(d, a[3][0], a[3][1], a[3][2], a[3][3], lo.w, hi.w, d[0], d[1], d[2], d[3]);
-                acc[b][0] = fmaf(group_sum_to_float(d[0]), s0, acc[b][0]);
-                acc[b][1] = fmaf(group_sum_to_float(d[1]), s0, acc[b][1]);
-                acc[b][2] = fmaf(group_sum_to_float(d[2]), s8, acc[b][2]);
-                acc[b][3] = fmaf(group_sum_to_float(d[3]), s8, acc[b][3]);
-            }
-        }
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) wide_tree_push<S>(tree[b][e], acc[b][e]);
+// Position in the slot-major sequence of groups: slot s (0..15), term c; slot s has ceil((ng - s) / 16)
+// groups s, s + 16, ...  `step` moves to the next position (warp-uniform integer work, no division).
+struct WideSeq {
+    int s, c;
+    __device__ __forceinline__ int group() const { return s + BM_SLOTS * c; }
+    __device__ __forceinline__ static int terms(int slot, int ng) { return (ng - slot + BM_SLOTS - 1) >> 4; }
+    __device__ __forceinline__ bool step(int ng) {             // true when the slot was finished by this step
+        if (++c < terms(s, ng)) return false;
+        c = 0;
+        ++s;
+        return true;
     }
 };
+
+// One 128-group for this warp's 16 weight rows x the CTA's 32 prompt rows: unpack the codes once, then
+// per block of 8 prompt rows four MMAs and `acc = fma((float)G, scale, acc)`.
+//   wts   this lane's code bytes of the group (row g of the warp's 16; row g + 8 is 8 rows further)
+//   act   this lane's activation bytes of the group (prompt row g of block 0)
+//   nb    this lane's C operands of the group (prompt rows 2q, 2q + 1 of block 0)
+// FIRST: the slot's first group (the accumulators start from zero).
+template <bool FIRST>
+__device__ __forceinline__ void wide_group(const unsigned char *wts, const unsigned char *act, const int *nb, float s0,
+                                           float s8, float (&acc)[4][4]) {
+    constexpr uint32_t M3 = 0x03030303u;
+    const uint2 x = *reinterpret_cast<const uint2 *>(wts);
+    const uint2 y = *reinterpret_cast<const uint2 *>(wts + 8 * kWideCodeStride);
+    // A operands of the four MMAs.  Bit plane t of a code word (codes 4e + t of its 16-code runs) meets
+    // activation word t of the same run; which two (plane, word) pairs share an MMA does not change the
+    // integer sum, so they are paired such that every B operand is an aligned register pair of one
+    // 16-byte activation load: (lo.x, lo.y), (lo.z, lo.w), (hi.x, hi.y), (hi.z, hi.w).
+    uint32_t a[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t xw = j < 2 ? x.x : x.y, yw = j < 2 ? y.x : y.y;
+        const int t = 2 * (j & 1);
+        a[j][0] = (xw >> (2 * t)) & M3;
+        a[j][1] = (yw >> (2 * t)) & M3;
+        a[j][2] = (xw >> (2 * t + 2)) & M3;
+        a[j][3] = (yw >> (2 * t + 2)) & M3;
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint4 lo = *reinterpret_cast<const uint4 *>(act + 8 * b * kWideActStride);
+        const uint4 hi = *reinterpret_cast<const uint4 *>(act + 8 * b * kWideActStride + 16);
+        const int2 c = *reinterpret_cast<const int2 *>(nb + 8 * b);
+        int d[4];
+        mma_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], lo.x, lo.y, c.x, c.y, c.x, c.y);
+        mma_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], lo.z, lo.w, d[0], d[1], d[2], d[3]);
+        mma_u8s8(d, a[2][0], a[2][1], a[2][2], a[2][3], hi.x, hi.y, d[0], d[1], d[2], d[3]);
+        mma_u8s8(d, a[3][0], a[3][1], a[3][2], a[3][3], hi.z, hi.w, d[0], d[1], d[2], d[3]);
+        acc[b][0] = fmaf(group_sum_to_float(d[0]), s0, FIRST ? 0.0f : acc[b][0]);
+        acc[b][1] = fmaf(group_sum_to_float(d[1]), s0, FIRST ? 0.0f : acc[b][1]);
+        acc[b][2] = fmaf(group_sum_to_float(d[2]), s8, FIRST ? 0.0f : acc[b][2]);
+        acc[b][3] = fmaf(group_sum_to_float(d[3]), s8, FIRST ? 0.0f : acc[b][3]);
+    }
+}
+
+// Requests of one group into position li of a stage buffer: every thread copies one 16-byte half of one
+// code row (128 rows x 2) and one 16-byte piece of one prompt row (32 rows x 8).
+__device__ __forceinline__ void wide_issue_codes(unsigned char *buf, int li, const uint8_t *src_row, int grp, int tid) {
+    cp_async16(buf + kWideTokens * kWideActStride + (tid >> 1) * kWideCodeStride + li * 32 + 16 * (tid & 1), src_row + grp * 32);
+}
+__device__ __forceinline__ void wide_issue_row(unsigned char *buf, int li, const int8_t *src_row, int grp, int tid) {
+    unsigned char *dst = buf + (tid >> 3) * kWideActStride + li * 128 + 16 * (tid & 7);
+    if (src_row != nullptr) cp_async16(dst, src_row + grp * 128);
+    else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// State of the copy pipeline.  Before the first group of stage st: the stage has landed - kWideStages
+// batches are out at stage 0, kWideStages - 1 + st later, and only the ones after batch st may still be in
+// flight; once every warp is past the barrier the buffer of stage st - 1 is free and takes stage
+// st - 1 + kWideStages.  Kept out of line: it runs once per kWideStageGroups groups, and the multiply
+// loop around it should stay small.
+struct WidePipe {
+    unsigned char *ring;
+    const uint8_t *code_src;      // this thread's half of a code row, group 0
+    const int8_t *row_src;        // this thread's piece of a prompt row, group 0 (null: past T)
+    WideSeq prod;                 // next group to request
+    int requested, ng;
+};
+__device__ __noinline__ void wide_enter_stage(WidePipe &pp, int st) {
+    const int tid = threadIdx.x;
+    if (st == 0) cp_async_wait_batches<kWideStages - 1>();
+    else cp_async_wait_batches<kWideStages - 2>();
+    __syncthreads();
+    if (st > 0) {
+        unsigned char *buf = pp.ring + ((st - 1) % kWideStages) * kWideStageBytes;
+        for (int li = 0; li < kWideStageGroups && pp.requested < pp.ng; ++li, ++pp.requested, pp.prod.step(pp.ng)) {
+            wide_issue_codes(buf, li, pp.code_src, pp.prod.group(), tid);
+            wide_issue_row(buf, li, pp.row_src, pp.prod.group(), tid);
+        }
+        cp_async_commit();
+    }
+}
 
 // grid (N / 128, ceil(T / 32)), 256 threads.  K % 128 == 0, N % 128 == 0.
 __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const WideParams p) {
     extern __shared__ __align__(16) unsigned char wsm[];
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
-    const int ng = p.K / BM_GROUP;
+    const int ng = p.K / BM_GROUP, scs = wide_scale_stride(ng);
     const int n0 = blockIdx.x * kWideRows, t0 = blockIdx.y * kWideTokens;
-    const int SB = wide_slots_per_stage(ng);
-    float tree[4][4][4];                     // [token block][fragment element][level]
-#pragma unroll
-    for (int b = 0; b < 4; ++b)
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-#pragma unroll
-            for (int l = 0; l < 4; ++l) tree[b][e][l] = 0.0f;
+    unsigned char *ring = wsm;
+    uint16_t *sc_tab = reinterpret_cast<uint16_t *>(wsm + kWideStages * kWideStageBytes);
+    int *nb_tab = reinterpret_cast<int *>(wsm + kWideStages * kWideStageBytes + (((size_t)kWideRows * scs * 2 + 15) & ~(size_t)15));
+    // what this thread copies of every group: its half of a code row, its piece of a prompt row (null: past T)
+    const uint8_t *code_src = p.B + (size_t)(n0 + (tid >> 1)) * (p.K / 4) + 16 * (tid & 1);
+    const int8_t *row_src = t0 + (tid >> 3) < p.T ? p.A + (size_t)(t0 + (tid >> 3)) * p.K + 16 * (tid & 7) : nullptr;
 
-    bool waited = !p.pdl;
-    for (int s0 = 0; s0 < BM_SLOTS; s0 += SB) {
-        // groups of this stage, slot-major: local index li <-> (slot s0 + i, term c) with group s0 + i + 16 c
-        int ngs = 0;
-        for (int i = 0; i < SB; ++i) ngs += (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS > 0 ? (ng - (s0 + i) + BM_SLOTS - 1) / BM_SLOTS : 0;
-        const WideSmem L = wide_smem_layout(ngs > 0 ? ngs : 1);
-        if (s0 > 0) __syncthreads();                          // everyone is done with the previous stage
-        // local index -> group, slot-major (every thread keeps the short table in registers)
-        int grp_of[kWideMaxStageGroups];
-        {
-            int li = 0;
-            for (int i = 0; i < SB; ++i)
-                for (int grp = s0 + i; grp < ng && li < kWideMaxStageGroups; grp += BM_SLOTS) grp_of[li++] = grp;
-        }
-        // weights first: they do not depend on the previous kernel in the stream.  Codes by 16-byte
-        // asynchronous copies; the scales (2 bytes per row and group) are fetched into registers together
-        // and stored afterwards, so that the stage costs one memory round trip, not one per group.
-        for (int e = tid; e < ngs * kWideRows * 2; e += kWideThreads) {
-            const int li = e / (kWideRows * 2), j2 = e - li * (kWideRows * 2), r = j2 >> 1, h = j2 & 1;
-            cp_async16(wsm + L.w_off + (size_t)r * L.w_stride + li * 32 + 16 * h,
-                       p.B + (size_t)(n0 + r) * (p.K / 4) + grp_of[li] * 32 + 16 * h);
-        }
-        constexpr int kScPer = (kWideMaxStageGroups * kWideRows + kWideThreads - 1) / kWideThreads;   // 6
-        uint16_t scv[kScPer];
-#pragma unroll
-        for (int k = 0; k < kScPer; ++k) {
-            const int e = tid + k * kWideThreads;
-            if (e < ngs * kWideRows) {
-                const int li = e / kWideRows, r = e - li * kWideRows;
-                scv[k] = p.ws[(size_t)(n0 + r) * ng + grp_of[li]];
-            }
-        }
-        if (!waited) { pdl_wait(); waited = true; }
-        for (int e = tid; e < ngs * kWideTokens * 8; e += kWideThreads) {
-            const int li = e / (kWideTokens * 8), j2 = e - li * (kWideTokens * 8), r = j2 >> 3, h = j2 & 7;
-            unsigned char *dst = wsm + L.act_off + (size_t)r * L.act_stride + li * 128 + 16 * h;
-            if (t0 + r < p.T) cp_async16(dst, p.A + (size_t)(t0 + r) * p.K + grp_of[li] * 128 + 16 * h);
-            else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        constexpr int kAsPer = (kWideMaxStageGroups * kWideTokens + kWideThreads - 1) / kWideThreads;  // 2
-        int asv[kAsPer];
-#pragma unroll
-        for (int k = 0; k < kAsPer; ++k) {
-            const int e = tid + k * kWideThreads;
-            asv[k] = 0;
-            if (e < ngs * kWideTokens) {
-                const int li = e / kWideTokens, r = e - li * kWideTokens;
-                if (t0 + r < p.T) asv[k] = p.asum[(size_t)(t0 + r) * ng + grp_of[li]];
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < kScPer; ++k) {
-            const int e = tid + k * kWideThreads;
-            if (e < ngs * kWideRows) {
-                const int li = e / kWideRows, r = e - li * kWideRows;
-                reinterpret_cast<uint16_t *>(wsm + L.sc_off)[r * ngs + li] = scv[k];
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < kAsPer; ++k) {
-            const int e = tid + k * kWideThreads;
-            if (e < ngs * kWideTokens) {
-                const int li = e / kWideTokens, r = e - li * kWideTokens;
-                reinterpret_cast<int *>(wsm + L.asum_off)[r * ngs + li] = asv[k];
-            }
-        }
-        cp_async_wait_all();
-        __syncthreads();
-        const unsigned char *act = wsm + L.act_off;
-        const unsigned char *wts = wsm + L.w_off + (size_t)(16 * warp) * L.w_stride;
-        const uint16_t *sc = reinterpret_cast<const uint16_t *>(wsm + L.sc_off) + (size_t)(16 * warp) * ngs;
-        const int *asum_s = reinterpret_cast<const int *>(wsm + L.asum_off);
-        int li = 0;
-        // the slots of this stage in ascending order; the slot number must be a compile-time constant for the tree
-#define BM_WIDE_SLOT(S_)                                                                                       \
-        if (S_ >= s0 && S_ < s0 + SB) {                                                                        \
-            const int nt = (ng - S_ + BM_SLOTS - 1) / BM_SLOTS > 0 ? (ng - S_ + BM_SLOTS - 1) / BM_SLOTS : 0;   \
-            WideSlot<S_>::run(act, wts, sc, asum_s, ngs, L, li, nt, g, q, tree);                               \
-            li += nt;                                                                                          \
-        }
-        BM_WIDE_SLOT(0) BM_WIDE_SLOT(1) BM_WIDE_SLOT(2) BM_WIDE_SLOT(3) BM_WIDE_SLOT(4) BM_WIDE_SLOT(5) BM_WIDE_SLOT(6)
-        BM_WIDE_SLOT(7) BM_WIDE_SLOT(8) BM_WIDE_SLOT(9) BM_WIDE_SLOT(10) BM_WIDE_SLOT(11) BM_WIDE_SLOT(12)
-        BM_WIDE_SLOT(13) BM_WIDE_SLOT(14) BM_WIDE_SLOT(15)
-#undef BM_WIDE_SLOT
+    // Weights first: the codes of the whole ring and the scales do not depend on the previous kernel in
+    // the stream.  Batch st of the asynchronous copies holds (at least) everything of stage st.
+    {
+        WideSeq w = {0, 0};
+        for (int i = 0; i < kWideStages * kWideStageGroups && i < ng; ++i, w.step(ng))
+            wide_issue_codes(ring + (i / kWideStageGroups) * kWideStageBytes, i % kWideStageGroups, code_src, w.group(), tid);
     }
-    // tree[..][3] holds the sum of the 16 slots; times 1/s of the prompt row, to bf16
+    for (int e = tid; e < kWideRows * ng; e += kWideThreads) {
+        const int r = e / ng, grp = e - r * ng;
+        sc_tab[r * scs + grp] = p.ws[(size_t)(n0 + r) * ng + grp];
+    }
+    if (p.pdl) pdl_wait();
+    WidePipe pp = {ring, code_src, row_src, {0, 0}, 0, ng};
+#pragma unroll
+    for (int st = 0; st < kWideStages; ++st) {
+        for (int li = 0; li < kWideStageGroups && pp.requested < ng; ++li, ++pp.requested, pp.prod.step(ng))
+            wide_issue_row(ring + st * kWideStageBytes, li, row_src, pp.prod.group(), tid);
+        cp_async_commit();
+    }
+    for (int e = tid; e < kWideTokens * ng; e += kWideThreads) {
+        const int r = e / ng, grp = e - r * ng;
+        nb_tab[grp * kWideNbStride + r] = kGroupSumBias - 2 * (t0 + r < p.T ? p.asum[(size_t)(t0 + r) * ng + grp] : 0);
+    }
+
+    const uint16_t *sc0 = sc_tab + (16 * warp + g) * scs, *sc8 = sc0 + 8 * scs;
+    const int *nb0 = nb_tab + 2 * q;
+    const int wbase = kWideTokens * kWideActStride + (16 * warp + g) * kWideCodeStride + 8 * q;
+    const int abase = g * kWideActStride + 32 * q;
+    int seq = 0;                             // position of the group being multiplied
+    // All groups of one slot into `acc` (zeros for a slot without groups: fewer than 16 groups in K).
+    auto run_slot = [&](int slot, float (&acc)[4][4]) {
+        const int nt = WideSeq::terms(slot, ng);
+        if (nt == 0) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[b][e] = 0.0f;
+            return;
+        }
+        for (int c = 0; c < nt; ++c, ++seq) {
+            const int st = seq / kWideStageGroups, li = seq % kWideStageGroups;
+            if (li == 0) wide_enter_stage(pp, st);
+            const unsigned char *buf = ring + (st % kWideStages) * kWideStageBytes;
+            const int grp = slot + BM_SLOTS * c;
+            const float s0 = bf16_bits_to_f32(sc0[grp]), s8 = bf16_bits_to_f32(sc8[grp]);
+            if (c == 0) wide_group<true>(buf + wbase + li * 32, buf + abase + li * 128, nb0 + grp * kWideNbStride, s0, s8, acc);
+            else wide_group<false>(buf + wbase + li * 32, buf + abase + li * 128, nb0 + grp * kWideNbStride, s0, s8, acc);
+        }
+    };
+    // The butterfly ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)) + ... with the slots taken in ascending order:
+    // four slots at a time give one level-2 value (l1 = a + b, then l1 + (a + b)); the four level-2 values
+    // are combined as (q0 + q1) + (q2 + q3).  `left + right` always has the earlier block on the left.
+    float total[4][4], half[4][4];           // [token block][fragment element]
+#pragma unroll 1
+    for (int quad = 0; quad < 4; ++quad) {
+        float a[4][4], b2[4][4], l1[4][4];
+        run_slot(4 * quad, a);
+        run_slot(4 * quad + 1, b2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) l1[b][e] = a[b][e] + b2[b][e];
+        run_slot(4 * quad + 2, a);
+        run_slot(4 * quad + 3, b2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = l1[b][e] + (a[b][e] + b2[b][e]);          // slots 4 quad .. 4 quad + 3
+                if (quad == 0) half[b][e] = v;                            // uniform branches
+                else if (quad == 1) total[b][e] = half[b][e] + v;
+                else if (quad == 2) half[b][e] = v;
+                else total[b][e] = total[b][e] + (half[b][e] + v);
+            }
+    }
+    // times 1/s of the prompt row, to bf16
     const int row = n0 + 16 * warp + g;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
         const int ta = t0 + 8 * b + 2 * q, tb = ta + 1;
         if (ta < p.T) {
             const float is = 1.0f / p.s[ta];
-            p.C[(size_t)ta * p.ldc + row] = bm_f32_to_bf16(tree[b][0][3] * is);
-            p.C[(size_t)ta * p.ldc + row + 8] = bm_f32_to_bf16(tree[b][2][3] * is);
+            p.C[(size_t)ta * p.ldc + row] = bm_f32_to_bf16(total[b][0] * is);
+            p.C[(size_t)ta * p.ldc + row + 8] = bm_f32_to_bf16(total[b][2] * is);
         }
         if (tb < p.T) {
             const float is = 1.0f / p.s[tb];
-            p.C[(size_t)tb * p.ldc + row] = bm_f32_to_bf16(tree[b][1][3] * is);
-            p.C[(size_t)tb * p.ldc + row + 8] = bm_f32_to_bf16(tree[b][3][3] * is);
+            p.C[(size_t)tb * p.ldc + row] = bm_f32_to_bf16(total[b][1] * is);
+            p.C[(size_t)tb * p.ldc + row + 8] = bm_f32_to_bf16(total[b][3] * is);
         }
     }
 }
