@@ -80,6 +80,24 @@ struct WideSeq {
     }
 };
 
+// Shared-memory loads by 32-bit shared address (the multiply loop keeps its addresses in 32-bit registers
+// with constant offsets instead of 64-bit generic pointers).
+__device__ __forceinline__ uint2 wide_lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 wide_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float wide_lds_bf16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory");
+    return __uint_as_float((uint32_t)v << 16);
+}
+
 // One 128-group for this warp's 16 weight rows x the CTA's 32 prompt rows: unpack the codes once, then
 // per block of 8 prompt rows four MMAs and `acc = fma((float)G, scale, acc)`.
 //   wts   this lane's code bytes of the group (row g of the warp's 16; row g + 8 is 8 rows further)
@@ -87,11 +105,10 @@ struct WideSeq {
 //   nb    this lane's C operands of the group (prompt rows 2q, 2q + 1 of block 0)
 // FIRST: the slot's first group (the accumulators start from zero).
 template <bool FIRST>
-__device__ __forceinline__ void wide_group(const unsigned char *wts, const unsigned char *act, const int *nb, float s0,
-                                           float s8, float (&acc)[4][4]) {
+__device__ __forceinline__ void wide_group(uint32_t wts, uint32_t act, uint32_t nb, float s0, float s8, float (&acc)[4][4]) {
     constexpr uint32_t M3 = 0x03030303u;
-    const uint2 x = *reinterpret_cast<const uint2 *>(wts);
-    const uint2 y = *reinterpret_cast<const uint2 *>(wts + 8 * kWideCodeStride);
+    const uint2 x = wide_lds64(wts);
+    const uint2 y = wide_lds64(wts + 8 * kWideCodeStride);
     // A operands of the four MMAs.  Bit plane t of a code word (codes 4e + t of its 16-code runs) meets
     // activation word t of the same run; which two (plane, word) pairs share an MMA does not change the
     // integer sum, so they are paired such that every B operand is an aligned register pair of one
@@ -108,11 +125,11 @@ __device__ __forceinline__ void wide_group(const unsigned char *wts, const unsig
     }
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-        const uint4 lo = *reinterpret_cast<const uint4 *>(act + 8 * b * kWideActStride);
-        const uint4 hi = *reinterpret_cast<const uint4 *>(act + 8 * b * kWideActStride + 16);
-        const int2 c = *reinterpret_cast<const int2 *>(nb + 8 * b);
+        const uint4 lo = wide_lds128(act + 8 * b * kWideActStride);
+        const uint4 hi = wide_lds128(act + 8 * b * kWideActStride + 16);
+        const uint2 c = wide_lds64(nb + 32 * b);
         int d[4];
-        mma_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], lo.x, lo.y, c.x, c.y, c.x, c.y);
+        mma_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], lo.x, lo.y, (int)c.x, (int)c.y, (int)c.x, (int)c.y);
         mma_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], lo.z, lo.w, d[0], d[1], d[2], d[3]);
         mma_u8s8(d, a[2][0], a[2][1], a[2][2], a[2][3], hi.x, hi.y, d[0], d[1], d[2], d[3]);
         mma_u8s8(d, a[3][0], a[3][1], a[3][2], a[3][3], hi.z, hi.w, d[0], d[1], d[2], d[3]);
@@ -199,10 +216,13 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
         nb_tab[grp * kWideNbStride + r] = kGroupSumBias - 2 * (t0 + r < p.T ? p.asum[(size_t)(t0 + r) * ng + grp] : 0);
     }
 
-    const uint16_t *sc0 = sc_tab + (16 * warp + g) * scs, *sc8 = sc0 + 8 * scs;
-    const int *nb0 = nb_tab + 2 * q;
-    const int wbase = kWideTokens * kWideActStride + (16 * warp + g) * kWideCodeStride + 8 * q;
-    const int abase = g * kWideActStride + 32 * q;
+    // 32-bit shared addresses of this lane's pieces: scales of rows g / g + 8, C operands of prompt rows
+    // 2q / 2q + 1, code bytes and activation bytes of group 0 of stage buffer 0
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+    const uint32_t sc0 = (uint32_t)__cvta_generic_to_shared(sc_tab + (16 * warp + g) * scs), sc8 = sc0 + 16 * scs;
+    const uint32_t nb0 = (uint32_t)__cvta_generic_to_shared(nb_tab + 2 * q);
+    const uint32_t wbase = ring_s + kWideTokens * kWideActStride + (16 * warp + g) * kWideCodeStride + 8 * q;
+    const uint32_t abase = ring_s + g * kWideActStride + 32 * q;
     int seq = 0;                             // position of the group being multiplied
     // All groups of one slot into `acc` (zeros for a slot without groups: fewer than 16 groups in K).
     auto run_slot = [&](int slot, float (&acc)[4][4]) {
@@ -217,11 +237,11 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
         for (int c = 0; c < nt; ++c, ++seq) {
             const int st = seq / kWideStageGroups, li = seq % kWideStageGroups;
             if (li == 0) wide_enter_stage(pp, st);
-            const unsigned char *buf = ring + (st % kWideStages) * kWideStageBytes;
+            const uint32_t boff = (st % kWideStages) * kWideStageBytes;
             const int grp = slot + BM_SLOTS * c;
-            const float s0 = bf16_bits_to_f32(sc0[grp]), s8 = bf16_bits_to_f32(sc8[grp]);
-            if (c == 0) wide_group<true>(buf + wbase + li * 32, buf + abase + li * 128, nb0 + grp * kWideNbStride, s0, s8, acc);
-            else wide_group<false>(buf + wbase + li * 32, buf + abase + li * 128, nb0 + grp * kWideNbStride, s0, s8, acc);
+            const float s0 = wide_lds_bf16(sc0 + 2 * grp), s8 = wide_lds_bf16(sc8 + 2 * grp);
+            if (c == 0) wide_group<true>(wbase + boff + li * 32, abase + boff + li * 128, nb0 + grp * (4 * kWideNbStride), s0, s8, acc);
+            else wide_group<false>(wbase + boff + li * 32, abase + boff + li * 128, nb0 + grp * (4 * kWideNbStride), s0, s8, acc);
         }
     };
     // The butterfly ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)) + ... with the slots taken in ascending order:
