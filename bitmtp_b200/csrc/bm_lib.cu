@@ -1062,7 +1062,9 @@ int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void 
     p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.pdl = pdl & BM_PDL_OVERLAP;
     const dim3 grid(N / bm::kWideRows, (T + bm::kWideTokens - 1) / bm::kWideTokens);
     if (grid.y > 65535) return BM_EINVAL;
-    return launch_ex(bm::t2_gemm_wide_kernel, grid, dim3(bm::kWideThreads), smem, static_cast<cudaStream_t>(stream), p.pdl, p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K == BM_SLOTS * BM_GROUP) return launch_ex(bm::t2_gemm_wide_kernel<true>, grid, dim3(bm::kWideThreads), smem, st, p.pdl, p);
+    return launch_ex(bm::t2_gemm_wide_kernel<false>, grid, dim3(bm::kWideThreads), smem, st, p.pdl, p);
 }
 
 namespace {

@@ -16,8 +16,8 @@
 // fp32 order (the GEMV's, see the header of t2_gemv.cuh): group g -> slot g % 16, slot = fma(G,
 // scale, slot) in ascending g, the 16 slots summed as a butterfly tree, times 1/s.  A wide tile cannot
 // hold 16 slot accumulators per output, so the groups are visited SLOT BY SLOT (s, s+16, s+32, ...:
-// one accumulator) and combined four slots at a time, (s0 + s1) + (s2 + s3), then the four such values
-// as (q0 + q1) + (q2 + q3): the additions are exactly the butterfly's.
+// one accumulator), and a finished slot is folded into a binary-counter tree (4 registers per output)
+// whose additions are exactly the butterfly's.
 //
 // CTA = 8 warps = 128 weight rows x 32 prompt rows.  The groups are taken in the slot-major sequence
 // (slot 0's groups, slot 1's, ...) in stages of kWideStageGroups: activations [32 rows][128 B per group]
@@ -80,6 +80,19 @@ struct WideSeq {
     }
 };
 
+// Folds the finished slot S (compile-time) into the binary-counter tree of one output: level l holds the
+// sum of a finished block of 2^l slots whose partner has not arrived yet; `left + right` with the earlier
+// block on the left, which is the butterfly order ((s0+s1)+(s2+s3))+... of the GEMV.  Straight-line code:
+// a run-time slot number here costs dozens of register moves per slot where the branches meet.
+template <int S>
+__device__ __forceinline__ void wide_tree_push(float (&tree)[4], float v) {
+    if (S & 1) { v = tree[0] + v; } else { tree[0] = v; return; }
+    if (S & 2) { v = tree[1] + v; } else { tree[1] = v; return; }
+    if (S & 4) { v = tree[2] + v; } else { tree[2] = v; return; }
+    if (S & 8) { v = tree[3] + v; } else { tree[3] = v; return; }
+    tree[3] = v;            // S == 15: the total
+}
+
 // Shared-memory loads by 32-bit shared address (the multiply loop keeps its addresses in 32-bit registers
 // with constant offsets instead of 64-bit generic pointers).
 __device__ __forceinline__ uint2 wide_lds64(uint32_t a) {
@@ -103,8 +116,6 @@ __device__ __forceinline__ float wide_lds_bf16(uint32_t a) {
 //   wts   this lane's code bytes of the group (row g of the warp's 16; row g + 8 is 8 rows further)
 //   act   this lane's activation bytes of the group (prompt row g of block 0)
 //   nb    this lane's C operands of the group (prompt rows 2q, 2q + 1 of block 0)
-// FIRST: the slot's first group (the accumulators start from zero).
-template <bool FIRST>
 __device__ __forceinline__ void wide_group(uint32_t wts, uint32_t act, uint32_t nb, float s0, float s8, float (&acc)[4][4]) {
     constexpr uint32_t M3 = 0x03030303u;
     const uint2 x = wide_lds64(wts);
@@ -133,10 +144,10 @@ __device__ __forceinline__ void wide_group(uint32_t wts, uint32_t act, uint32_t 
         mma_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], lo.z, lo.w, d[0], d[1], d[2], d[3]);
         mma_u8s8(d, a[2][0], a[2][1], a[2][2], a[2][3], hi.x, hi.y, d[0], d[1], d[2], d[3]);
         mma_u8s8(d, a[3][0], a[3][1], a[3][2], a[3][3], hi.z, hi.w, d[0], d[1], d[2], d[3]);
-        acc[b][0] = fmaf(group_sum_to_float(d[0]), s0, FIRST ? 0.0f : acc[b][0]);
-        acc[b][1] = fmaf(group_sum_to_float(d[1]), s0, FIRST ? 0.0f : acc[b][1]);
-        acc[b][2] = fmaf(group_sum_to_float(d[2]), s8, FIRST ? 0.0f : acc[b][2]);
-        acc[b][3] = fmaf(group_sum_to_float(d[3]), s8, FIRST ? 0.0f : acc[b][3]);
+        acc[b][0] = fmaf(group_sum_to_float(d[0]), s0, acc[b][0]);
+        acc[b][1] = fmaf(group_sum_to_float(d[1]), s0, acc[b][1]);
+        acc[b][2] = fmaf(group_sum_to_float(d[2]), s8, acc[b][2]);
+        acc[b][3] = fmaf(group_sum_to_float(d[3]), s8, acc[b][3]);
     }
 }
 
@@ -179,6 +190,9 @@ __device__ __noinline__ void wide_enter_stage(WidePipe &pp, int st) {
 }
 
 // grid (N / 128, ceil(T / 32)), 256 threads.  K % 128 == 0, N % 128 == 0.
+// ONE: K == 2048, one group per slot - the position in the sequence, its stage and its place in the stage are
+// compile-time constants and the loop over a slot's groups disappears.
+template <bool ONE>
 __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const WideParams p) {
     extern __shared__ __align__(16) unsigned char wsm[];
     pdl_launch_dependents();
@@ -199,9 +213,11 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
         for (int i = 0; i < kWideStages * kWideStageGroups && i < ng; ++i, w.step(ng))
             wide_issue_codes(ring + (i / kWideStageGroups) * kWideStageBytes, i % kWideStageGroups, code_src, w.group(), tid);
     }
-    for (int e = tid; e < kWideRows * ng; e += kWideThreads) {
-        const int r = e / ng, grp = e - r * ng;
-        sc_tab[r * scs + grp] = p.ws[(size_t)(n0 + r) * ng + grp];
+    // (eight lanes walk one row's groups: no division by the run-time group count anywhere in this kernel)
+#pragma unroll
+    for (int j = 0; j < kWideRows / 32; ++j) {
+        const int r = (tid >> 3) + 32 * j;
+        for (int grp = tid & 7; grp < ng; grp += 8) sc_tab[r * scs + grp] = p.ws[(size_t)(n0 + r) * ng + grp];
     }
     if (p.pdl) pdl_wait();
     WidePipe pp = {ring, code_src, row_src, {0, 0}, 0, ng};
@@ -211,9 +227,11 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
             wide_issue_row(ring + st * kWideStageBytes, li, row_src, pp.prod.group(), tid);
         cp_async_commit();
     }
-    for (int e = tid; e < kWideTokens * ng; e += kWideThreads) {
-        const int r = e / ng, grp = e - r * ng;
-        nb_tab[grp * kWideNbStride + r] = kGroupSumBias - 2 * (t0 + r < p.T ? p.asum[(size_t)(t0 + r) * ng + grp] : 0);
+    {
+        const int r = tid >> 3;                                      // 32 prompt rows x 8 lanes
+        const bool live = t0 + r < p.T;
+        for (int grp = tid & 7; grp < ng; grp += 8)
+            nb_tab[grp * kWideNbStride + r] = kGroupSumBias - 2 * (live ? p.asum[(size_t)(t0 + r) * ng + grp] : 0);
     }
 
     // 32-bit shared addresses of this lane's pieces: scales of rows g / g + 8, C operands of prompt rows
@@ -224,52 +242,38 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
     const uint32_t wbase = ring_s + kWideTokens * kWideActStride + (16 * warp + g) * kWideCodeStride + 8 * q;
     const uint32_t abase = ring_s + g * kWideActStride + 32 * q;
     int seq = 0;                             // position of the group being multiplied
-    // All groups of one slot into `acc` (zeros for a slot without groups: fewer than 16 groups in K).
-    auto run_slot = [&](int slot, float (&acc)[4][4]) {
-        const int nt = WideSeq::terms(slot, ng);
-        if (nt == 0) {
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[b][e] = 0.0f;
-            return;
-        }
-        for (int c = 0; c < nt; ++c, ++seq) {
-            const int st = seq / kWideStageGroups, li = seq % kWideStageGroups;
-            if (li == 0) wide_enter_stage(pp, st);
-            const uint32_t boff = (st % kWideStages) * kWideStageBytes;
-            const int grp = slot + BM_SLOTS * c;
-            const float s0 = wide_lds_bf16(sc0 + 2 * grp), s8 = wide_lds_bf16(sc8 + 2 * grp);
-            if (c == 0) wide_group<true>(wbase + boff + li * 32, abase + boff + li * 128, nb0 + grp * (4 * kWideNbStride), s0, s8, acc);
-            else wide_group<false>(wbase + boff + li * 32, abase + boff + li * 128, nb0 + grp * (4 * kWideNbStride), s0, s8, acc);
-        }
-    };
-    // The butterfly ((s0+s1)+(s2+s3)) + ((s4+s5)+(s6+s7)) + ... with the slots taken in ascending order:
-    // four slots at a time give one level-2 value (l1 = a + b, then l1 + (a + b)); the four level-2 values
-    // are combined as (q0 + q1) + (q2 + q3).  `left + right` always has the earlier block on the left.
-    float total[4][4], half[4][4];           // [token block][fragment element]
-#pragma unroll 1
-    for (int quad = 0; quad < 4; ++quad) {
-        float a[4][4], b2[4][4], l1[4][4];
-        run_slot(4 * quad, a);
-        run_slot(4 * quad + 1, b2);
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) l1[b][e] = a[b][e] + b2[b][e];
-        run_slot(4 * quad + 2, a);
-        run_slot(4 * quad + 3, b2);
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float v = l1[b][e] + (a[b][e] + b2[b][e]);          // slots 4 quad .. 4 quad + 3
-                if (quad == 0) half[b][e] = v;                            // uniform branches
-                else if (quad == 1) total[b][e] = half[b][e] + v;
-                else if (quad == 2) half[b][e] = v;
-                else total[b][e] = total[b][e] + (half[b][e] + v);
-            }
+    float tree[4][4][4];                     // [token block][fragment element][level]
+    // The slots in ascending order, the slot number a compile-time constant for the tree; one copy of the
+    // multiply per slot, its groups (s, s + 16, ...) in a run-time loop.
+#define BM_WIDE_SLOT(S_)                                                                                          \
+    {                                                                                                             \
+        float acc[4][4];                                                                                          \
+        _Pragma("unroll") for (int b = 0; b < 4; ++b)                                                             \
+            _Pragma("unroll") for (int e = 0; e < 4; ++e) acc[b][e] = 0.0f;                                       \
+        if (ONE) {                                                                                                \
+            constexpr int st = S_ / kWideStageGroups, li = S_ % kWideStageGroups;                                 \
+            constexpr uint32_t boff = (st % kWideStages) * kWideStageBytes;                                       \
+            if (li == 0) wide_enter_stage(pp, st);                                                                \
+            wide_group(wbase + boff + li * 32, abase + boff + li * 128, nb0 + S_ * (4 * kWideNbStride),           \
+                       wide_lds_bf16(sc0 + 2 * S_), wide_lds_bf16(sc8 + 2 * S_), acc);                            \
+        } else {                                                                                                  \
+            const int nt = WideSeq::terms(S_, ng);                                                                \
+            for (int c = 0; c < nt; ++c, ++seq) {                                                                 \
+                const int st = seq / kWideStageGroups, li = seq % kWideStageGroups;                               \
+                if (li == 0) wide_enter_stage(pp, st);                                                            \
+                const uint32_t boff = (st % kWideStages) * kWideStageBytes;                                       \
+                const int grp = S_ + BM_SLOTS * c;                                                                \
+                wide_group(wbase + boff + li * 32, abase + boff + li * 128, nb0 + grp * (4 * kWideNbStride),      \
+                           wide_lds_bf16(sc0 + 2 * grp), wide_lds_bf16(sc8 + 2 * grp), acc);                      \
+            }                                                                                                     \
+        }                                                                                                         \
+        _Pragma("unroll") for (int b = 0; b < 4; ++b)                                                             \
+            _Pragma("unroll") for (int e = 0; e < 4; ++e) wide_tree_push<S_>(tree[b][e], acc[b][e]);              \
     }
+    BM_WIDE_SLOT(0) BM_WIDE_SLOT(1) BM_WIDE_SLOT(2) BM_WIDE_SLOT(3) BM_WIDE_SLOT(4) BM_WIDE_SLOT(5) BM_WIDE_SLOT(6)
+    BM_WIDE_SLOT(7) BM_WIDE_SLOT(8) BM_WIDE_SLOT(9) BM_WIDE_SLOT(10) BM_WIDE_SLOT(11) BM_WIDE_SLOT(12)
+    BM_WIDE_SLOT(13) BM_WIDE_SLOT(14) BM_WIDE_SLOT(15)
+#undef BM_WIDE_SLOT
     // times 1/s of the prompt row, to bf16
     const int row = n0 + 16 * warp + g;
 #pragma unroll
@@ -277,13 +281,13 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
         const int ta = t0 + 8 * b + 2 * q, tb = ta + 1;
         if (ta < p.T) {
             const float is = 1.0f / p.s[ta];
-            p.C[(size_t)ta * p.ldc + row] = bm_f32_to_bf16(total[b][0] * is);
-            p.C[(size_t)ta * p.ldc + row + 8] = bm_f32_to_bf16(total[b][2] * is);
+            p.C[(size_t)ta * p.ldc + row] = bm_f32_to_bf16(tree[b][0][3] * is);
+            p.C[(size_t)ta * p.ldc + row + 8] = bm_f32_to_bf16(tree[b][2][3] * is);
         }
         if (tb < p.T) {
             const float is = 1.0f / p.s[tb];
-            p.C[(size_t)tb * p.ldc + row] = bm_f32_to_bf16(total[b][1] * is);
-            p.C[(size_t)tb * p.ldc + row + 8] = bm_f32_to_bf16(total[b][3] * is);
+            p.C[(size_t)tb * p.ldc + row] = bm_f32_to_bf16(tree[b][1][3] * is);
+            p.C[(size_t)tb * p.ldc + row + 8] = bm_f32_to_bf16(tree[b][3][3] * is);
         }
     }
 }
