@@ -1050,7 +1050,7 @@ int bm_t2_gemm_wide(const void *A_prep, const void *a_sums, const void *B, void 
         K < BM_GROUP || (K % BM_GROUP) != 0 || ldc < N)
         return BM_EINVAL;
     if (!aligned16(A_prep) || !aligned16(B)) return BM_EINVAL;
-    const size_t smem = bm::wide_smem_bytes(K / BM_GROUP);
+    const size_t smem = bm::wide_smem_bytes(K / BM_GROUP, K == BM_SLOTS * BM_GROUP);
     if (smem > (size_t)kMaxSmemPerCta) return BM_EINVAL;
     bm::WideParams p;
     p.A = static_cast<const int8_t *>(A_prep);

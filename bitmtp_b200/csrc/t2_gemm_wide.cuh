@@ -39,12 +39,13 @@ constexpr int kWideStageGroups = 4;     // groups per stage
 constexpr int kWideStages = 2;          // stage buffers
 // Strides chosen so that the fragment reads are free of bank conflicts: activation rows (16-byte reads of
 // 8 rows x 4 quarters) want an odd number of 16-byte units, code rows (8-byte reads of 4 rows x 4
-// quarters) 32 mod 128 bytes, the C-operand table (8-byte reads, stores along the group index) 34 words.
+// quarters) 32 or 96 mod 128 bytes, the C-operand table (8-byte reads, stores along the group index) 34 words.
 constexpr int kWideActStride = kWideStageGroups * 128 + 16;
 constexpr int kWideCodeStride = kWideStageGroups * 32 + 32;
 constexpr int kWideStageBytes = kWideTokens * kWideActStride + kWideRows * kWideCodeStride;
 constexpr int kWideNbStride = kWideTokens + 2;
-static_assert((kWideActStride / 16) % 2 == 1 && kWideCodeStride % 128 == 32, "bank-conflict-free strides");
+static_assert((kWideActStride / 16) % 2 == 1 && (kWideCodeStride % 128 == 32 || kWideCodeStride % 128 == 96),
+              "bank-conflict-free strides");
 
 struct WideParams {
     const int8_t *A;        // [T, K] GEMV-ready INT8 rows
@@ -59,10 +60,13 @@ struct WideParams {
 // Scale-table row stride in bf16 elements: ng + 2 makes the 32-bit word stride odd when ng % 4 == 0.
 __host__ __device__ inline int wide_scale_stride(int ng) { return ng + 2; }
 
-__host__ __device__ inline size_t wide_smem_bytes(int ng) {
+// `park`: the K = 2048 build parks the sum of slots 0-7 of every output in shared memory while slots 8-15 are
+// multiplied (16 registers fewer where the tree is fullest).
+__host__ __device__ inline size_t wide_smem_bytes(int ng, bool park = false) {
     size_t off = (size_t)kWideStages * kWideStageBytes;
     off += ((size_t)kWideRows * wide_scale_stride(ng) * 2 + 15) & ~(size_t)15;
-    off += (size_t)ng * kWideNbStride * 4;
+    off += ((size_t)ng * kWideNbStride * 4 + 15) & ~(size_t)15;
+    if (park) off += (size_t)kWideThreads * 16 * 4;
     return off;
 }
 
@@ -165,8 +169,7 @@ __device__ __forceinline__ void wide_issue_row(unsigned char *buf, int li, const
 // State of the copy pipeline.  Before the first group of stage st: the stage has landed - kWideStages
 // batches are out at stage 0, kWideStages - 1 + st later, and only the ones after batch st may still be in
 // flight; once every warp is past the barrier the buffer of stage st - 1 is free and takes stage
-// st - 1 + kWideStages.  Kept out of line: it runs once per kWideStageGroups groups, and the multiply
-// loop around it should stay small.
+// st - 1 + kWideStages.
 struct WidePipe {
     unsigned char *ring;
     const uint8_t *code_src;      // this thread's half of a code row, group 0
@@ -174,7 +177,7 @@ struct WidePipe {
     WideSeq prod;                 // next group to request
     int requested, ng;
 };
-__device__ __noinline__ void wide_enter_stage(WidePipe &pp, int st) {
+__device__ __forceinline__ void wide_enter_stage(WidePipe &pp, int st) {
     const int tid = threadIdx.x;
     if (st == 0) cp_async_wait_batches<kWideStages - 1>();
     else cp_async_wait_batches<kWideStages - 2>();
@@ -202,6 +205,7 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
     unsigned char *ring = wsm;
     uint16_t *sc_tab = reinterpret_cast<uint16_t *>(wsm + kWideStages * kWideStageBytes);
     int *nb_tab = reinterpret_cast<int *>(wsm + kWideStages * kWideStageBytes + (((size_t)kWideRows * scs * 2 + 15) & ~(size_t)15));
+    float4 *parked = reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(nb_tab) + (((size_t)ng * kWideNbStride * 4 + 15) & ~(size_t)15));
     // what this thread copies of every group: its half of a code row, its piece of a prompt row (null: past T)
     const uint8_t *code_src = p.B + (size_t)(n0 + (tid >> 1)) * (p.K / 4) + 16 * (tid & 1);
     const int8_t *row_src = t0 + (tid >> 3) < p.T ? p.A + (size_t)(t0 + (tid >> 3)) * p.K + 16 * (tid & 7) : nullptr;
@@ -267,8 +271,18 @@ __global__ void __launch_bounds__(kWideThreads, 2) t2_gemm_wide_kernel(const Wid
                            wide_lds_bf16(sc0 + 2 * grp), wide_lds_bf16(sc8 + 2 * grp), acc);                      \
             }                                                                                                     \
         }                                                                                                         \
+        if (ONE && S_ == 15) {                                                                                    \
+            _Pragma("unroll") for (int b = 0; b < 4; ++b) {                                                       \
+                const float4 low = parked[b * kWideThreads + tid];                                                \
+                tree[b][0][3] = low.x; tree[b][1][3] = low.y; tree[b][2][3] = low.z; tree[b][3][3] = low.w;       \
+            }                                                                                                     \
+        }                                                                                                         \
         _Pragma("unroll") for (int b = 0; b < 4; ++b)                                                             \
             _Pragma("unroll") for (int e = 0; e < 4; ++e) wide_tree_push<S_>(tree[b][e], acc[b][e]);              \
+        if (ONE && S_ == 7) {                                                                                     \
+            _Pragma("unroll") for (int b = 0; b < 4; ++b)                                                         \
+                parked[b * kWideThreads + tid] = make_float4(tree[b][0][3], tree[b][1][3], tree[b][2][3], tree[b][3][3]); \
+        }                                                                                                         \
     }
     BM_WIDE_SLOT(0) BM_WIDE_SLOT(1) BM_WIDE_SLOT(2) BM_WIDE_SLOT(3) BM_WIDE_SLOT(4) BM_WIDE_SLOT(5) BM_WIDE_SLOT(6)
     BM_WIDE_SLOT(7) BM_WIDE_SLOT(8) BM_WIDE_SLOT(9) BM_WIDE_SLOT(10) BM_WIDE_SLOT(11) BM_WIDE_SLOT(12)
