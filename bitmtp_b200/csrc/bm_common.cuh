@@ -121,6 +121,36 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait_batches() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// ---- thread-block clusters ----------------------------------------------------
+// One barrier phase = arrive + wait by every
+// thread of every CTA of the cluster that has not exited (a hardware barrier, no polling of memory), and
+// reads of another CTA's shared memory through its cluster-wide address.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_map(const void *own_shared, uint32_t rank) {
+    uint32_t mapped;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(mapped) : "r"((uint32_t)__cvta_generic_to_shared(own_shared)), "r"(rank));
+    return mapped;
+}
+__device__ __forceinline__ float4 cluster_ld4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 cluster_ld2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_st_f32(uint32_t a, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_st_s32(uint32_t a, int v) {
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+
 // ---- warp reductions in the oracle's butterfly order -------------------------
 // Exact int32 -> fp32 of a group sum without the conversion unit.  A group sum is at most 128 * 127 * 3
 // in magnitude, so kGroupSumBias + G is the bit pattern of the float 1.5 * 2^23 + G; subtracting 1.5 * 2^23

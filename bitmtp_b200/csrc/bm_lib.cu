@@ -1011,6 +1011,48 @@ int bm_draft_chain_split(const void *logits, int D, int vocab, int ld, float tau
         return BM_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     bm::LogitScratch *sc = static_cast<bm::LogitScratch *>(scratch);
+    {
+        // One launch with a cluster per row when the device holds all D clusters at once; else the two launches below.
+        static std::atomic<int> held[8];                              // clusters the device holds, +1 (0: not asked yet)
+        const int dev = current_device().device;
+        const int nchunks = (vocab + 255) / 256, per = (nchunks + bm::kDraftClusterCtas - 1) / bm::kDraftClusterCtas;
+        const size_t smem = (size_t)per * 256 * sizeof(float);
+        if (dev >= 0 && dev < 8 && smem <= 96 * 1024) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(bm::kDraftClusterCtas, D);
+            cfg.blockDim = dim3(256);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = bm::kDraftClusterCtas;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t e = cudaFuncSetAttribute(bm::draft_chain_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)(96 * 1024));
+            int n = held[dev].load(std::memory_order_relaxed) - 1;
+            if (e == cudaSuccess && n < 0) {
+                int clusters = 0;
+                e = cudaFuncSetAttribute(bm::draft_chain_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                cudaLaunchConfig_t probe = cfg;
+                probe.gridDim = dim3(bm::kDraftClusterCtas, bm::kLogitMaxRows);
+                probe.dynamicSmemBytes = 96 * 1024;
+                if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&clusters, bm::draft_chain_cluster_kernel, &probe);
+                if (e != cudaSuccess) cudaGetLastError();             // an unsupported size is an answer, not a failure
+                n = e == cudaSuccess && clusters > 0 ? clusters : 0;
+                held[dev].store(n + 1, std::memory_order_relaxed);
+                e = cudaSuccess;
+            }
+            if (e == cudaSuccess && D <= n) {
+                count_launch();
+                return cuda_status(cudaLaunchKernelEx(&cfg, bm::draft_chain_cluster_kernel, static_cast<const float *>(logits),
+                                                      vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_buf),
+                                                      static_cast<float *>(conf), D, tau, static_cast<int *>(n_out), sc));
+            }
+        }
+    }
     count_launch();
     bm::argmax_split_kernel<<<dim3(bm::logit_splits(D), D), 256, 0, st>>>(
         static_cast<const float *>(logits), vocab, ld, static_cast<int64_t *>(idx), static_cast<float *>(max_buf), sc);

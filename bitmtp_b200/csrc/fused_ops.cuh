@@ -747,6 +747,113 @@ __global__ void __launch_bounds__(256) confidence_split_kernel(const float *__re
     sc->rows_done = 0u;
 }
 
+// ---- the confidence chain of a draft block in ONE launch -----------------------------------------
+// argmax_split_kernel + confidence_split_kernel as one kernel: the kDraftClusterCtas CTAs of a logit row are a
+// thread-block cluster (grid (kDraftClusterCtas, D), cluster (kDraftClusterCtas, 1, 1)).  Each CTA reads its
+// range of whole 256-element chunks ONCE, into shared memory, and finds its maximum; the partial maxima go to
+// every CTA of the cluster through distributed shared memory, so after one cluster barrier each CTA knows the
+// row's maximum and argmax (same comparison, ranges in ascending order) and sums exp(x - max) over its chunks
+// from shared memory in the oracle's order (lane = 8 consecutive terms, butterfly); the chunk sums go to the
+// first CTA of the cluster, which after a second barrier adds them in ascending order and finishes the row as
+// confidence_split_kernel does (the last row to finish writes the chain length).  Same results, one launch
+// instead of two, the logits read once instead of twice, no fence / ticket / read-back inside a row.
+constexpr int kDraftClusterCtas = 16;
+
+__global__ void __launch_bounds__(256) draft_chain_cluster_kernel(const float *__restrict__ logits, int vocab, int ld,
+                                                                 int64_t *__restrict__ idx, float *__restrict__ max_out,
+                                                                 float *__restrict__ conf, int D, float tau,
+                                                                 int *__restrict__ n_out, LogitScratch *sc) {
+    extern __shared__ __align__(16) float slice[];            // this CTA's chunks of the row
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ float part_max[kDraftClusterCtas];
+    __shared__ int part_idx[kDraftClusterCtas];
+    __shared__ float sums[kConfMaxChunks];                    // chunk sums of the whole row (used in CTA 0)
+    __shared__ float row_best;
+    __shared__ int row_idx;
+    const int rank = blockIdx.x, r = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    cluster_arrive();                      // waited for below, before the first store into another CTA: all have started
+    const float *x = logits + (size_t)r * ld;
+    const int nchunks = (vocab + 255) / 256;
+    const int per = (nchunks + kDraftClusterCtas - 1) / kDraftClusterCtas;
+    const int c_lo = min(nchunks, rank * per), c_hi = min(nchunks, (rank + 1) * per);
+    const int v_lo = min(vocab, c_lo * 256), v_hi = min(vocab, c_hi * 256);
+    // the whole range is requested at once (16-byte asynchronous copies where the row is aligned for them, so
+    // that a thread has all its loads in flight together), then scanned from shared memory
+    const int len = v_hi - v_lo;
+    const bool vec = (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+    const int len4 = vec ? len / 4 : 0;
+    for (int i = threadIdx.x; i < len4; i += 256) cp_async16(slice + 4 * i, x + v_lo + 4 * i);
+    for (int i = 4 * len4 + threadIdx.x; i < len; i += 256) slice[i] = x[v_lo + i];
+    cp_async_wait_all();
+    __syncthreads();
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < len; i += 256) {
+        const float f = slice[i];
+        if (bm_argmax_better(f, v_lo + i, best, bi)) { best = f; bi = v_lo + i; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (bm_argmax_better(ob, oi, best, bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    cluster_wait();
+    if (warp == 0) {
+        // lane t hands this CTA's partial to CTA t of the cluster
+        best = sv[0]; bi = si[0];
+        for (int w = 1; w < 8; ++w)
+            if (bm_argmax_better(sv[w], si[w], best, bi)) { best = sv[w]; bi = si[w]; }
+        if (lane < kDraftClusterCtas) {
+            cluster_st_f32(cluster_map(&part_max[rank], (uint32_t)lane), best);
+            cluster_st_s32(cluster_map(&part_idx[rank], (uint32_t)lane), bi);
+        }
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (threadIdx.x == 0) {
+        best = -INFINITY;
+        bi = 0x7fffffff;
+        for (int s = 0; s < kDraftClusterCtas; ++s)
+            if (bm_argmax_better(part_max[s], part_idx[s], best, bi)) { best = part_max[s]; bi = part_idx[s]; }
+        row_best = best;
+        row_idx = bi;
+    }
+    __syncthreads();
+    const float mx = row_best;
+    for (int c = c_lo + warp; c < c_hi; c += 8) {
+        const int v0 = c * 256 + lane * 8;
+        float acc = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (v0 + e < vocab) acc += bm_expf(slice[v0 + e - v_lo] - mx);
+        acc = warp_sum_butterfly(acc);
+        if (lane == 0) cluster_st_f32(cluster_map(&sums[c], 0u), acc);
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (rank != 0 || threadIdx.x != 0) return;
+    float total = 0.0f;
+    for (int c = 0; c < nchunks; ++c) total += sums[c];
+    const float lse = mx + bm_logf(total);
+    conf[r] = bm_expf(mx - lse);
+    idx[r] = row_idx;
+    max_out[r] = mx;
+    __threadfence();
+    if (atomicAdd(&sc->rows_done, 1u) != (unsigned int)(D - 1)) return;
+    // last row: the chain length over all confidences
+    __threadfence();
+    int n = 1;
+    for (int q = 1; q < D; ++q) {
+        if (__ldcg(&conf[q]) > tau) ++n; else break;
+    }
+    *n_out = n;
+    sc->rows_done = 0u;
+}
+
 __global__ void verify_accept_kernel(const int64_t *draft, const int64_t *verify, int D, int *out) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     int n = 0;

@@ -115,29 +115,6 @@ __device__ __forceinline__ int attn_cache_len(const AttnParams &p) {
     return min(max(p.state->cache_len, 0), p.sigma);
 }
 
-// Thread-block-cluster primitives of the cluster build: one barrier phase = arrive + wait by every
-// thread of every CTA of the cluster that has not exited (a hardware barrier, no polling of memory), and
-// reads of another CTA's shared memory through its cluster-wide address.
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t cluster_map(const void *own_shared, uint32_t rank) {
-    uint32_t mapped;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-                 : "=r"(mapped) : "r"((uint32_t)__cvta_generic_to_shared(own_shared)), "r"(rank));
-    return mapped;
-}
-__device__ __forceinline__ float4 cluster_ld4(uint32_t a) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
-    return v;
-}
-__device__ __forceinline__ float2 cluster_ld2(uint32_t a) {
-    float2 v;
-    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
-    return v;
-}
-
 // q/k head norm + RoPE of one 128-wide head vector by one warp, as qknorm_rope_kvappend_kernel does it:
 // lane l owns elements 4l..4l+3 (`raw`: its four bf16 inputs, `wraw`: its norm weights, `craw` / `sraw`:
 // its cos / sin table entries), the RoPE partner lives in lane l ^ 16.  o[] receives the sums before

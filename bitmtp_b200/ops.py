@@ -229,7 +229,8 @@ def argmax_rows(logits: torch.Tensor, *, out=None, scratch: Optional[torch.Tenso
 
 def draft_chain(logits: torch.Tensor, tau: float, *, bufs=None, scratch: Optional[torch.Tensor] = None):
     """Returns (idx int64 [D], iter_accept int32 [1] (device), conf fp32 [D]).  With `scratch`
-    (logit_scratch) the two reductions run on 16-128 CTAs per row."""
+    (logit_scratch) a row is reduced by many CTAs: one launch with a 16-CTA cluster per row, or, where the
+    device cannot hold the clusters, the argmax and the confidence launch on 16-128 CTAs per row."""
     D, vocab = logits.shape
     dev = logits.device
     if bufs is None:

@@ -323,7 +323,9 @@ int bm_draft_chain(const void *logits, int D, int vocab, int ld, float tau, void
 /* The two reductions above spread over 16 to 128 CTAs per logit row (more when there are few rows) (one CTA per row leaves most of the GPU idle on
  * rows of 151936 values); same results bit for bit.  `scratch`: bm_logit_scratch_bytes() bytes of device
  * memory, 16-byte aligned, zero before its first use (the kernels leave its counters zero), not shared by
- * calls that may run at the same time.  rows, D <= 32. */
+ * calls that may run at the same time.  rows, D <= 32.  bm_draft_chain_split is ONE launch where the device holds a
+ * 16-CTA thread-block cluster per row (each CTA reads its part of the row once, maxima and chunk sums travel
+ * through distributed shared memory), else an argmax launch followed by a confidence launch. */
 long long bm_logit_scratch_bytes(void);
 int bm_argmax_rows_split(const void *logits, int rows, int vocab, int ld, void *idx, void *max_out, void *scratch,
                          void *stream);

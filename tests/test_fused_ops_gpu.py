@@ -494,7 +494,7 @@ def test_width1_row_fused_register_kernel_equals_staged_kernel(src_mode, N, K, s
 @pytest.mark.parametrize("rows,vocab,ld", [(8, 151936, 151936), (9, 151669, 151936), (1, 1000, 1000), (17, 4099, 4100),
                                            (32, 300, 333)])
 def test_split_logit_reductions_equal_the_single_cta_kernels(rows, vocab, ld):
-    """bm_argmax_rows_split / bm_draft_chain_split (16-128 CTAs per row, last-arriver combine) against
+    """bm_argmax_rows_split / bm_draft_chain_split (many CTAs per row: last-arriver combine, or one cluster per row) against
     bm_argmax_rows / bm_draft_chain: indices, confidences (bit for bit) and chain lengths, with ties in
     the rows, ragged vocabulary sizes and unaligned leading dimensions; three calls in a row on one scratch
     show that the ticket counters are left clean."""

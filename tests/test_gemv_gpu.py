@@ -260,7 +260,7 @@ def test_launch_counter_counts_this_librarys_launches():
     scratch = ops.logit_scratch(dev)
     before = lib.bm_launch_count()
     ops.draft_chain(logits, 0.5, scratch=scratch)
-    assert lib.bm_launch_count() - before == 2
+    assert lib.bm_launch_count() - before in (1, 2)       # one cluster launch, or argmax + confidence where clusters do not fit
     torch.cuda.synchronize()
 
 
