@@ -459,8 +459,12 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
     pipelined = bufs.gen_buf.is_cuda
     depth = 2 if pipelined else 1
     if pipelined:
+        # the token's copy to the host runs on a stream of its own, behind an event, so that it does not sit
+        # between two replays on the stream that computes
         host_tok = torch.empty(depth, dtype=torch.int64).pin_memory()
         seen = [torch.cuda.Event() for _ in range(depth)]
+        made = [torch.cuda.Event() for _ in range(depth)]
+        main, side = torch.cuda.current_stream(bufs.gen_buf.device), torch.cuda.Stream(bufs.gen_buf.device)
     last_dev = None
     top = atlas.segment_ladder[-1]
     while gen_count < max_gen_len:
@@ -474,8 +478,12 @@ def fast_ar_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Ten
             if last_dev.data_ptr() != slot.data_ptr():
                 slot.copy_(last_dev)
             if pipelined:
-                host_tok[launched % depth:launched % depth + 1].copy_(slot, non_blocking=True)
-                seen[launched % depth].record()
+                k = launched % depth
+                made[k].record(main)
+                side.wait_event(made[k])
+                with torch.cuda.stream(side):
+                    host_tok[k:k + 1].copy_(slot, non_blocking=True)
+                    seen[k].record(side)
             launched += 1
         if launched == gen_count:
             break                                  # the largest segment is full
