@@ -180,7 +180,9 @@ int64_t bm_verify_attention_scratch_bytes(int M, int H, int sigma);
  *   att_out bf16 [M, H*128] or NULL; q_out / q_prep / asum: the quantised rows (see
  *   bm_quant_rows); s_out fp32 [M].  H*128 a multiple of 256; sigma <= 8064.
  * Two launches: the attention itself (scores, softmax, numerators and the merge of the
- * split-KV partials by the last CTA to finish) and the flat quantisation of its rows.
+ * split-KV partials - by the last CTA to finish, or, where the device holds the whole grid
+ * as thread-block clusters, through distributed shared memory; same order, same bits) and
+ * the flat quantisation of its rows.
  * Visibility follows the reference's draft / verify / ar masks.  Replaces the
  * attention and o-projection input quantisation of
  * Attention.forward_sdlm_graph_kernel (src/bonsai_sft/gpu/model.py:989-1005) and the
