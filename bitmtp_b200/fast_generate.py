@@ -352,7 +352,9 @@ class _Session:
         if n_pend < P:
             tok[n_pend:P].zero_()
             pos[n_pend:P].zero_()
-        tok[P:P + 1].copy_(bufs.pending_buf[n_pend - 1:n_pend])
+        # the block's anchor: the last pending token, or, for a block with nothing pending (the first block of the
+        # confidence policy), the last history token, which the caller left in pending_buf[0]
+        tok[P:P + 1].copy_(bufs.pending_buf[n_pend - 1:n_pend] if n_pend > 0 else bufs.pending_buf[0:1])
         if P + 1 < M:
             tok[P + 1:].fill_(self.MASK)
         torch.add(bufs.pos_arange[:n_pend], self.cache_len, out=pos[:n_pend])
@@ -529,11 +531,20 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
         hybrid_m = 6 if D == 8 else (3 if D == 4 else max(1, (3 * D) // 4))
 
     prefill_time, next_tok, t0 = ses.start()
-    if bufs.has_eos and next_tok in eos_ids:
-        return bufs.gen_buf[:0].clone(), _empty_stats(prefill_time, ses.seq_len, with_draft=True)
-
-    bufs.pending_buf[0] = next_tok
-    n_pend, gen_count, n_iters = 1, 1, 1
+    # The confidence policy opens with a block of its own (fast_generate.py:322-351, 424-430): the last prompt
+    # token re-fed as the anchor at its own position plus D - 1 mask rows, nothing pending, the history row of
+    # the anchor hidden - a draft replay with n_pend = 0.  Its tokens are the request's untimed output and its
+    # time belongs to the prefill, as in the reference.  The other policies take the prompt's greedy next token.
+    first_block = policy == "conf"
+    if first_block:
+        bufs.pending_buf[0:1].copy_(ses.prompt_ids[-1:])
+        n_pend, gen_count, n_iters = 0, 0, 0
+    else:
+        if bufs.has_eos and next_tok in eos_ids:
+            return bufs.gen_buf[:0].clone(), _empty_stats(prefill_time, ses.seq_len, with_draft=True)
+        bufs.pending_buf[0] = next_tok
+        n_pend, gen_count, n_iters = 1, 1, 1
+    untimed = gen_count
     eos_found = False
     n_conf_path = n_verify_path = draft_iters = drafted_total = 0
     accepted_draft_total = verifier_bonus_total = 0
@@ -612,6 +623,12 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
             gen_count += n_commit
         elif policy != "spec":
             eos_found = True
+        if first_block:
+            first_block = False
+            untimed = gen_count
+            torch.cuda.synchronize()
+            prefill_time = time.time() - t0
+            t1 = time.time()
         if eos_found or gen_count >= max_gen_len or n_commit <= 0:
             break
         n_pend = 1 if use_verify else n_commit
@@ -627,24 +644,29 @@ def _draft_verify_generate(model, atlas, input_ids, *, policy: str, threshold: f
         raise RuntimeError(f"{policy} drafted-token accounting mismatch")
     if draft_iters != n_conf_path + n_verify_path:
         raise RuntimeError(f"{policy} path/iteration accounting mismatch")
-    if n_iters != draft_iters + 1:
+    prompt_token = 0 if policy == "conf" else 1             # outputs that came from the prompt's own logits
+    if n_iters != draft_iters + prompt_token:
         raise RuntimeError(f"{policy} n_iters accounting mismatch")
-    if n_out != 1 + accepted_draft_total + verifier_bonus_total:
+    if n_out != prompt_token + accepted_draft_total + verifier_bonus_total:
         raise RuntimeError(f"{policy} output-origin accounting mismatch")
     if verifier_bonus_total > n_verify_path:
         raise RuntimeError(f"{policy} verifier bonus count exceeds verify paths")
     if accepted_draft_total > drafted_total:
         raise RuntimeError(f"{policy} accepted draft count exceeds drafted count")
-    per_iter = (n_out - 1) / draft_iters if draft_iters > 0 else 0.0
+    committed = n_out - prompt_token
+    per_iter = committed / draft_iters if draft_iters > 0 else 0.0
+    untimed = min(untimed, n_out)
+    if policy == "conf" and n_out - untimed <= 0:
+        decode_time = 1e-9                                  # everything came with the first block (fast_generate.py:436-441)
     return out, {
         "prefill_time": prefill_time, "decode_time": decode_time, "total_time": time.time() - t0,
         "prefill_tokens": ses.seq_len, "decode_tokens": n_out,
-        "timed_decode_tokens": max(0, n_out - 1), "untimed_output_tokens": min(1, n_out),
+        "timed_decode_tokens": max(0, n_out - untimed), "untimed_output_tokens": untimed,
         "n_iters": n_iters, "avg_accept": per_iter, "ttft": prefill_time,
         "draft_iters": draft_iters, "drafted_tokens": drafted_total,
         "accepted_drafts": accepted_draft_total,
         "accept_rate": accepted_draft_total / drafted_total if drafted_total > 0 else 0.0,
-        "verifier_bonus_tokens": verifier_bonus_total, "committed_tokens": n_out - 1,
+        "verifier_bonus_tokens": verifier_bonus_total, "committed_tokens": committed,
         "committed_per_iter": per_iter,
         "conf_path_frac": n_conf_path / max(1, n_conf_path + n_verify_path),
         "n_conf_path": n_conf_path, "n_verify_path": n_verify_path,

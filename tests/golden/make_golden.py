@@ -411,6 +411,23 @@ class OracleBackedModel:
         return torch.from_numpy(logits)
 
 
+    def forward_sdlm_decode(self, token_values, positions, cache, block_size, cache_len=None, causal_attn=True):
+        """The eager block decode the reference's confidence loop opens with (fast_generate.py:322-351): the D rows
+        [anchor, MASK ...] over the prompt's K/V with the key just before the block hidden
+        (model.py:462-505) - a draft-role forward with nothing pending, by the oracle."""
+        from oracle import oracle as O
+        om = self.om
+        D = int(token_values.shape[0])
+        past = int(cache[0][0].shape[2]) if cache_len is None else int(cache_len)
+        kv = om.new_kv(past, D)
+        for i in range(om.L):
+            kv[0, i, 0, :, :past, :] = O.torch_to_u16(cache[i][0][0, :, :past, :])
+            kv[1, i, 0, :, :past, :] = O.torch_to_u16(cache[i][1][0, :, :past, :])
+        lg = om.forward(token_values.numpy(), positions.numpy(), kv, sigma=past, role=0, cache_len=past, n_pend=0,
+                        logits_start=0, logits_end=D)
+        return torch.from_numpy(lg), None, None
+
+
 def make_cpu_atlas(ref, om, args, segment_ladder, m_set, roles, check_masks=True):
     """A GraphAtlas whose graphs replay the CPU oracle forward; everything else (mask
     templates, prepare_step, commit_kv, migrate_segment, select_segment) is the reference's
@@ -483,9 +500,18 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind
     D = cfg["block_size"]
     torch.cuda.synchronize = lambda *a, **k: None
     torch.cuda.empty_cache = lambda *a, **k: None
-    orig_chain, orig_accept = RG._fused_draft_chain, RG._fused_verify_accept
+    orig_chain, orig_accept, orig_conf = RG._fused_draft_chain, RG._fused_verify_accept, RG._confidence_accept
     from bitmtp_b200 import synthetic
     policy = synthetic.AcceptancePolicy(accept_kind, D, seed=accept_seed)
+
+    def conf_accept(logits, threshold, eos_ids, Dd):
+        # _confidence_accept (fast_generate.py:354-386) with the oracle's confidences and, where the plan says
+        # so, the policy's chain length; no end-of-sequence id is special for random-init weights
+        idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
+        a = policy.chain_count()
+        n = n if a is None else a
+        toks = [int(t) for t in idx[:n]]
+        return toks, len(toks), False
 
     def chain(logits, threshold):
         idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
@@ -496,13 +522,13 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind
         a = policy.accept_count()
         return orig_accept(draft_tokens, verify_tokens, Dd) if a is None else torch.tensor(a)
 
-    RG._fused_draft_chain, RG._fused_verify_accept = chain, accept
+    RG._fused_draft_chain, RG._fused_verify_accept, RG._confidence_accept = chain, accept, conf_accept
     try:
         fn = {"ar": RG.fast_ar_generate, "spec": RG.fast_speculative_generate,
-              "hybrid": RG.fast_hybrid_generate}[mode]
+              "hybrid": RG.fast_hybrid_generate, "conf": RG.fast_confidence_generate}[mode]
         out, stats = fn(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=())
     finally:
-        RG._fused_draft_chain, RG._fused_verify_accept = orig_chain, orig_accept
+        RG._fused_draft_chain, RG._fused_verify_accept, RG._confidence_accept = orig_chain, orig_accept, orig_conf
     keep = {k: v for k, v in stats.items() if not k.endswith("_time") and k != "ttft"}
     return out.tolist(), keep
 
@@ -521,7 +547,10 @@ def make_streams(ref, out_path, full=False):
              ("tiny", 8, "spec", "forced", 33, 40), ("tiny_g4", 8, "hybrid", "forced", 50, 40),
              ("tiny_g4", 8, "hybrid", "free", 50, 40), ("tiny", 4, "hybrid", "forced", 21, 30),
              ("tiny", 4, "spec", "free", 21, 30), ("tiny", 8, "hybrid", "categorical", 37, 96),
-             ("tiny_g4", 8, "spec", "categorical", 29, 60), ("tiny", 4, "hybrid", "categorical", 19, 40)]
+             ("tiny_g4", 8, "spec", "categorical", 29, 60), ("tiny", 4, "hybrid", "categorical", 19, 40),
+             # the confidence policy: its first block is the reference's eager block decode
+             ("tiny", 8, "conf", "free", 24, 40), ("tiny", 8, "conf", "forced", 33, 48),
+             ("tiny_g4", 8, "conf", "categorical", 29, 60), ("tiny", 4, "conf", "categorical", 19, 40)]
     for (gname, D, mode, accept_kind, plen, ntok) in plans:
         cfg = synthetic.make_config(geoms[gname], block_size=D)
         state = synthetic.make_state(cfg, seed=7)

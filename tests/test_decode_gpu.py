@@ -81,7 +81,7 @@ def test_token_streams_match_reference_loops(rec, monkeypatch):
         monkeypatch.setattr(FG, "_fused_verify_accept", fa)
     prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
     fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
-          "hybrid": FG.fast_hybrid_generate}[rec["mode"]]
+          "hybrid": FG.fast_hybrid_generate, "conf": FG.fast_confidence_generate}[rec["mode"]]
     out, stats = fn(model, atlas, prompt, max_gen_len=rec["new_tokens"], eos_ids=())
     assert native.lib().bm_device_error() == 0
     assert out.cpu().tolist() == rec["tokens"]

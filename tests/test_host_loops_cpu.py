@@ -15,7 +15,7 @@ from tests.cpu_atlas import CpuAtlas, OracleModel, patched_host_ops
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "streams.json")
 RECORDS = json.load(open(GOLDEN))
 MODES = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
-         "hybrid": FG.fast_hybrid_generate}
+         "hybrid": FG.fast_hybrid_generate, "conf": FG.fast_confidence_generate}
 
 
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
