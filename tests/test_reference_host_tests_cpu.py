@@ -4,7 +4,9 @@ Where a checkout of the reference is at hand (BITMTP_REFERENCE, or a `reference`
 repository), its test modules for the runtime contracts are loaded from where they lie and executed with
 `bonsai_sft.gpu.<module>` resolved to `bitmtp_b200.<module>`: option validation and role / width schedules of the
 CLI, the kernel-shape registry, the strict-verification rules, the width selector, tokenizer / artifact
-preflight, runtime profiles, release scope and the converter's input checks.  Nothing of the reference is copied;
+preflight, runtime profiles, release scope, the converter's input checks, and the evaluation driver's routing
+checks (every recipe's widths and head precision reach the adapter; the keywords the adapter passes to the
+decode loops exist in this package's signatures).  Nothing of the reference is copied;
 without a checkout the module is skipped.  The methods listed in NOT_APPLICABLE are left out, each with its reason.
 """
 import importlib
@@ -22,7 +24,7 @@ REF_TESTS = os.path.join(REF, "tests")
 
 MODULES = ("test_bonsai_d4", "test_bonsai_strict_verifier", "test_bonsai_contracts",
            "test_generation_artifact_preflight", "test_orin_runtime", "test_bonsai_release_scope", "test_bonsai_cpu",
-           "test_bonsai_converter")
+           "test_bonsai_converter", "test_evaluation_platforms")
 MIRRORED = ("contracts", "run_generation", "fast_generate", "fast_runtime", "runtime_config", "model", "generate",
             "convert_bonsai_mtp_to_gpu", "checkpoint_validation")
 
@@ -42,6 +44,8 @@ NOT_APPLICABLE = {
     "test_bonsai_cpu.test_ar_keeps_last_history_slot": "additive mask tensors do not exist",
     "test_bonsai_cpu.test_public_4b_guard_precedes_cuda_or_library_load": "every 1 <= M <= 32 is served; the registry check is opt-in",
     "test_bonsai_converter.test_valid_q1_synthetic_conversion_preserves_dtypes": "T2-g128 only",
+    # the evaluation driver's own preflight wants lm-eval installed
+    "test_evaluation_platforms.test_check_only_never_initializes_runtime_or_cuda": "lm-eval is not installed here",
 }
 
 pytestmark = pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="no checkout of the reference at hand")
@@ -50,7 +54,11 @@ pytestmark = pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="no checkou
 @pytest.fixture(scope="module")
 def aliased():
     """`bonsai_sft.gpu.*` -> `bitmtp_b200.*` for the duration of this module."""
-    saved = {k: v for k, v in sys.modules.items() if k == "bonsai_sft" or k.startswith("bonsai_sft.")}
+    saved = {k: v for k, v in sys.modules.items() if k.split(".")[0] in ("bonsai_sft", "benchmarks")}
+    for k in saved:
+        del sys.modules[k]
+    saved_path = list(sys.path)
+    sys.path.insert(0, REF)                    # the reference's `benchmarks` package (its evaluation adapter and driver)
     pkg, gpu = types.ModuleType("bonsai_sft"), types.ModuleType("bonsai_sft.gpu")
     pkg.__path__, gpu.__path__ = [], []
     pkg.gpu = gpu
@@ -60,9 +68,10 @@ def aliased():
         sys.modules["bonsai_sft.gpu." + name] = mod
         setattr(gpu, name, mod)
     yield
-    for k in [k for k in sys.modules if k == "bonsai_sft" or k.startswith("bonsai_sft.")]:
+    for k in [k for k in sys.modules if k.split(".")[0] in ("bonsai_sft", "benchmarks")]:
         del sys.modules[k]
     sys.modules.update(saved)
+    sys.path[:] = saved_path
 
 
 def _cases(module_name):
