@@ -101,3 +101,19 @@ def test_adapter_accounting_over_this_runtime(adapter, recipe, accept):
         assert st["accepted_drafts"] + st["verifier_bonus_tokens"] == sum(len(o) for o in outs) - (
             0 if wrap.mode == "confidence" else len(outs))
     assert len(wrap._request_receipts) == len(lengths)
+
+
+@pytest.mark.parametrize("recipe,geometry,D", [("bonsai_1p7b_h20_d8_hybrid", "BONSAI_1P7B", 8),
+                                               ("bonsai_1p7b_h20_d4_hybrid", "BONSAI_1P7B", 4),
+                                               ("bonsai_4b_h20_d8_hybrid", "BONSAI_4B", 8),
+                                               ("bonsai_1p7b_h20_sft_ar", "BONSAI_1P7B", 8)])
+def test_adapter_accepts_this_packages_model_arguments(adapter, recipe, geometry, D):
+    """`validate_bonsai_config(profile, vars(m.args))`, the check the adapter's init() runs on the loaded model
+    (benchmarks/bonsai_adapter.py:121-122): every field it reads exists in this package's ModelArgs with the type
+    it insists on, for the released geometries (vocabulary 151669)."""
+    _, profiles = adapter
+    cfg = synthetic.make_config(dict(getattr(synthetic, geometry), vocab_size=151669), block_size=D)
+    profiles.validate_bonsai_config(profiles.PROFILES[recipe], vars(generate.args_from_config(cfg)))
+    wrong = dict(vars(generate.args_from_config(cfg)), kernel_kind="q1")
+    with pytest.raises(ValueError):
+        profiles.validate_bonsai_config(profiles.PROFILES[recipe], wrong)
