@@ -713,10 +713,10 @@ def fast_hybrid_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch
 def fast_confidence_generate(model: Transformer, atlas: GraphAtlas, input_ids: torch.Tensor,
                              threshold: float = 0.9, max_gen_len: int = 512, eos_ids=_BONSAI_EOS_IDS,
                              use_fp8_draft: bool = False, use_bf16_draft: bool = False) -> Tuple[torch.Tensor, dict]:
-    """Confidence-chain decode without verification (fast_generate.py:393-571).  One
-    difference from the reference: its first block is a variable-shape forward over
-    [last prompt token | MASK x (D-1)]; here the first token is the prefill's greedy argmax
-    and every block goes through a captured draft graph, as in the other policies."""
+    """Confidence-chain decode without verification (fast_generate.py:393-571).  The first block is
+    the reference's ([last prompt token | MASK x (D-1)] over the prompt's K/V, nothing pending, its tokens
+    the request's untimed output); the reference runs it as an eager variable-shape forward, here it is a
+    replay of the width-D draft graph with n_pend = 0, like every later block."""
     return _draft_verify_generate(model, atlas, input_ids, policy="conf", threshold=threshold,
                                   hybrid_m=None, max_gen_len=max_gen_len, eos_ids=eos_ids,
                                   use_fp8_draft=use_fp8_draft, use_bf16_draft=use_bf16_draft,
