@@ -486,7 +486,8 @@ def make_cpu_atlas(ref, om, args, segment_ladder, m_set, roles, check_masks=True
     return atlas
 
 
-def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind, ladder, m_set, accept_seed=0):
+def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind, ladder, m_set, accept_seed=0,
+                       eos_ids=()):
     RG = ref.generate
     om = O.OracleModel(cfg, state, max_positions=max(ladder) + max(m_set))
     args = ref.model.ModelArgs(dim=cfg["dim"], n_layers=cfg["n_layers"], n_heads=cfg["n_heads"],
@@ -510,8 +511,13 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind
         idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
         a = policy.chain_count()
         n = n if a is None else a
-        toks = [int(t) for t in idx[:n]]
-        return toks, len(toks), False
+        toks, hit = [], False
+        for t in idx[:n]:                      # truncate at the first end-of-sequence id, which is not emitted
+            if int(t) in eos_ids:
+                hit = True
+                break
+            toks.append(int(t))
+        return toks, len(toks), hit
 
     def chain(logits, threshold):
         idx, n, _ = O.draft_chain(logits.numpy(), float(threshold))
@@ -526,7 +532,7 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind
     try:
         fn = {"ar": RG.fast_ar_generate, "spec": RG.fast_speculative_generate,
               "hybrid": RG.fast_hybrid_generate, "conf": RG.fast_confidence_generate}[mode]
-        out, stats = fn(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=())
+        out, stats = fn(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=frozenset(eos_ids))
     finally:
         RG._fused_draft_chain, RG._fused_verify_accept, RG._confidence_accept = orig_chain, orig_accept, orig_conf
     keep = {k: v for k, v in stats.items() if not k.endswith("_time") and k != "ttft"}
@@ -563,6 +569,28 @@ def make_streams(ref, out_path, full=False):
                             accept_seed=plen, ladder=[64, 256], m_set=list(m_set), tokens=toks, stats=stats))
         print(gname, D, mode, accept_kind, len(toks), "tokens", "iters", stats.get("n_iters"),
               "verify paths", stats.get("n_verify_path"))
+    # End-of-sequence handling: the same loops with one id of their own stream declared end-of-sequence (the
+    # id nearest to 60 % of the stream that has not occurred before it), so that the policies stop inside a block.
+    for (gname, D, mode, accept_kind, plen, ntok) in [("tiny", 8, "ar", "free", 24, 20), ("tiny", 8, "spec", "forced", 33, 40),
+                                                      ("tiny_g4", 8, "spec", "categorical", 29, 60),
+                                                      ("tiny", 8, "hybrid", "categorical", 37, 96),
+                                                      ("tiny", 8, "hybrid", "forced", 40, 64),
+                                                      ("tiny_g4", 8, "conf", "categorical", 29, 60),
+                                                      ("tiny", 8, "conf", "forced", 33, 48)]:
+        base = next(r for r in records if (r["geometry"], r["cfg"]["block_size"], r["mode"], r["accept"], r["prompt_len"])
+                    == (gname, D, mode, accept_kind, plen) and not r.get("eos_ids"))
+        toks = base["tokens"]
+        firsts = [i for i in range(2, len(toks)) if toks[i] not in toks[:i]]
+        k = min(firsts, key=lambda i: abs(i - 0.6 * len(toks))) if firsts else 0     # a one-id stream: its first output
+        eos = [toks[k]]
+        cfg = base["cfg"]
+        state = synthetic.make_state(cfg, seed=7)
+        prompt = synthetic.random_prompt(plen, cfg["vocab_size"], seed=plen)
+        got, stats = run_reference_loop(ref, O, cfg, state, mode, prompt, ntok, accept_kind, (64, 256), base["m_set"],
+                                        accept_seed=plen, eos_ids=eos)
+        assert got == toks[:len(got)] and len(got) < len(toks), (mode, len(got), len(toks))
+        records.append(dict(base, tokens=got, stats=stats, eos_ids=eos))
+        print(gname, D, mode, accept_kind, "eos", eos, "at", k, "->", len(got), "tokens")
     with open(out_path, "w") as f:
         json.dump(records, f)
     print("wrote", out_path)

@@ -67,7 +67,7 @@ def test_forward_matches_oracle(oracle, geom, role, M, cache_len, n_pend):
 
 
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
-                                                         f"{r['accept']}")
+                                                         f"{r['accept']}" + ("-eos" if r.get("eos_ids") else ""))
 def test_token_streams_match_reference_loops(rec, monkeypatch):
     cfg = rec["cfg"]
     model, _ = _model(cfg, rec["state_seed"], max(rec["ladder"]) + max(rec["m_set"]))
@@ -82,7 +82,7 @@ def test_token_streams_match_reference_loops(rec, monkeypatch):
     prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
     fn = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
           "hybrid": FG.fast_hybrid_generate, "conf": FG.fast_confidence_generate}[rec["mode"]]
-    out, stats = fn(model, atlas, prompt, max_gen_len=rec["new_tokens"], eos_ids=())
+    out, stats = fn(model, atlas, prompt, max_gen_len=rec["new_tokens"], eos_ids=frozenset(rec.get("eos_ids", ())))
     assert native.lib().bm_device_error() == 0
     assert out.cpu().tolist() == rec["tokens"]
     for key, want in rec["stats"].items():

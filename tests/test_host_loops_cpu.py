@@ -19,7 +19,7 @@ MODES = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
 
 
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
-                                                         f"{r['accept']}")
+                                                         f"{r['accept']}" + ("-eos" if r.get("eos_ids") else ""))
 def test_stream_matches_reference_loops(rec):
     cfg = rec["cfg"]
     state = synthetic.make_state(cfg, seed=rec["state_seed"])
@@ -31,7 +31,7 @@ def test_stream_matches_reference_loops(rec):
     policy = synthetic.AcceptancePolicy(rec["accept"], cfg["block_size"], seed=rec["accept_seed"])
     with patched_host_ops(cfg["block_size"], policy):
         out, stats = MODES[rec["mode"]](OracleModel(om, args), atlas, prompt,
-                                        max_gen_len=rec["new_tokens"], eos_ids=())
+                                        max_gen_len=rec["new_tokens"], eos_ids=frozenset(rec.get("eos_ids", ())))
     assert out.tolist() == rec["tokens"]
     for key, want in rec["stats"].items():
         assert stats[key] == pytest.approx(want), key
