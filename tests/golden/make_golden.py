@@ -487,7 +487,7 @@ def make_cpu_atlas(ref, om, args, segment_ladder, m_set, roles, check_masks=True
 
 
 def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind, ladder, m_set, accept_seed=0,
-                       eos_ids=()):
+                       eos_ids=(), exact_m1_verify=False):
     RG = ref.generate
     om = O.OracleModel(cfg, state, max_positions=max(ladder) + max(m_set))
     args = ref.model.ModelArgs(dim=cfg["dim"], n_layers=cfg["n_layers"], n_heads=cfg["n_heads"],
@@ -532,7 +532,8 @@ def run_reference_loop(ref, O, cfg, state, mode, prompt, new_tokens, accept_kind
     try:
         fn = {"ar": RG.fast_ar_generate, "spec": RG.fast_speculative_generate,
               "hybrid": RG.fast_hybrid_generate, "conf": RG.fast_confidence_generate}[mode]
-        out, stats = fn(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=frozenset(eos_ids))
+        kw = dict(exact_m1_verify=True) if exact_m1_verify else {}
+        out, stats = fn(model, atlas, prompt, max_gen_len=new_tokens, eos_ids=frozenset(eos_ids), **kw)
     finally:
         RG._fused_draft_chain, RG._fused_verify_accept, RG._confidence_accept = orig_chain, orig_accept, orig_conf
     keep = {k: v for k, v in stats.items() if not k.endswith("_time") and k != "ttft"}
@@ -591,6 +592,22 @@ def make_streams(ref, out_path, full=False):
         assert got == toks[:len(got)] and len(got) < len(toks), (mode, len(got), len(toks))
         records.append(dict(base, tokens=got, stats=stats, eos_ids=eos))
         print(gname, D, mode, accept_kind, "eos", eos, "at", k, "->", len(got), "tokens")
+    # The width-1 verifier (`exact_m1_verify=True`): every draft token is checked by AR replays instead of one
+    # width-(D+1) replay; the accepted length is then measured, not drawn.
+    for (gname, D, mode, accept_kind, plen, ntok) in [("tiny_g4", 8, "spec", "categorical", 29, 40),
+                                                      ("tiny", 8, "hybrid", "categorical", 37, 64),
+                                                      ("tiny", 4, "hybrid", "categorical", 19, 40)]:
+        cfg = synthetic.make_config(geoms[gname], block_size=D)
+        state = synthetic.make_state(cfg, seed=7)
+        prompt = synthetic.random_prompt(plen, cfg["vocab_size"], seed=plen)
+        m_set = (1, 8, 9, 10, 12, 16, 17) if D == 8 else (1, 4, 5, 6, 7, 8, 9)
+        toks, stats = run_reference_loop(ref, O, cfg, state, mode, prompt, ntok, accept_kind, (64, 256), m_set,
+                                         accept_seed=plen, exact_m1_verify=True)
+        records.append(dict(geometry=gname, cfg=cfg, state_seed=7, prompt_seed=plen, prompt_len=plen,
+                            new_tokens=ntok, mode=mode, forced=False, accept=accept_kind, accept_seed=plen,
+                            ladder=[64, 256], m_set=list(m_set), tokens=toks, stats=stats, exact_m1_verify=True))
+        print(gname, D, mode, accept_kind, "exact-m1", len(toks), "tokens", "verify paths", stats.get("n_verify_path"),
+              "accepted", stats.get("accepted_drafts"))
     with open(out_path, "w") as f:
         json.dump(records, f)
     print("wrote", out_path)

@@ -19,7 +19,8 @@ MODES = {"ar": FG.fast_ar_generate, "spec": FG.fast_speculative_generate,
 
 
 @pytest.mark.parametrize("rec", RECORDS, ids=lambda r: f"{r['geometry']}-D{r['cfg']['block_size']}-{r['mode']}-"
-                                                         f"{r['accept']}" + ("-eos" if r.get("eos_ids") else ""))
+                                                         f"{r['accept']}" + ("-eos" if r.get("eos_ids") else "") +
+                                                         ("-m1verify" if r.get("exact_m1_verify") else ""))
 def test_stream_matches_reference_loops(rec):
     cfg = rec["cfg"]
     state = synthetic.make_state(cfg, seed=rec["state_seed"])
@@ -30,8 +31,9 @@ def test_stream_matches_reference_loops(rec):
     prompt = synthetic.random_prompt(rec["prompt_len"], cfg["vocab_size"], seed=rec["prompt_seed"])
     policy = synthetic.AcceptancePolicy(rec["accept"], cfg["block_size"], seed=rec["accept_seed"])
     with patched_host_ops(cfg["block_size"], policy):
-        out, stats = MODES[rec["mode"]](OracleModel(om, args), atlas, prompt,
-                                        max_gen_len=rec["new_tokens"], eos_ids=frozenset(rec.get("eos_ids", ())))
+        extra = dict(exact_m1_verify=True) if rec.get("exact_m1_verify") else {}
+        out, stats = MODES[rec["mode"]](OracleModel(om, args), atlas, prompt, max_gen_len=rec["new_tokens"],
+                                        eos_ids=frozenset(rec.get("eos_ids", ())), **extra)
     assert out.tolist() == rec["tokens"]
     for key, want in rec["stats"].items():
         assert stats[key] == pytest.approx(want), key
